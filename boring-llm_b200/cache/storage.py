@@ -1,0 +1,57 @@
+"""Device tensors behind the cache manager's page and slot numbers.
+
+For every paged group one tensor `[layers in group, 2 (keys, values), pages, kv heads, page size,
+head size]`: the rows of one (page, kv head) lie together, so a kernel reads a page of one head as
+one contiguous tile. For every state group one tensor `[layers in group, request slots, *shape]`.
+Keys are stored after rotation, values as projected (src/model.br:1814-1820).
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from .manager import CacheManager
+
+_TORCH_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
+
+
+class CacheStorage:
+    def __init__(self, manager: CacheManager, kv_dtype: torch.dtype, device):
+        self.manager = manager
+        self.kv_dtype = kv_dtype
+        self.device = torch.device(device)
+        self.kv: List[torch.Tensor] = []
+        for g in manager.paged_groups:
+            self.kv.append(torch.zeros(
+                (len(g.cache_layers), 2, manager.num_pages, g.spec.n_kv_heads, manager.page_size,
+                 g.spec.head_dim), dtype=kv_dtype, device=self.device))
+        self.state: List[torch.Tensor] = []
+        for sg in manager.state_groups:
+            self.state.append(torch.zeros(
+                (len(sg.cache_layers), manager.max_requests) + tuple(sg.spec.shape),
+                dtype=_TORCH_DTYPES[sg.spec.dtype], device=self.device))
+        manager._on_slot_assigned = self.zero_slot
+
+    def zero_slot(self, slot: int) -> None:
+        for t in self.state:
+            t[:, slot].zero_()
+
+    def keys(self, cache_layer: int) -> torch.Tensor:
+        kind, gi, li = self.manager.layer_location[cache_layer]
+        assert kind == "paged"
+        return self.kv[gi][li, 0]
+
+    def values(self, cache_layer: int) -> torch.Tensor:
+        kind, gi, li = self.manager.layer_location[cache_layer]
+        assert kind == "paged"
+        return self.kv[gi][li, 1]
+
+    def layer_state(self, cache_layer: int) -> torch.Tensor:
+        """`[request slots, *shape]` of one cache layer with fixed-size state."""
+        kind, gi, li = self.manager.layer_location[cache_layer]
+        assert kind == "state"
+        return self.state[gi][li]
+
+    def bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.kv + self.state)

@@ -1,0 +1,48 @@
+// C interface of the kernel library. Every function returns 0 on success; otherwise
+// bl_last_error() describes what was refused or what failed. Pointers are device pointers
+// unless a comment says otherwise; `stream` is a cudaStream_t.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+const char* bl_last_error(void);
+int bl_device_check(void);   // 0 when the current device can run this library (compute capability 10.x)
+
+// out[t, :] = table[ids[t], :] as 32-bit floats (the residual stream).
+int bl_embed(const void* table, int table_dtype, const int* ids, float* out,
+             int T, int d, int vocab, void* stream);
+
+// y[r, :] = x[row_idx ? row_idx[r] : r, :] / sqrt(mean(x^2) + eps) * w, statistics in 32-bit.
+int bl_rmsnorm(const float* x, const int* row_idx, const void* w, int w_dtype, void* y, int y_dtype,
+               int rows, int d, float eps, void* stream);
+
+// Plain matrix product on CUDA cores, 32-bit accumulation in ascending k for every output element:
+// out[M, N] = epilogue(x[M, K] . W[N, K]^T). For BL_EPI_SWIGLU W has 2N rows (gate, then up).
+int bl_gemm_plain(const void* x, int x_dtype, const void* w, int w_dtype, const void* bias, int bias_dtype,
+                  void* out, int out_dtype, int M, int N, int K, int epilogue, void* stream);
+
+// Splits rows of joined [q | k | v] projections, rotates q and k by position (pairs (j, j + n_rot/2)
+// inside each head, angle = float(position) * inv_freq[j], cos and sin times mscale) and writes k and v
+// into the pages of the token's request. k_cache/v_cache may be null: then only q is produced.
+int bl_rope_kv_write(const float* qkv, const int* positions, const int* tok_req, const int* block_table,
+                     int max_pages, const float* inv_freq, int rot_half, float mscale,
+                     void* q_out, void* k_cache, void* v_cache, int dtype,
+                     int T, int H, int KV, int dh, int page_size, void* stream);
+
+// Plain paged causal attention: one warp per (token, head), keys visited in ascending position.
+// Token t of request r = tok_req[t] stands at position ctx_len[r] - (cu_q[r+1] - cu_q[r]) + (t - cu_q[r])
+// and sees keys j <= position with j + window > position (window 0: all of them).
+int bl_attention_plain(const void* q, const void* k_cache, const void* v_cache, int dtype,
+                       const int* tok_req, const int* cu_q, const int* ctx_len, const int* block_table,
+                       int max_pages, void* out, int T, int H, int KV, int dh, int page_size,
+                       int window, float scale, void* stream);
+
+// out_ids[r] = index of the first maximum of logits[r, :].
+int bl_argmax(const float* logits, int* out_ids, int rows, int vocab, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,50 @@
+// Shared helpers of the engine's CUDA sources: storage types, error reporting, warp reductions.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+// Storage type codes of the C interface.
+#define BL_F32 0
+#define BL_BF16 1
+
+// Epilogues of the matrix products.
+#define BL_EPI_NONE 0      // out = acc
+#define BL_EPI_BIAS 1      // out = acc + bias[n]
+#define BL_EPI_RESIDUAL 2  // out (32-bit, in place) = out + acc
+#define BL_EPI_SWIGLU 3    // out[m, n] = silu(acc_gate[m, n]) * acc_up[m, n]; W holds gate rows then up rows
+
+void bl_set_error(const char* fmt, ...);
+
+#define BL_FAIL(...) do { bl_set_error(__VA_ARGS__); return 1; } while (0)
+#define BL_CHECK_LAUNCH(name) do { cudaError_t e_ = cudaGetLastError(); \
+    if (e_ != cudaSuccess) BL_FAIL("%s: launch failed: %s", name, cudaGetErrorString(e_)); } while (0)
+#define BL_CUDA(call) do { cudaError_t e_ = (call); \
+    if (e_ != cudaSuccess) BL_FAIL("%s failed: %s", #call, cudaGetErrorString(e_)); } while (0)
+
+__device__ __forceinline__ float bl_load(const float* p) { return *p; }
+__device__ __forceinline__ float bl_load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void bl_store(float* p, float v) { *p = v; }
+__device__ __forceinline__ void bl_store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// Reads element i of an array whose storage type is known only at run time (small vectors:
+// norm weights, biases; a tensor stored in 32-bit stays 32-bit beside bfloat16 matrices).
+__device__ __forceinline__ float bl_load_any(const void* p, int dtype, size_t i) {
+    return dtype == BL_F32 ? ((const float*)p)[i] : __bfloat162float(((const __nv_bfloat16*)p)[i]);
+}
+
+__device__ __forceinline__ float bl_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float bl_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// x / (1 + exp(-x)), as src/math.br:232-233.
+__device__ __forceinline__ float bl_silu(float x) { return x / (1.0f + expf(-x)); }

@@ -1,0 +1,205 @@
+// Embedding gather, RMSNorm, rotary positions with the paged cache write, arg-max.
+// Formulas follow the reference's CPU math: rms_norm (src/math.br:18-36), rope_apply_at
+// (src/math.br:128-157); the reference's GPU counterparts are rms_norm_gpu (src/math_gpu.br:2163-2191),
+// split_and_rope_qkv_gpu (:2428-2488) and prepare_qkv_decode_slice (:4008-4076).
+#include "common.cuh"
+#include "api.h"
+#include <string.h>
+
+static thread_local char g_error[1024] = "";
+
+void bl_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+extern "C" const char* bl_last_error(void) { return g_error; }
+
+extern "C" int bl_device_check(void) {
+    int dev = 0;
+    BL_CUDA(cudaGetDevice(&dev));
+    cudaDeviceProp prop;
+    BL_CUDA(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10)
+        BL_FAIL("this library is built for sm_100a (compute capability 10.x); device %d is %d.%d",
+                dev, prop.major, prop.minor);
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+template <typename TT>
+__global__ void embed_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ out, int d) {
+    const int t = blockIdx.x;
+    const size_t row = (size_t)ids[t] * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) out[(size_t)t * d + i] = bl_load(table + row + i);
+}
+
+extern "C" int bl_embed(const void* table, int table_dtype, const int* ids, float* out,
+                        int T, int d, int vocab, void* stream) {
+    if (T <= 0) return 0;
+    if (d <= 0 || vocab <= 0) BL_FAIL("bl_embed: bad sizes d=%d vocab=%d", d, vocab);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (table_dtype == BL_F32)
+        embed_kernel<float><<<T, 128, 0, s>>>((const float*)table, ids, out, d);
+    else if (table_dtype == BL_BF16)
+        embed_kernel<__nv_bfloat16><<<T, 128, 0, s>>>((const __nv_bfloat16*)table, ids, out, d);
+    else
+        BL_FAIL("bl_embed: unknown table dtype %d", table_dtype);
+    BL_CHECK_LAUNCH("bl_embed");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// One block of 128 threads per row. The sum of squares is reduced in a fixed order that depends
+// only on d, so a row's result does not depend on how many rows the call has.
+template <typename TY>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_idx,
+                               const void* __restrict__ w, int w_dtype, TY* __restrict__ y,
+                               int d, float eps) {
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(row_idx ? row_idx[r] : r) * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) { float v = x[src + i]; ss += v * v; }
+    ss = bl_warp_sum(ss);
+    __shared__ float part[4];
+    __shared__ float inv_s;
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float tot = (part[0] + part[1]) + (part[2] + part[3]);
+        inv_s = 1.0f / sqrtf(tot / (float)d + eps);
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    for (int i = threadIdx.x; i < d; i += blockDim.x)
+        bl_store(y + (size_t)r * d + i, x[src + i] * inv * bl_load_any(w, w_dtype, i));
+}
+
+extern "C" int bl_rmsnorm(const float* x, const int* row_idx, const void* w, int w_dtype, void* y,
+                          int y_dtype, int rows, int d, float eps, void* stream) {
+    if (rows <= 0) return 0;
+    if (d <= 0) BL_FAIL("bl_rmsnorm: bad width %d", d);
+    if (w_dtype != BL_F32 && w_dtype != BL_BF16) BL_FAIL("bl_rmsnorm: unknown weight dtype %d", w_dtype);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (y_dtype == BL_F32)
+        rmsnorm_kernel<float><<<rows, 128, 0, s>>>(x, row_idx, w, w_dtype, (float*)y, d, eps);
+    else if (y_dtype == BL_BF16)
+        rmsnorm_kernel<__nv_bfloat16><<<rows, 128, 0, s>>>(x, row_idx, w, w_dtype, (__nv_bfloat16*)y, d, eps);
+    else
+        BL_FAIL("bl_rmsnorm: unknown output dtype %d", y_dtype);
+    BL_CHECK_LAUNCH("bl_rmsnorm");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// One block per token. Work items: (head, pair) for q and k heads, then the v elements.
+template <typename TT>
+__global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int* __restrict__ positions,
+                                     const int* __restrict__ tok_req, const int* __restrict__ block_table,
+                                     int max_pages, const float* __restrict__ inv_freq, int rot_half,
+                                     float mscale, TT* __restrict__ q_out, TT* __restrict__ k_cache,
+                                     TT* __restrict__ v_cache, int H, int KV, int dh, int page_size) {
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = dh / 2;
+    const int width = (H + 2 * KV) * dh;
+    const float* row = qkv + (size_t)t * width;
+    size_t page_base = 0;
+    bool write = k_cache != nullptr;
+    if (write) {
+        const int page = block_table[(size_t)tok_req[t] * max_pages + pos / page_size];
+        if (page < 0) write = false;       // the host never schedules this; keep memory safe anyway
+        page_base = ((size_t)(page < 0 ? 0 : page) * KV) * page_size * dh + (size_t)(pos % page_size) * dh;
+    }
+    const int n_rot_items = (H + KV) * half;
+    for (int it = threadIdx.x; it < n_rot_items; it += blockDim.x) {
+        const int head = it / half, j = it % half;
+        const float* src = row + (size_t)head * dh;      // q heads first, then k heads: same row layout
+        int i0, i1;
+        float c = 1.f, s = 0.f;
+        if (j < rot_half) {
+            i0 = j; i1 = j + rot_half;
+            const float angle = (float)pos * inv_freq[j];
+            c = cosf(angle) * mscale;
+            s = sinf(angle) * mscale;
+        } else {                                         // dimensions past the rotated ones pass through
+            i0 = 2 * j; i1 = 2 * j + 1;
+        }
+        const float x0 = src[i0], x1 = src[i1];
+        const float y0 = x0 * c - x1 * s, y1 = x0 * s + x1 * c;
+        if (head < H) {
+            TT* dst = q_out + (size_t)t * H * dh + (size_t)head * dh;
+            bl_store(dst + i0, y0); bl_store(dst + i1, y1);
+        } else if (write) {
+            TT* dst = k_cache + page_base + (size_t)(head - H) * page_size * dh;
+            bl_store(dst + i0, y0); bl_store(dst + i1, y1);
+        }
+    }
+    if (write) {
+        const float* vsrc = row + (size_t)(H + KV) * dh;
+        for (int it = threadIdx.x; it < KV * dh; it += blockDim.x) {
+            const int head = it / dh, i = it % dh;
+            bl_store(v_cache + page_base + (size_t)head * page_size * dh + i, vsrc[it]);
+        }
+    }
+}
+
+extern "C" int bl_rope_kv_write(const float* qkv, const int* positions, const int* tok_req,
+                                const int* block_table, int max_pages, const float* inv_freq,
+                                int rot_half, float mscale, void* q_out, void* k_cache, void* v_cache,
+                                int dtype, int T, int H, int KV, int dh, int page_size, void* stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || KV <= 0 || dh <= 0 || dh % 2 != 0 || page_size <= 0 || max_pages <= 0)
+        BL_FAIL("bl_rope_kv_write: bad sizes H=%d KV=%d head=%d page=%d max_pages=%d", H, KV, dh, page_size, max_pages);
+    if (rot_half < 0 || rot_half > dh / 2) BL_FAIL("bl_rope_kv_write: %d rotated pairs do not fit a head of %d", rot_half, dh);
+    if ((k_cache == nullptr) != (v_cache == nullptr)) BL_FAIL("bl_rope_kv_write: key and value cache must both be given or both be null");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == BL_F32)
+        rope_kv_write_kernel<float><<<T, 128, 0, s>>>(qkv, positions, tok_req, block_table, max_pages, inv_freq,
+            rot_half, mscale, (float*)q_out, (float*)k_cache, (float*)v_cache, H, KV, dh, page_size);
+    else if (dtype == BL_BF16)
+        rope_kv_write_kernel<__nv_bfloat16><<<T, 128, 0, s>>>(qkv, positions, tok_req, block_table, max_pages, inv_freq,
+            rot_half, mscale, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, H, KV, dh, page_size);
+    else
+        BL_FAIL("bl_rope_kv_write: unknown dtype %d", dtype);
+    BL_CHECK_LAUNCH("bl_rope_kv_write");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// First maximum wins, as sample_greedy (src/sampling.br:239-249: strict '>').
+__global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (idx == 0x7fffffff || v > best) { best = v; idx = i; }
+    }
+    __shared__ float sv[256];
+    __shared__ int si[256];
+    sv[threadIdx.x] = best; si[threadIdx.x] = idx;
+    __syncthreads();
+    for (int o = blockDim.x / 2; o > 0; o >>= 1) {
+        if (threadIdx.x < o) {
+            const float v2 = sv[threadIdx.x + o]; const int i2 = si[threadIdx.x + o];
+            if (i2 != 0x7fffffff && (si[threadIdx.x] == 0x7fffffff || v2 > sv[threadIdx.x] ||
+                                     (v2 == sv[threadIdx.x] && i2 < si[threadIdx.x]))) {
+                sv[threadIdx.x] = v2; si[threadIdx.x] = i2;
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = si[0];
+}
+
+extern "C" int bl_argmax(const float* logits, int* out_ids, int rows, int vocab, void* stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0) BL_FAIL("bl_argmax: bad vocabulary %d", vocab);
+    argmax_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(logits, out_ids, vocab);
+    BL_CHECK_LAUNCH("bl_argmax");
+    return 0;
+}

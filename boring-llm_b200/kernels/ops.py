@@ -1,0 +1,142 @@
+"""Typed Python front of the kernel library: every function takes torch CUDA tensors, checks what
+the C side cannot see (devices, dtypes, shapes, contiguity) and launches on torch's current stream.
+Nothing here computes on the CPU or through a library model: without the built library and an
+sm_100a device these functions raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import library
+
+F32, BF16 = 0, 1
+EPI_NONE, EPI_BIAS, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
+
+_checked_device = False
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported tensor dtype {t.dtype}: kernels take float32 or bfloat16")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _lib():
+    global _checked_device
+    lib = library.load()
+    if not _checked_device:
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: this engine runs on an sm_100a GPU only (there is no CPU path)")
+        if lib.bl_device_check() != 0:
+            raise KernelError(lib.bl_last_error().decode())
+        _checked_device = True
+    return lib
+
+
+def _call(fn, *args):
+    if fn(*args) != 0:
+        raise KernelError(library.load().bl_last_error().decode())
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, shape=None):
+    if not t.is_cuda:
+        raise KernelError(f"{name}: must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: must be {dtype}, got {t.dtype}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise KernelError(f"{name}: must have shape {tuple(shape)}, got {tuple(t.shape)}")
+
+
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = table[ids[t]] widened to 32-bit. The caller has checked that ids lie inside the table."""
+    T = ids.shape[0]
+    V, d = table.shape
+    _need(table, "table"); _need(ids, "ids", torch.int32, (T,)); _need(out, "out", torch.float32, (T, d))
+    _call(_lib().bl_embed, _p(table), _dt(table), _p(ids), _p(out), T, d, V, _stream())
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            row_idx: Optional[torch.Tensor] = None) -> None:
+    """out[r] = rmsnorm(x[row_idx[r]] if row_idx is given else x[r]) * weight."""
+    d = x.shape[1]
+    rows = out.shape[0]
+    _need(x, "x", torch.float32); _need(weight, "weight", None, (d,)); _need(out, "out", None, (rows, d))
+    if row_idx is not None:
+        _need(row_idx, "row_idx", torch.int32, (rows,))
+    elif x.shape[0] != rows:
+        raise KernelError("rmsnorm: x and out differ in rows")
+    _call(_lib().bl_rmsnorm, _p(x), _p(row_idx), _p(weight), _dt(weight), _p(out), _dt(out),
+          rows, d, ctypes.c_float(eps), _stream())
+
+
+def gemm_plain(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+               epilogue: int = EPI_NONE) -> None:
+    """out = epilogue(x @ w.T) on CUDA cores with 32-bit accumulation."""
+    M, K = x.shape
+    N = out.shape[1]
+    rows_w = 2 * N if epilogue == EPI_SWIGLU else N
+    _need(x, "x"); _need(w, "w", None, (rows_w, K)); _need(out, "out", None, (M, N))
+    if bias is not None:
+        _need(bias, "bias", None, (N,))
+    _call(_lib().bl_gemm_plain, _p(x), _dt(x), _p(w), _dt(w), _p(bias), _dt(bias) if bias is not None else 0,
+          _p(out), _dt(out), M, N, K, epilogue, _stream())
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, tok_req: torch.Tensor,
+                  block_table: torch.Tensor, inv_freq: torch.Tensor, rot_half: int, mscale: float,
+                  q_out: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                  H: int, KV: int, dh: int) -> None:
+    """Rotates q and k of joined [q | k | v] rows and writes k, v into the request's pages."""
+    T = qkv.shape[0]
+    _need(qkv, "qkv", torch.float32, (T, (H + 2 * KV) * dh))
+    _need(positions, "positions", torch.int32, (T,)); _need(tok_req, "tok_req", torch.int32, (T,))
+    _need(block_table, "block_table", torch.int32); _need(inv_freq, "inv_freq", torch.float32, (dh // 2,))
+    _need(q_out, "q_out", None, (T, H * dh))
+    page_size = 1
+    if k_cache is not None:
+        _need(k_cache, "k_cache", q_out.dtype); _need(v_cache, "v_cache", q_out.dtype, k_cache.shape)
+        if k_cache.shape[1] != KV or k_cache.shape[3] != dh:
+            raise KernelError(f"k_cache: shape {tuple(k_cache.shape)} does not hold {KV} heads of {dh}")
+        page_size = k_cache.shape[2]
+    _call(_lib().bl_rope_kv_write, _p(qkv), _p(positions), _p(tok_req), _p(block_table),
+          block_table.shape[1], _p(inv_freq), rot_half, ctypes.c_float(mscale), _p(q_out), _p(k_cache),
+          _p(v_cache), _dt(q_out), T, H, KV, dh, page_size, _stream())
+
+
+def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_req: torch.Tensor,
+                    cu_q: torch.Tensor, ctx_len: torch.Tensor, block_table: torch.Tensor,
+                    out: torch.Tensor, H: int, window: int, scale: float) -> None:
+    """Paged causal grouped-query attention, one warp per (token, head)."""
+    T = q.shape[0]
+    _, KV, page_size, dh = k_cache.shape
+    _need(q, "q", k_cache.dtype, (T, H * dh)); _need(k_cache, "k_cache"); _need(v_cache, "v_cache", k_cache.dtype, k_cache.shape)
+    _need(tok_req, "tok_req", torch.int32, (T,)); _need(cu_q, "cu_q", torch.int32); _need(ctx_len, "ctx_len", torch.int32)
+    _need(block_table, "block_table", torch.int32); _need(out, "out", q.dtype, (T, H * dh))
+    _call(_lib().bl_attention_plain, _p(q), _p(k_cache), _p(v_cache), _dt(q), _p(tok_req), _p(cu_q),
+          _p(ctx_len), _p(block_table), block_table.shape[1], _p(out), T, H, KV, dh, page_size, window,
+          ctypes.c_float(scale), _stream())
+
+
+def argmax(logits: torch.Tensor, out_ids: torch.Tensor) -> None:
+    rows, V = logits.shape
+    _need(logits, "logits", torch.float32); _need(out_ids, "out_ids", torch.int32, (rows,))
+    _call(_lib().bl_argmax, _p(logits), _p(out_ids), rows, V, _stream())

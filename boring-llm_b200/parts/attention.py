@@ -1,0 +1,96 @@
+"""Mixers: the parts of a block that let tokens see one another."""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from ..cache import PagedKVSpec
+from ..kernels import ops
+from ..weights import TensorSpec, MATRIX, BIAS
+from .base import Part, to_device_matrix, to_device_vector
+from .linear import linear, EPI_BIAS, EPI_NONE, EPI_RESIDUAL
+from .rotary import RotaryTable
+
+
+class Mixer(Part):
+    """Interface of a mixer.
+
+    `cache_spec()` says what one cache layer of this mixer needs (`PagedKVSpec`, `StateSpec` or
+    None). `forward(ctx, h, residual, cache_layer, write_cache)` reads the normed rows `h` [T, dim],
+    adds its result into the 32-bit `residual` [T, dim] in place, and may read and write the cache
+    layer it is given through `ctx.kv(cache_layer)` / `ctx.state(cache_layer)`. With `write_cache`
+    false it reads a layer that another call has written in this step.
+    """
+
+    def cache_spec(self):
+        return None
+
+    def forward(self, ctx, h, residual, cache_layer: Optional[int], write_cache: bool = True) -> None:
+        raise NotImplementedError
+
+
+class GQAAttention(Mixer):
+    """Causal grouped-query attention over the paged cache.
+
+    q, k, v = h.Wq^T + bq, h.Wk^T + bk, h.Wv^T + bv as ONE joined product (src/model.br:765-768,
+    864-869, 1113-1115); q and k rotated by position; k cached after rotation, v as projected
+    (:1814-1820); softmax(q.k^T * scale) over the keys a token may see (src/math.br:304-359);
+    out.Wo^T added to the residual stream (src/model.br:1328-1334).
+    """
+
+    def __init__(self, dim: int, n_heads: int, n_kv_heads: int, head_dim: int, rotary: Optional[RotaryTable],
+                 names: Dict[str, str], qkv_bias: bool = True, out_bias: bool = False, window: int = 0,
+                 scale: Optional[float] = None):
+        super().__init__(names)
+        if n_heads % n_kv_heads != 0:
+            raise ValueError(f"{n_heads} query heads cannot share {n_kv_heads} key/value heads")
+        if out_bias:
+            raise NotImplementedError("an output-projection bias is not supported")
+        self.dim, self.H, self.KV, self.dh = dim, n_heads, n_kv_heads, head_dim
+        self.rotary = rotary if rotary is not None else RotaryTable(head_dim, 10000.0, n_rot=0)
+        self.qkv_bias, self.window = qkv_bias, int(window)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.w_qkv = self.b_qkv = self.wo = None
+
+    def local_specs(self):
+        s = {"wq": TensorSpec((self.H * self.dh, self.dim), MATRIX),
+             "wk": TensorSpec((self.KV * self.dh, self.dim), MATRIX),
+             "wv": TensorSpec((self.KV * self.dh, self.dim), MATRIX),
+             "wo": TensorSpec((self.dim, self.H * self.dh), MATRIX)}
+        if self.qkv_bias:
+            s.update({"bq": TensorSpec((self.H * self.dh,), BIAS), "bk": TensorSpec((self.KV * self.dh,), BIAS),
+                      "bv": TensorSpec((self.KV * self.dh,), BIAS)})
+        return s
+
+    def place(self, local, dtype, device):
+        self.w_qkv = to_device_matrix(torch.cat([local["wq"], local["wk"], local["wv"]], dim=0), dtype, device)
+        self.wo = to_device_matrix(local["wo"], dtype, device)
+        if self.qkv_bias:
+            b = [local["bq"], local["bk"], local["bv"]]
+            if any(t.dtype == torch.float32 for t in b):
+                b = [t.to(torch.float32) for t in b]
+            self.b_qkv = to_device_vector(torch.cat(b, dim=0), dtype, device)
+        self.rotary.to(device)
+
+    def cache_spec(self):
+        return PagedKVSpec(self.KV, self.dh, self.window)
+
+    def forward(self, ctx, h, residual, cache_layer, write_cache=True):
+        T = h.shape[0]
+        width = (self.H + 2 * self.KV) * self.dh
+        qkv = ctx.empty((T, width), torch.float32)
+        linear(ctx, h, self.w_qkv, qkv, self.b_qkv, EPI_BIAS if self.qkv_bias else EPI_NONE)
+        k_cache, v_cache, table = ctx.kv(cache_layer)
+        q = ctx.empty((T, self.H * self.dh))
+        ops.rope_kv_write(qkv, ctx.positions, ctx.tok_req, table, self.rotary.inv_freq, self.rotary.rot_half,
+                          self.rotary.mscale, q, k_cache if write_cache else None,
+                          v_cache if write_cache else None, self.H, self.KV, self.dh)
+        attn = ctx.empty((T, self.H * self.dh))
+        self.attend(ctx, q, k_cache, v_cache, table, attn)
+        linear(ctx, attn, self.wo, residual, None, EPI_RESIDUAL)
+
+    def attend(self, ctx, q, k_cache, v_cache, table, out):
+        ops.attention_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, out,
+                            self.H, self.window, self.scale)

@@ -1,0 +1,114 @@
+"""What every part shares: the declaration of its tensors, and the step context it runs in.
+
+A part (a norm, a position encoding, a mixer, a feed-forward, a block, an embedding, an output
+head) takes every size and constant as a constructor argument and never learns which model it is
+in. It declares its tensors under local names; the architecture's builder maps local names to
+checkpoint names (role of the reference's per-architecture tensor names, src/model.br:614-690).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..weights import TensorSpec
+
+
+class Part:
+    """Base of all parts. `names` maps each local tensor name to its checkpoint name."""
+
+    def __init__(self, names: Optional[Dict[str, str]] = None):
+        self.names: Dict[str, str] = dict(names or {})
+
+    # -- tensors ---------------------------------------------------------------------------------
+    def local_specs(self) -> Dict[str, TensorSpec]:
+        """Local tensor name -> what it must look like."""
+        return {}
+
+    def children(self) -> Sequence["Part"]:
+        return ()
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        """Checkpoint tensor name -> spec, for this part and the parts inside it."""
+        out: Dict[str, TensorSpec] = {}
+        for local, spec in self.local_specs().items():
+            if local not in self.names:
+                raise KeyError(f"{type(self).__name__}: no checkpoint name given for tensor '{local}'")
+            out[self.names[local]] = spec
+        for c in self.children():
+            for k, v in c.tensor_specs().items():
+                if k in out and out[k] != v:
+                    raise ValueError(f"tensor {k} is declared twice with different shapes")
+                out[k] = v
+        return out
+
+    def load(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
+        """Takes this part's tensors (by checkpoint name) to the device. `dtype` is the engine's
+        matrix dtype: bfloat16 matrices stay, float32 mode widens everything to 32-bit."""
+        local = {l: tensors[self.names[l]] for l in self.local_specs()}
+        self.place(local, dtype, device)
+        for c in self.children():
+            c.load(tensors, dtype, device)
+
+    def place(self, local: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
+        """Default: each local tensor becomes an attribute of the same name."""
+        for name, t in local.items():
+            setattr(self, name, to_device_matrix(t, dtype, device) if t.dim() >= 2 else to_device_vector(t, dtype, device))
+
+
+def to_device_matrix(t: torch.Tensor, dtype: torch.dtype, device) -> torch.Tensor:
+    """Matrices take the engine's dtype (the tensor cores want bfloat16; the 32-bit path wants float32)."""
+    return t.to(device=device, dtype=dtype).contiguous()
+
+
+def to_device_vector(t: torch.Tensor, dtype: torch.dtype, device) -> torch.Tensor:
+    """Small vectors (norm weights, biases) keep 32-bit storage when they have it; in float32 mode
+    bfloat16 ones are widened."""
+    if dtype == torch.float32 or t.dtype == torch.float32:
+        return t.to(device=device, dtype=torch.float32).contiguous()
+    return t.to(device=device, dtype=torch.bfloat16).contiguous()
+
+
+@dataclass
+class StepContext:
+    """Everything a part may look at while one step runs. Device tensors are int32.
+
+    The batch is flat: `T` tokens of `R` requests, request r owning tokens cu_q[r] .. cu_q[r+1] - 1
+    at positions ctx_len[r] - q_len[r] .. ctx_len[r] - 1.
+    """
+    dtype: torch.dtype
+    device: torch.device
+    T: int
+    R: int
+    token_ids: torch.Tensor            # [T]
+    positions: torch.Tensor            # [T] absolute position of each token
+    tok_req: torch.Tensor              # [T] index (in this batch) of the token's request
+    cu_q: torch.Tensor                 # [R + 1]
+    ctx_len: torch.Tensor              # [R] tokens the request holds after this step
+    slots: torch.Tensor                # [R] the request's state slot
+    logit_rows: torch.Tensor           # [N] flat token indices whose logits are wanted
+    block_tables: List[torch.Tensor]   # per paged group: [R, width]
+    q_lens: List[int]                  # host copies, for parts that choose a kernel or loop on the host
+    ctx_lens: List[int]
+    slot_list: List[int]
+    storage: object                    # cache.CacheStorage
+    fast: bool = True                  # False: plain kernels only (the twins)
+
+    @property
+    def max_q_len(self) -> int:
+        return max(self.q_lens) if self.q_lens else 0
+
+    def kv(self, cache_layer: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """(keys, values, block table) of a cache layer: pages `[pages, kv heads, page size, head size]`."""
+        kind, gi, li = self.storage.manager.layer_location[cache_layer]
+        if kind != "paged":
+            raise TypeError(f"cache layer {cache_layer} holds fixed-size state, not pages")
+        return self.storage.kv[gi][li, 0], self.storage.kv[gi][li, 1], self.block_tables[gi]
+
+    def state(self, cache_layer: int) -> torch.Tensor:
+        """`[request slots, *shape]` of a cache layer with fixed-size state; index it with `slots`."""
+        return self.storage.layer_state(cache_layer)
+
+    def empty(self, shape, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

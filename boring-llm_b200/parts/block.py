@@ -1,0 +1,27 @@
+"""How a norm, a mixer and a feed-forward are arranged in one layer."""
+from __future__ import annotations
+
+from typing import Optional
+
+from .base import Part
+
+
+class PreNormBlock(Part):
+    """x += mixer(norm1(x)); x += ffn(norm2(x)): sequential residuals around pre-norms, the
+    arrangement of the reference's plain layer (src/model.br:1297-1358 with residual_type 0)."""
+
+    def __init__(self, mixer_norm, mixer, ffn_norm, ffn):
+        super().__init__()
+        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
+
+    def children(self):
+        return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, ctx, x, cache_layer: Optional[int], write_cache: bool = True) -> None:
+        h = self.mixer_norm.forward(ctx, x)
+        self.mixer.forward(ctx, h, x, cache_layer, write_cache)
+        h = self.ffn_norm.forward(ctx, x)
+        self.ffn.forward(ctx, h, x)

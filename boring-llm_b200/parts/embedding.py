@@ -1,0 +1,57 @@
+"""Token embedding and output head."""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..kernels import ops
+from ..weights import TensorSpec, MATRIX
+from .base import Part, to_device_matrix
+from .linear import linear, EPI_NONE
+
+
+class Embedding(Part):
+    """x[t] = table[token[t]] (src/model.br:1286-1295; the reference's embedding scale is 1 here),
+    widened to the 32-bit residual stream."""
+
+    def __init__(self, vocab: int, dim: int, names: Dict[str, str]):
+        super().__init__(names)
+        self.vocab, self.dim = vocab, dim
+        self.table: Optional[torch.Tensor] = None
+
+    def local_specs(self):
+        return {"table": TensorSpec((self.vocab, self.dim), MATRIX)}
+
+    def place(self, local, dtype, device):
+        self.table = to_device_matrix(local["table"], dtype, device)
+
+    def forward(self, ctx) -> torch.Tensor:
+        x = ctx.empty((ctx.T, self.dim), torch.float32)
+        ops.embed(self.table, ctx.token_ids, x)
+        return x
+
+
+class OutputHead(Part):
+    """logits = y . W^T in 32-bit, no bias (src/model.br:1360-1362). Tied to an embedding: the
+    table is shared, not copied (src/model.br:686-690)."""
+
+    def __init__(self, vocab: int, dim: int, names: Dict[str, str], tied_to: Optional[Embedding] = None):
+        super().__init__(names)
+        self.vocab, self.dim, self.tied_to = vocab, dim, tied_to
+        self.weight: Optional[torch.Tensor] = None
+
+    def local_specs(self):
+        return {} if self.tied_to is not None else {"weight": TensorSpec((self.vocab, self.dim), MATRIX)}
+
+    def place(self, local, dtype, device):
+        if self.tied_to is None:
+            self.weight = to_device_matrix(local["weight"], dtype, device)
+
+    def matrix(self) -> torch.Tensor:
+        return self.tied_to.table if self.tied_to is not None else self.weight
+
+    def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:
+        logits = ctx.empty((y.shape[0], self.vocab), torch.float32)
+        linear(ctx, y, self.matrix(), logits, None, EPI_NONE)
+        return logits

@@ -1,0 +1,43 @@
+"""Feed-forward parts: rows in, rows out, no cache."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..weights import TensorSpec, MATRIX
+from .base import Part, to_device_matrix
+from .linear import linear, EPI_RESIDUAL, EPI_SWIGLU
+
+
+class FeedForward(Part):
+    """Interface: `forward(ctx, h, residual)` reads the normed rows `h` [T, dim] and adds its
+    result into the 32-bit `residual` [T, dim] in place."""
+
+    def forward(self, ctx, h, residual) -> None:
+        raise NotImplementedError
+
+
+class SwiGLU(FeedForward):
+    """down(silu(gate(h)) * up(h)), no biases (src/math.br:232-233, 246-261). Gate and up run as
+    one joined product over [Wg; Wu] (src/model.br:788-792) whose epilogue combines them
+    (src/math_gpu.br:2673-2692); the down product adds into the residual stream."""
+
+    def __init__(self, dim: int, hidden: int, names: Dict[str, str]):
+        super().__init__(names)
+        self.dim, self.hidden = dim, hidden
+        self.w_gate_up = self.w_down = None
+
+    def local_specs(self):
+        return {"w_gate": TensorSpec((self.hidden, self.dim), MATRIX),
+                "w_up": TensorSpec((self.hidden, self.dim), MATRIX),
+                "w_down": TensorSpec((self.dim, self.hidden), MATRIX)}
+
+    def place(self, local, dtype, device):
+        self.w_gate_up = to_device_matrix(torch.cat([local["w_gate"], local["w_up"]], dim=0), dtype, device)
+        self.w_down = to_device_matrix(local["w_down"], dtype, device)
+
+    def forward(self, ctx, h, residual):
+        act = ctx.empty((h.shape[0], self.hidden))
+        linear(ctx, h, self.w_gate_up, act, None, EPI_SWIGLU)
+        linear(ctx, act, self.w_down, residual, None, EPI_RESIDUAL)

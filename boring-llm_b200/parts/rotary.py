@@ -1,0 +1,32 @@
+"""Position encodings applied between projection and cache write."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+
+class RotaryTable:
+    """Per-pair rotation table, as the reference builds it (src/math.br:107-113, 161-171):
+    `inv_freq[j] = 1 / base^(2j / n_rot)` in 32-bit for the n_rot/2 rotated pairs, zero past them, a
+    magnitude scale for cos/sin and the number of rotated pairs. Pairs are NEOX style
+    (j, j + n_rot/2) inside each head (src/math.br:145-148); every variant of rotary scaling is just
+    another table, so the kernel never branches on the variant.
+    """
+
+    def __init__(self, head_dim: int, base: float, n_rot: int | None = None, mscale: float = 1.0):
+        n_rot = head_dim if n_rot is None else n_rot
+        if n_rot % 2 != 0 or n_rot > head_dim or n_rot < 0:
+            raise ValueError(f"rotary: {n_rot} rotated dimensions do not fit a head of {head_dim}")
+        self.head_dim, self.base, self.n_rot, self.mscale = head_dim, float(base), n_rot, float(mscale)
+        self.rot_half = n_rot // 2
+        f = np.zeros(head_dim // 2, dtype=np.float32)
+        j = np.arange(self.rot_half, dtype=np.float32)
+        if self.rot_half:
+            expo = (np.float32(2.0) * j) / np.float32(n_rot)
+            f[: self.rot_half] = np.float32(1.0) / np.power(np.float32(base), expo, dtype=np.float32)
+        self.inv_freq_host = f
+        self.inv_freq: torch.Tensor | None = None
+
+    def to(self, device):
+        self.inv_freq = torch.from_numpy(self.inv_freq_host).to(device)
+        return self
