@@ -43,6 +43,17 @@ int bl_attention_plain(const void* q, const void* k_cache, const void* v_cache, 
 // out_ids[r] = index of the first maximum of logits[r, :].
 int bl_argmax(const float* logits, int* out_ids, int rows, int vocab, void* stream);
 
+// One token per row: greedy where temperature[r] <= 0, else temperature sampling with the optional
+// top_k (0: off), top_p (>= 1: off) and min_p (0: off) cuts over candidates in descending logit order;
+// uniform[r] in [0, 1) is the row's random number (unused by greedy rows).
+int bl_sample(const float* logits, int rows, int vocab, const float* temperature, const int* top_k,
+              const float* top_p, const float* min_p, const float* uniform, int* out_ids, void* stream);
+
+// logits[r, t] is divided by penalty[r] when positive, multiplied otherwise, for each token t in
+// tokens[offsets[r] .. offsets[r+1]) (the host lists each distinct token once).
+int bl_repeat_penalty(float* logits, int rows, int vocab, const int* tokens, const int* offsets,
+                      const float* penalty, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

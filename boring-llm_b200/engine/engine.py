@@ -1,0 +1,106 @@
+"""The Python entry point: token ids in, token ids out.
+
+`Engine.generate` plays the reference's `generate_kv` (src/model.br:2280-2306: chunked prefill,
+then sample, stop on an end token, else feed the token back), for many requests at once: the
+scheduler builds each step's batch, the runner computes logits, the device sampler picks tokens.
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..config import EngineOptions
+from ..models.loading import load_model
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .runner import ModelRunner, StepEntry
+from .scheduler import Request, Scheduler
+
+
+class Engine:
+    def __init__(self, model_dir: str, options: Optional[EngineOptions] = None, **overrides):
+        """Loads the model folder (config.json chooses the model class) onto the device.
+        `overrides` set fields of `EngineOptions` (dtype, ctx_size, max_tokens, ...)."""
+        if options is None:
+            options = EngineOptions(**overrides)
+        elif overrides:
+            raise TypeError("give either options or keyword overrides, not both")
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device: this engine runs on an sm_100a GPU only (there is no CPU path)")
+        self.options = options
+        self.config, self.model = load_model(model_dir, options.dtype, options.device)
+        max_pos = getattr(self.config, "max_position_embeddings", None)
+        if max_pos is not None and options.ctx_size > max_pos:
+            raise ValueError(f"ctx_size {options.ctx_size} exceeds the model's max_position_embeddings {max_pos}")
+        self.runner = ModelRunner(self.model, options)
+        self.scheduler = Scheduler(self.runner.cache, options)
+        self.sampler = Sampler(options.device)
+        self._ids = itertools.count()
+        self.stats_time = {"steps": 0, "step_seconds": 0.0}
+
+    # ---- requests ----------------------------------------------------------------------------------
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, request_id=None) -> Request:
+        if params is None:
+            params = SamplingParams()
+        if not params.eos_token_ids and not params.ignore_eos:
+            params.eos_token_ids = tuple(getattr(self.config, "eos_token_ids", ()))
+        for t in prompt:
+            if not 0 <= int(t) < self.runner.vocab_size:
+                raise ValueError(f"token id {t} is outside the vocabulary (0..{self.runner.vocab_size - 1})")
+        rid = request_id if request_id is not None else next(self._ids)
+        return self.scheduler.add(rid, prompt, params)
+
+    def step(self) -> List[Request]:
+        """One scheduler step. Returns the requests that finished in it."""
+        sched = self.scheduler.schedule()
+        if sched is None:
+            return []
+        t0 = time.perf_counter()
+        logits = self.runner.step(sched.entries)
+        rows = [(r.params, r.rng, r.tokens) for r, s in zip(sched.requests, sched.samples) if s]
+        sampled = self.sampler.sample(logits, rows) if rows else []
+        self.stats_time["steps"] += 1
+        self.stats_time["step_seconds"] += time.perf_counter() - t0
+        return self.scheduler.apply(sched, sampled)
+
+    def run_until_done(self) -> None:
+        while self.scheduler.has_work():
+            before = (len(self.scheduler.waiting), len(self.scheduler.running), len(self.scheduler.finished))
+            self.step()
+            after = (len(self.scheduler.waiting), len(self.scheduler.running), len(self.scheduler.finished))
+            if before == after and not self.scheduler.running:
+                raise RuntimeError("the scheduler made no progress with requests still waiting")
+
+    def generate(self, prompts: Sequence[Sequence[int]], n_predict: int = 40, temperature: float = 0.0,
+                 seed: int = 0, top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0,
+                 repeat_penalty: float = 1.0, repeat_last_n: int = 64,
+                 eos_token_ids: Optional[Sequence[int]] = None, ignore_eos: bool = False) -> List[List[int]]:
+        """Generated token ids for each prompt (lists of token ids), in the prompts' order. Request i
+        draws from a generator seeded with `seed + i`, so a batch and the same prompts one by one
+        give the same tokens."""
+        reqs = []
+        for i, prompt in enumerate(prompts):
+            params = SamplingParams(n_predict=n_predict, temperature=temperature, seed=seed + i, top_k=top_k,
+                                    top_p=top_p, min_p=min_p, repeat_penalty=repeat_penalty,
+                                    repeat_last_n=repeat_last_n,
+                                    eos_token_ids=tuple(eos_token_ids) if eos_token_ids is not None else (),
+                                    ignore_eos=ignore_eos)
+            reqs.append(self.add_request(prompt, params))
+        self.run_until_done()
+        return [list(r.output) for r in reqs]
+
+    def stats(self) -> dict:
+        s = dict(self.runner.cache.stats())
+        s.update(steps=self.runner.steps, tokens_run=self.runner.tokens_run,
+                 preemptions=self.scheduler.num_preemptions, **self.stats_time)
+        return s
+
+
+def generate(model_dir: str, prompts: Sequence[Sequence[int]], n_predict: int = 40, temperature: float = 0.0,
+             seed: int = 0, dtype: str = "bfloat16", ctx_size: int = 4096, **sampling) -> List[List[int]]:
+    """One call from a model folder and prompts (token ids) to generated token ids."""
+    eng = Engine(model_dir, dtype=dtype, ctx_size=ctx_size, max_num_seqs=max(1, min(64, len(prompts))))
+    return eng.generate(prompts, n_predict=n_predict, temperature=temperature, seed=seed, **sampling)

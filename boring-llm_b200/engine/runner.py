@@ -1,0 +1,189 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted places out.
+
+The reference has four single-sequence functions in this role: `prefill_gpu_quantized`,
+`prefill_step_gpu_quantized` (append n tokens after `cache.pos`, last-row logits),
+`forward_batch_gpu_quantized` (same, every row's logits) and `forward_step` (one token)
+(src/model.br:1747, 1852, 1935, 2043). Here one function runs any mix of them as one flat batch:
+portions of prompts beside single decoded tokens, cut anywhere. It runs only the tokens it is given,
+against the cache that earlier steps left, and is free of policy: which tokens to run is the
+scheduler's (or the trace's) business.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, CacheStorage
+from ..config import EngineOptions
+from ..models.loading import torch_dtype
+from ..parts import StepContext
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request and the places among them whose logits are wanted."""
+    request_id: object
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class OutOfPages(RuntimeError):
+    """The step needs more cache pages than are free. Nothing was changed."""
+
+
+class StepError(ValueError):
+    """A step that cannot run: an unknown token id, a request past its context size, ..."""
+
+
+class ModelRunner:
+    def __init__(self, model, options: EngineOptions, vocab_size: Optional[int] = None):
+        self.model = model
+        self.options = options
+        self.device = torch.device(options.device)
+        self.dtype = torch_dtype(options.dtype)
+        self.vocab_size = vocab_size if vocab_size is not None else model.vocab_size
+        self.cache = CacheManager(model.cache_specs(), options.page_size, options.capacity_tokens,
+                                  options.max_num_seqs)
+        self.storage = CacheStorage(self.cache, self.dtype, self.device)
+        self.fast = True            # False: plain kernels only
+        self._pinned: List[torch.Tensor] = []
+        self._pinned_events: List[Optional[torch.cuda.Event]] = []
+        self._pinned_next = 0
+        self.steps = 0
+        self.tokens_run = 0
+
+    # ---- requests --------------------------------------------------------------------------------
+    def add_request(self, request_id) -> None:
+        self.cache.add_request(request_id)
+
+    def free_request(self, request_id) -> None:
+        self.cache.free(request_id)
+
+    def has_request(self, request_id) -> bool:
+        return request_id in self.cache
+
+    # ---- the step ----------------------------------------------------------------------------------
+    def _host_buffer(self, n_ints: int) -> torch.Tensor:
+        """One of two pinned staging buffers, reused once the copy that last read it is done."""
+        if len(self._pinned) < 2:
+            self._pinned.append(torch.empty(max(n_ints, 1 << 14), dtype=torch.int32).pin_memory())
+            self._pinned_events.append(None)
+            i = len(self._pinned) - 1
+        else:
+            i = self._pinned_next
+            self._pinned_next = (i + 1) % 2
+            if self._pinned_events[i] is not None:
+                self._pinned_events[i].synchronize()
+            if self._pinned[i].numel() < n_ints:
+                self._pinned[i] = torch.empty(n_ints * 2, dtype=torch.int32).pin_memory()
+        self._slot_index = i
+        return self._pinned[i]
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs the entries' tokens as one batch; returns float32 logits `[wanted, vocab]` on the
+        device, in the order of the entries and of each entry's `want`. Requests not seen before
+        are admitted; pages are reserved here, and an `OutOfPages` leaves everything as it was."""
+        page = self.options.page_size
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        for e in entries:
+            if e.request_id in seen:
+                raise StepError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            if len(e.tokens) == 0:
+                raise StepError(f"request {e.request_id!r}: no tokens in its entry")
+            for t in e.tokens:
+                if not 0 <= int(t) < self.vocab_size:
+                    raise StepError(f"request {e.request_id!r}: token id {t} is outside the vocabulary (0..{self.vocab_size - 1})")
+            for w in e.want:
+                if not 0 <= int(w) < len(e.tokens):
+                    raise StepError(f"request {e.request_id!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
+        new_ids = [e.request_id for e in entries if e.request_id not in self.cache]
+        free_slots = self.cache.max_requests - len(self.cache.live_requests())
+        if len(new_ids) > free_slots:
+            raise StepError(f"{len(new_ids)} new requests but only {free_slots} free request slots")
+        # all-or-nothing reservation across the whole batch
+        need = [0] * len(self.cache.paged_groups)
+        for e in entries:
+            held = self.cache.get(e.request_id) if e.request_id in self.cache else None
+            n_have = held.num_tokens if held else 0
+            if n_have + len(e.tokens) > self.options.ctx_size:
+                raise StepError(f"request {e.request_id!r}: {n_have + len(e.tokens)} tokens exceed the context size {self.options.ctx_size}")
+            total = -(-(n_have + len(e.tokens)) // page)
+            for gi in range(len(need)):
+                need[gi] += max(0, total - (len(held.tables[gi]) if held else 0))
+        free = self.cache.free_pages()
+        if any(n > f for n, f in zip(need, free)):
+            raise OutOfPages(f"the step needs {need} pages per group, {free} are free")
+        for rid in new_ids:
+            self.cache.add_request(rid)
+        for e in entries:
+            ok = self.cache.reserve(e.request_id, len(e.tokens))
+            assert ok, "reservation was checked for the whole batch"
+
+        R = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        N = sum(len(e.want) for e in entries)
+        G = len(self.cache.paged_groups)
+        rcs = [self.cache.get(e.request_id) for e in entries]
+        width = max(1, max(len(t) for rc in rcs for t in (rc.tables or [[0]])))
+        width = -(-width // 8) * 8
+        n_ints = 3 * T + (R + 1) + 2 * R + N + G * R * width
+        host = self._host_buffer(n_ints)
+        h = host.numpy()
+        o = 0
+        token_ids = h[o:o + T]; o += T
+        positions = h[o:o + T]; o += T
+        tok_req = h[o:o + T]; o += T
+        cu_q = h[o:o + R + 1]; o += R + 1
+        ctx_len = h[o:o + R]; o += R
+        slots = h[o:o + R]; o += R
+        logit_rows = h[o:o + N]; o += N
+        tables = h[o:o + G * R * width].reshape(G, R, width); o += G * R * width
+        tables[...] = -1
+        t0 = 0
+        n_want = 0
+        q_lens, ctx_lens, slot_list = [], [], []
+        for r, (e, rc) in enumerate(zip(entries, rcs)):
+            n = len(e.tokens)
+            token_ids[t0:t0 + n] = np.asarray(e.tokens, dtype=np.int32)
+            positions[t0:t0 + n] = np.arange(rc.num_tokens, rc.num_tokens + n, dtype=np.int32)
+            tok_req[t0:t0 + n] = r
+            cu_q[r] = t0
+            ctx_len[r] = rc.num_tokens + n
+            slots[r] = rc.slot
+            for w in e.want:
+                logit_rows[n_want] = t0 + int(w)
+                n_want += 1
+            for gi in range(G):
+                tab = rc.tables[gi]
+                tables[gi, r, :len(tab)] = tab
+            q_lens.append(n); ctx_lens.append(rc.num_tokens + n); slot_list.append(rc.slot)
+            t0 += n
+        cu_q[R] = T
+        dev = torch.empty(n_ints, dtype=torch.int32, device=self.device)
+        dev.copy_(host[:n_ints], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._pinned_events[self._slot_index] = ev
+        o = 0
+        def take(n):
+            nonlocal o
+            v = dev[o:o + n]; o += n
+            return v
+        ctx = StepContext(
+            dtype=self.dtype, device=self.device, T=T, R=R,
+            token_ids=take(T), positions=take(T), tok_req=take(T), cu_q=take(R + 1), ctx_len=take(R),
+            slots=take(R), logit_rows=take(N),
+            block_tables=[take(R * width).view(R, width) for _ in range(G)],
+            q_lens=q_lens, ctx_lens=ctx_lens, slot_list=slot_list, storage=self.storage, fast=self.fast)
+        logits = self.model.forward(ctx)
+        for e in entries:
+            self.cache.commit(e.request_id, len(e.tokens))
+        self.steps += 1
+        self.tokens_run += T
+        return logits

@@ -140,3 +140,24 @@ def argmax(logits: torch.Tensor, out_ids: torch.Tensor) -> None:
     rows, V = logits.shape
     _need(logits, "logits", torch.float32); _need(out_ids, "out_ids", torch.int32, (rows,))
     _call(_lib().bl_argmax, _p(logits), _p(out_ids), rows, V, _stream())
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           min_p: torch.Tensor, uniform: torch.Tensor, out_ids: torch.Tensor) -> None:
+    """One token per row: greedy where temperature <= 0, else temperature sampling after the top-k,
+    top-p and min-p cuts, with the row's uniform random number."""
+    rows, V = logits.shape
+    _need(logits, "logits", torch.float32)
+    _need(temperature, "temperature", torch.float32, (rows,)); _need(top_k, "top_k", torch.int32, (rows,))
+    _need(top_p, "top_p", torch.float32, (rows,)); _need(min_p, "min_p", torch.float32, (rows,))
+    _need(uniform, "uniform", torch.float32, (rows,)); _need(out_ids, "out_ids", torch.int32, (rows,))
+    _call(_lib().bl_sample, _p(logits), rows, V, _p(temperature), _p(top_k), _p(top_p), _p(min_p),
+          _p(uniform), _p(out_ids), _stream())
+
+
+def repeat_penalty(logits: torch.Tensor, tokens: torch.Tensor, offsets: torch.Tensor, penalty: torch.Tensor) -> None:
+    """In place: logits[r, t] /= penalty[r] if positive else *= penalty[r], for the listed tokens of row r."""
+    rows, V = logits.shape
+    _need(logits, "logits", torch.float32); _need(tokens, "tokens", torch.int32)
+    _need(offsets, "offsets", torch.int32, (rows + 1,)); _need(penalty, "penalty", torch.float32, (rows,))
+    _call(_lib().bl_repeat_penalty, _p(logits), rows, V, _p(tokens), _p(offsets), _p(penalty), _stream())
