@@ -1,0 +1,116 @@
+"""Generation through the Python entry point: greedy tokens equal the plain implementation's, sampled
+tokens are reproducible and follow the plain sampler, the scheduler's preemption does not change them."""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_model as plain
+
+pytestmark = pytest.mark.gpu
+
+PROMPTS = {"A": [7, 16, 33], "B": [1, 5, 19, 64]}
+N_NEW = {"A": 8, "B": 12}
+
+
+def prompts_for(name):
+    vocab = helpers.TINY[name]["vocab_size"]
+    return [helpers.random_tokens(vocab, n, 500 + n) for n in PROMPTS[name]]
+
+
+def check_greedy(d, prompt, out, dtype):
+    """Every generated token is the plain implementation's arg-max given the engine's own prefix; in
+    bfloat16 a near-tie (gap below the tolerance) may go either way."""
+    cfg, W = plain.read_model_folder(d)
+    logits = plain.forward(cfg, W, prompt + out).numpy()
+    scale = np.abs(logits).max()
+    for i, tok in enumerate(out):
+        row = logits[len(prompt) - 1 + i]
+        best = int(np.argmax(row))
+        if tok != best:
+            gap = row[best] - row[tok]
+            assert dtype == "bfloat16" and gap <= 2 * helpers.TOL[dtype] * scale, (
+                f"token {i}: engine chose {tok}, plain {best} (gap {gap:.3e})")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_equals_the_plain_implementation(model_folders, name, dtype):
+    from boring_llm_b200 import Engine
+    d = model_folders(name, dtype, 0.02)                  # the benchmark's weight scale
+    eng = Engine(d, dtype=dtype, ctx_size=128, max_num_seqs=4, max_tokens=512, prefill_chunk=8)
+    prompts = prompts_for(name)
+    outs = eng.generate(prompts, n_predict=N_NEW[name], ignore_eos=True)
+    assert [len(o) for o in outs] == [N_NEW[name]] * len(prompts)
+    for p, o in zip(prompts, outs):
+        check_greedy(d, p, o, dtype)
+        if dtype == "float32":
+            cfg, W = plain.read_model_folder(d)
+            assert o == plain.greedy_generate(cfg, W, p, len(o))
+    # one by one gives the same tokens as the batch
+    solo = [eng.generate([p], n_predict=N_NEW[name], ignore_eos=True)[0] for p in prompts]
+    assert solo == outs
+    s = eng.stats()
+    assert s["live_requests"] == 0 and s["pages_in_use"] == [0]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_preemption_does_not_change_the_tokens(model_folders, dtype):
+    from boring_llm_b200 import Engine
+    d = model_folders("B", dtype)
+    prompts = [helpers.random_tokens(320, n, 900 + n) for n in (30, 41, 25, 38)]
+    roomy = Engine(d, dtype=dtype, ctx_size=128, max_num_seqs=4, max_tokens=1024, prefill_chunk=16)
+    want = roomy.generate(prompts, n_predict=24, ignore_eos=True)
+    tight = Engine(d, dtype=dtype, ctx_size=128, max_num_seqs=4, max_tokens=160, prefill_chunk=16,
+                   max_num_batched_tokens=32)
+    got = tight.generate(prompts, n_predict=24, ignore_eos=True)
+    assert tight.stats()["preemptions"] >= 1
+    if dtype == "float32":
+        assert got == want
+    else:
+        for p, o in zip(prompts, got):
+            check_greedy(d, p, o, dtype)
+    tight.runner.cache.check()
+    assert tight.stats()["pages_in_use"] == [0]
+
+
+def test_temperature_sampling_is_seeded_and_follows_the_plain_sampler(model_folders):
+    from boring_llm_b200 import Engine
+    d = model_folders("B", "float32")
+    eng = Engine(d, dtype="float32", ctx_size=128, max_num_seqs=4, max_tokens=512, prefill_chunk=8)
+    prompts = prompts_for("B")
+    a = eng.generate(prompts, n_predict=12, temperature=0.8, seed=3, ignore_eos=True)
+    b = eng.generate(prompts, n_predict=12, temperature=0.8, seed=3, ignore_eos=True)
+    c = eng.generate(prompts, n_predict=12, temperature=0.8, seed=4, ignore_eos=True)
+    assert a == b and a != c
+    # request i draws from the generator seeded with seed + i: replay it on the plain side
+    cfg, W = plain.read_model_folder(d)
+    for i, (p, out) in enumerate(zip(prompts, a)):
+        state = plain.seed_rng(3 + i)
+        toks = list(p)
+        for tok in out:
+            logits = plain.forward(cfg, W, toks)[-1].numpy()
+            want, state = plain.sample(state, logits, 0.8)
+            assert tok == want
+            toks.append(tok)
+    k = eng.generate(prompts[:2], n_predict=6, temperature=1.5, seed=1, top_k=1, ignore_eos=True)
+    g = eng.generate(prompts[:2], n_predict=6, ignore_eos=True)
+    assert k == g                                           # top_k 1 is greedy
+
+
+def test_end_token_and_context_limit(model_folders):
+    from boring_llm_b200 import Engine
+    from boring_llm_b200.engine import AdmissionError
+    d = model_folders("A", "float32")
+    eng = Engine(d, dtype="float32", ctx_size=48, max_num_seqs=2, max_tokens=128)
+    p = helpers.random_tokens(256, 10, 1)
+    free = eng.generate([p], n_predict=10, ignore_eos=True)[0]
+    stop = free[3]
+    cut = eng.generate([p], n_predict=10, eos_token_ids=[stop])[0]
+    assert cut == free[:free.index(stop) + 1]               # returned, not fed (src/model.br:2299-2300)
+    full = eng.generate([p], n_predict=-1, ignore_eos=True)[0]
+    assert len(p) + len(full) == 48
+    with pytest.raises(AdmissionError):
+        eng.generate([list(range(48))], n_predict=1)
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.generate([[1, 2, 999]], n_predict=1)

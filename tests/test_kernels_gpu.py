@@ -1,0 +1,311 @@
+"""Each CUDA kernel alone against a plain 64-bit PyTorch restatement of the same formula, at sizes
+other than the engine's (odd widths, head sizes in steps of 16, group sizes 1/7/8, ragged pages)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def ops():
+    from boring_llm_b200.kernels import ops as o
+    return o
+
+
+def close(got, want, dtype, what=""):
+    tol = 2e-5 if dtype == torch.float32 else 1.6e-2
+    got, want = got.double().cpu(), want.double().cpu()
+    scale = max(want.abs().max().item(), 1e-6)
+    err = (got - want).abs().max().item()
+    assert err <= tol * scale, f"{what}: max |diff| {err:.3e} > {tol:.0e} * {scale:.3f}"
+
+
+def data(shape, salt, dtype=torch.float32):
+    """Deterministic values that are not exactly representable in half precision
+    (as test/test_math_gpu_real.br:25-31 chooses them)."""
+    n = int(np.prod(shape))
+    i = torch.arange(n, dtype=torch.float64)
+    x = ((i * 7 + salt * 13) % 101) / 101 * 4 - 2
+    return x.reshape(shape).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    table = data((77, 100), 1, dtype)
+    ids = torch.tensor([0, 76, 5, 5, 33], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 100, device=DEV)
+    ops().embed(table, ids, out)
+    assert torch.equal(out, table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("d", [1, 70, 896, 1000])
+@pytest.mark.parametrize("wdtype,ydtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                           (torch.float32, torch.bfloat16)])
+def test_rmsnorm(d, wdtype, ydtype):
+    x = data((9, d), 2) * 3
+    w = (data((d,), 3) * 0.25 + 1).to(wdtype)
+    y = torch.empty(9, d, dtype=ydtype, device=DEV)
+    ops().rmsnorm(x, w, 1e-5, y)
+    want = plain.rms_norm(x.double().cpu(), w.double().cpu(), 1e-5)
+    close(y, want, ydtype, "rmsnorm")
+    idx = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+    y2 = torch.empty(3, d, dtype=ydtype, device=DEV)
+    ops().rmsnorm(x, w, 1e-5, y2, idx)
+    assert torch.equal(y2, y[idx.long()])                 # a row's result does not depend on the row count
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (33, 129, 70), (130, 64, 257), (5, 200, 96)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemm_plain_epilogues(M, N, K, dtype):
+    o = ops()
+    x = (data((M, K), 4) * 0.5).to(dtype)
+    w = (data((2 * N, K), 5) * 0.25).to(dtype)
+    b = (data((N,), 6)).to(dtype)
+    xd, wd, bd = x.double().cpu(), w.double().cpu(), b.double().cpu()
+    out = torch.empty(M, N, device=DEV)
+    o.gemm_plain(x, w[:N].contiguous(), out)
+    close(out, xd @ wd[:N].T, torch.float32, "none")
+    o.gemm_plain(x, w[:N].contiguous(), out, b, o.EPI_BIAS)
+    close(out, xd @ wd[:N].T + bd, torch.float32, "bias")
+    res = data((M, N), 7)
+    acc = res.clone()
+    o.gemm_plain(x, w[:N].contiguous(), acc, None, o.EPI_RESIDUAL)
+    close(acc, res.double().cpu() + xd @ wd[:N].T, torch.float32, "residual")
+    act = torch.empty(M, N, dtype=dtype, device=DEV)
+    o.gemm_plain(x, w, act, None, o.EPI_SWIGLU)
+    g, u = xd @ wd[:N].T, xd @ wd[N:].T
+    close(act, plain.silu(g) * u, dtype, "swiglu")
+    # rows do not depend on how many rows the call has
+    one = torch.empty(1, N, device=DEV)
+    o.gemm_plain(x[M - 1:M].contiguous(), w[:N].contiguous(), one)
+    o.gemm_plain(x, w[:N].contiguous(), out)
+    assert torch.equal(one[0], out[M - 1])
+
+
+def paged_setup(ctx_lens, q_lens, KV, dh, page, dtype, seed, extra_pages=5):
+    """Random block tables over a shuffled pool; pages nobody owns and rows past a request's length
+    hold large junk that must never be read into a result."""
+    rng = np.random.default_rng(seed)
+    R = len(ctx_lens)
+    n_pages = [-(-c // page) for c in ctx_lens]
+    total = sum(n_pages) + extra_pages
+    perm = rng.permutation(total)
+    width = max(n_pages) + 2
+    table = np.full((R, width), -1, dtype=np.int32)
+    at = 0
+    for r in range(R):
+        table[r, :n_pages[r]] = perm[at:at + n_pages[r]]
+        at += n_pages[r]
+    kc = torch.full((total, KV, page, dh), 1.0e4, dtype=dtype, device=DEV)
+    vc = torch.full((total, KV, page, dh), -1.0e4, dtype=dtype, device=DEV)
+    cu = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    T = int(cu[-1])
+    tok_req = np.repeat(np.arange(R), q_lens).astype(np.int32)
+    positions = np.concatenate([np.arange(c - q, c) for c, q in zip(ctx_lens, q_lens)]).astype(np.int32)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+    return dict(R=R, T=T, table=t(table), table_np=table, kc=kc, vc=vc, cu_q=t(cu), ctx_len=t(np.array(ctx_lens, dtype=np.int32)),
+                tok_req=t(tok_req), positions=t(positions), positions_np=positions, tok_req_np=tok_req)
+
+
+def fill_cache(s, k_full, v_full, page):
+    """k_full[r]: [ctx, KV, dh] -> pages."""
+    for r, (k, v) in enumerate(zip(k_full, v_full)):
+        for p in range(k.shape[0]):
+            pg = int(s["table_np"][r, p // page])
+            s["kc"][pg, :, p % page, :] = k[p].to(s["kc"].dtype)
+            s["vc"][pg, :, p % page, :] = v[p].to(s["vc"].dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,KV,dh,rot", [(4, 2, 16, 16), (7, 1, 48, 48), (8, 8, 64, 32), (2, 1, 128, 128)])
+def test_rope_and_cache_write(dtype, H, KV, dh, rot):
+    o = ops()
+    page = 16
+    ctx_lens, q_lens = [5, 40, 17], [5, 9, 1]
+    s = paged_setup(ctx_lens, q_lens, KV, dh, page, dtype, 3)
+    T = s["T"]
+    qkv = data((T, (H + 2 * KV) * dh), 8)
+    base = 1.0e6
+    j = np.arange(rot // 2, dtype=np.float32)
+    inv = np.zeros(dh // 2, dtype=np.float32)
+    inv[:rot // 2] = np.float32(1.0) / np.power(np.float32(base), (np.float32(2.0) * j) / np.float32(rot), dtype=np.float32)
+    q_out = torch.empty(T, H * dh, dtype=dtype, device=DEV)
+    before_k = s["kc"].clone()
+    o.rope_kv_write(qkv, s["positions"], s["tok_req"], s["table"], torch.from_numpy(inv).to(DEV), rot // 2, 1.0,
+                    q_out, s["kc"], s["vc"], H, KV, dh)
+    x = qkv.double().cpu()
+    pos = s["positions_np"]
+
+    def rot_ref(t, n_heads):                       # NEOX pairs (j, j + rot/2) in the first `rot` dimensions
+        t = t.reshape(T, n_heads, dh)
+        r = plain.rope_neox(t[..., :rot], pos, inv[:rot // 2])
+        return torch.cat([r, t[..., rot:]], dim=-1)
+
+    q_ref = rot_ref(x[:, :H * dh], H).reshape(T, H * dh)
+    k_ref = rot_ref(x[:, H * dh:(H + KV) * dh], KV)
+    v_ref = x[:, (H + KV) * dh:].reshape(T, KV, dh)
+    close(q_out, q_ref, dtype, "q")
+    touched = torch.zeros(s["kc"].shape[0], page, dtype=torch.bool)                  # [pages, rows]
+    for t in range(T):
+        pg = int(s["table_np"][s["tok_req_np"][t], pos[t] // page]); row = pos[t] % page
+        close(s["kc"][pg, :, row, :], k_ref[t], dtype, "k page")
+        close(s["vc"][pg, :, row, :], v_ref[t], dtype, "v page")
+        touched[pg, row] = True
+    # nothing else in the pool was written
+    mask = touched.to(DEV)[:, None, :, None].expand_as(s["kc"])
+    assert torch.equal(s["kc"][~mask], before_k[~mask])
+    # without caches only q is produced
+    q2 = torch.empty_like(q_out)
+    o.rope_kv_write(qkv, s["positions"], s["tok_req"], s["table"], torch.from_numpy(inv).to(DEV), rot // 2, 1.0,
+                    q2, None, None, H, KV, dh)
+    assert torch.equal(q2, q_out)
+
+
+def attention_case(o, fn, dtype, H, KV, dh, ctx_lens, q_lens, window, seed, plant=True):
+    page = 16
+    s = paged_setup(ctx_lens, q_lens, KV, dh, page, dtype, seed)
+    g = torch.Generator().manual_seed(seed)
+    k_full = [torch.randn(c, KV, dh, generator=g, dtype=torch.float64) for c in ctx_lens]
+    v_full = [torch.randn(c, KV, dh, generator=g, dtype=torch.float64) for c in ctx_lens]
+    q_rows = [torch.randn(q, H, dh, generator=g, dtype=torch.float64) for q in q_lens]
+    if plant:
+        # one far key per request gets a score that stands out for the last query: a kernel that
+        # skips it, reads a neighbour or the wrong page changes the output beyond any tolerance
+        for r, c in enumerate(ctx_lens):
+            far = 0 if window == 0 else max(0, c - window)       # the first key the last query may see
+            k_full[r][far] = 0.0
+            k_full[r][far, :, 0] = 6.0
+            q_rows[r][-1, :, 0] = 3.0 * math.sqrt(dh)           # its score: 3 sqrt(dh) * 6 / sqrt(dh) = 18
+            if window > 0 and far > 0:
+                # the key just outside the window would score 30: a window that is one too wide shows
+                k_full[r][far - 1] = 0.0
+                k_full[r][far - 1, :, 0] = 10.0
+    k_full = [k.to(dtype).double() for k in k_full]
+    v_full = [v.to(dtype).double() for v in v_full]
+    q_rows = [q.to(dtype).double() for q in q_rows]
+    fill_cache(s, k_full, v_full, page)
+    q = torch.cat([x.reshape(x.shape[0], H * dh) for x in q_rows]).to(dtype).to(DEV)
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(dh)
+    fn(q, s["kc"], s["vc"], s["tok_req"], s["cu_q"], s["ctx_len"], s["table"], out, H, window, scale)
+    at = 0
+    for r, (c, n) in enumerate(zip(ctx_lens, q_lens)):
+        # whole-sequence plain attention; the chunk's queries are the last n rows
+        q_all = torch.zeros(c, H, dh, dtype=torch.float64)
+        q_all[c - n:] = q_rows[r]
+        want = plain.gqa_attention(q_all, k_full[r], v_full[r], scale, window)[c - n:].reshape(n, H * dh)
+        close(out[at:at + n], want, dtype, f"request {r} (ctx {c}, q {n}, window {window})")
+        at += n
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,KV,dh", [(4, 2, 16), (7, 1, 64), (8, 1, 128), (3, 3, 48), (2, 1, 256), (14, 2, 64)])
+def test_attention_plain_shapes(dtype, H, KV, dh):
+    o = ops()
+    # decode at 1, 37, 300, 520 keys (test/test_math_gpu_real.br:57-73), chunks over an existing cache with
+    # offsets off every tile size, a whole prompt, a two-token portion
+    attention_case(o, o.attention_plain, dtype, H, KV, dh, [1, 37, 300, 520], [1, 1, 1, 1], 0, 1)
+    attention_case(o, o.attention_plain, dtype, H, KV, dh, [333, 70, 16, 33], [70, 70, 2, 17], 0, 2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [1, 15, 16, 17, 40])
+def test_attention_plain_window_edges(dtype, window):
+    o = ops()
+    attention_case(o, o.attention_plain, dtype, 4, 2, 32, [50, 16, 90, 17], [1, 16, 33, 2], window, 5)
+
+
+def test_argmax_first_maximum_wins():
+    o = ops()
+    x = data((6, 1000), 9)
+    x[0, 17] = 50; x[0, 900] = 50
+    x[1, 999] = 60
+    x[2, 0] = 70
+    x[3] = -5.0
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    o.argmax(x, out)
+    want = [int(torch.argmax(r).item()) for r in x.cpu()]
+    assert out.cpu().tolist()[:3] == [17, 999, 0] and out.cpu().tolist()[3] == 0
+    assert out.cpu().tolist()[4:] == want[4:]
+
+
+@pytest.mark.parametrize("vocab", [37, 1000, 151936])
+def test_sampler_matches_the_plain_sampler(vocab):
+    o = ops()
+    rng = np.random.default_rng(vocab)
+    rows = 24
+    logits = (rng.standard_normal((rows, vocab)) * 3).astype(np.float32)
+    logits[5, 10] = logits[5, 20] = logits[5].max() + 1      # exact ties at the top
+    temps = np.array([0.0, 0.8, 1.0, 0.3, 2.0, 1.0] * 4, dtype=np.float32)
+    top_k = np.array([0, 0, 40, 5, 0, 2, 0, 1] * 3, dtype=np.int32)
+    top_p = np.array([1.0, 0.9, 1.0, 0.5, 1.0, 1.0, 0.1, 1.0] * 3, dtype=np.float32)
+    min_p = np.array([0.0, 0.0, 0.0, 0.05, 0.2, 0.0] * 4, dtype=np.float32)
+    state = plain.seed_rng(7)
+    us = []
+    want = []
+    for r in range(rows):
+        u = 0.0
+        if temps[r] > 0:
+            before = state
+            tok, state = plain.sample(before, logits[r], float(temps[r]), int(top_k[r]), float(top_p[r]), float(min_p[r]))
+            u, _ = plain.rng_next_f32(before)
+        else:
+            tok, _ = plain.sample(state, logits[r], 0.0)
+        us.append(u); want.append(tok)
+    t = lambda a: torch.from_numpy(a).to(DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    o.sample(t(logits), t(temps), t(top_k), t(top_p), t(min_p), t(np.array(us, dtype=np.float32)), out)
+    assert out.cpu().tolist() == want
+    out2 = torch.empty_like(out)
+    o.sample(t(logits), t(temps), t(top_k), t(top_p), t(min_p), t(np.array(us, dtype=np.float32)), out2)
+    assert torch.equal(out, out2)                             # the same on every run
+
+
+def test_sampler_distribution():
+    o = ops()
+    logits = torch.tensor([0.1, 2.0, -1.0, 1.5, 0.5], device=DEV).repeat(4000, 1)
+    g = plain.seed_rng(3)
+    us = []
+    for _ in range(4000):
+        u, g = plain.rng_next_f32(g)
+        us.append(u)
+    n = 4000
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    one = lambda v, dt: torch.full((n,), v, dtype=dt, device=DEV)
+    o.sample(logits, one(1.0, torch.float32), one(0, torch.int32), one(1.0, torch.float32), one(0.0, torch.float32),
+             torch.tensor(us, device=DEV), out)
+    p = torch.softmax(logits[0].double().cpu(), 0)
+    freq = torch.bincount(out.cpu().long(), minlength=5).double() / n
+    assert (freq - p).abs().max() < 0.03
+
+
+def test_repeat_penalty():
+    o = ops()
+    logits = torch.tensor([[1.0, -2.0, 3.0, 0.0], [1.0, -2.0, 3.0, 4.0]], device=DEV)
+    o.repeat_penalty(logits, torch.tensor([0, 1, 3, 2], dtype=torch.int32, device=DEV),
+                     torch.tensor([0, 3, 4], dtype=torch.int32, device=DEV), torch.tensor([2.0, 1.0], device=DEV))
+    assert logits.cpu().tolist() == [[0.5, -4.0, 3.0, 0.0], [1.0, -2.0, 3.0, 4.0]]
+
+
+def test_kernels_refuse_what_they_cannot_run():
+    from boring_llm_b200.kernels import KernelError
+    o = ops()
+    q = torch.zeros(1, 2 * 272, device=DEV)
+    kc = torch.zeros(1, 1, 16, 272, device=DEV)
+    i = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match="head size"):
+        o.attention_plain(q, kc, kc, i, torch.tensor([0, 1], dtype=torch.int32, device=DEV), i + 1, i.view(1, 1), q.clone(), 2, 0, 1.0)
+    with pytest.raises(KernelError, match="share"):
+        o.attention_plain(torch.zeros(1, 3 * 16, device=DEV), torch.zeros(1, 2, 16, 16, device=DEV),
+                          torch.zeros(1, 2, 16, 16, device=DEV), i, torch.tensor([0, 1], dtype=torch.int32, device=DEV),
+                          i + 1, i.view(1, 1), torch.zeros(1, 48, device=DEV), 3, 0, 1.0)
+    with pytest.raises(KernelError, match="contiguous"):
+        o.gemm_plain(torch.zeros(4, 8, device=DEV).t(), torch.zeros(3, 4, device=DEV), torch.zeros(8, 3, device=DEV))
+    with pytest.raises(KernelError, match="CUDA"):
+        o.argmax(torch.zeros(2, 3), torch.zeros(2, dtype=torch.int32))

@@ -1,0 +1,156 @@
+"""Trace replay against the plain implementation: each request alone and whole; most of it in one step
+and the last 32 tokens one by one; in portions of changing size down to two tokens; and mixed, up to
+four live requests with portions of some beside single tokens of others and so few pages that they
+are used again. In float32 and in bfloat16, for three tiny configurations."""
+import os
+
+import numpy as np
+import pytest
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+# prompts + continuations, as lengths: a one-token prompt, lengths off every page edge, one over 4 pages
+LENGTHS = {"A": [7 + 8, 16 + 8, 33 + 8, 70], "B": [1 + 12, 5 + 12, 19 + 12, 64 + 12], "C": [3, 45, 64, 90]}
+
+
+def requests_for(name):
+    vocab = helpers.TINY[name]["vocab_size"]
+    return {f"{name}{i}": helpers.random_tokens(vocab, n, 100 * helpers.SEEDS[name] + i)
+            for i, n in enumerate(LENGTHS[name])}
+
+
+def check_rows(rows, expected, dtype, what):
+    for rid, want in expected.items():
+        got = np.stack([rows[(rid, p)] for p in range(want.shape[0])])
+        helpers.assert_close(got, want, dtype, f"{what}, request {rid}")
+
+
+@pytest.fixture(scope="module")
+def expected(model_folders):
+    cache = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in cache:
+            d = model_folders(name, dtype)
+            cache[(name, dtype)] = {rid: helpers.plain_logits(d, toks) for rid, toks in requests_for(name).items()}
+        return cache[(name, dtype)]
+    return get
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_all_ways_of_cutting_agree_with_the_plain_implementation(model_folders, expected, name, dtype):
+    d = model_folders(name, dtype)
+    reqs = requests_for(name)
+    want = expected(name, dtype)
+    by_mode = {}
+    for mode, cut in [("whole", helpers.cut_whole), ("tail one by one", helpers.cut_tail_singly),
+                      ("changing portions", None)]:
+        steps, n0 = [], 0
+        for i, (rid, toks) in enumerate(reqs.items()):
+            sizes = cut(toks) if cut else helpers.cut_varying(toks, 17 + i)
+            s = helpers.solo_trace(rid, toks, sizes, n0)
+            steps += s; n0 += len(s)
+        outputs, runner = helpers.run_inprocess(d, dtype, steps, max_tokens=128)
+        rows = helpers.collect_rows(steps, outputs)
+        check_rows(rows, want, dtype, f"{name} {dtype} {mode}")
+        by_mode[mode] = rows
+    steps, peak = helpers.mixed_trace(reqs, seed=5, max_live=4)
+    assert any(len(s["entries"]) > 1 and min(len(e["tokens"]) for e in s["entries"]) == 1
+               and max(len(e["tokens"]) for e in s["entries"]) > 1 for s in steps), "no step mixes portions and single tokens"
+    # run the same mixed trace twice over in one pool, so the second pass lands on used pages
+    again = [dict(s, step=s["step"] + len(steps),
+                  entries=[dict(e, id=e["id"] + "'") for e in s["entries"]], end=[r + "'" for r in s["end"]]) for s in steps]
+    outputs, runner = helpers.run_inprocess(d, dtype, steps + again, max_tokens=peak)
+    assert max(runner.cache.stats()["pages_high_water"]) <= peak // 16
+    rows = helpers.collect_rows(steps + again, outputs)
+    check_rows(rows, want, dtype, f"{name} {dtype} mixed")
+    check_rows({(rid[:-1], p): v for (rid, p), v in rows.items() if rid.endswith("'")}, want, dtype,
+               f"{name} {dtype} mixed, second pass on used pages")
+    by_mode["mixed"] = rows
+    if dtype == "float32":
+        # the 32-bit path computes a position the same way however the work is cut
+        ref = by_mode["whole"]
+        scale = max(np.abs(v).max() for v in ref.values())
+        for mode, rows in by_mode.items():
+            worst = max(np.abs(rows[k] - ref[k]).max() for k in ref)
+            assert worst <= 2e-6 * scale, f"{name}: '{mode}' differs from 'whole' by {worst:.3e}"
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16")])
+def test_the_trace_run_program(model_folders, expected, tmp_path, name, dtype):
+    """bin/trace_run as a user drives it: a line in, `done <step>` out, files per step, exit code 0."""
+    d = model_folders(name, dtype)
+    reqs = requests_for(name)
+    steps, peak = helpers.mixed_trace(reqs, seed=9, max_live=4)
+    steps.append({"step": steps[-1]["step"] + 1, "entries": [{"id": "nolog", "tokens": [1, 2, 3], "want": []}], "end": ["nolog"]})
+    out = str(tmp_path / "out")
+    env = dict(os.environ, HOME=str(tmp_path / "home"))
+    outputs = helpers.run_trace_program(d, dtype, steps, peak, out, helpers.TINY[name]["vocab_size"], env)
+    rows = helpers.collect_rows(steps, outputs)
+    check_rows(rows, expected(name, dtype), dtype, f"trace_run {name} {dtype}")
+
+
+def test_long_decoding_and_first_tokens(model_folders):
+    """300 tokens decoded one by one after a short prompt (19 pages, past a window many times over), and
+    the very first positions of a sequence, where a page, a chunk and a window all begin."""
+    for name, dtype in [("C", "float32"), ("C", "bfloat16"), ("A", "bfloat16")]:
+        d = model_folders(name, dtype)
+        toks = helpers.random_tokens(helpers.TINY[name]["vocab_size"], 5 + 300, 77)
+        steps = helpers.solo_trace("long", toks, [5] + [1] * 300)
+        outputs, _ = helpers.run_inprocess(d, dtype, steps, max_tokens=320)
+        rows = helpers.collect_rows(steps, outputs)
+        want = helpers.plain_logits(d, toks)
+        got = np.stack([rows[("long", p)] for p in range(len(toks))])
+        helpers.assert_close(got, want, dtype, f"long decoding {name} {dtype}")
+        helpers.assert_close(got[:3], want[:3], dtype, f"first tokens {name} {dtype}")
+        steps = helpers.solo_trace("one", toks[:4], [1, 1, 2])
+        outputs, _ = helpers.run_inprocess(d, dtype, steps, max_tokens=64)
+        rows = helpers.collect_rows(steps, outputs)
+        helpers.assert_close(np.stack([rows[("one", p)] for p in range(4)]), want[:4], dtype, "token by token from the start")
+
+
+def test_a_far_key_decides_the_answer(model_folders, tmp_path):
+    """Random weights give near-uniform attention, which would hide a skipped key among hundreds. Here the
+    first layer's query/key weights are scaled up so attention is sharp, and a 260-token prompt is
+    replayed whole and in portions in bfloat16: dropping or misplacing any single key moves the logits."""
+    import plain_model as plain
+    from boring_llm_b200.weights import SafetensorsFile, write_safetensors
+    import shutil
+    src = model_folders("B", "bfloat16")
+    d = str(tmp_path / "sharp")
+    shutil.copytree(src, d)
+    f = SafetensorsFile(os.path.join(d, "model.safetensors"))
+    t = {n: f.tensor(n).clone() for n in f.names()}
+    f.close()
+    for n in t:
+        if "q_proj.weight" in n or "k_proj.weight" in n:
+            t[n] = (t[n].float() * 3.0).to(t[n].dtype)
+    write_safetensors(os.path.join(d, "model.safetensors"), t)
+    toks = helpers.random_tokens(320, 260, 5)
+    want = helpers.plain_logits(d, toks)
+    for sizes in ([260], [200] + [1] * 60, helpers.cut_varying(toks, 3)):
+        steps = helpers.solo_trace("s", toks, sizes)
+        outputs, _ = helpers.run_inprocess(d, "bfloat16", steps, max_tokens=320)
+        rows = helpers.collect_rows(steps, outputs)
+        helpers.assert_close(np.stack([rows[("s", p)] for p in range(260)]), want, "bfloat16", f"sharp attention, cuts {sizes[:4]}...")
+
+
+def test_steps_that_cannot_run_are_refused(model_folders):
+    from boring_llm_b200.engine.runner import OutOfPages, StepEntry, StepError
+    d = model_folders("A", "float32")
+    _, runner = helpers.run_inprocess(d, "float32", [], max_tokens=64)
+    with pytest.raises(StepError, match="outside the vocabulary"):
+        runner.step([StepEntry("a", [1, 256], [0])])
+    with pytest.raises(StepError, match="wanted place"):
+        runner.step([StepEntry("a", [1, 2], [2])])
+    with pytest.raises(StepError, match="twice"):
+        runner.step([StepEntry("a", [1], []), StepEntry("a", [2], [])])
+    with pytest.raises(OutOfPages):
+        runner.step([StepEntry("a", [1] * 40, []), StepEntry("b", [1] * 40, [])])
+    assert runner.cache.free_pages() == [4] and not runner.cache.live_requests()     # nothing was changed
+    runner.step([StepEntry("a", [1] * 40, [])])
+    with pytest.raises(StepError, match="context size"):
+        runner.step([StepEntry("a", [1] * 30, [])])
