@@ -54,6 +54,25 @@ int bl_sample(const float* logits, int rows, int vocab, const float* temperature
 int bl_repeat_penalty(float* logits, int rows, int vocab, const int* tokens, const int* offsets,
                       const float* penalty, void* stream);
 
+// Matrix product for few rows (decode): bfloat16 x[M, K] and W[N, K] read once from global memory straight
+// into tensor-core registers. K must be a multiple of 8, x and W 16-byte aligned. Same epilogues as bl_gemm_plain.
+int bl_gemm_skinny(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype,
+                   int M, int N, int K, int epilogue, void* stream);
+
+// Tensor-core paged attention (bfloat16, pages of 16 tokens, head sizes 16/32/48/64/96/128).
+int bl_attention_mma_supported(int dh, int page_size);
+// Prefill shape: tiles[n_tiles][2] = (request, first token of a 64-token tile within the request's new tokens).
+int bl_attention_prefill(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                         const int* ctx_len, const int* block_table, int max_pages, const int* tiles, int n_tiles,
+                         void* out, int H, int KV, int dh, int page_size, int window, float scale, void* stream);
+// Decode shape: reqs[n] = requests with one new token; their keys are cut into n_splits slices that a second
+// kernel merges. scratch: bl_attention_decode_scratch_floats(n, H, dh, n_splits) floats (none for one slice).
+long long bl_attention_decode_scratch_floats(int n, int H, int dh, int n_splits);
+int bl_attention_decode(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                        const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
+                        int n_splits, float* scratch, void* out, int H, int KV, int dh, int page_size,
+                        int window, float scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

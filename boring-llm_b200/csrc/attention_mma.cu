@@ -1,0 +1,427 @@
+// Paged causal grouped-query attention on tensor cores (bfloat16 operands, 32-bit accumulation and
+// softmax statistics), in two shapes that share their inner loops:
+//   prefill: a block is 64 consecutive tokens of one request and one query head, 16 rows per warp, and
+//            walks the request's keys in blocks of 64 (four 16-token pages) up to the diagonal;
+//   decode:  a block is one single-token request, one key/value head and one slice of its keys; the 16 MMA
+//            rows are the query heads that share that key/value head (every key and value is read once
+//            for all of them), the four warps take a page each of every 64-key block, and slices of long
+//            contexts are merged by a second small kernel from partial (max, sum, output) triples.
+// Keys and values come from the request's pages through its block table with 16-byte cp.async copies into
+// padded shared-memory tiles, double buffered. Softmax is the online form of the reference's flash kernels
+// (FlashAttnRegKernel, src/math_gpu.br:3309-3504: running max m, sum l, rescale by exp(m - m_new)); the
+// split of one query's keys and its merge follow FlashDecodeKernel / FlashDecodeCombineKernel
+// (:3520-3679) and the sharing of key/value reads across a group follows FlashDecodeWarpTail128Kernel
+// (:3793-3925). Scores are scaled after the dot product (src/math.br:319-322); a key j is visible to a query
+// at position p when j <= p and, with a window, j + window > p (:327-328).
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+
+constexpr int PAGE = 16;
+constexpr int KB = 64;            // keys per block
+constexpr int THREADS = 128;
+constexpr int PAD = 8;            // bfloat16 elements of padding per shared-memory row (keeps ldmatrix conflict-free)
+
+struct AttnParams {
+    const __nv_bfloat16* q; const __nv_bfloat16* kc; const __nv_bfloat16* vc; __nv_bfloat16* out;
+    const int* cu_q; const int* ctx_len; const int* block_table; int max_pages;
+    const int* work;              // prefill: [n][2] (request, first token of the tile within the request); decode: [n] requests
+    float* part_o; float* part_ml; int n_splits;
+    int H, KV, window; float scale_log2;
+};
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(addr), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" :: "n"(N)); }
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+template <int DH>
+struct Tiles {
+    static constexpr int ROW = DH + PAD;
+    static constexpr int STAGE = 2 * KB * ROW;                    // elements: K tile then V tile
+    static constexpr int BYTES = 2 * STAGE * (int)sizeof(__nv_bfloat16);
+};
+
+// Copies keys [key0, key0 + 64) of one key/value head into a stage; keys outside [lo, hi] or on a page that the
+// table no longer holds become zeros (they are masked, and zeros keep the value product finite).
+template <int DH>
+__device__ __forceinline__ void load_block(__nv_bfloat16* stage, const AttnParams& p, const int* table, int kvh,
+                                           int key0, int lo, int hi) {
+    constexpr int CH = DH / 8;                                    // 16-byte chunks per row
+    constexpr int ROW = Tiles<DH>::ROW;
+    __nv_bfloat16* ks = stage;
+    __nv_bfloat16* vs = stage + KB * ROW;
+    for (int i = threadIdx.x; i < KB * CH; i += THREADS) {
+        const int r = i / CH, c = i % CH;
+        const int key = key0 + r;
+        int page = -1;
+        if (key >= lo && key <= hi) page = table[key / PAGE];
+        __nv_bfloat16* kd = ks + r * ROW + c * 8;
+        __nv_bfloat16* vd = vs + r * ROW + c * 8;
+        if (page >= 0) {
+            const size_t off = (((size_t)page * p.KV + kvh) * PAGE + (key % PAGE)) * DH + c * 8;
+            cp_async16(kd, p.kc + off);
+            cp_async16(vd, p.vc + off);
+        } else {
+            *reinterpret_cast<uint4*>(kd) = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(vd) = make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+}
+
+// One warp, 16 rows, NT n-tiles of 8 keys starting at key `koff` of the staged block.
+template <int DH, int NT>
+__device__ __forceinline__ void block_step(const __nv_bfloat16* stage, int koff, int key_abs0,
+                                           const unsigned (&qf)[DH / 16][4], float (&o)[DH / 8][4],
+                                           float (&m)[2], float (&l)[2], const int (&pos)[2], int window,
+                                           float scale_log2) {
+    constexpr int ROW = Tiles<DH>::ROW;
+    const __nv_bfloat16* ks = stage;
+    const __nv_bfloat16* vs = stage + KB * ROW;
+    const int lane = threadIdx.x & 31, t = lane & 3;
+    const int mi = lane >> 3, ri = lane & 7;                      // ldmatrix: which 8x8 matrix, which row of it
+    float s[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+#pragma unroll
+    for (int np = 0; np < NT / 2; ++np) {
+#pragma unroll
+        for (int kk = 0; kk < DH / 16; ++kk) {
+            unsigned b[4];
+            ldmatrix_x4(b, ks + (koff + np * 16 + (mi >> 1) * 8 + ri) * ROW + kk * 16 + (mi & 1) * 8);
+            mma_bf16(s[2 * np], qf[kk], b[0], b[1]);
+            mma_bf16(s[2 * np + 1], qf[kk], b[2], b[3]);
+        }
+    }
+    // scale, mask, running maximum
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int j = key_abs0 + koff + n * 8 + 2 * t + (c & 1);
+            const int p = pos[c >> 1];
+            const bool seen = j <= p && (window <= 0 || j + window > p);
+            const float v = seen ? s[n][c] * scale_log2 : -INFINITY;
+            s[n][c] = v;
+            mx[c >> 1] = fmaxf(mx[c >> 1], v);
+        }
+    }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(m[h], mx[h]);
+        m_use[h] = m_new == -INFINITY ? 0.f : m_new;              // a row that has seen no key yet
+        alpha[h] = exp2f(m[h] - m_use[h]);                         // exp2(-inf) = 0 on the first block
+        m[h] = m_new;
+        l[h] *= alpha[h];
+    }
+#pragma unroll
+    for (int n = 0; n < DH / 8; ++n) { o[n][0] *= alpha[0]; o[n][1] *= alpha[0]; o[n][2] *= alpha[1]; o[n][3] *= alpha[1]; }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const float e = exp2f(s[n][c] - m_use[c >> 1]);
+            s[n][c] = e;
+            l[c >> 1] += e;
+        }
+    }
+    // out += P . V, P rounded to bfloat16 as the tensor cores' left operand
+#pragma unroll
+    for (int kk = 0; kk < NT / 2; ++kk) {
+        unsigned a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int np = 0; np < DH / 16; ++np) {
+            unsigned b[4];
+            ldmatrix_x4_trans(b, vs + (koff + kk * 16 + (mi & 1) * 8 + ri) * ROW + np * 16 + (mi >> 1) * 8);
+            mma_bf16(o[2 * np], a, b[0], b[1]);
+            mma_bf16(o[2 * np + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+template <int DH, bool DECODE>
+__global__ void __launch_bounds__(THREADS)
+attention_mma_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int G = p.H / p.KV;
+    int r, kvh, head0, tok0, split = 0;
+    if (DECODE) {
+        r = p.work[blockIdx.z];
+        const int groups16 = (G + 15) / 16;
+        kvh = blockIdx.y / groups16;
+        head0 = kvh * G + (blockIdx.y % groups16) * 16;           // first of up to 16 query heads of this block
+        split = blockIdx.x;
+        tok0 = 0;
+    } else {
+        r = p.work[2 * blockIdx.x];
+        tok0 = p.work[2 * blockIdx.x + 1];
+        head0 = blockIdx.y;
+        kvh = head0 / G;
+    }
+    const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin, ctx = p.ctx_len[r];
+    const int* table = p.block_table + (size_t)r * p.max_pages;
+    // rows g and g + 8 of this warp
+    int pos[2], tok[2], head[2];
+    bool valid[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int row = g + 8 * h;
+        if (DECODE) {
+            tok[h] = 0; head[h] = head0 + row;
+            valid[h] = head[h] < (kvh + 1) * G && q_len > 0;
+        } else {
+            tok[h] = tok0 + warp * 16 + row; head[h] = head0;
+            valid[h] = tok[h] < q_len;
+        }
+        pos[h] = valid[h] ? ctx - q_len + tok[h] : -1;            // an invalid row sees nothing
+    }
+    // the block's range of keys
+    const int first_tok = DECODE ? 0 : tok0;
+    const int last_tok = DECODE ? 0 : min(q_len, tok0 + KB) - 1;
+    const int p_first = ctx - q_len + first_tok, p_last = ctx - q_len + last_tok;
+    const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
+    const int hi = p_last;
+    int b_begin = lo / KB, b_end = hi / KB + 1;
+    if (q_len <= 0) b_end = b_begin;
+    if (DECODE) {
+        const int nb = b_end - b_begin;
+        const int per = (nb + p.n_splits - 1) / p.n_splits;
+        const int s0 = b_begin + split * per;
+        b_end = min(b_end, s0 + per);
+        b_begin = min(s0, b_end);
+    }
+    unsigned qf[DH / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < DH / 16; ++kk) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            unsigned lo32 = 0u, hi32 = 0u;
+            if (valid[h]) {
+                const __nv_bfloat16* qp = p.q + ((size_t)(q_begin + tok[h]) * p.H + head[h]) * DH + kk * 16 + 2 * t;
+                lo32 = *reinterpret_cast<const unsigned*>(qp);
+                hi32 = *reinterpret_cast<const unsigned*>(qp + 8);
+            }
+            qf[kk][h] = lo32; qf[kk][2 + h] = hi32;
+        }
+    }
+    float o[DH / 8][4];
+#pragma unroll
+    for (int n = 0; n < DH / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    constexpr int STAGE = Tiles<DH>::STAGE;
+    if (b_begin < b_end) load_block<DH>(smem, p, table, kvh, b_begin * KB, lo, hi);
+    cp_async_commit();
+    for (int b = b_begin; b < b_end; ++b) {
+        const int st = (b - b_begin) & 1;
+        if (b + 1 < b_end) load_block<DH>(smem + (st ^ 1) * STAGE, p, table, kvh, (b + 1) * KB, lo, hi);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (DECODE)
+            block_step<DH, 2>(smem + st * STAGE, warp * 16, b * KB, qf, o, m, l, pos, p.window, p.scale_log2);
+        else
+            block_step<DH, 8>(smem + st * STAGE, 0, b * KB, qf, o, m, l, pos, p.window, p.scale_log2);
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    if (!DECODE) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if (!valid[h]) continue;
+            const float inv = l[h] > 0.f ? 1.0f / l[h] : 0.f;
+            __nv_bfloat16* op = p.out + ((size_t)(q_begin + tok[h]) * p.H + head[h]) * DH + 2 * t;
+#pragma unroll
+            for (int n = 0; n < DH / 8; ++n)
+                *reinterpret_cast<unsigned*>(op + n * 8) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+        }
+        return;
+    }
+    // decode: merge the four warps (same 16 rows, different keys), then write the slice's result
+    __syncthreads();
+    float* so = reinterpret_cast<float*>(smem_raw);               // [4 warps][16 rows][DH]
+    float* sm = so + 4 * 16 * DH;                                 // [4][16] maxima
+    float* sl = sm + 4 * 16;                                      // [4][16] sums
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int row = g + 8 * h;
+        if (t == 0) { sm[warp * 16 + row] = m[h]; sl[warp * 16 + row] = l[h]; }
+#pragma unroll
+        for (int n = 0; n < DH / 8; ++n) {
+            so[(warp * 16 + row) * DH + n * 8 + 2 * t] = o[n][2 * h];
+            so[(warp * 16 + row) * DH + n * 8 + 2 * t + 1] = o[n][2 * h + 1];
+        }
+    }
+    __syncthreads();
+    const int rows_here = min(16, (kvh + 1) * G - head0);
+    const int q_tok = q_begin;
+    for (int i = threadIdx.x; i < rows_here * DH; i += THREADS) {
+        const int row = i / DH, d = i % DH;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm[w * 16 + row]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = sm[w * 16 + row];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+            L += sl[w * 16 + row] * f;
+            O += so[(w * 16 + row) * DH + d] * f;
+        }
+        const int hd = head0 + row;
+        if (q_len <= 0) continue;
+        if (p.n_splits == 1) {
+            p.out[((size_t)q_tok * p.H + hd) * DH + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        } else {
+            const size_t slot = ((size_t)blockIdx.z * p.H + hd) * p.n_splits + split;
+            p.part_o[slot * DH + d] = O;
+            if (d == 0) { p.part_ml[slot * 2] = M; p.part_ml[slot * 2 + 1] = L; }
+        }
+    }
+}
+
+// Merges the slices of one (request, head): out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
+// (FlashDecodeCombineKernel, src/math_gpu.br:3597-3631).
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       const int* __restrict__ work, const int* __restrict__ cu_q,
+                                       __nv_bfloat16* __restrict__ out, int H, int DH, int n_splits) {
+    const int idx = blockIdx.x, hd = blockIdx.y;
+    const int r = work[idx];
+    if (cu_q[r + 1] - cu_q[r] <= 0) return;
+    const size_t base = ((size_t)idx * H + hd) * n_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+    for (int d = threadIdx.x; d < DH; d += blockDim.x) {
+        float L = 0.f, O = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = part_ml[(base + s) * 2];
+            const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+            L += part_ml[(base + s) * 2 + 1] * f;
+            O += part_o[(base + s) * DH + d] * f;
+        }
+        out[((size_t)cu_q[r] * H + hd) * DH + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    }
+}
+
+template <int DH, bool DECODE>
+int launch(const AttnParams& p, dim3 grid, cudaStream_t s) {
+    static bool configured = false;                               // per template instance
+    const int bytes = Tiles<DH>::BYTES > (int)((4 * 16 * DH + 128) * sizeof(float)) ? Tiles<DH>::BYTES
+                                                                                     : (int)((4 * 16 * DH + 128) * sizeof(float));
+    if (!configured) {
+        BL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<DH, DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+        configured = true;
+    }
+    attention_mma_kernel<DH, DECODE><<<grid, THREADS, bytes, s>>>(p);
+    BL_CHECK_LAUNCH("bl_attention_mma");
+    return 0;
+}
+
+template <bool DECODE>
+int dispatch(int dh, const AttnParams& p, dim3 grid, cudaStream_t s) {
+    switch (dh) {
+        case 16: return launch<16, DECODE>(p, grid, s);
+        case 32: return launch<32, DECODE>(p, grid, s);
+        case 48: return launch<48, DECODE>(p, grid, s);
+        case 64: return launch<64, DECODE>(p, grid, s);
+        case 96: return launch<96, DECODE>(p, grid, s);
+        case 128: return launch<128, DECODE>(p, grid, s);
+        default: BL_FAIL("bl_attention_mma: head size %d is not built (16, 32, 48, 64, 96, 128); use the plain kernel", dh);
+    }
+}
+
+int check(int H, int KV, int dh, int page_size, int max_pages, int window) {
+    if (H <= 0 || KV <= 0 || H % KV != 0) BL_FAIL("bl_attention_mma: %d heads cannot share %d key/value heads", H, KV);
+    if (page_size != PAGE) BL_FAIL("bl_attention_mma: pages of %d tokens are not built (16 only); use the plain kernel", page_size);
+    if (max_pages <= 0 || window < 0) BL_FAIL("bl_attention_mma: bad table width or window");
+    if (dh != 16 && dh != 32 && dh != 48 && dh != 64 && dh != 96 && dh != 128)
+        BL_FAIL("bl_attention_mma: head size %d is not built (16, 32, 48, 64, 96, 128); use the plain kernel", dh);
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int bl_attention_mma_supported(int dh, int page_size) {
+    return page_size == PAGE && (dh == 16 || dh == 32 || dh == 48 || dh == 64 || dh == 96 || dh == 128);
+}
+
+// Prefill shape. tiles: [n_tiles][2] = (request, first token of a 64-token tile inside the request's new tokens).
+extern "C" int bl_attention_prefill(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                                    const int* ctx_len, const int* block_table, int max_pages, const int* tiles,
+                                    int n_tiles, void* out, int H, int KV, int dh, int page_size, int window,
+                                    float scale, void* stream) {
+    if (n_tiles <= 0) return 0;
+    if (check(H, KV, dh, page_size, max_pages, window)) return 1;
+    AttnParams p;
+    p.q = (const __nv_bfloat16*)q; p.kc = (const __nv_bfloat16*)k_cache; p.vc = (const __nv_bfloat16*)v_cache;
+    p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
+    p.work = tiles; p.part_o = nullptr; p.part_ml = nullptr; p.n_splits = 1; p.H = H; p.KV = KV; p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    return dispatch<false>(dh, p, dim3(n_tiles, H, 1), (cudaStream_t)stream);
+}
+
+// Floats of scratch that bl_attention_decode needs for n requests and n_splits slices (0 when n_splits is 1).
+extern "C" long long bl_attention_decode_scratch_floats(int n, int H, int dh, int n_splits) {
+    return n_splits <= 1 ? 0 : (long long)n * H * n_splits * (dh + 2);
+}
+
+// Decode shape. reqs: [n] indices of single-token requests. scratch: bl_attention_decode_scratch_floats() floats.
+extern "C" int bl_attention_decode(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                                   const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
+                                   int n_splits, float* scratch, void* out, int H, int KV, int dh, int page_size,
+                                   int window, float scale, void* stream) {
+    if (n <= 0) return 0;
+    if (check(H, KV, dh, page_size, max_pages, window)) return 1;
+    if (n_splits < 1 || n_splits > 65535) BL_FAIL("bl_attention_decode: %d slices", n_splits);
+    if (n_splits > 1 && scratch == nullptr) BL_FAIL("bl_attention_decode: slices need scratch memory");
+    AttnParams p;
+    p.q = (const __nv_bfloat16*)q; p.kc = (const __nv_bfloat16*)k_cache; p.vc = (const __nv_bfloat16*)v_cache;
+    p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
+    p.work = reqs; p.n_splits = n_splits; p.H = H; p.KV = KV; p.window = window;
+    p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)n * H * n_splits * dh : nullptr;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    const int G = H / KV;
+    if (dispatch<true>(dh, p, dim3(n_splits, KV * ((G + 15) / 16), n), (cudaStream_t)stream)) return 1;
+    if (n_splits > 1) {
+        attention_merge_kernel<<<dim3(n, H), dh < 32 ? 32 : dh, 0, (cudaStream_t)stream>>>(
+            p.part_o, p.part_ml, reqs, cu_q, p.out, H, dh, n_splits);
+        BL_CHECK_LAUNCH("bl_attention_decode merge");
+    }
+    return 0;
+}

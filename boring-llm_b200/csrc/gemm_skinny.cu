@@ -1,0 +1,141 @@
+// Matrix product for few rows (decode steps, short portions): out[M, N] = epilogue(x[M, K] . W[N, K]^T) with
+// M up to a few dozen tokens. The step is bound by reading W once from HBM, so W goes straight from global
+// memory into tensor-core registers with 16-byte loads and never touches shared memory: the product is
+// computed transposed (rows of W are the MMA's M dimension, tokens its N dimension of 8), and because a dot
+// product does not care about the order of its terms, each thread's 8 contiguous k values are dealt to the
+// MMA's k slots as they lie; x is read with the same dealing. A block of 8 warps owns 16 output columns;
+// the warps take 32-wide k chunks in turn and their partial sums are added in warp order, so a token's
+// result does not depend on what else is in the batch.
+// Role in the reference: the seq = 1 "warp-broadcast" matvec, one warp per output row
+// (WarpBroadcastKernel, src/math_gpu.br:1038-1106); formula y = x . W^T (src/math.br:66-82).
+#include "common.cuh"
+#include "api.h"
+#include <mma.h>
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int COLS = 16;          // output columns (rows of W) per block
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p, bool ok) {
+    return ok ? __ldg(reinterpret_cast<const uint4*>(p)) : make_uint4(0u, 0u, 0u, 0u);
+}
+
+// MT: groups of 8 tokens handled by one block (M tile = 8 * MT).
+template <int MT, int EPI, typename TO>
+__global__ void __launch_bounds__(WARPS * 32)
+gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                   const void* __restrict__ bias, int bias_dtype, TO* __restrict__ out,
+                   int M, int N, int K, int m_groups) {
+    constexpr bool GLU = EPI == BL_EPI_SWIGLU;
+    __shared__ float red[GLU ? 2 : 1][WARPS][COLS][MT * 8 + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = (blockIdx.x / m_groups) * COLS;
+    const int m0 = (blockIdx.x % m_groups) * (MT * 8);
+    float acc[MT][4], acu[GLU ? MT : 1][4];
+#pragma unroll
+    for (int j = 0; j < MT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { acc[j][i] = 0.f; if (GLU) acu[j][i] = 0.f; }
+    const int r_lo = n0 + g, r_hi = n0 + g + 8;
+    const bool lo_ok = r_lo < N, hi_ok = r_hi < N;
+    const __nv_bfloat16* w_lo = w + (size_t)r_lo * K;
+    const __nv_bfloat16* w_hi = w + (size_t)r_hi * K;
+    const __nv_bfloat16* u_lo = w + (size_t)(N + r_lo) * K;      // up rows follow the N gate rows
+    const __nv_bfloat16* u_hi = w + (size_t)(N + r_hi) * K;
+    for (int k = warp * 32 + 8 * t; k < K; k += WARPS * 32) {
+        const uint4 a_lo = ld16(w_lo + k, lo_ok), a_hi = ld16(w_hi + k, hi_ok);
+        uint4 g_lo, g_hi;
+        if (GLU) { g_lo = ld16(u_lo + k, lo_ok); g_hi = ld16(u_hi + k, hi_ok); }
+#pragma unroll
+        for (int j = 0; j < MT; ++j) {
+            const int tok = m0 + 8 * j + g;
+            const uint4 b = ld16(x + (size_t)tok * K + k, tok < M);
+            mma_bf16(acc[j], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
+            mma_bf16(acc[j], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
+            if (GLU) {
+                mma_bf16(acu[j], g_lo.x, g_hi.x, g_lo.y, g_hi.y, b.x, b.y);
+                mma_bf16(acu[j], g_lo.z, g_hi.z, g_lo.w, g_hi.w, b.z, b.w);
+            }
+        }
+    }
+    // c0, c1: (column g, tokens 2t, 2t+1); c2, c3: (column g + 8, tokens 2t, 2t+1)
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+        red[0][warp][g][8 * j + 2 * t] = acc[j][0];     red[0][warp][g][8 * j + 2 * t + 1] = acc[j][1];
+        red[0][warp][g + 8][8 * j + 2 * t] = acc[j][2]; red[0][warp][g + 8][8 * j + 2 * t + 1] = acc[j][3];
+        if (GLU) {
+            red[1][warp][g][8 * j + 2 * t] = acu[j][0];     red[1][warp][g][8 * j + 2 * t + 1] = acu[j][1];
+            red[1][warp][g + 8][8 * j + 2 * t] = acu[j][2]; red[1][warp][g + 8][8 * j + 2 * t + 1] = acu[j][3];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < COLS * MT * 8; i += WARPS * 32) {
+        const int c = i % COLS, tok = i / COLS;
+        const int n = n0 + c, m = m0 + tok;
+        if (n >= N || m >= M) continue;
+        float v = 0.f, u = 0.f;
+#pragma unroll
+        for (int wp = 0; wp < WARPS; ++wp) { v += red[0][wp][c][tok]; if (GLU) u += red[1][wp][c][tok]; }
+        TO* dst = out + (size_t)m * N + n;
+        if (EPI == BL_EPI_BIAS) v += bl_load_any(bias, bias_dtype, n);
+        if (EPI == BL_EPI_RESIDUAL) v += bl_load(dst);
+        if (GLU) v = bl_silu(v) * u;
+        bl_store(dst, v);
+    }
+}
+
+template <int MT, typename TO>
+int launch(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K,
+           int epi, cudaStream_t s) {
+    const int m_groups = (M + MT * 8 - 1) / (MT * 8);
+    const int blocks = ((N + COLS - 1) / COLS) * m_groups;
+#define BL_GO(E) gemm_skinny_kernel<MT, E, TO><<<blocks, WARPS * 32, 0, s>>>((const __nv_bfloat16*)x, \
+        (const __nv_bfloat16*)w, bias, bias_dtype, (TO*)out, M, N, K, m_groups)
+    switch (epi) {
+        case BL_EPI_NONE: BL_GO(BL_EPI_NONE); break;
+        case BL_EPI_BIAS: BL_GO(BL_EPI_BIAS); break;
+        case BL_EPI_RESIDUAL: BL_GO(BL_EPI_RESIDUAL); break;
+        case BL_EPI_SWIGLU: BL_GO(BL_EPI_SWIGLU); break;
+        default: BL_FAIL("bl_gemm_skinny: unknown epilogue %d", epi);
+    }
+#undef BL_GO
+    BL_CHECK_LAUNCH("bl_gemm_skinny");
+    return 0;
+}
+
+}  // namespace
+
+// bfloat16 x and W; K a multiple of 8 and both base addresses 16-byte aligned (16-byte loads); any M, N.
+// Meant for M up to a few dozen: W is read once per 32 tokens.
+extern "C" int bl_gemm_skinny(const void* x, const void* w, const void* bias, int bias_dtype, void* out,
+                              int out_dtype, int M, int N, int K, int epilogue, void* stream) {
+    if (M <= 0) return 0;
+    if (N <= 0 || K <= 0) BL_FAIL("bl_gemm_skinny: bad sizes N=%d K=%d", N, K);
+    if (K % 8 != 0) BL_FAIL("bl_gemm_skinny: K=%d is not a multiple of 8 (use the plain kernel)", K);
+    if (((uintptr_t)x | (uintptr_t)w) & 15) BL_FAIL("bl_gemm_skinny: x and W must be 16-byte aligned");
+    if (epilogue == BL_EPI_BIAS && (bias == nullptr || (bias_dtype != BL_F32 && bias_dtype != BL_BF16)))
+        BL_FAIL("bl_gemm_skinny: bias epilogue needs a float32 or bfloat16 bias");
+    if (epilogue == BL_EPI_RESIDUAL && out_dtype != BL_F32)
+        BL_FAIL("bl_gemm_skinny: the residual stream is 32-bit; output dtype must be float32");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == BL_F32) {
+        if (M <= 8) return launch<1, float>(x, w, bias, bias_dtype, out, M, N, K, epilogue, s);
+        if (M <= 16) return launch<2, float>(x, w, bias, bias_dtype, out, M, N, K, epilogue, s);
+        return launch<4, float>(x, w, bias, bias_dtype, out, M, N, K, epilogue, s);
+    }
+    if (out_dtype == BL_BF16) {
+        if (M <= 8) return launch<1, __nv_bfloat16>(x, w, bias, bias_dtype, out, M, N, K, epilogue, s);
+        if (M <= 16) return launch<2, __nv_bfloat16>(x, w, bias, bias_dtype, out, M, N, K, epilogue, s);
+        return launch<4, __nv_bfloat16>(x, w, bias, bias_dtype, out, M, N, K, epilogue, s);
+    }
+    BL_FAIL("bl_gemm_skinny: unknown output dtype %d", out_dtype);
+}

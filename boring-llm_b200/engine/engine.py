@@ -31,7 +31,10 @@ class Engine:
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device: this engine runs on an sm_100a GPU only (there is no CPU path)")
         self.options = options
-        self.config, self.model = load_model(model_dir, options.dtype, options.device)
+        if isinstance(model_dir, tuple):
+            self.config, self.model = model_dir          # (configuration, model already on the device)
+        else:
+            self.config, self.model = load_model(model_dir, options.dtype, options.device)
         max_pos = getattr(self.config, "max_position_embeddings", None)
         if max_pos is not None and options.ctx_size > max_pos:
             raise ValueError(f"ctx_size {options.ctx_size} exceeds the model's max_position_embeddings {max_pos}")
@@ -39,7 +42,12 @@ class Engine:
         self.scheduler = Scheduler(self.runner.cache, options)
         self.sampler = Sampler(options.device)
         self._ids = itertools.count()
-        self.stats_time = {"steps": 0, "step_seconds": 0.0}
+        self.stats_time = {"engine_steps": 0, "step_seconds": 0.0}
+
+    @classmethod
+    def from_model(cls, config, model, options: EngineOptions) -> "Engine":
+        """An engine around a model that is already built and loaded on the device."""
+        return cls((config, model), options)
 
     # ---- requests ----------------------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, request_id=None) -> Request:
@@ -62,7 +70,7 @@ class Engine:
         logits = self.runner.step(sched.entries)
         rows = [(r.params, r.rng, r.tokens) for r, s in zip(sched.requests, sched.samples) if s]
         sampled = self.sampler.sample(logits, rows) if rows else []
-        self.stats_time["steps"] += 1
+        self.stats_time["engine_steps"] += 1
         self.stats_time["step_seconds"] += time.perf_counter() - t0
         return self.scheduler.apply(sched, sampled)
 

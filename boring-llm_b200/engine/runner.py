@@ -132,7 +132,9 @@ class ModelRunner:
         rcs = [self.cache.get(e.request_id) for e in entries]
         width = max(1, max(len(t) for rc in rcs for t in (rc.tables or [[0]])))
         width = -(-width // 8) * 8
-        n_ints = 3 * T + (R + 1) + 2 * R + N + G * R * width
+        tiles = [(r, t0) for r, e in enumerate(entries) if len(e.tokens) > 1 for t0 in range(0, len(e.tokens), 64)]
+        singles = [r for r, e in enumerate(entries) if len(e.tokens) == 1]
+        n_ints = 3 * T + (R + 1) + 2 * R + N + G * R * width + 2 * len(tiles) + len(singles)
         host = self._host_buffer(n_ints)
         h = host.numpy()
         o = 0
@@ -145,6 +147,12 @@ class ModelRunner:
         logit_rows = h[o:o + N]; o += N
         tables = h[o:o + G * R * width].reshape(G, R, width); o += G * R * width
         tables[...] = -1
+        tile_arr = h[o:o + 2 * len(tiles)]; o += 2 * len(tiles)
+        single_arr = h[o:o + len(singles)]; o += len(singles)
+        if tiles:
+            tile_arr[:] = np.asarray(tiles, dtype=np.int32).reshape(-1)
+        if singles:
+            single_arr[:] = np.asarray(singles, dtype=np.int32)
         t0 = 0
         n_want = 0
         q_lens, ctx_lens, slot_list = [], [], []
@@ -181,6 +189,11 @@ class ModelRunner:
             slots=take(R), logit_rows=take(N),
             block_tables=[take(R * width).view(R, width) for _ in range(G)],
             q_lens=q_lens, ctx_lens=ctx_lens, slot_list=slot_list, storage=self.storage, fast=self.fast)
+        if tiles:
+            ctx.prefill_tiles = take(2 * len(tiles)).view(len(tiles), 2)
+        if singles:
+            ctx.decode_reqs = take(len(singles))
+            ctx.max_decode_ctx = max(ctx_lens[r] for r in singles)
         logits = self.model.forward(ctx)
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))

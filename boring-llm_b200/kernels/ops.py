@@ -50,7 +50,12 @@ def _lib():
     return lib
 
 
+launch_count = 0          # kernels launched through this module since import (the benchmark reads it)
+
+
 def _call(fn, *args):
+    global launch_count
+    launch_count += 1
     if fn(*args) != 0:
         raise KernelError(library.load().bl_last_error().decode())
 
@@ -161,3 +166,68 @@ def repeat_penalty(logits: torch.Tensor, tokens: torch.Tensor, offsets: torch.Te
     _need(logits, "logits", torch.float32); _need(tokens, "tokens", torch.int32)
     _need(offsets, "offsets", torch.int32, (rows + 1,)); _need(penalty, "penalty", torch.float32, (rows,))
     _call(_lib().bl_repeat_penalty, _p(logits), rows, V, _p(tokens), _p(offsets), _p(penalty), _stream())
+
+
+def gemm_skinny_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                epilogue: int = EPI_NONE) -> None:
+    """out = epilogue(x @ w.T) for few rows: W streams once from HBM into tensor-core registers."""
+    M, K = x.shape
+    N = out.shape[1]
+    rows_w = 2 * N if epilogue == EPI_SWIGLU else N
+    _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16, (rows_w, K)); _need(out, "out", None, (M, N))
+    if bias is not None:
+        _need(bias, "bias", None, (N,))
+    _call(_lib().bl_gemm_skinny, _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0, _p(out), _dt(out),
+          M, N, K, epilogue, _stream())
+
+
+def attention_mma_supported(dtype: torch.dtype, dh: int, page_size: int) -> bool:
+    return dtype == torch.bfloat16 and bool(library.load().bl_attention_mma_supported(dh, page_size))
+
+
+def attention_prefill(q, k_cache, v_cache, cu_q, ctx_len, block_table, tiles, out, H: int, window: int,
+                      scale: float) -> None:
+    """Tensor-core attention for requests with several new tokens. tiles: int32 [n, 2] = (request, first token
+    of a 64-token tile among the request's new tokens)."""
+    T = q.shape[0]
+    _, KV, page_size, dh = k_cache.shape
+    _need(q, "q", torch.bfloat16, (T, H * dh)); _need(k_cache, "k_cache", torch.bfloat16)
+    _need(v_cache, "v_cache", torch.bfloat16, k_cache.shape); _need(out, "out", torch.bfloat16, (T, H * dh))
+    _need(cu_q, "cu_q", torch.int32); _need(ctx_len, "ctx_len", torch.int32); _need(block_table, "block_table", torch.int32)
+    _need(tiles, "tiles", torch.int32)
+    _call(_lib().bl_attention_prefill, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
+          block_table.shape[1], _p(tiles), tiles.shape[0], _p(out), H, KV, dh, page_size, window,
+          ctypes.c_float(scale), _stream())
+
+
+def attention_decode(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_splits: int, out, H: int, window: int,
+                     scale: float, scratch: Optional[torch.Tensor] = None) -> None:
+    """Tensor-core attention for requests with one new token; `reqs` int32 [n] lists them. The keys of each are
+    cut into `n_splits` slices; with more than one, `scratch` (float32, `attention_decode_scratch(...)` elements)
+    holds the slices' partial results."""
+    T = q.shape[0]
+    _, KV, page_size, dh = k_cache.shape
+    n = reqs.shape[0]
+    _need(q, "q", torch.bfloat16, (T, H * dh)); _need(k_cache, "k_cache", torch.bfloat16)
+    _need(v_cache, "v_cache", torch.bfloat16, k_cache.shape); _need(out, "out", torch.bfloat16, (T, H * dh))
+    _need(cu_q, "cu_q", torch.int32); _need(ctx_len, "ctx_len", torch.int32); _need(block_table, "block_table", torch.int32)
+    _need(reqs, "reqs", torch.int32, (n,))
+    need = attention_decode_scratch(n, H, dh, n_splits)
+    if need:
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+        _need(scratch, "scratch", torch.float32)
+        if scratch.numel() < need:
+            raise KernelError(f"scratch: {scratch.numel()} floats, {need} needed")
+    _call(_lib().bl_attention_decode, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
+          block_table.shape[1], _p(reqs), n, n_splits, _p(scratch if need else None), _p(out), H, KV, dh, page_size,
+          window, ctypes.c_float(scale), _stream())
+
+
+def attention_decode_scratch(n: int, H: int, dh: int, n_splits: int) -> int:
+    return 0 if n_splits <= 1 else n * H * n_splits * (dh + 2)

@@ -14,6 +14,9 @@ from .linear import linear, EPI_BIAS, EPI_NONE, EPI_RESIDUAL
 from .rotary import RotaryTable
 
 
+DECODE_TARGET_BLOCKS = 4 * 148     # blocks wanted in flight when one query's keys are cut into slices
+
+
 class Mixer(Part):
     """Interface of a mixer.
 
@@ -92,5 +95,20 @@ class GQAAttention(Mixer):
         linear(ctx, attn, self.wo, residual, None, EPI_RESIDUAL)
 
     def attend(self, ctx, q, k_cache, v_cache, table, out):
-        ops.attention_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, out,
-                            self.H, self.window, self.scale)
+        """Tensor-core kernels for bfloat16 where they are built (pages of 16, common head sizes): one launch for
+        the requests with several new tokens, one for those with a single token. Otherwise, and always in
+        float32, the plain kernel."""
+        if not (ctx.fast and ops.attention_mma_supported(q.dtype, self.dh, k_cache.shape[2])):
+            ops.attention_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, out,
+                                self.H, self.window, self.scale)
+            return
+        if ctx.prefill_tiles is not None:
+            ops.attention_prefill(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.prefill_tiles, out,
+                                  self.H, self.window, self.scale)
+        if ctx.decode_reqs is not None:
+            n = ctx.decode_reqs.shape[0]
+            groups = self.KV * (-(-(self.H // self.KV) // 16))
+            longest = ctx.max_decode_ctx if self.window <= 0 else min(ctx.max_decode_ctx, self.window + 64)
+            n_splits = max(1, min(-(-longest // 64), -(-DECODE_TARGET_BLOCKS // (n * groups))))
+            ops.attention_decode(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.decode_reqs, n_splits, out,
+                                 self.H, self.window, self.scale)

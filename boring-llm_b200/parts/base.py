@@ -94,6 +94,9 @@ class StepContext:
     slot_list: List[int]
     storage: object                    # cache.CacheStorage
     fast: bool = True                  # False: plain kernels only (the twins)
+    prefill_tiles: Optional[torch.Tensor] = None   # [n, 2] (request, first token of a 64-token tile) for q_len > 1
+    decode_reqs: Optional[torch.Tensor] = None     # [n] requests with exactly one new token
+    max_decode_ctx: int = 0                        # longest context among them (an upper bound is enough)
 
     @property
     def max_q_len(self) -> int:

@@ -33,8 +33,11 @@ SEEDS = {"A": 0, "B": 1, "C": 2}
 # Largest allowed |engine - plain| as a fraction of the largest |plain logit| of the compared rows.
 # float32: every product is a 32-bit FMA chain of a few hundred terms through a few layers (about 1e3 ulps
 # of headroom); bfloat16: activations are rounded to 8 bits of mantissa at every kernel boundary.
-TOL = {"float32": 1e-4, "bfloat16": 4e-2}
-MEAN_TOL = {"float32": 2e-5, "bfloat16": 8e-3}
+TOL = {"float32": 1e-4, "bfloat16": 1.5e-2}
+MEAN_TOL = {"float32": 2e-5, "bfloat16": 1.5e-3}
+# bfloat16 engine against the PURE 64-bit plain implementation (no rounding of stored tensors on the plain
+# side): only meaningful for well-conditioned models, i.e. the benchmark's N(0, 0.02) weights
+TOL_PURE_BF16 = 4e-2
 
 
 def write_tiny_model(path, name, dtype="float32", std=0.25, seed=None):
@@ -44,18 +47,20 @@ def write_tiny_model(path, name, dtype="float32", std=0.25, seed=None):
     return cfg
 
 
-def plain_logits(model_dir, tokens):
-    """float64 logits of every position from the plain implementation."""
+def plain_logits(model_dir, tokens, dtype="float32"):
+    """float64 logits of every position from the plain implementation. For a bfloat16 engine the
+    plain side rounds what such an engine stores between kernels (see plain_model.forward)."""
     import plain_model
     cfg, W = plain_model.read_model_folder(model_dir)
-    return plain_model.forward(cfg, W, tokens).numpy()
+    stored = plain_model.round_bf16 if dtype == "bfloat16" else None
+    return plain_model.forward(cfg, W, tokens, stored=stored).numpy()
 
 
 def random_tokens(vocab, n, seed):
     return np.random.default_rng(seed).integers(0, vocab, n).tolist()
 
 
-def assert_close(got, want, dtype, what=""):
+def assert_close(got, want, dtype, what="", tol=None, mean_tol=None):
     got = np.asarray(got, dtype=np.float64)
     want = np.asarray(want, dtype=np.float64)
     assert got.shape == want.shape, f"{what}: shape {got.shape} vs {want.shape}"
@@ -63,10 +68,13 @@ def assert_close(got, want, dtype, what=""):
     scale = max(np.abs(want).max(), 1e-6)
     err = np.abs(got - want)
     worst = np.unravel_index(np.argmax(err), err.shape)
-    assert err.max() <= TOL[dtype] * scale, (
-        f"{what}: max |diff| {err.max():.3e} at {worst} exceeds {TOL[dtype]:.0e} * {scale:.3f}")
-    assert err.mean() <= MEAN_TOL[dtype] * scale, (
-        f"{what}: mean |diff| {err.mean():.3e} exceeds {MEAN_TOL[dtype]:.0e} * {scale:.3f}")
+    tol = TOL[dtype] if tol is None else tol
+    assert err.max() <= tol * scale, (
+        f"{what}: max |diff| {err.max():.3e} at {worst} exceeds {tol:.0e} * {scale:.3f}")
+    if mean_tol is None:
+        mean_tol = MEAN_TOL[dtype]
+    assert err.mean() <= mean_tol * scale, (
+        f"{what}: mean |diff| {err.mean():.3e} exceeds {mean_tol:.0e} * {scale:.3f}")
 
 
 # ---- traces ------------------------------------------------------------------------------------------

@@ -125,9 +125,22 @@ def swiglu_ffn(x, w_gate, w_up, w_down):
 
 
 # ---- the whole model -------------------------------------------------------------------------------
-def forward(cfg, W, tokens, dtype=torch.float64):
+def round_bf16(x):
+    """Rounds to the nearest bfloat16 value (ties to even) and widens back."""
+    return x.to(torch.bfloat16).to(x.dtype)
+
+
+def forward(cfg, W, tokens, dtype=torch.float64, stored=None):
     """Logits of every position of one whole sequence: src/model.br:1280-1362 with every optional
-    branch neutral, as the reference runs GGUF arch `qwen2`."""
+    branch neutral, as the reference runs GGUF arch `qwen2`.
+
+    `stored`: None computes everything in `dtype`. `round_bf16` additionally rounds the tensors that a
+    bfloat16 engine STORES between its kernels (normed rows, rotated q and k, v, the attention output,
+    the SwiGLU product); everything inside a formula (products' sums, softmax, norms' statistics,
+    rotation, the residual stream, logits) stays in `dtype`. With it the comparison is about the
+    formulas and the cache, not about how well a random model happens to be conditioned.
+    """
+    st = stored if stored is not None else (lambda t: t)
     W = {k: v.to(dtype) for k, v in W.items()}
     H, KV = cfg["num_attention_heads"], cfg.get("num_key_value_heads", cfg["num_attention_heads"])
     dh = cfg.get("head_dim") or cfg["hidden_size"] // H
@@ -140,19 +153,19 @@ def forward(cfg, W, tokens, dtype=torch.float64):
     x = W["model.embed_tokens.weight"][tokens]                                   # :1286-1295
     for l in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{l}."
-        h = rms_norm(x, W[p + "input_layernorm.weight"], eps)                    # :1310
+        h = st(rms_norm(x, W[p + "input_layernorm.weight"], eps))                # :1310
         bias = (p + "self_attn.q_proj.bias") in W
         q = linear(h, W[p + "self_attn.q_proj.weight"], W[p + "self_attn.q_proj.bias"] if bias else None)
         k = linear(h, W[p + "self_attn.k_proj.weight"], W[p + "self_attn.k_proj.bias"] if bias else None)
-        v = linear(h, W[p + "self_attn.v_proj.weight"], W[p + "self_attn.v_proj.bias"] if bias else None)
-        q = rope_neox(q.reshape(seq, H, dh), pos, inv_freq)                      # :1317-1319
-        k = rope_neox(k.reshape(seq, KV, dh), pos, inv_freq)
-        a = gqa_attention(q, k, v.reshape(seq, KV, dh), 1.0 / math.sqrt(dh), windows[l])   # :1323-1324
+        v = st(linear(h, W[p + "self_attn.v_proj.weight"], W[p + "self_attn.v_proj.bias"] if bias else None))
+        q = st(rope_neox(q.reshape(seq, H, dh), pos, inv_freq))                  # :1317-1319
+        k = st(rope_neox(k.reshape(seq, KV, dh), pos, inv_freq))
+        a = st(gqa_attention(q, k, v.reshape(seq, KV, dh), 1.0 / math.sqrt(dh), windows[l]))   # :1323-1324
         x = x + linear(a.reshape(seq, H * dh), W[p + "self_attn.o_proj.weight"])  # :1328-1334
-        h = rms_norm(x, W[p + "post_attention_layernorm.weight"], eps)           # :1340
-        x = x + swiglu_ffn(h, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"],
-                           W[p + "mlp.down_proj.weight"])                        # :1346-1356
-    y = rms_norm(x, W["model.norm.weight"], eps)                                 # :1360
+        h = st(rms_norm(x, W[p + "post_attention_layernorm.weight"], eps))       # :1340
+        act = st(silu(linear(h, W[p + "mlp.gate_proj.weight"])) * linear(h, W[p + "mlp.up_proj.weight"]))
+        x = x + linear(act, W[p + "mlp.down_proj.weight"])                       # :1346-1356, src/math.br:246-261
+    y = st(rms_norm(x, W["model.norm.weight"], eps))                             # :1360
     out_w = W["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else W["lm_head.weight"]
     return linear(y, out_w)                                                      # :1361
 

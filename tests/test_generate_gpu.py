@@ -22,7 +22,7 @@ def check_greedy(d, prompt, out, dtype):
     """Every generated token is the plain implementation's arg-max given the engine's own prefix; in
     bfloat16 a near-tie (gap below the tolerance) may go either way."""
     cfg, W = plain.read_model_folder(d)
-    logits = plain.forward(cfg, W, prompt + out).numpy()
+    logits = plain.forward(cfg, W, prompt + out, stored=plain.round_bf16 if dtype == "bfloat16" else None).numpy()
     scale = np.abs(logits).max()
     for i, tok in enumerate(out):
         row = logits[len(prompt) - 1 + i]

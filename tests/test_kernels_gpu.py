@@ -309,3 +309,101 @@ def test_kernels_refuse_what_they_cannot_run():
         o.gemm_plain(torch.zeros(4, 8, device=DEV).t(), torch.zeros(3, 4, device=DEV), torch.zeros(8, 3, device=DEV))
     with pytest.raises(KernelError, match="CUDA"):
         o.argmax(torch.zeros(2, 3), torch.zeros(2, dtype=torch.int32))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 7, 8), (8, 1152, 896), (5, 200, 96), (17, 129, 80), (33, 64, 264), (64, 4864 // 8, 176),
+                                   (100, 50, 64)])
+def test_gemm_skinny_epilogues(M, N, K):
+    o = ops()
+    dtype = torch.bfloat16
+    x = (data((M, K), 14) * 0.5).to(dtype)
+    w = (data((2 * N, K), 15) * 0.25).to(dtype)
+    b = data((N,), 16)
+    xd, wd, bd = x.double().cpu(), w.double().cpu(), b.double().cpu()
+    wn = w[:N].contiguous()
+    out = torch.empty(M, N, device=DEV)
+    o.gemm_skinny(x, wn, out)
+    close(out, xd @ wd[:N].T, torch.float32, "none")
+    o.gemm_skinny(x, wn, out, b, o.EPI_BIAS)
+    close(out, xd @ wd[:N].T + bd, torch.float32, "bias f32")
+    o.gemm_skinny(x, wn, out, b.to(dtype), o.EPI_BIAS)
+    close(out, xd @ wd[:N].T + b.to(dtype).double().cpu(), torch.float32, "bias bf16")
+    res = data((M, N), 17)
+    acc = res.clone()
+    o.gemm_skinny(x, wn, acc, None, o.EPI_RESIDUAL)
+    close(acc, res.double().cpu() + xd @ wd[:N].T, torch.float32, "residual")
+    act = torch.empty(M, N, dtype=dtype, device=DEV)
+    o.gemm_skinny(x, w, act, None, o.EPI_SWIGLU)
+    close(act, plain.silu(xd @ wd[:N].T) * (xd @ wd[N:].T), dtype, "swiglu")
+    # a row's result does not depend on the other rows of the call
+    one = torch.empty(1, N, device=DEV)
+    o.gemm_skinny(x[M - 1:M].contiguous(), wn, one)
+    o.gemm_skinny(x, wn, out)
+    assert torch.equal(one[0], out[M - 1])
+    # and it is the plain kernel's twin
+    twin = torch.empty(M, N, device=DEV)
+    o.gemm_plain(x, wn, twin)
+    close(out, twin.double(), torch.float32, "twin")
+
+
+def test_gemm_skinny_refuses_unaligned_k():
+    from boring_llm_b200.kernels import KernelError
+    o = ops()
+    x = torch.zeros(2, 12, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(3, 12, dtype=torch.bfloat16, device=DEV)
+    assert not o.gemm_skinny_supported(x, w)
+    with pytest.raises(KernelError, match="multiple of 8"):
+        o.gemm_skinny(x, w, torch.zeros(2, 3, device=DEV))
+
+
+def mma_attention(q, kc, vc, tok_req, cu_q, ctx_len, table, out, H, window, scale, n_splits=None):
+    """Runs the tensor-core kernels the way the attention part does: tiles for requests with several new
+    tokens, the decode shape (with slices) for single tokens."""
+    o = ops()
+    cu = cu_q.cpu().tolist()
+    q_lens = [b - a for a, b in zip(cu[:-1], cu[1:])]
+    tiles = [(r, t0) for r, n in enumerate(q_lens) if n > 1 for t0 in range(0, n, 64)]
+    singles = [r for r, n in enumerate(q_lens) if n == 1]
+    out.fill_(float("nan"))
+    if tiles:
+        o.attention_prefill(q, kc, vc, cu_q, ctx_len, table, torch.tensor(tiles, dtype=torch.int32, device=DEV), out, H, window, scale)
+    if singles:
+        longest = max(ctx_len.cpu().tolist())
+        for splits in ([n_splits] if n_splits else [1, 3, max(1, -(-longest // 64))]):
+            o.attention_decode(q, kc, vc, cu_q, ctx_len, table, torch.tensor(singles, dtype=torch.int32, device=DEV),
+                               splits, out, H, window, scale)
+            if splits != 1:
+                ref1 = out.clone()
+                o.attention_decode(q, kc, vc, cu_q, ctx_len, table, torch.tensor(singles, dtype=torch.int32, device=DEV),
+                                   1, out, H, window, scale)
+                assert (out.float() - ref1.float()).abs().max().item() <= 2e-2 * max(1.0, out.float().abs().max().item())
+
+
+@pytest.mark.parametrize("H,KV,dh", [(4, 2, 16), (7, 1, 64), (8, 1, 128), (3, 3, 48), (14, 2, 64), (6, 2, 32), (34, 2, 96)])
+def test_attention_mma_shapes(H, KV, dh):
+    o = ops()
+    assert o.attention_mma_supported(torch.bfloat16, dh, 16)
+    attention_case(o, mma_attention, torch.bfloat16, H, KV, dh, [1, 37, 300, 520], [1, 1, 1, 1], 0, 1)
+    attention_case(o, mma_attention, torch.bfloat16, H, KV, dh, [333, 70, 16, 33], [70, 70, 2, 17], 0, 2)
+    attention_case(o, mma_attention, torch.bfloat16, H, KV, dh, [64, 65, 128, 200, 129], [64, 1, 128, 1, 65], 0, 3)
+
+
+@pytest.mark.parametrize("window", [1, 15, 16, 17, 40, 64, 100])
+def test_attention_mma_window_edges(window):
+    o = ops()
+    attention_case(o, mma_attention, torch.bfloat16, 4, 2, 32, [50, 16, 90, 17, 300], [1, 16, 33, 2, 1], window, 5)
+    attention_case(o, mma_attention, torch.bfloat16, 4, 2, 64, [200, 131], [150, 1], window, 6)
+
+
+def test_attention_mma_is_refused_where_it_is_not_built():
+    from boring_llm_b200.kernels import KernelError
+    o = ops()
+    assert not o.attention_mma_supported(torch.bfloat16, 80, 16)
+    assert not o.attention_mma_supported(torch.bfloat16, 64, 32)
+    assert not o.attention_mma_supported(torch.float32, 64, 16)
+    i = torch.zeros(1, dtype=torch.int32, device=DEV)
+    q = torch.zeros(1, 80, dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros(1, 1, 16, 80, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelError, match="head size 80"):
+        o.attention_decode(q, kc, kc, torch.tensor([0, 1], dtype=torch.int32, device=DEV), i + 1, i.view(1, 1), i, 1,
+                           q.clone(), 1, 0, 1.0)
