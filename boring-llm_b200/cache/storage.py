@@ -1,6 +1,6 @@
 """Device tensors behind the cache manager's page and slot numbers.
 
-For every paged group one tensor `[layers in group, 2 (keys, values), pages, kv heads, page size,
+For every paged group one tensor `[layers in group, 2 (keys, values), pages + 1, kv heads, page size,
 head size]`: the rows of one (page, kv head) lie together, so a kernel reads a page of one head as
 one contiguous tile. For every state group one tensor `[layers in group, request slots, *shape]`.
 Keys are stored after rotation, values as projected (src/model.br:1814-1820).
@@ -21,15 +21,19 @@ class CacheStorage:
         self.manager = manager
         self.kv_dtype = kv_dtype
         self.device = torch.device(device)
+        # One page and one slot more than the manager hands out: rows that only pad a batch to a fixed
+        # size (captured CUDA graphs) write there, where no request ever reads.
+        self.trash_page = manager.num_pages
+        self.trash_slot = manager.max_requests
         self.kv: List[torch.Tensor] = []
         for g in manager.paged_groups:
             self.kv.append(torch.zeros(
-                (len(g.cache_layers), 2, manager.num_pages, g.spec.n_kv_heads, manager.page_size,
+                (len(g.cache_layers), 2, manager.num_pages + 1, g.spec.n_kv_heads, manager.page_size,
                  g.spec.head_dim), dtype=kv_dtype, device=self.device))
         self.state: List[torch.Tensor] = []
         for sg in manager.state_groups:
             self.state.append(torch.zeros(
-                (len(sg.cache_layers), manager.max_requests) + tuple(sg.spec.shape),
+                (len(sg.cache_layers), manager.max_requests + 1) + tuple(sg.spec.shape),
                 dtype=_TORCH_DTYPES[sg.spec.dtype], device=self.device))
         manager._on_slot_assigned = self.zero_slot
 

@@ -51,14 +51,18 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     const __nv_bfloat16* w_hi = w + (size_t)r_hi * K;
     const __nv_bfloat16* u_lo = w + (size_t)(N + r_lo) * K;      // up rows follow the N gate rows
     const __nv_bfloat16* u_hi = w + (size_t)(N + r_hi) * K;
-    for (int k = warp * 32 + 8 * t; k < K; k += WARPS * 32) {
-        const uint4 a_lo = ld16(w_lo + k, lo_ok), a_hi = ld16(w_hi + k, hi_ok);
+    // the loop bound is the same for every lane of a warp (the MMA needs all 32 lanes); a lane whose
+    // 8 values lie past K loads zeros
+    for (int kc = warp * 32; kc < K; kc += WARPS * 32) {
+        const int k = kc + 8 * t;
+        const bool k_ok = k < K;
+        const uint4 a_lo = ld16(w_lo + k, lo_ok && k_ok), a_hi = ld16(w_hi + k, hi_ok && k_ok);
         uint4 g_lo, g_hi;
-        if (GLU) { g_lo = ld16(u_lo + k, lo_ok); g_hi = ld16(u_hi + k, hi_ok); }
+        if (GLU) { g_lo = ld16(u_lo + k, lo_ok && k_ok); g_hi = ld16(u_hi + k, hi_ok && k_ok); }
 #pragma unroll
         for (int j = 0; j < MT; ++j) {
             const int tok = m0 + 8 * j + g;
-            const uint4 b = ld16(x + (size_t)tok * K + k, tok < M);
+            const uint4 b = ld16(x + (size_t)tok * K + k, tok < M && k_ok);
             mma_bf16(acc[j], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
             mma_bf16(acc[j], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
             if (GLU) {

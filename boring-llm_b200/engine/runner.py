@@ -38,6 +38,70 @@ class StepError(ValueError):
     """A step that cannot run: an unknown token id, a request past its context size, ..."""
 
 
+GRAPH_MAX_BATCH = 64          # decode steps of up to this many requests replay a captured CUDA graph
+
+
+class _DecodeGraph:
+    """A captured decode step for a fixed number of rows. All per-step inputs live in one int32 device
+    buffer that a single copy refreshes before each replay; rows beyond the live requests point at the
+    storage's spare page and slot."""
+
+    def __init__(self, runner: "ModelRunner", rows: int):
+        self.rows = rows
+        G = len(runner.cache.paged_groups)
+        W = runner._table_width
+        B = rows
+        sizes = [("token_ids", B), ("positions", B), ("ctx_len", B), ("slots", B), ("tables", G * B * W),
+                 ("tok_req", B), ("cu_q", B + 1), ("logit_rows", B), ("decode_reqs", B)]
+        total = sum(n for _, n in sizes)
+        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self.dev = torch.zeros(total, dtype=torch.int32, device=runner.device)
+        self.h: Dict[str, np.ndarray] = {}
+        self.d: Dict[str, torch.Tensor] = {}
+        o = 0
+        hn = self.host.numpy()
+        for name, n in sizes:
+            self.h[name] = hn[o:o + n]
+            self.d[name] = self.dev[o:o + n]
+            o += n
+        self.dynamic_ints = 4 * B + G * B * W          # the leading fields change every step
+        self.h["tables"] = self.h["tables"].reshape(G, B, W)
+        ar = np.arange(B, dtype=np.int32)
+        self.h["tok_req"][:] = ar; self.h["logit_rows"][:] = ar; self.h["decode_reqs"][:] = ar
+        self.h["cu_q"][:] = np.arange(B + 1, dtype=np.int32)
+        self.trash_page, self.trash_slot = runner.storage.trash_page, runner.storage.trash_slot
+        self.fill_padding(0)
+        self.dev.copy_(self.host)
+        self.ctx = StepContext(
+            dtype=runner.dtype, device=runner.device, T=B, R=B, token_ids=self.d["token_ids"],
+            positions=self.d["positions"], tok_req=self.d["tok_req"], cu_q=self.d["cu_q"], ctx_len=self.d["ctx_len"],
+            slots=self.d["slots"], logit_rows=self.d["logit_rows"],
+            block_tables=[self.d["tables"][g * B * W:(g + 1) * B * W].view(B, W) for g in range(G)],
+            q_lens=[1] * B, ctx_lens=[runner.options.ctx_size] * B, slot_list=[runner.storage.trash_slot] * B,
+            storage=runner.storage, fast=True, decode_reqs=self.d["decode_reqs"],
+            max_decode_ctx=runner.options.ctx_size)
+        # run once outside a capture (first-use set-up inside the kernels), then capture
+        side = torch.cuda.Stream(device=runner.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            runner.model.forward(self.ctx)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = runner.model.forward(self.ctx)
+        self.copied = torch.cuda.Event()
+
+    def fill_padding(self, live: int) -> None:
+        h = self.h
+        h["token_ids"][live:] = 0
+        h["positions"][live:] = 0
+        h["ctx_len"][live:] = 1
+        h["slots"][live:] = self.trash_slot
+        h["tables"][:, live:, :] = -1
+        h["tables"][:, live:, 0] = self.trash_page
+
+
 class ModelRunner:
     def __init__(self, model, options: EngineOptions, vocab_size: Optional[int] = None):
         self.model = model
@@ -54,6 +118,9 @@ class ModelRunner:
         self._pinned_next = 0
         self.steps = 0
         self.tokens_run = 0
+        self.graph_steps = 0
+        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._table_width = -(-(-(-options.ctx_size // options.page_size)) // 8) * 8
 
     # ---- requests --------------------------------------------------------------------------------
     def add_request(self, request_id) -> None:
@@ -82,10 +149,51 @@ class ModelRunner:
         self._slot_index = i
         return self._pinned[i]
 
+    def _graphed_decode(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """A step in which every request has exactly one token: replays the captured graph of the next
+        larger row count. Reservation, commit and the returned logits are those of the general path."""
+        R = len(entries)
+        rows = 1
+        while rows < R:
+            rows *= 2
+        gr = self._graphs.get(rows)
+        if gr is None:
+            gr = self._graphs[rows] = _DecodeGraph(self, rows)
+        gr.copied.synchronize()                        # the previous copy out of the pinned buffer is done
+        h = gr.h
+        slot_list = []
+        for r, e in enumerate(entries):
+            rc = self.cache.get(e.request_id)
+            h["token_ids"][r] = int(e.tokens[0])
+            h["positions"][r] = rc.num_tokens
+            h["ctx_len"][r] = rc.num_tokens + 1
+            h["slots"][r] = rc.slot
+            slot_list.append(rc.slot)
+            for gi, tab in enumerate(rc.tables):
+                row = h["tables"][gi, r]
+                row[:len(tab)] = tab
+                row[len(tab):] = -1
+        gr.fill_padding(R)
+        gr.ctx.slot_list = slot_list + [gr.trash_slot] * (rows - R)
+        gr.dev[:gr.dynamic_ints].copy_(gr.host[:gr.dynamic_ints], non_blocking=True)
+        gr.copied.record()
+        gr.graph.replay()
+        for e in entries:
+            self.cache.commit(e.request_id, 1)
+        self.steps += 1
+        self.graph_steps += 1
+        self.tokens_run += R
+        wanted = [r for r, e in enumerate(entries) if len(e.want)]
+        if len(wanted) == R:
+            return gr.logits[:R]
+        return gr.logits[torch.tensor(wanted, dtype=torch.long, device=self.device)] if wanted else gr.logits[:0]
+
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs the entries' tokens as one batch; returns float32 logits `[wanted, vocab]` on the
         device, in the order of the entries and of each entry's `want`. Requests not seen before
-        are admitted; pages are reserved here, and an `OutOfPages` leaves everything as it was."""
+        are admitted; pages are reserved here, and an `OutOfPages` leaves everything as it was.
+        The returned tensor may be a view of a buffer that the next step overwrites: use or copy it
+        before stepping again."""
         page = self.options.page_size
         if not entries:
             raise StepError("a step needs at least one entry")
@@ -125,6 +233,9 @@ class ModelRunner:
             ok = self.cache.reserve(e.request_id, len(e.tokens))
             assert ok, "reservation was checked for the whole batch"
 
+        if (self.options.cuda_graphs and self.fast and self.dtype == torch.bfloat16
+                and getattr(self.model, "graph_safe", False) and len(entries) <= GRAPH_MAX_BATCH and all(len(e.tokens) == 1 for e in entries)):
+            return self._graphed_decode(entries)
         R = len(entries)
         T = sum(len(e.tokens) for e in entries)
         N = sum(len(e.want) for e in entries)

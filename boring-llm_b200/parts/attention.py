@@ -27,6 +27,10 @@ class Mixer(Part):
     false it reads a layer that another call has written in this step.
     """
 
+    # True when forward() only launches work on the current stream from device-side inputs (no host loops
+    # over the batch, no host reads): such a mixer may be captured in a CUDA graph and replayed.
+    graph_safe = False
+
     def cache_spec(self):
         return None
 
@@ -42,6 +46,7 @@ class GQAAttention(Mixer):
     (:1814-1820); softmax(q.k^T * scale) over the keys a token may see (src/math.br:304-359);
     out.Wo^T added to the residual stream (src/model.br:1328-1334).
     """
+    graph_safe = True
 
     def __init__(self, dim: int, n_heads: int, n_kv_heads: int, head_dim: int, rotary: Optional[RotaryTable],
                  names: Dict[str, str], qkv_bias: bool = True, out_bias: bool = False, window: int = 0,

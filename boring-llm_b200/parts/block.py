@@ -20,6 +20,10 @@ class PreNormBlock(Part):
     def cache_spec(self):
         return self.mixer.cache_spec()
 
+    @property
+    def graph_safe(self) -> bool:
+        return bool(getattr(self.mixer, "graph_safe", False) and getattr(self.ffn, "graph_safe", False))
+
     def forward(self, ctx, x, cache_layer: Optional[int], write_cache: bool = True) -> None:
         h = self.mixer_norm.forward(ctx, x)
         self.mixer.forward(ctx, h, x, cache_layer, write_cache)

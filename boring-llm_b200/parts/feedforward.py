@@ -12,7 +12,8 @@ from .linear import linear, EPI_RESIDUAL, EPI_SWIGLU
 
 class FeedForward(Part):
     """Interface: `forward(ctx, h, residual)` reads the normed rows `h` [T, dim] and adds its
-    result into the 32-bit `residual` [T, dim] in place."""
+    result into the 32-bit `residual` [T, dim] in place. `graph_safe` as for mixers."""
+    graph_safe = False
 
     def forward(self, ctx, h, residual) -> None:
         raise NotImplementedError
@@ -22,6 +23,7 @@ class SwiGLU(FeedForward):
     """down(silu(gate(h)) * up(h)), no biases (src/math.br:232-233, 246-261). Gate and up run as
     one joined product over [Wg; Wu] (src/model.br:788-792) whose epilogue combines them
     (src/math_gpu.br:2673-2692); the down product adds into the residual stream."""
+    graph_safe = True
 
     def __init__(self, dim: int, hidden: int, names: Dict[str, str]):
         super().__init__(names)

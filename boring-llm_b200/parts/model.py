@@ -53,6 +53,11 @@ class DecoderModel(Part):
     def vocab_size(self) -> int:
         return self.head.vocab
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a decode step of this model may be captured in a CUDA graph and replayed."""
+        return all(getattr(b, "graph_safe", False) for b in self.blocks)
+
     def cache_specs(self) -> list:
         """What each cache layer needs, indexed by cache layer (None where unused)."""
         n = 1 + max([c.cache for c in self.schedule if c.cache is not None], default=-1)

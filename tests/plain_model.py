@@ -92,10 +92,11 @@ def rope_neox(x, positions, inv_freq):
     return torch.cat([a * c - b * s, a * s + b * c], dim=-1)
 
 
-def gqa_attention(q, k, v, scale, window=0):
+def gqa_attention(q, k, v, scale, window=0, p_stored=None):
     """src/math.br:304-359: kv head = head / (H / KV); score = dot * scale; query i sees keys j <= i
     and, with a window, only j + window > i; softmax with the maximum subtracted; out = p . v.
-    q: [seq, H, dh]; k, v: [seq, KV, dh]."""
+    q: [seq, H, dh]; k, v: [seq, KV, dh]. `p_stored` rounds the softmax numerators exp(s - max) the way a
+    bfloat16 engine's tensor cores take them as an operand of p . v (the sum that divides stays exact)."""
     seq, H, dh = q.shape
     KV = k.shape[1]
     group = H // KV
@@ -109,8 +110,10 @@ def gqa_attention(q, k, v, scale, window=0):
         sc = (q[:, h] @ k[:, kv].T) * scale
         sc = torch.where(allowed, sc, torch.full_like(sc, -1e30))
         p = torch.exp(sc - sc.max(-1, keepdim=True).values)
-        p = p / p.sum(-1, keepdim=True)
-        out[:, h] = p @ v[:, kv]
+        total = p.sum(-1, keepdim=True)
+        if p_stored is not None:
+            p = p_stored(p)
+        out[:, h] = (p @ v[:, kv]) / total
     return out
 
 
@@ -160,7 +163,7 @@ def forward(cfg, W, tokens, dtype=torch.float64, stored=None):
         v = st(linear(h, W[p + "self_attn.v_proj.weight"], W[p + "self_attn.v_proj.bias"] if bias else None))
         q = st(rope_neox(q.reshape(seq, H, dh), pos, inv_freq))                  # :1317-1319
         k = st(rope_neox(k.reshape(seq, KV, dh), pos, inv_freq))
-        a = st(gqa_attention(q, k, v.reshape(seq, KV, dh), 1.0 / math.sqrt(dh), windows[l]))   # :1323-1324
+        a = st(gqa_attention(q, k, v.reshape(seq, KV, dh), 1.0 / math.sqrt(dh), windows[l], stored))   # :1323-1324
         x = x + linear(a.reshape(seq, H * dh), W[p + "self_attn.o_proj.weight"])  # :1328-1334
         h = st(rms_norm(x, W[p + "post_attention_layernorm.weight"], eps))       # :1340
         act = st(silu(linear(h, W[p + "mlp.gate_proj.weight"])) * linear(h, W[p + "mlp.up_proj.weight"]))
