@@ -91,7 +91,7 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_engine(n_layers, max_seqs, steps_total):
+def build_engine(n_layers, max_seqs, steps_total, cuda_graphs=True):
     import torch
     import boring_llm_b200 as b
     from boring_llm_b200.config import EngineOptions
@@ -109,7 +109,8 @@ def build_engine(n_layers, max_seqs, steps_total):
     model.load(tensors, torch.bfloat16, torch.device("cuda:0"))
     del tensors
     opts = EngineOptions(dtype="bfloat16", ctx_size=CONTEXT, max_num_seqs=max_seqs, max_tokens=(CONTEXT + 16) * max_seqs,
-                         max_num_batched_tokens=max(PREFILL_TOKENS, max_seqs), prefill_chunk=PREFILL_TOKENS)
+                         max_num_batched_tokens=max(PREFILL_TOKENS, max_seqs), prefill_chunk=PREFILL_TOKENS,
+                         cuda_graphs=cuda_graphs)
     return cfg, Engine.from_model(cfg, model, opts)
 
 
@@ -172,7 +173,7 @@ def decode_device_timed(eng, batch, steps, warmup):
         toks = out.cpu().tolist()
         if it >= warmup:
             total_ms += e0.elapsed_time(e1)
-            launches += ops.launch_count - l0
+            launches += ops.launch_count - l0 + eng.runner.last_step_graph_kernels
     drop_requests(eng, reqs)
     return batch * steps / (total_ms / 1e3), total_ms / steps, launches
 
@@ -238,6 +239,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=SIZES["num_hidden_layers"])
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step singly (for profilers)")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="run one part only and print its figures (for profilers; not the benchmark line)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -251,8 +255,17 @@ def main():
     assert torch.cuda.is_available(), "bench.py needs a GPU"
     pk = peaks()
     warmup = max(3, args.warmup)
-    cfg, eng = build_engine(args.layers, 64, args.steps + warmup)
+    cfg, eng = build_engine(args.layers, 64, args.steps + warmup, not args.no_graphs)
     weight_bytes, kv_tok, prefill_flops = model_figures(args.layers)
+    if args.only == "decode":
+        tps, ms_step, launches = decode_device_timed(eng, args.batch, args.steps, warmup)
+        print(json.dumps({"only": "decode", "batch": args.batch, "tokens_per_s": round(tps, 1), "ms_per_step": round(ms_step, 4),
+                          "launches": launches, "layers": args.layers}))
+        return 0
+    if args.only == "prefill":
+        pre_ms = prefill_timed(eng, reps=1)
+        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3), "layers": args.layers}))
+        return 0
     clocks = ClockSampler()
     clocks.start()
     tps, ms_step, launches = decode_device_timed(eng, args.batch, args.steps, warmup)

@@ -73,6 +73,13 @@ int bl_attention_decode(const void* q, const void* k_cache, const void* v_cache,
                         int n_splits, float* scratch, void* out, int H, int KV, int dh, int page_size,
                         int window, float scale, void* stream);
 
+// Matrix product for many rows (prefill) on tcgen05 tensor cores with TMA-fed shared-memory tiles and the
+// accumulator in tensor memory. bfloat16 x[M, K] and W[N, K]; K a multiple of 8, x and W 16-byte aligned.
+int bl_gemm_tc(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype,
+               int M, int N, int K, int epilogue, void* stream);
+// *status = 0 unless a block of bl_gemm_tc gave up on a bounded wait since the last call (synchronises the device).
+int bl_gemm_tc_status(int* status);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,295 @@
+// Matrix product for many rows (prefill) on the fifth-generation tensor cores:
+// out[M, N] = epilogue(x[M, K] . W[N, K]^T), bfloat16 operands, 32-bit accumulation in tensor memory.
+//
+// One block computes one 128 x 128 tile of the output. A single thread feeds a three-stage ring of
+// shared-memory tiles with TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast: every block fetches
+// its own tiles; rows and k past the matrices' edges arrive as zeros), a single thread of another warp
+// issues tcgen05.mma (M 128, N 128, K 16; four per 64-wide k block) on those tiles in place, and
+// tcgen05.commit hands each stage back to the loader and, after the last k block, the accumulator to the
+// epilogue. All four warps then read their 32 lanes of the accumulator with tcgen05.ld and apply the
+// epilogue (bias, residual add into the 32-bit stream, or SwiGLU over a tile whose first 64 columns are
+// gate rows of W and last 64 the matching up rows). Two blocks fit an SM (96 KB of stages, 128 of 512
+// tensor-memory columns each), so one block's epilogue overlaps the other's main loop.
+//
+// Every wait on an mbarrier is bounded: when a bound runs out the block records a code in a status word,
+// drains its own copies, frees its tensor memory and returns; bl_gemm_tc_status() reports it on the host.
+// Role in the reference: the compiler's "native" tensor schedule for prefill matmuls
+// (kernel.tensors.linear, src/math_gpu.br:1998-2030; boring.toml:8-26); formula y = x . W^T (src/math.br:66-82).
+#include "common.cuh"
+#include "api.h"
+#include <cuda.h>
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64, STAGES = 3;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int TMEM_COLS = 128;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+__device__ int g_status = 0;      // 0 = fine; else the code of the first wait that ran out
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait. Returns false when the bound ran out or another thread of the block has given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (*give_up) return false;
+    }
+    *give_up = 1;
+    atomicCAS(&g_status, 0, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major operand tile with 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    const uint32_t lo = ((addr >> 4) & 0x3FFFu) | (1u << 16);                 // start address, leading offset 1
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);               // stride offset, version 1, SWIZZLE_128B
+    return ((uint64_t)hi << 32) | lo;
+}
+// kind::f16 instruction descriptor: D 32-bit, A and B bfloat16 and K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+template <int EPI, typename TO>
+__global__ void __launch_bounds__(128)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const void* __restrict__ bias, int bias_dtype, TO* __restrict__ out, int M, int N, int K) {
+    constexpr bool GLU = EPI == BL_EPI_SWIGLU;
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;              // tiles need 1024-byte alignment
+    unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + STAGES * STAGE_BYTES;                         // full[S], empty[S], accum
+    volatile int* give_up = reinterpret_cast<volatile int*>(aligned + STAGES * STAGE_BYTES + 128);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + STAGES * STAGE_BYTES + 136);
+    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, accum = bars + 16 * STAGES;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tile = blockIdx.x, m0 = blockIdx.y * BM;
+    const int n0 = n_tile * (GLU ? BN / 2 : BN);                              // first output column of the tile
+    const int kblocks = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        *give_up = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // loader: wait until the MMAs that read a stage are done, then refill it
+        int issued = 0;
+        for (int kb = 0; kb < kblocks; ++kb) {
+            const int s = kb % STAGES;
+            if (kb >= STAGES && !mbar_wait(empty0 + 8 * s, ((kb / STAGES) & 1) ^ 1, give_up, 1)) break;
+            const uint32_t a_dst = base + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
+            mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+            tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * BK, m0);
+            if (GLU) {                                                          // 64 gate rows, then the 64 up rows that match
+                tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BK, n0);
+                tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, kb * BK, N + n0);
+            } else {
+                tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BK, n0);
+            }
+            issued = kb + 1;
+        }
+        if (*give_up)                                                           // let our own copies land before leaving
+            for (int kb = max(0, issued - STAGES); kb < issued; ++kb)
+                mbar_wait(full0 + 8 * (kb % STAGES), (kb / STAGES) & 1, give_up, 0);
+    } else if (warp == 1 && lane == 0) {
+        // issuer: four K = 16 MMAs per stage; the accumulator starts from zero at the first of them
+        for (int kb = 0; kb < kblocks; ++kb) {
+            const int s = kb % STAGES;
+            if (!mbar_wait(full0 + 8 * s, (kb / STAGES) & 1, give_up, 2)) break;
+            fence_after_sync();
+            const uint64_t a_desc = smem_desc(base + s * STAGE_BYTES);
+            const uint64_t b_desc = smem_desc(base + s * STAGE_BYTES + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k)                                   // 32 bytes along K inside the swizzled row
+                umma_bf16(tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb | k) != 0);
+            umma_commit(empty0 + 8 * s);
+        }
+        umma_commit(accum);
+    }
+    __syncwarp();
+    const bool ready = mbar_wait(accum, 0, give_up, 3);
+    fence_after_sync();
+    if (ready && !*give_up) {
+        const int m = m0 + warp * 32 + lane;
+        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+        if (GLU) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t g[32], u[32];
+                tmem_ld32(lane_addr + c * 32, g);
+                tmem_ld32(lane_addr + 64 + c * 32, u);
+                tmem_ld_wait();
+                if (m < M) {
+                    TO* dst = out + (size_t)m * N + n0 + c * 32;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (n0 + c * 32 + j < N) bl_store(dst + j, bl_silu(__uint_as_float(g[j])) * __uint_as_float(u[j]));
+                }
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(lane_addr + c * 32, r);
+                tmem_ld_wait();
+                if (m < M) {
+                    TO* dst = out + (size_t)m * N + n0 + c * 32;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int n = n0 + c * 32 + j;
+                        if (n >= N) continue;
+                        float v = __uint_as_float(r[j]);
+                        if (EPI == BL_EPI_BIAS) v += bl_load_any(bias, bias_dtype, n);
+                        if (EPI == BL_EPI_RESIDUAL) v += bl_load(dst + j);
+                        bl_store(dst + j, v);
+                    }
+                }
+            }
+        }
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 0) {
+        fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// A row-major [rows, K] bfloat16 matrix as a 2-D tensor map with boxes of box_rows x 64 elements, 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+    EncodeTiled enc = encode_fn();
+    if (enc == nullptr) BL_FAIL("bl_gemm_tc: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) BL_FAIL("bl_gemm_tc: cuTensorMapEncodeTiled failed with code %d (rows %d, K %d)", (int)r, rows, K);
+    return 0;
+}
+
+template <int EPI, typename TO>
+int launch(const CUtensorMap& a, const CUtensorMap& b, const void* bias, int bias_dtype, void* out, int M, int N, int K,
+           cudaStream_t s) {
+    static bool configured = false;
+    if (!configured) {
+        BL_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured = true;
+    }
+    const int cols_per_tile = EPI == BL_EPI_SWIGLU ? BN / 2 : BN;
+    dim3 grid((N + cols_per_tile - 1) / cols_per_tile, (M + BM - 1) / BM);
+    gemm_tc_kernel<EPI, TO><<<grid, 128, SMEM_BYTES, s>>>(a, b, bias, bias_dtype, (TO*)out, M, N, K);
+    BL_CHECK_LAUNCH("bl_gemm_tc");
+    return 0;
+}
+
+}  // namespace
+
+// bfloat16 x[M, K] and W[N, K] (2N rows for BL_EPI_SWIGLU); K a multiple of 8, both 16-byte aligned.
+extern "C" int bl_gemm_tc(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype,
+                          int M, int N, int K, int epilogue, void* stream) {
+    if (M <= 0) return 0;
+    if (N <= 0 || K <= 0) BL_FAIL("bl_gemm_tc: bad sizes N=%d K=%d", N, K);
+    if (K % 8 != 0) BL_FAIL("bl_gemm_tc: K=%d is not a multiple of 8 (TMA rows must be 16-byte multiples)", K);
+    if (((uintptr_t)x | (uintptr_t)w) & 15) BL_FAIL("bl_gemm_tc: x and W must be 16-byte aligned");
+    if (epilogue == BL_EPI_BIAS && (bias == nullptr || (bias_dtype != BL_F32 && bias_dtype != BL_BF16)))
+        BL_FAIL("bl_gemm_tc: bias epilogue needs a float32 or bfloat16 bias");
+    const bool glu = epilogue == BL_EPI_SWIGLU;
+    CUtensorMap a, b;
+    if (make_map(&a, x, M, K, BM)) return 1;
+    if (make_map(&b, w, glu ? 2 * N : N, K, glu ? BN / 2 : BN)) return 1;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == BL_F32) {
+        switch (epilogue) {
+            case BL_EPI_NONE: return launch<BL_EPI_NONE, float>(a, b, bias, bias_dtype, out, M, N, K, s);
+            case BL_EPI_BIAS: return launch<BL_EPI_BIAS, float>(a, b, bias, bias_dtype, out, M, N, K, s);
+            case BL_EPI_RESIDUAL: return launch<BL_EPI_RESIDUAL, float>(a, b, bias, bias_dtype, out, M, N, K, s);
+            case BL_EPI_SWIGLU: return launch<BL_EPI_SWIGLU, float>(a, b, bias, bias_dtype, out, M, N, K, s);
+        }
+    } else if (out_dtype == BL_BF16) {
+        switch (epilogue) {
+            case BL_EPI_NONE: return launch<BL_EPI_NONE, __nv_bfloat16>(a, b, bias, bias_dtype, out, M, N, K, s);
+            case BL_EPI_BIAS: return launch<BL_EPI_BIAS, __nv_bfloat16>(a, b, bias, bias_dtype, out, M, N, K, s);
+            case BL_EPI_SWIGLU: return launch<BL_EPI_SWIGLU, __nv_bfloat16>(a, b, bias, bias_dtype, out, M, N, K, s);
+            case BL_EPI_RESIDUAL: BL_FAIL("bl_gemm_tc: the residual stream is 32-bit; output dtype must be float32");
+        }
+    } else {
+        BL_FAIL("bl_gemm_tc: unknown output dtype %d", out_dtype);
+    }
+    BL_FAIL("bl_gemm_tc: unknown epilogue %d", epilogue);
+}
+
+// Reads and clears the status word: 0 when no block has given up on a wait since the last call
+// (1 loader, 2 issuer, 3 epilogue). Synchronises the device.
+extern "C" int bl_gemm_tc_status(int* status) {
+    int v = 0, zero = 0;
+    BL_CUDA(cudaMemcpyFromSymbol(&v, g_status, sizeof(int)));
+    if (v != 0) BL_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(int)));
+    *status = v;
+    return 0;
+}

@@ -87,9 +87,12 @@ class _DecodeGraph:
             runner.model.forward(self.ctx)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        from ..kernels import ops
+        before = ops.launch_count
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self.logits = runner.model.forward(self.ctx)
+        self.kernels = ops.launch_count - before       # kernels of this library that one replay launches
         self.copied = torch.cuda.Event()
 
     def fill_padding(self, live: int) -> None:
@@ -119,6 +122,7 @@ class ModelRunner:
         self.steps = 0
         self.tokens_run = 0
         self.graph_steps = 0
+        self.last_step_graph_kernels = 0               # kernels launched by the last step through a graph replay
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self._table_width = -(-(-(-options.ctx_size // options.page_size)) // 8) * 8
 
@@ -178,6 +182,7 @@ class ModelRunner:
         gr.dev[:gr.dynamic_ints].copy_(gr.host[:gr.dynamic_ints], non_blocking=True)
         gr.copied.record()
         gr.graph.replay()
+        self.last_step_graph_kernels = gr.kernels
         for e in entries:
             self.cache.commit(e.request_id, 1)
         self.steps += 1
@@ -236,6 +241,7 @@ class ModelRunner:
         if (self.options.cuda_graphs and self.fast and self.dtype == torch.bfloat16
                 and getattr(self.model, "graph_safe", False) and len(entries) <= GRAPH_MAX_BATCH and all(len(e.tokens) == 1 for e in entries)):
             return self._graphed_decode(entries)
+        self.last_step_graph_kernels = 0
         R = len(entries)
         T = sum(len(e.tokens) for e in entries)
         N = sum(len(e.want) for e in entries)

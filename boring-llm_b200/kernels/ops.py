@@ -231,3 +231,26 @@ def attention_decode(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_sp
 
 def attention_decode_scratch(n: int, H: int, dh: int, n_splits: int) -> int:
     return 0 if n_splits <= 1 else n * H * n_splits * (dh + 2)
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+            epilogue: int = EPI_NONE) -> None:
+    """out = epilogue(x @ w.T) for many rows: tcgen05 tensor cores, TMA-fed tiles, accumulator in tensor memory.
+    Same operand rules as `gemm_skinny` (`gemm_skinny_supported`)."""
+    M, K = x.shape
+    N = out.shape[1]
+    rows_w = 2 * N if epilogue == EPI_SWIGLU else N
+    _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16, (rows_w, K)); _need(out, "out", None, (M, N))
+    if bias is not None:
+        _need(bias, "bias", None, (N,))
+    _call(_lib().bl_gemm_tc, _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0, _p(out), _dt(out),
+          M, N, K, epilogue, _stream())
+
+
+def check_status() -> None:
+    """Raises if a tensor-core block gave up on one of its bounded waits since the last check. Synchronises."""
+    v = ctypes.c_int(0)
+    _call(_lib().bl_gemm_tc_status, ctypes.byref(v))
+    if v.value != 0:
+        who = {1: "the TMA loader", 2: "the MMA issuer", 3: "the epilogue"}.get(v.value, "a thread")
+        raise KernelError(f"bl_gemm_tc: {who} gave up on a bounded wait (code {v.value}); results of that launch are invalid")

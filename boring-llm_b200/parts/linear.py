@@ -12,14 +12,17 @@ import torch
 from ..kernels import ops
 from ..kernels.ops import EPI_NONE, EPI_BIAS, EPI_RESIDUAL, EPI_SWIGLU
 
-SKINNY_MAX_ROWS = 256     # up to here W streams through registers; above, tiles of W are worth staging
+SKINNY_MAX_ROWS = 64      # up to here W streams through registers; above, 128-row tiles go to tcgen05
 
 
 def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
            epilogue: int = EPI_NONE) -> None:
     """out = epilogue(x @ w.T). float32 operands always take the plain CUDA-core kernel (true 32-bit);
     bfloat16 operands take a tensor-core kernel chosen by the number of rows."""
-    if ctx.fast and x.shape[0] <= SKINNY_MAX_ROWS and ops.gemm_skinny_supported(x, w):
-        ops.gemm_skinny(x, w, out, bias, epilogue)
+    if ctx.fast and ops.gemm_skinny_supported(x, w):
+        if x.shape[0] <= SKINNY_MAX_ROWS:
+            ops.gemm_skinny(x, w, out, bias, epilogue)
+        else:
+            ops.gemm_tc(x, w, out, bias, epilogue)
     else:
         ops.gemm_plain(x, w, out, bias, epilogue)

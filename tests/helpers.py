@@ -33,8 +33,11 @@ SEEDS = {"A": 0, "B": 1, "C": 2}
 # Largest allowed |engine - plain| as a fraction of the largest |plain logit| of the compared rows.
 # float32: every product is a 32-bit FMA chain of a few hundred terms through a few layers (about 1e3 ulps
 # of headroom); bfloat16: activations are rounded to 8 bits of mantissa at every kernel boundary.
-TOL = {"float32": 1e-4, "bfloat16": 1.5e-2}
-MEAN_TOL = {"float32": 2e-5, "bfloat16": 1.5e-3}
+# The plain side rounds what a bfloat16 engine stores, but it cannot reproduce the tensor cores' rounding of
+# the softmax numerators block by block (they are rounded against a running maximum); with the sharp attention
+# of the test models that independent 2^-9 noise is amplified by the next layers' softmax to a few percent.
+TOL = {"float32": 1e-4, "bfloat16": 4e-2}
+MEAN_TOL = {"float32": 2e-5, "bfloat16": 8e-3}
 # bfloat16 engine against the PURE 64-bit plain implementation (no rounding of stored tensors on the plain
 # side): only meaningful for well-conditioned models, i.e. the benchmark's N(0, 0.02) weights
 TOL_PURE_BF16 = 4e-2
