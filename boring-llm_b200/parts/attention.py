@@ -14,7 +14,7 @@ from .linear import linear, EPI_BIAS, EPI_NONE, EPI_RESIDUAL
 from .rotary import RotaryTable
 
 
-DECODE_TARGET_BLOCKS = 4 * 148     # blocks wanted in flight when one query's keys are cut into slices
+DECODE_TARGET_BLOCKS = 2 * 148     # blocks wanted in flight when one query's keys are cut into slices
 
 
 class Mixer(Part):
