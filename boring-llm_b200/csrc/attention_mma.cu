@@ -425,3 +425,47 @@ extern "C" int bl_attention_decode(const void* q, const void* k_cache, const voi
     }
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Decode attention for callers that must not allocate. See no_alloc.h.
+// ---------------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+namespace {
+
+// Partial results of the slices live here instead of in memory the caller allocates. The array is part of the
+// library's image on every GPU that loads it (8 MiB each, until the process exits).
+static __device__ __align__(256) float g_static_scratch[BL_NO_ALLOC_SCRATCH_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch_ptr[MAX_DEVICES] = {};   // device address of the array, per device, looked up once
+
+}  // namespace
+
+extern "C" int bl_attention_decode_no_alloc(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                                            const int* ctx_len, const int* block_table, int max_pages,
+                                            const int* reqs, int n, int n_splits, void* out, int H, int KV, int dh,
+                                            int page_size, int window, float scale, void* stream) {
+    if (n <= 0) return 0;
+    if (n_splits < 1) BL_FAIL("bl_attention_decode_no_alloc: %d slices", n_splits);
+    const long long need = bl_attention_decode_scratch_floats(n, H, dh, n_splits);
+    if (need > (long long)BL_NO_ALLOC_SCRATCH_FLOATS)
+        BL_FAIL("bl_attention_decode_no_alloc: %d requests x %d heads x %d slices x head size %d need %lld floats of "
+                "scratch, the built-in array holds %d; use fewer slices or the allocating entry point",
+                n, H, n_splits, dh, need, BL_NO_ALLOC_SCRATCH_FLOATS);
+    int dev = -1;
+    BL_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) BL_FAIL("bl_attention_decode_no_alloc: device %d is outside 0..%d", dev, MAX_DEVICES - 1);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        // In host code the array's name stands for a host-side shadow, not for device memory: a kernel handed
+        // `g_static_scratch` itself would fault or touch the wrong memory. The device address has to be asked for,
+        // with this device current, and it differs from device to device.
+        float* p = nullptr;
+        BL_CUDA(cudaGetSymbolAddress((void**)&p, g_static_scratch));
+        if (p == nullptr) BL_FAIL("bl_attention_decode_no_alloc: the scratch array has no address on device %d", dev);
+        g_static_scratch_ptr[dev] = p;
+    }
+    return bl_attention_decode(q, k_cache, v_cache, cu_q, ctx_len, block_table, max_pages, reqs, n, n_splits,
+                               n_splits > 1 ? g_static_scratch_ptr[dev] : nullptr, out, H, KV, dh, page_size, window,
+                               scale, stream);
+}
