@@ -80,6 +80,18 @@ int bl_gemm_tc(const void* x, const void* w, const void* bias, int bias_dtype, v
 // *status = 0 unless a block of bl_gemm_tc gave up on a bounded wait since the last call (synchronises the device).
 int bl_gemm_tc_status(int* status);
 
+// Fused kernels for steps with few rows (decode_fused.cu): the RMS norm in front of a product, and the split,
+// rotation and cache write behind the q/k/v product, folded into the product.
+int bl_norm_gemm_supported(int K);
+int bl_norm_gemm(const float* x, const int* row_idx, const void* norm_w, int norm_w_dtype, float eps,
+                 const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K,
+                 int epilogue, void* stream);
+int bl_norm_qkv_rope(const float* x, const void* norm_w, int norm_w_dtype, float eps, const void* w_qkv,
+                     const void* bias, int bias_dtype, const int* positions, const int* tok_req,
+                     const int* block_table, int max_pages, const float* inv_freq, float mscale,
+                     void* q_out, void* k_cache, void* v_cache, int M, int K, int H, int KV, int dh,
+                     int page_size, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

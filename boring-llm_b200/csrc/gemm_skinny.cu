@@ -51,23 +51,35 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     const __nv_bfloat16* w_hi = w + (size_t)r_hi * K;
     const __nv_bfloat16* u_lo = w + (size_t)(N + r_lo) * K;      // up rows follow the N gate rows
     const __nv_bfloat16* u_hi = w + (size_t)(N + r_hi) * K;
-    // the loop bound is the same for every lane of a warp (the MMA needs all 32 lanes); a lane whose
-    // 8 values lie past K loads zeros
-    for (int kc = warp * 32; kc < K; kc += WARPS * 32) {
-        const int k = kc + 8 * t;
-        const bool k_ok = k < K;
-        const uint4 a_lo = ld16(w_lo + k, lo_ok && k_ok), a_hi = ld16(w_hi + k, hi_ok && k_ok);
-        uint4 g_lo, g_hi;
-        if (GLU) { g_lo = ld16(u_lo + k, lo_ok && k_ok); g_hi = ld16(u_hi + k, hi_ok && k_ok); }
+    // The loop bounds are the same for every lane of a warp (the MMA needs all 32 lanes); a lane whose 8 values
+    // lie past K loads zeros. UNROLL chunks are fetched before any is used, so that each warp keeps enough
+    // 16-byte loads in flight to cover the latency of HBM.
+    constexpr int UNROLL = MT <= 2 ? 4 : 2;
+    for (int kc0 = warp * 32; kc0 < K; kc0 += UNROLL * WARPS * 32) {
+        uint4 a_lo[UNROLL], a_hi[UNROLL], g_lo[GLU ? UNROLL : 1], g_hi[GLU ? UNROLL : 1], b[UNROLL][MT];
 #pragma unroll
-        for (int j = 0; j < MT; ++j) {
-            const int tok = m0 + 8 * j + g;
-            const uint4 b = ld16(x + (size_t)tok * K + k, tok < M && k_ok);
-            mma_bf16(acc[j], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
-            mma_bf16(acc[j], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
-            if (GLU) {
-                mma_bf16(acu[j], g_lo.x, g_hi.x, g_lo.y, g_hi.y, b.x, b.y);
-                mma_bf16(acu[j], g_lo.z, g_hi.z, g_lo.w, g_hi.w, b.z, b.w);
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = kc0 + u * WARPS * 32 + 8 * t;
+            const bool k_ok = k < K;
+            a_lo[u] = ld16(w_lo + k, lo_ok && k_ok);
+            a_hi[u] = ld16(w_hi + k, hi_ok && k_ok);
+            if (GLU) { g_lo[u] = ld16(u_lo + k, lo_ok && k_ok); g_hi[u] = ld16(u_hi + k, hi_ok && k_ok); }
+#pragma unroll
+            for (int j = 0; j < MT; ++j) {
+                const int tok = m0 + 8 * j + g;
+                b[u][j] = ld16(x + (size_t)tok * K + k, tok < M && k_ok);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+            for (int j = 0; j < MT; ++j) {
+                mma_bf16(acc[j], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b[u][j].x, b[u][j].y);
+                mma_bf16(acc[j], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b[u][j].z, b[u][j].w);
+                if (GLU) {
+                    mma_bf16(acu[j], g_lo[u].x, g_hi[u].x, g_lo[u].y, g_hi[u].y, b[u][j].x, b[u][j].y);
+                    mma_bf16(acu[j], g_lo[u].z, g_hi[u].z, g_lo[u].w, g_hi[u].w, b[u][j].z, b[u][j].w);
+                }
             }
         }
     }

@@ -254,3 +254,52 @@ def check_status() -> None:
     if v.value != 0:
         who = {1: "the TMA loader", 2: "the MMA issuer", 3: "the epilogue"}.get(v.value, "a thread")
         raise KernelError(f"bl_gemm_tc: {who} gave up on a bounded wait (code {v.value}); results of that launch are invalid")
+
+
+def norm_gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the fused norm + product kernels take these operands (float32 rows, bfloat16 matrix)."""
+    return (x.dtype == torch.float32 and w.dtype == torch.bfloat16 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and bool(library.load().bl_norm_gemm_supported(x.shape[1])))
+
+
+def norm_gemm(x: torch.Tensor, norm_w: torch.Tensor, eps: float, w: torch.Tensor, out: torch.Tensor,
+              bias: Optional[torch.Tensor] = None, epilogue: int = EPI_NONE,
+              row_idx: Optional[torch.Tensor] = None) -> None:
+    """out = epilogue(rmsnorm(x[row_idx]) @ w.T) in one launch, for few rows. EPI_NONE / EPI_BIAS write float32,
+    EPI_SWIGLU (w with twice the rows) writes bfloat16."""
+    K = x.shape[1]
+    M, N = out.shape
+    rows_w = 2 * N if epilogue == EPI_SWIGLU else N
+    _need(x, "x", torch.float32); _need(norm_w, "norm_w", None, (K,)); _need(w, "w", torch.bfloat16, (rows_w, K))
+    _need(out, "out", torch.bfloat16 if epilogue == EPI_SWIGLU else torch.float32)
+    if row_idx is not None:
+        _need(row_idx, "row_idx", torch.int32, (M,))
+    elif x.shape[0] != M:
+        raise KernelError("norm_gemm: x and out differ in rows")
+    if bias is not None:
+        _need(bias, "bias", None, (N,))
+    _call(_lib().bl_norm_gemm, _p(x), _p(row_idx), _p(norm_w), _dt(norm_w), ctypes.c_float(eps), _p(w), _p(bias),
+          _dt(bias) if bias is not None else 0, _p(out), M, N, K, epilogue, _stream())
+
+
+def norm_qkv_rope(x: torch.Tensor, norm_w: torch.Tensor, eps: float, w_qkv: torch.Tensor, bias: Optional[torch.Tensor],
+                  positions: torch.Tensor, tok_req: torch.Tensor, block_table: torch.Tensor, inv_freq: torch.Tensor,
+                  mscale: float, q_out: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                  H: int, KV: int, dh: int) -> None:
+    """rmsnorm -> joined q/k/v product (+ bias) -> rotation of q and k -> k, v into the pages, q out, in one launch."""
+    M, K = x.shape
+    _need(x, "x", torch.float32); _need(norm_w, "norm_w", None, (K,)); _need(w_qkv, "w_qkv", torch.bfloat16, ((H + 2 * KV) * dh, K))
+    _need(positions, "positions", torch.int32, (M,)); _need(tok_req, "tok_req", torch.int32, (M,))
+    _need(block_table, "block_table", torch.int32); _need(inv_freq, "inv_freq", torch.float32, (dh // 2,))
+    _need(q_out, "q_out", torch.bfloat16, (M, H * dh))
+    if bias is not None:
+        _need(bias, "bias", None, ((H + 2 * KV) * dh,))
+    page_size = 1
+    if k_cache is not None:
+        _need(k_cache, "k_cache", torch.bfloat16); _need(v_cache, "v_cache", torch.bfloat16, k_cache.shape)
+        if k_cache.shape[1] != KV or k_cache.shape[3] != dh:
+            raise KernelError(f"k_cache: shape {tuple(k_cache.shape)} does not hold {KV} heads of {dh}")
+        page_size = k_cache.shape[2]
+    _call(_lib().bl_norm_qkv_rope, _p(x), _p(norm_w), _dt(norm_w), ctypes.c_float(eps), _p(w_qkv), _p(bias),
+          _dt(bias) if bias is not None else 0, _p(positions), _p(tok_req), _p(block_table), block_table.shape[1],
+          _p(inv_freq), ctypes.c_float(mscale), _p(q_out), _p(k_cache), _p(v_cache), M, K, H, KV, dh, page_size, _stream())

@@ -11,7 +11,10 @@ from ..kernels import ops
 from ..weights import TensorSpec, MATRIX, BIAS
 from .base import Part, to_device_matrix, to_device_vector
 from .linear import linear, EPI_BIAS, EPI_NONE, EPI_RESIDUAL
+from .norm import RMSNorm
 from .rotary import RotaryTable
+
+FUSED_MAX_ROWS = 64       # steps with at most this many rows take the fused norm + product kernels
 
 
 DECODE_TARGET_BLOCKS = 2 * 148     # blocks wanted in flight when one query's keys are cut into slices
@@ -36,6 +39,11 @@ class Mixer(Part):
 
     def forward(self, ctx, h, residual, cache_layer: Optional[int], write_cache: bool = True) -> None:
         raise NotImplementedError
+
+    def forward_fused_norm(self, ctx, x, norm, cache_layer: Optional[int], write_cache: bool = True) -> bool:
+        """Optional: run `norm` and this mixer on the residual stream `x` in fused kernels and return True,
+        or return False to be called with the normed rows as usual."""
+        return False
 
 
 class GQAAttention(Mixer):
@@ -98,6 +106,23 @@ class GQAAttention(Mixer):
         attn = ctx.empty((T, self.H * self.dh))
         self.attend(ctx, q, k_cache, v_cache, table, attn)
         linear(ctx, attn, self.wo, residual, None, EPI_RESIDUAL)
+
+    def forward_fused_norm(self, ctx, x, norm, cache_layer, write_cache=True) -> bool:
+        """Few rows in bfloat16: norm, joined product, bias, rotation and cache write are ONE kernel."""
+        T = x.shape[0]
+        if not (ctx.fast and ctx.dtype == torch.bfloat16 and T <= FUSED_MAX_ROWS and isinstance(norm, RMSNorm)
+                and self.rotary.rot_half * 2 == self.dh and self.dh % 16 == 0
+                and ops.norm_gemm_supported(x, self.w_qkv)):
+            return False
+        k_cache, v_cache, table = ctx.kv(cache_layer)
+        q = ctx.empty((T, self.H * self.dh))
+        ops.norm_qkv_rope(x, norm.weight, norm.eps, self.w_qkv, self.b_qkv if self.qkv_bias else None,
+                          ctx.positions, ctx.tok_req, table, self.rotary.inv_freq, self.rotary.mscale, q,
+                          k_cache if write_cache else None, v_cache if write_cache else None, self.H, self.KV, self.dh)
+        attn = ctx.empty((T, self.H * self.dh))
+        self.attend(ctx, q, k_cache, v_cache, table, attn)
+        linear(ctx, attn, self.wo, x, None, EPI_RESIDUAL)
+        return True
 
     def attend(self, ctx, q, k_cache, v_cache, table, out):
         """Tensor-core kernels for bfloat16 where they are built (pages of 16, common head sizes): one launch for

@@ -25,7 +25,10 @@ class PreNormBlock(Part):
         return bool(getattr(self.mixer, "graph_safe", False) and getattr(self.ffn, "graph_safe", False))
 
     def forward(self, ctx, x, cache_layer: Optional[int], write_cache: bool = True) -> None:
-        h = self.mixer_norm.forward(ctx, x)
-        self.mixer.forward(ctx, h, x, cache_layer, write_cache)
-        h = self.ffn_norm.forward(ctx, x)
-        self.ffn.forward(ctx, h, x)
+        # a mixer or feed-forward may take the norm in front of it into its first kernel (steps with few rows)
+        if not self.mixer.forward_fused_norm(ctx, x, self.mixer_norm, cache_layer, write_cache):
+            h = self.mixer_norm.forward(ctx, x)
+            self.mixer.forward(ctx, h, x, cache_layer, write_cache)
+        if not self.ffn.forward_fused_norm(ctx, x, self.ffn_norm):
+            h = self.ffn_norm.forward(ctx, x)
+            self.ffn.forward(ctx, h, x)

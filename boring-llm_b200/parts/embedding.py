@@ -51,6 +51,17 @@ class OutputHead(Part):
     def matrix(self) -> torch.Tensor:
         return self.tied_to.table if self.tied_to is not None else self.weight
 
+    def forward_fused_norm(self, ctx, x: torch.Tensor, norm, row_idx: torch.Tensor) -> Optional[torch.Tensor]:
+        """Final norm and output product in one kernel for few rows; None when that is not possible."""
+        from .attention import FUSED_MAX_ROWS
+        from .norm import RMSNorm
+        if not (ctx.fast and ctx.dtype == torch.bfloat16 and row_idx.shape[0] <= FUSED_MAX_ROWS
+                and isinstance(norm, RMSNorm) and ops.norm_gemm_supported(x, self.matrix())):
+            return None
+        logits = ctx.empty((row_idx.shape[0], self.vocab), torch.float32)
+        ops.norm_gemm(x, norm.weight, norm.eps, self.matrix(), logits, None, EPI_NONE, row_idx)
+        return logits
+
     def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:
         logits = ctx.empty((y.shape[0], self.vocab), torch.float32)
         linear(ctx, y, self.matrix(), logits, None, EPI_NONE)

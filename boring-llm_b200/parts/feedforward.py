@@ -5,6 +5,7 @@ from typing import Dict
 
 import torch
 
+from ..kernels import ops
 from ..weights import TensorSpec, MATRIX
 from .base import Part, to_device_matrix
 from .linear import linear, EPI_RESIDUAL, EPI_SWIGLU
@@ -17,6 +18,11 @@ class FeedForward(Part):
 
     def forward(self, ctx, h, residual) -> None:
         raise NotImplementedError
+
+    def forward_fused_norm(self, ctx, x, norm) -> bool:
+        """Optional: run `norm` and this feed-forward on the residual stream `x` in fused kernels and return
+        True, or return False to be called with the normed rows as usual."""
+        return False
 
 
 class SwiGLU(FeedForward):
@@ -38,6 +44,17 @@ class SwiGLU(FeedForward):
     def place(self, local, dtype, device):
         self.w_gate_up = to_device_matrix(torch.cat([local["w_gate"], local["w_up"]], dim=0), dtype, device)
         self.w_down = to_device_matrix(local["w_down"], dtype, device)
+
+    def forward_fused_norm(self, ctx, x, norm) -> bool:
+        from .attention import FUSED_MAX_ROWS
+        from .norm import RMSNorm
+        if not (ctx.fast and ctx.dtype == torch.bfloat16 and x.shape[0] <= FUSED_MAX_ROWS and isinstance(norm, RMSNorm)
+                and ops.norm_gemm_supported(x, self.w_gate_up)):
+            return False
+        act = ctx.empty((x.shape[0], self.hidden))
+        ops.norm_gemm(x, norm.weight, norm.eps, self.w_gate_up, act, None, EPI_SWIGLU)
+        linear(ctx, act, self.w_down, x, None, EPI_RESIDUAL)
+        return True
 
     def forward(self, ctx, h, residual):
         act = ctx.empty((h.shape[0], self.hidden))

@@ -78,5 +78,8 @@ class DecoderModel(Part):
             self.blocks[call.block].forward(ctx, x, call.cache, call.write_cache)
         if ctx.logit_rows.shape[0] == 0:
             return ctx.empty((0, self.vocab_size), torch.float32)
-        y = self.final_norm.forward(ctx, x, ctx.logit_rows)
-        return self.head.forward(ctx, y)
+        fused = getattr(self.head, "forward_fused_norm", None)
+        logits = fused(ctx, x, self.final_norm, ctx.logit_rows) if fused is not None else None
+        if logits is None:
+            logits = self.head.forward(ctx, self.final_norm.forward(ctx, x, ctx.logit_rows))
+        return logits

@@ -441,3 +441,76 @@ def test_gemm_tc_epilogues(M, N, K):
     o.gemm_tc(x, wn, half)
     close(half, xd @ wd[:N].T, dtype, "bfloat16 output")
     o.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 7, 8), (8, 4864 // 16, 896), (17, 129, 96), (33, 50, 200), (64, 80, 264), (5, 1000, 80)])
+def test_norm_gemm_fused(M, N, K):
+    """The fused norm + product kernels against 64-bit arithmetic (the norm's output rounded to bfloat16, as
+    the unfused kernels store it) and against the unfused kernels."""
+    o = ops()
+    bf = torch.bfloat16
+    rows = M + 3
+    x = data((rows, K), 31) * 3
+    nw = (data((K,), 32) * 0.25 + 1).to(bf)
+    w = (data((2 * N, K), 33) * 0.25).to(bf)
+    b = data((N,), 34)
+    idx = torch.tensor([(i * 7) % rows for i in range(M)], dtype=torch.int32, device=DEV)
+    xs = x[idx.long()].contiguous()
+    h = plain.round_bf16(plain.rms_norm(xs.double().cpu(), nw.double().cpu(), 1e-5))
+    wd = w.double().cpu()
+    wn = w[:N].contiguous()
+    out = torch.full((M, N), float("nan"), device=DEV)
+    o.norm_gemm(xs, nw, 1e-5, wn, out)
+    close(out, h @ wd[:N].T, torch.float32, "plain")
+    o.norm_gemm(x, nw, 1e-5, wn, out, None, o.EPI_NONE, idx)
+    close(out, h @ wd[:N].T, torch.float32, "gathered rows")
+    o.norm_gemm(xs, nw, 1e-5, wn, out, b, o.EPI_BIAS)
+    close(out, h @ wd[:N].T + b.double().cpu(), torch.float32, "bias")
+    act = torch.full((M, N), float("nan"), dtype=bf, device=DEV)
+    o.norm_gemm(xs, nw, 1e-5, w, act, None, o.EPI_SWIGLU)
+    close(act, plain.silu(h @ wd[:N].T) * (h @ wd[N:].T), bf, "swiglu")
+    # the unfused twins
+    hb = torch.empty(M, K, dtype=bf, device=DEV)
+    o.rmsnorm(xs, nw, 1e-5, hb)
+    twin = torch.empty(M, N, device=DEV)
+    o.gemm_plain(hb, wn, twin)
+    o.norm_gemm(xs, nw, 1e-5, wn, out)
+    close(out, twin.double(), torch.float32, "twin")
+    one = torch.empty(1, N, device=DEV)
+    o.norm_gemm(xs[M - 1:M].contiguous(), nw, 1e-5, wn, one)
+    assert torch.equal(one[0], out[M - 1])            # a row does not depend on the rows beside it
+
+
+@pytest.mark.parametrize("H,KV,dh,d", [(4, 2, 16, 64), (3, 1, 32, 96), (5, 5, 48, 80), (14, 2, 64, 896), (2, 1, 128, 200)])
+@pytest.mark.parametrize("bias", [True, False])
+def test_norm_qkv_rope_fused(H, KV, dh, d, bias):
+    """One launch against the three kernels it replaces (norm, joined product with bias, rotation + cache write)."""
+    o = ops()
+    bf = torch.bfloat16
+    page = 16
+    ctx_lens, q_lens = [5, 40, 17, 300], [5, 9, 1, 1]
+    s = paged_setup(ctx_lens, q_lens, KV, dh, page, bf, 9)
+    s2 = paged_setup(ctx_lens, q_lens, KV, dh, page, bf, 9)
+    T = s["T"]
+    x = data((T, d), 41) * 2
+    nw = (data((d,), 42) * 0.25 + 1).to(bf)
+    w = (data(((H + 2 * KV) * dh, d), 43) * 0.2).to(bf)
+    b = (data(((H + 2 * KV) * dh,), 44) * 0.5).to(bf) if bias else None
+    j = np.arange(dh // 2, dtype=np.float32)
+    inv = torch.from_numpy(np.float32(1.0) / np.power(np.float32(1.0e4), (np.float32(2.0) * j) / np.float32(dh), dtype=np.float32)).to(DEV)
+    # unfused
+    h = torch.empty(T, d, dtype=bf, device=DEV)
+    o.rmsnorm(x, nw, 1e-6, h)
+    qkv = torch.empty(T, (H + 2 * KV) * dh, device=DEV)
+    o.gemm_plain(h, w, qkv, b, o.EPI_BIAS if bias else o.EPI_NONE)
+    q_ref = torch.empty(T, H * dh, dtype=bf, device=DEV)
+    o.rope_kv_write(qkv, s["positions"], s["tok_req"], s["table"], inv, dh // 2, 1.0, q_ref, s["kc"], s["vc"], H, KV, dh)
+    # fused
+    q = torch.full((T, H * dh), float("nan"), dtype=bf, device=DEV)
+    o.norm_qkv_rope(x, nw, 1e-6, w, b, s2["positions"], s2["tok_req"], s2["table"], inv, 1.0, q, s2["kc"], s2["vc"], H, KV, dh)
+    close(q, q_ref.double(), bf, "q")
+    close(s2["kc"], s["kc"].double(), bf, "key pages")          # junk in untouched rows is identical on both sides
+    close(s2["vc"], s["vc"].double(), bf, "value pages")
+    q_only = torch.empty_like(q)
+    o.norm_qkv_rope(x, nw, 1e-6, w, b, s2["positions"], s2["tok_req"], s2["table"], inv, 1.0, q_only, None, None, H, KV, dh)
+    assert torch.equal(q_only, q)
