@@ -92,6 +92,9 @@ int bl_norm_qkv_rope(const float* x, const void* norm_w, int norm_w_dtype, float
                      void* q_out, void* k_cache, void* v_cache, int M, int K, int H, int KV, int dh,
                      int page_size, void* stream);
 
+// Programmatic dependent launch for the small kernels of a step (on by default): 0 launches them the ordinary way.
+void bl_set_dependent_launch(int on);
+
 #ifdef __cplusplus
 }
 #endif

@@ -176,6 +176,7 @@ attention_mma_kernel(const AttnParams p) {
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int G = p.H / p.KV;
+    bl_pdl_trigger();
     int r, kvh, head0, tok0, split = 0;
     if (DECODE) {
         r = p.work[blockIdx.z];
@@ -190,6 +191,7 @@ attention_mma_kernel(const AttnParams p) {
         head0 = blockIdx.y;
         kvh = head0 / G;
     }
+    // the step's index arrays are written before its first kernel: they may be read before the wait
     const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin, ctx = p.ctx_len[r];
     const int* table = p.block_table + (size_t)r * p.max_pages;
     // rows g and g + 8 of this warp
@@ -222,6 +224,7 @@ attention_mma_kernel(const AttnParams p) {
         b_end = min(b_end, s0 + per);
         b_begin = min(s0, b_end);
     }
+    bl_pdl_wait();                                    // q and the newest keys and values come from the kernel before
     unsigned qf[DH / 16][4];
 #pragma unroll
     for (int kk = 0; kk < DH / 16; ++kk) {
@@ -317,25 +320,62 @@ attention_mma_kernel(const AttnParams p) {
 }
 
 // Merges the slices of one (request, head): out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
-// (FlashDecodeCombineKernel, src/math_gpu.br:3597-3631).
-__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                       const int* __restrict__ work, const int* __restrict__ cu_q,
-                                       __nv_bfloat16* __restrict__ out, int H, int DH, int n_splits) {
+// (FlashDecodeCombineKernel, src/math_gpu.br:3597-3631). One block of 128 threads per (request, head): the
+// slices' maxima and sums are read by as many threads at once, then each thread adds up a quarter of the
+// slices for one or more output dimensions with four loads in flight, and the quarters are added in order.
+__global__ void __launch_bounds__(128)
+attention_merge_kernel(const float* part_o, const float* part_ml /* both written by the kernel before */,
+                       const int* __restrict__ work, const int* __restrict__ cu_q,
+                       __nv_bfloat16* __restrict__ out, int H, int DH, int n_splits) {
+    __shared__ float sf[256];          // weight 2^(m_s - M) of each slice (n_splits <= 256)
+    __shared__ float sacc[4][128];
+    __shared__ float sL;
+    bl_pdl_trigger();
     const int idx = blockIdx.x, hd = blockIdx.y;
     const int r = work[idx];
+    bl_pdl_wait();
     if (cu_q[r + 1] - cu_q[r] <= 0) return;
     const size_t base = ((size_t)idx * H + hd) * n_splits;
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-    for (int d = threadIdx.x; d < DH; d += blockDim.x) {
-        float L = 0.f, O = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float ms = part_ml[(base + s) * 2];
-            const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
-            L += part_ml[(base + s) * 2 + 1] * f;
-            O += part_o[(base + s) * DH + d] * f;
+    float mloc = -INFINITY;
+    for (int s = threadIdx.x; s < n_splits; s += 128) mloc = fmaxf(mloc, part_ml[(base + s) * 2]);
+    mloc = bl_warp_max(mloc);
+    if ((threadIdx.x & 31) == 0) sacc[0][threadIdx.x >> 5] = mloc;
+    __syncthreads();
+    const float M = fmaxf(fmaxf(sacc[0][0], sacc[0][1]), fmaxf(sacc[0][2], sacc[0][3]));
+    __syncthreads();
+    for (int s = threadIdx.x; s < n_splits; s += 128) {
+        const float ms = part_ml[(base + s) * 2];
+        sf[s] = ms == -INFINITY ? 0.f : exp2f(ms - M);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float L = 0.f;
+        for (int s = 0; s < n_splits; ++s) L += part_ml[(base + s) * 2 + 1] * sf[s];
+        sL = L;
+    }
+    const int quarter = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per = (n_splits + 3) / 4;
+    const int s0 = quarter * per, s1 = min(n_splits, s0 + per);
+    for (int d0 = 0; d0 < DH; d0 += 32) {
+        const int d = d0 + lane;
+        float acc = 0.f;
+        if (d < DH) {
+            int s = s0;
+            for (; s + 4 <= s1; s += 4) {
+                const float a0 = part_o[(base + s) * DH + d], a1 = part_o[(base + s + 1) * DH + d];
+                const float a2 = part_o[(base + s + 2) * DH + d], a3 = part_o[(base + s + 3) * DH + d];
+                acc += a0 * sf[s]; acc += a1 * sf[s + 1]; acc += a2 * sf[s + 2]; acc += a3 * sf[s + 3];
+            }
+            for (; s < s1; ++s) acc += part_o[(base + s) * DH + d] * sf[s];
         }
-        out[((size_t)cu_q[r] * H + hd) * DH + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        sacc[quarter][lane] = acc;
+        __syncthreads();
+        if (quarter == 0 && d < DH) {
+            const float O = (sacc[0][lane] + sacc[1][lane]) + (sacc[2][lane] + sacc[3][lane]);
+            const float L = sL;
+            out[((size_t)cu_q[r] * H + hd) * DH + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        }
+        __syncthreads();
     }
 }
 
@@ -348,7 +388,7 @@ int launch(const AttnParams& p, dim3 grid, cudaStream_t s) {
         BL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<DH, DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
         configured = true;
     }
-    attention_mma_kernel<DH, DECODE><<<grid, THREADS, bytes, s>>>(p);
+    BL_CUDA(bl_launch_dependent(attention_mma_kernel<DH, DECODE>, grid, dim3(THREADS), (size_t)bytes, s, p));
     BL_CHECK_LAUNCH("bl_attention_mma");
     return 0;
 }
@@ -408,7 +448,7 @@ extern "C" int bl_attention_decode(const void* q, const void* k_cache, const voi
                                    int window, float scale, void* stream) {
     if (n <= 0) return 0;
     if (check(H, KV, dh, page_size, max_pages, window)) return 1;
-    if (n_splits < 1 || n_splits > 65535) BL_FAIL("bl_attention_decode: %d slices", n_splits);
+    if (n_splits < 1 || n_splits > 256) BL_FAIL("bl_attention_decode: %d slices (1..256)", n_splits);
     if (n_splits > 1 && scratch == nullptr) BL_FAIL("bl_attention_decode: slices need scratch memory");
     AttnParams p;
     p.q = (const __nv_bfloat16*)q; p.kc = (const __nv_bfloat16*)k_cache; p.vc = (const __nv_bfloat16*)v_cache;
@@ -419,9 +459,8 @@ extern "C" int bl_attention_decode(const void* q, const void* k_cache, const voi
     const int G = H / KV;
     if (dispatch<true>(dh, p, dim3(n_splits, KV * ((G + 15) / 16), n), (cudaStream_t)stream)) return 1;
     if (n_splits > 1) {
-        attention_merge_kernel<<<dim3(n, H), dh < 32 ? 32 : dh, 0, (cudaStream_t)stream>>>(
-            p.part_o, p.part_ml, reqs, cu_q, p.out, H, dh, n_splits);
-        BL_CHECK_LAUNCH("bl_attention_decode merge");
+        BL_CUDA(bl_launch_dependent(attention_merge_kernel, dim3(n, H), dim3(128), 0, (cudaStream_t)stream,
+                                    (const float*)p.part_o, (const float*)p.part_ml, reqs, cu_q, p.out, H, dh, n_splits));
     }
     return 0;
 }

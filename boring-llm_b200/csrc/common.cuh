@@ -48,3 +48,25 @@ __device__ __forceinline__ float bl_warp_max(float v) {
 
 // x / (1 + exp(-x)), as src/math.br:232-233.
 __device__ __forceinline__ float bl_silu(float x) { return x / (1.0f + expf(-x)); }
+
+// Programmatic dependent launch. A kernel launched with bl_launch_dependent() may start while its predecessor
+// on the stream is still running; whatever it does before bl_pdl_wait() must touch only data that no earlier
+// kernel of the step writes (weights, the step's index arrays). bl_pdl_wait() returns once the predecessor has
+// completed and its writes are visible. bl_pdl_trigger() lets the successor be scheduled as soon as every block
+// of this kernel has issued it. Both are no-ops in a kernel that was launched the ordinary way.
+__device__ __forceinline__ void bl_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void bl_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool bl_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+cudaError_t bl_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = bl_pdl_enabled() ? 1 : 0;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

@@ -85,7 +85,9 @@ fused_norm_gemm_kernel(const FusedParams p) {
             if (GLU) { g_lo[u] = ld16(u_lo + k, lo_ok && k_ok); g_hi[u] = ld16(u_hi + k, hi_ok && k_ok); }
         }
     };
-    fetch(warp * 32);                                  // W is on its way while the rows are normalised
+    bl_pdl_trigger();
+    fetch(warp * 32);                                  // W is on its way while the kernel before this one finishes
+    bl_pdl_wait();                                     // from here on the residual stream may be read
 
     // normalise this block's rows into shared memory: warp w takes rows w, w + 8, ...
     for (int i = warp; i < TOK; i += WARPS) {
@@ -228,7 +230,7 @@ int launch(const FusedParams& p, int tiles, cudaStream_t s) {
         BL_CUDA(cudaFuncSetAttribute(fused_norm_gemm_kernel<MT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT));
         configured = SMEM_LIMIT;
     }
-    fused_norm_gemm_kernel<MT, MODE><<<tiles * p.m_groups, WARPS * 32, bytes, s>>>(p);
+    BL_CUDA(bl_launch_dependent(fused_norm_gemm_kernel<MT, MODE>, dim3(tiles * p.m_groups), dim3(WARPS * 32), bytes, s, p));
     BL_CHECK_LAUNCH("bl_norm_gemm");
     return 0;
 }

@@ -17,6 +17,11 @@ void bl_set_error(const char* fmt, ...) {
 
 extern "C" const char* bl_last_error(void) { return g_error; }
 
+static bool g_pdl = true;
+bool bl_pdl_enabled() { return g_pdl; }
+// 0 switches programmatic dependent launch off for the kernels that use it (for measurements); default on.
+extern "C" void bl_set_dependent_launch(int on) { g_pdl = on != 0; }
+
 extern "C" int bl_device_check(void) {
     int dev = 0;
     BL_CUDA(cudaGetDevice(&dev));
@@ -32,6 +37,8 @@ extern "C" int bl_device_check(void) {
 template <typename TT>
 __global__ void embed_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int d) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
     const int t = blockIdx.x;
     const size_t row = (size_t)ids[t] * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) out[(size_t)t * d + i] = bl_load(table + row + i);
@@ -43,9 +50,9 @@ extern "C" int bl_embed(const void* table, int table_dtype, const int* ids, floa
     if (d <= 0 || vocab <= 0) BL_FAIL("bl_embed: bad sizes d=%d vocab=%d", d, vocab);
     cudaStream_t s = (cudaStream_t)stream;
     if (table_dtype == BL_F32)
-        embed_kernel<float><<<T, 128, 0, s>>>((const float*)table, ids, out, d);
+        BL_CUDA(bl_launch_dependent(embed_kernel<float>, dim3(T), dim3(128), 0, s, (const float*)table, ids, out, d));
     else if (table_dtype == BL_BF16)
-        embed_kernel<__nv_bfloat16><<<T, 128, 0, s>>>((const __nv_bfloat16*)table, ids, out, d);
+        BL_CUDA(bl_launch_dependent(embed_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, s, (const __nv_bfloat16*)table, ids, out, d));
     else
         BL_FAIL("bl_embed: unknown table dtype %d", table_dtype);
     BL_CHECK_LAUNCH("bl_embed");
@@ -56,9 +63,12 @@ extern "C" int bl_embed(const void* table, int table_dtype, const int* ids, floa
 // One block of 128 threads per row. The sum of squares is reduced in a fixed order that depends
 // only on d, so a row's result does not depend on how many rows the call has.
 template <typename TY>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_idx,
+__global__ void rmsnorm_kernel(const float* x /* written by the kernel before: no read-only cache */,
+                               const int* __restrict__ row_idx,
                                const void* __restrict__ w, int w_dtype, TY* __restrict__ y,
                                int d, float eps) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
     const int r = blockIdx.x;
     const size_t src = (size_t)(row_idx ? row_idx[r] : r) * d;
     float ss = 0.f;
@@ -85,9 +95,9 @@ extern "C" int bl_rmsnorm(const float* x, const int* row_idx, const void* w, int
     if (w_dtype != BL_F32 && w_dtype != BL_BF16) BL_FAIL("bl_rmsnorm: unknown weight dtype %d", w_dtype);
     cudaStream_t s = (cudaStream_t)stream;
     if (y_dtype == BL_F32)
-        rmsnorm_kernel<float><<<rows, 128, 0, s>>>(x, row_idx, w, w_dtype, (float*)y, d, eps);
+        BL_CUDA(bl_launch_dependent(rmsnorm_kernel<float>, dim3(rows), dim3(128), 0, s, x, row_idx, w, w_dtype, (float*)y, d, eps));
     else if (y_dtype == BL_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<rows, 128, 0, s>>>(x, row_idx, w, w_dtype, (__nv_bfloat16*)y, d, eps);
+        BL_CUDA(bl_launch_dependent(rmsnorm_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, s, x, row_idx, w, w_dtype, (__nv_bfloat16*)y, d, eps));
     else
         BL_FAIL("bl_rmsnorm: unknown output dtype %d", y_dtype);
     BL_CHECK_LAUNCH("bl_rmsnorm");
@@ -97,11 +107,13 @@ extern "C" int bl_rmsnorm(const float* x, const int* row_idx, const void* w, int
 // ---------------------------------------------------------------------------------------------
 // One block per token. Work items: (head, pair) for q and k heads, then the v elements.
 template <typename TT>
-__global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int* __restrict__ positions,
+__global__ void rope_kv_write_kernel(const float* qkv /* written by the kernel before */, const int* __restrict__ positions,
                                      const int* __restrict__ tok_req, const int* __restrict__ block_table,
                                      int max_pages, const float* __restrict__ inv_freq, int rot_half,
                                      float mscale, TT* __restrict__ q_out, TT* __restrict__ k_cache,
                                      TT* __restrict__ v_cache, int H, int KV, int dh, int page_size) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int half = dh / 2;
@@ -158,11 +170,12 @@ extern "C" int bl_rope_kv_write(const float* qkv, const int* positions, const in
     if ((k_cache == nullptr) != (v_cache == nullptr)) BL_FAIL("bl_rope_kv_write: key and value cache must both be given or both be null");
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == BL_F32)
-        rope_kv_write_kernel<float><<<T, 128, 0, s>>>(qkv, positions, tok_req, block_table, max_pages, inv_freq,
-            rot_half, mscale, (float*)q_out, (float*)k_cache, (float*)v_cache, H, KV, dh, page_size);
+        BL_CUDA(bl_launch_dependent(rope_kv_write_kernel<float>, dim3(T), dim3(128), 0, s, qkv, positions, tok_req, block_table,
+            max_pages, inv_freq, rot_half, mscale, (float*)q_out, (float*)k_cache, (float*)v_cache, H, KV, dh, page_size));
     else if (dtype == BL_BF16)
-        rope_kv_write_kernel<__nv_bfloat16><<<T, 128, 0, s>>>(qkv, positions, tok_req, block_table, max_pages, inv_freq,
-            rot_half, mscale, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, H, KV, dh, page_size);
+        BL_CUDA(bl_launch_dependent(rope_kv_write_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, s, qkv, positions, tok_req,
+            block_table, max_pages, inv_freq, rot_half, mscale, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
+            (__nv_bfloat16*)v_cache, H, KV, dh, page_size));
     else
         BL_FAIL("bl_rope_kv_write: unknown dtype %d", dtype);
     BL_CHECK_LAUNCH("bl_rope_kv_write");

@@ -31,7 +31,8 @@ __device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p, bool ok) {
 // MT: groups of 8 tokens handled by one block (M tile = 8 * MT).
 template <int MT, int EPI, typename TO>
 __global__ void __launch_bounds__(WARPS * 32)
-gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no read-only cache */,
+                   const __nv_bfloat16* __restrict__ w,
                    const void* __restrict__ bias, int bias_dtype, TO* __restrict__ out,
                    int M, int N, int K, int m_groups) {
     constexpr bool GLU = EPI == BL_EPI_SWIGLU;
@@ -52,11 +53,12 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     const __nv_bfloat16* u_lo = w + (size_t)(N + r_lo) * K;      // up rows follow the N gate rows
     const __nv_bfloat16* u_hi = w + (size_t)(N + r_hi) * K;
     // The loop bounds are the same for every lane of a warp (the MMA needs all 32 lanes); a lane whose 8 values
-    // lie past K loads zeros. UNROLL chunks are fetched before any is used, so that each warp keeps enough
-    // 16-byte loads in flight to cover the latency of HBM.
+    // lie past K loads zeros. UNROLL chunks of W are fetched before any is used, so that each warp keeps enough
+    // 16-byte loads in flight to cover the latency of HBM; the first fetch is issued before the kernel waits
+    // for its predecessor, since W does not depend on it.
     constexpr int UNROLL = MT <= 2 ? 4 : 2;
-    for (int kc0 = warp * 32; kc0 < K; kc0 += UNROLL * WARPS * 32) {
-        uint4 a_lo[UNROLL], a_hi[UNROLL], g_lo[GLU ? UNROLL : 1], g_hi[GLU ? UNROLL : 1], b[UNROLL][MT];
+    uint4 a_lo[UNROLL], a_hi[UNROLL], g_lo[GLU ? UNROLL : 1], g_hi[GLU ? UNROLL : 1];
+    auto fetch = [&](int kc0) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int k = kc0 + u * WARPS * 32 + 8 * t;
@@ -64,10 +66,21 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
             a_lo[u] = ld16(w_lo + k, lo_ok && k_ok);
             a_hi[u] = ld16(w_hi + k, hi_ok && k_ok);
             if (GLU) { g_lo[u] = ld16(u_lo + k, lo_ok && k_ok); g_hi[u] = ld16(u_hi + k, hi_ok && k_ok); }
+        }
+    };
+    bl_pdl_trigger();
+    fetch(warp * 32);
+    bl_pdl_wait();
+    for (int kc0 = warp * 32; kc0 < K; kc0 += UNROLL * WARPS * 32) {
+        uint4 b[UNROLL][MT];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = kc0 + u * WARPS * 32 + 8 * t;
 #pragma unroll
             for (int j = 0; j < MT; ++j) {
                 const int tok = m0 + 8 * j + g;
-                b[u][j] = ld16(x + (size_t)tok * K + k, tok < M && k_ok);
+                b[u][j] = (tok < M && k < K) ? *reinterpret_cast<const uint4*>(x + (size_t)tok * K + k)
+                                             : make_uint4(0u, 0u, 0u, 0u);
             }
         }
 #pragma unroll
@@ -82,6 +95,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                 }
             }
         }
+        const int next = kc0 + UNROLL * WARPS * 32;
+        if (next < K) fetch(next);
     }
     // c0, c1: (column g, tokens 2t, 2t+1); c2, c3: (column g + 8, tokens 2t, 2t+1)
 #pragma unroll
@@ -114,8 +129,8 @@ int launch(const void* x, const void* w, const void* bias, int bias_dtype, void*
            int epi, cudaStream_t s) {
     const int m_groups = (M + MT * 8 - 1) / (MT * 8);
     const int blocks = ((N + COLS - 1) / COLS) * m_groups;
-#define BL_GO(E) gemm_skinny_kernel<MT, E, TO><<<blocks, WARPS * 32, 0, s>>>((const __nv_bfloat16*)x, \
-        (const __nv_bfloat16*)w, bias, bias_dtype, (TO*)out, M, N, K, m_groups)
+#define BL_GO(E) BL_CUDA(bl_launch_dependent(gemm_skinny_kernel<MT, E, TO>, dim3(blocks), dim3(WARPS * 32), 0, s, \
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, bias_dtype, (TO*)out, M, N, K, m_groups))
     switch (epi) {
         case BL_EPI_NONE: BL_GO(BL_EPI_NONE); break;
         case BL_EPI_BIAS: BL_GO(BL_EPI_BIAS); break;

@@ -149,7 +149,7 @@ __device__ Cut select_prefix(const RowCtx& c, int mode, unsigned long long targe
 }
 
 __global__ void __launch_bounds__(THREADS)
-sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
+sample_kernel(const float* logits /* written by the kernel before */, int vocab, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
               const float* __restrict__ uniform, int* __restrict__ out_ids) {
     __shared__ unsigned long long hist[256];
@@ -158,6 +158,8 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     __shared__ int sh_cnt[THREADS];
     __shared__ float red_v[THREADS / 32];
     __shared__ int red_i[THREADS / 32];
+    bl_pdl_trigger();
+    bl_pdl_wait();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * vocab;
     // the first maximum (lowest id among equals): the greedy token and the softmax's reference point
@@ -234,8 +236,8 @@ extern "C" int bl_sample(const float* logits, int rows, int vocab, const float* 
                          void* stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) BL_FAIL("bl_sample: bad vocabulary %d", vocab);
-    sample_kernel<<<rows, THREADS, 0, (cudaStream_t)stream>>>(logits, vocab, temperature, top_k, top_p, min_p,
-                                                              uniform, out_ids);
+    BL_CUDA(bl_launch_dependent(sample_kernel, dim3(rows), dim3(THREADS), 0, (cudaStream_t)stream, logits, vocab,
+                                temperature, top_k, top_p, min_p, uniform, out_ids));
     BL_CHECK_LAUNCH("bl_sample");
     return 0;
 }

@@ -14,7 +14,7 @@ from .linear import linear, EPI_BIAS, EPI_NONE, EPI_RESIDUAL
 from .norm import RMSNorm
 from .rotary import RotaryTable
 
-FUSED_MAX_ROWS = 64       # steps with at most this many rows take the fused norm + product kernels
+FUSED_MAX_ROWS = 32       # steps with at most this many rows take the fused norm + product kernels
 
 
 DECODE_TARGET_BLOCKS = 2 * 148     # blocks wanted in flight when one query's keys are cut into slices
@@ -139,6 +139,6 @@ class GQAAttention(Mixer):
             n = ctx.decode_reqs.shape[0]
             groups = self.KV * (-(-(self.H // self.KV) // 16))
             longest = ctx.max_decode_ctx if self.window <= 0 else min(ctx.max_decode_ctx, self.window + 64)
-            n_splits = max(1, min(-(-longest // 64), -(-DECODE_TARGET_BLOCKS // (n * groups))))
+            n_splits = max(1, min(-(-longest // 64), -(-DECODE_TARGET_BLOCKS // (n * groups)), 256))
             ops.attention_decode(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.decode_reqs, n_splits, out,
                                  self.H, self.window, self.scale)

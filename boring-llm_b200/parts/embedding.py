@@ -11,6 +11,9 @@ from .base import Part, to_device_matrix
 from .linear import linear, EPI_NONE
 
 
+FUSED_MAX_COLUMNS = 16384
+
+
 class Embedding(Part):
     """x[t] = table[token[t]] (src/model.br:1286-1295; the reference's embedding scale is 1 here),
     widened to the 32-bit residual stream."""
@@ -55,7 +58,10 @@ class OutputHead(Part):
         """Final norm and output product in one kernel for few rows; None when that is not possible."""
         from .attention import FUSED_MAX_ROWS
         from .norm import RMSNorm
+        # every block of the fused kernel normalises the rows again: worth it for a few hundred blocks, not for
+        # the thousands that a large vocabulary makes
         if not (ctx.fast and ctx.dtype == torch.bfloat16 and row_idx.shape[0] <= FUSED_MAX_ROWS
+                and self.vocab <= FUSED_MAX_COLUMNS
                 and isinstance(norm, RMSNorm) and ops.norm_gemm_supported(x, self.matrix())):
             return None
         logits = ctx.empty((row_idx.shape[0], self.vocab), torch.float32)
