@@ -259,8 +259,22 @@ def main():
     weight_bytes, kv_tok, prefill_flops = model_figures(args.layers)
     if args.only == "decode":
         tps, ms_step, launches = decode_device_timed(eng, args.batch, args.steps, warmup)
-        print(json.dumps({"only": "decode", "batch": args.batch, "tokens_per_s": round(tps, 1), "ms_per_step": round(ms_step, 4),
-                          "launches": launches, "layers": args.layers}))
+        out = {"only": "decode", "batch": args.batch, "tokens_per_s": round(tps, 1), "ms_per_step": round(ms_step, 4),
+               "launches": launches, "layers": args.layers}
+        rows = 1
+        while rows < args.batch:
+            rows *= 2
+        gr = eng.runner._graphs.get(rows)
+        if gr is not None:          # the captured step alone, replayed back to back: the GPU's share of a step
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(20):
+                gr.graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            out["graph_replay_ms"] = round(e0.elapsed_time(e1) / 20, 4)
+        print(json.dumps(out))
         return 0
     if args.only == "prefill":
         pre_ms = prefill_timed(eng, reps=1)

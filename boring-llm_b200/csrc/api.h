@@ -65,12 +65,13 @@ int bl_attention_mma_supported(int dh, int page_size);
 int bl_attention_prefill(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
                          const int* ctx_len, const int* block_table, int max_pages, const int* tiles, int n_tiles,
                          void* out, int H, int KV, int dh, int page_size, int window, float scale, void* stream);
-// Decode shape: reqs[n] = requests with one new token; their keys are cut into n_splits slices that a second
-// kernel merges. scratch: bl_attention_decode_scratch_floats(n, H, dh, n_splits) floats (none for one slice).
+// Decode shape: reqs[n] = requests with one new token; their keys are cut into n_splits slices (up to 256) that
+// the last block to finish merges. scratch: bl_attention_decode_scratch_floats(n, H, dh, n_splits) floats (none for one slice).
 long long bl_attention_decode_scratch_floats(int n, int H, int dh, int n_splits);
+// counters: n * KV * ceil((H / KV) / 16) ints that are zero at the call and zero again when it is done.
 int bl_attention_decode(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
                         const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
-                        int n_splits, float* scratch, void* out, int H, int KV, int dh, int page_size,
+                        int n_splits, float* scratch, int* counters, void* out, int H, int KV, int dh, int page_size,
                         int window, float scale, void* stream);
 
 // Matrix product for many rows (prefill) on tcgen05 tensor cores with TMA-fed shared-memory tiles and the
@@ -94,6 +95,9 @@ int bl_norm_qkv_rope(const float* x, const void* norm_w, int norm_w_dtype, float
 
 // Programmatic dependent launch for the small kernels of a step (on by default): 0 launches them the ordinary way.
 void bl_set_dependent_launch(int on);
+
+// Writes the GPU's nanosecond timer to buf[slot] once everything before it on the stream has finished.
+int bl_stamp(unsigned long long* buf, int slot, void* stream);
 
 #ifdef __cplusplus
 }

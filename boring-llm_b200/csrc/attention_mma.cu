@@ -28,6 +28,7 @@ struct AttnParams {
     const int* cu_q; const int* ctx_len; const int* block_table; int max_pages;
     const int* work;              // prefill: [n][2] (request, first token of the tile within the request); decode: [n] requests
     float* part_o; float* part_ml; int n_splits;
+    int* counters;                // decode with slices: one per (request, head group), zero between launches
     int H, KV, window; float scale_log2;
 };
 
@@ -224,6 +225,21 @@ attention_mma_kernel(const AttnParams p) {
         b_end = min(b_end, s0 + per);
         b_begin = min(s0, b_end);
     }
+    if (DECODE) {
+        // the cached keys and values of earlier tokens do not depend on the kernel before: start them on their
+        // way into L2 (the newest token's row is written there by that kernel; L2 stays coherent with it)
+        constexpr int LINES = PAGE * DH * 2 / 128 > 0 ? PAGE * DH * 2 / 128 : 1;     // 128-byte lines per (page, head)
+        const int first_page = b_begin * (KB / PAGE), last_page = min(b_end * (KB / PAGE), hi / PAGE + 1);
+        for (int i = threadIdx.x; i < (last_page - first_page) * LINES; i += THREADS) {
+            const int pg = first_page + i / LINES;
+            const int page = pg * PAGE + PAGE - 1 >= lo ? table[pg] : -1;
+            if (page >= 0) {
+                const size_t off = (((size_t)page * p.KV + kvh) * PAGE) * DH * 2 + (size_t)(i % LINES) * 128;
+                bl_prefetch_l2(reinterpret_cast<const char*>(p.kc) + off);
+                bl_prefetch_l2(reinterpret_cast<const char*>(p.vc) + off);
+            }
+        }
+    }
     bl_pdl_wait();                                    // q and the newest keys and values come from the kernel before
     unsigned qf[DH / 16][4];
 #pragma unroll
@@ -317,73 +333,85 @@ attention_mma_kernel(const AttnParams p) {
             if (d == 0) { p.part_ml[slot * 2] = M; p.part_ml[slot * 2 + 1] = L; }
         }
     }
-}
-
-// Merges the slices of one (request, head): out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
-// (FlashDecodeCombineKernel, src/math_gpu.br:3597-3631). One block of 128 threads per (request, head): the
-// slices' maxima and sums are read by as many threads at once, then each thread adds up a quarter of the
-// slices for one or more output dimensions with four loads in flight, and the quarters are added in order.
-__global__ void __launch_bounds__(128)
-attention_merge_kernel(const float* part_o, const float* part_ml /* both written by the kernel before */,
-                       const int* __restrict__ work, const int* __restrict__ cu_q,
-                       __nv_bfloat16* __restrict__ out, int H, int DH, int n_splits) {
-    __shared__ float sf[256];          // weight 2^(m_s - M) of each slice (n_splits <= 256)
-    __shared__ float sacc[4][128];
-    __shared__ float sL;
-    bl_pdl_trigger();
-    const int idx = blockIdx.x, hd = blockIdx.y;
-    const int r = work[idx];
-    bl_pdl_wait();
-    if (cu_q[r + 1] - cu_q[r] <= 0) return;
-    const size_t base = ((size_t)idx * H + hd) * n_splits;
-    float mloc = -INFINITY;
-    for (int s = threadIdx.x; s < n_splits; s += 128) mloc = fmaxf(mloc, part_ml[(base + s) * 2]);
-    mloc = bl_warp_max(mloc);
-    if ((threadIdx.x & 31) == 0) sacc[0][threadIdx.x >> 5] = mloc;
-    __syncthreads();
-    const float M = fmaxf(fmaxf(sacc[0][0], sacc[0][1]), fmaxf(sacc[0][2], sacc[0][3]));
-    __syncthreads();
-    for (int s = threadIdx.x; s < n_splits; s += 128) {
-        const float ms = part_ml[(base + s) * 2];
-        sf[s] = ms == -INFINITY ? 0.f : exp2f(ms - M);
-    }
+    if (p.n_splits == 1 || q_len <= 0) return;
+    // The block that finishes last among the slices of this (request, head group) merges them:
+    // out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M) (FlashDecodeCombineKernel, src/math_gpu.br:3597-3631).
+    // Slices are added in slice order whoever merges, so the result does not depend on which block was last.
+    __shared__ int s_last;
+    __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        float L = 0.f;
-        for (int s = 0; s < n_splits; ++s) L += part_ml[(base + s) * 2 + 1] * sf[s];
-        sL = L;
+        int* counter = p.counters + (size_t)blockIdx.z * gridDim.y + blockIdx.y;
+        const int ticket = atomicAdd(counter, 1);
+        s_last = ticket == p.n_splits - 1;
+        if (s_last) *counter = 0;                                  // ready for the next launch
     }
-    const int quarter = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int per = (n_splits + 3) / 4;
-    const int s0 = quarter * per, s1 = min(n_splits, s0 + per);
-    for (int d0 = 0; d0 < DH; d0 += 32) {
-        const int d = d0 + lane;
-        float acc = 0.f;
-        if (d < DH) {
-            int s = s0;
-            for (; s + 4 <= s1; s += 4) {
-                const float a0 = part_o[(base + s) * DH + d], a1 = part_o[(base + s + 1) * DH + d];
-                const float a2 = part_o[(base + s + 2) * DH + d], a3 = part_o[(base + s + 3) * DH + d];
-                acc += a0 * sf[s]; acc += a1 * sf[s + 1]; acc += a2 * sf[s + 2]; acc += a3 * sf[s + 3];
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float* wts = reinterpret_cast<float*>(smem_raw);               // [rows_here][n_splits] weights 2^(m_s - M), then L per row
+    float* sL = wts + 16 * p.n_splits;
+    for (int row = warp; row < rows_here; row += 4) {
+        const float2* ml = reinterpret_cast<const float2*>(p.part_ml) + ((size_t)blockIdx.z * p.H + head0 + row) * p.n_splits;
+        // every lane's (max, sum) pairs are loaded at once (up to 8 per lane: 256 slices), then used twice
+        float2 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int s2 = lane + 32 * i;
+            v[i] = s2 < p.n_splits ? __ldcg(ml + s2) : make_float2(-INFINITY, 0.f);
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mx = fmaxf(mx, v[i].x);
+        mx = bl_warp_max(mx);
+        float lsum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {                              // lanes in slice order, 32 slices at a time
+            if (32 * i >= p.n_splits) break;
+            const int s2 = lane + 32 * i;
+            const float f = v[i].x == -INFINITY ? 0.f : exp2f(v[i].x - mx);
+            float lv = v[i].y * f;
+            if (s2 < p.n_splits) wts[row * p.n_splits + s2] = f;
+#pragma unroll
+            for (int o2 = 1; o2 < 32; o2 <<= 1) {                  // a prefix sum keeps the order of the additions fixed
+                const float up = __shfl_up_sync(0xffffffffu, lv, o2);
+                if (lane >= o2) lv += up;
             }
-            for (; s < s1; ++s) acc += part_o[(base + s) * DH + d] * sf[s];
+            lsum += __shfl_sync(0xffffffffu, lv, 31);
         }
-        sacc[quarter][lane] = acc;
-        __syncthreads();
-        if (quarter == 0 && d < DH) {
-            const float O = (sacc[0][lane] + sacc[1][lane]) + (sacc[2][lane] + sacc[3][lane]);
-            const float L = sL;
-            out[((size_t)cu_q[r] * H + hd) * DH + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        if (lane == 0) sL[row] = lsum;
+    }
+    __syncthreads();
+    // one thread per (row, four dimensions): sixteen 16-byte loads in flight, slices added in slice order
+    constexpr int D4 = DH / 4;
+    for (int i = threadIdx.x; i < rows_here * D4; i += THREADS) {
+        const int row = i / D4, d = (i % D4) * 4;
+        const float4* po = reinterpret_cast<const float4*>(p.part_o + (((size_t)blockIdx.z * p.H + head0 + row) * p.n_splits) * DH + d);
+        float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < p.n_splits; s0 += 16) {
+            float4 a[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                a[j] = s0 + j < p.n_splits ? __ldcg(po + (size_t)(s0 + j) * D4) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float f = s0 + j < p.n_splits ? wts[row * p.n_splits + s0 + j] : 0.f;
+                O.x += a[j].x * f; O.y += a[j].y * f; O.z += a[j].z * f; O.w += a[j].w * f;
+            }
         }
-        __syncthreads();
+        const float L = sL[row];
+        const float inv = L > 0.f ? 1.0f / L : 0.f;
+        __nv_bfloat16* dst = p.out + ((size_t)q_tok * p.H + head0 + row) * DH + d;
+        *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(O.x * inv, O.y * inv), pack_bf16(O.z * inv, O.w * inv));
     }
 }
 
 template <int DH, bool DECODE>
 int launch(const AttnParams& p, dim3 grid, cudaStream_t s) {
     static bool configured = false;                               // per template instance
-    const int bytes = Tiles<DH>::BYTES > (int)((4 * 16 * DH + 128) * sizeof(float)) ? Tiles<DH>::BYTES
-                                                                                     : (int)((4 * 16 * DH + 128) * sizeof(float));
+    int bytes = Tiles<DH>::BYTES;                                  // the stages; reused by the merges
+    if (bytes < (int)((4 * 16 * DH + 128) * sizeof(float))) bytes = (int)((4 * 16 * DH + 128) * sizeof(float));
+    if (bytes < (int)((16 * 256 + 16) * sizeof(float))) bytes = (int)((16 * 256 + 16) * sizeof(float));
     if (!configured) {
         BL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<DH, DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
         configured = true;
@@ -431,7 +459,7 @@ extern "C" int bl_attention_prefill(const void* q, const void* k_cache, const vo
     AttnParams p;
     p.q = (const __nv_bfloat16*)q; p.kc = (const __nv_bfloat16*)k_cache; p.vc = (const __nv_bfloat16*)v_cache;
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
-    p.work = tiles; p.part_o = nullptr; p.part_ml = nullptr; p.n_splits = 1; p.H = H; p.KV = KV; p.window = window;
+    p.work = tiles; p.part_o = nullptr; p.part_ml = nullptr; p.counters = nullptr; p.n_splits = 1; p.H = H; p.KV = KV; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     return dispatch<false>(dh, p, dim3(n_tiles, H, 1), (cudaStream_t)stream);
 }
@@ -444,25 +472,22 @@ extern "C" long long bl_attention_decode_scratch_floats(int n, int H, int dh, in
 // Decode shape. reqs: [n] indices of single-token requests. scratch: bl_attention_decode_scratch_floats() floats.
 extern "C" int bl_attention_decode(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
                                    const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
-                                   int n_splits, float* scratch, void* out, int H, int KV, int dh, int page_size,
-                                   int window, float scale, void* stream) {
+                                   int n_splits, float* scratch, int* counters, void* out, int H, int KV, int dh,
+                                   int page_size, int window, float scale, void* stream) {
     if (n <= 0) return 0;
     if (check(H, KV, dh, page_size, max_pages, window)) return 1;
     if (n_splits < 1 || n_splits > 256) BL_FAIL("bl_attention_decode: %d slices (1..256)", n_splits);
-    if (n_splits > 1 && scratch == nullptr) BL_FAIL("bl_attention_decode: slices need scratch memory");
+    if (n_splits > 1 && (scratch == nullptr || counters == nullptr))
+        BL_FAIL("bl_attention_decode: slices need scratch memory and zeroed counters");
     AttnParams p;
     p.q = (const __nv_bfloat16*)q; p.kc = (const __nv_bfloat16*)k_cache; p.vc = (const __nv_bfloat16*)v_cache;
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
     p.work = reqs; p.n_splits = n_splits; p.H = H; p.KV = KV; p.window = window;
     p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)n * H * n_splits * dh : nullptr;
+    p.counters = counters;
     p.scale_log2 = scale * 1.4426950408889634f;
     const int G = H / KV;
-    if (dispatch<true>(dh, p, dim3(n_splits, KV * ((G + 15) / 16), n), (cudaStream_t)stream)) return 1;
-    if (n_splits > 1) {
-        BL_CUDA(bl_launch_dependent(attention_merge_kernel, dim3(n, H), dim3(128), 0, (cudaStream_t)stream,
-                                    (const float*)p.part_o, (const float*)p.part_ml, reqs, cu_q, p.out, H, dh, n_splits));
-    }
-    return 0;
+    return dispatch<true>(dh, p, dim3(n_splits, KV * ((G + 15) / 16), n), (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -476,8 +501,13 @@ namespace {
 // library's image on every GPU that loads it (8 MiB each, until the process exits).
 static __device__ __align__(256) float g_static_scratch[BL_NO_ALLOC_SCRATCH_FLOATS];
 
+// One counter per (request, head group) for the merge; zero when the library is loaded, and every launch leaves
+// them at zero again.
+static __device__ __align__(256) int g_static_counters[BL_NO_ALLOC_COUNTERS];
+
 constexpr int MAX_DEVICES = 64;
 float* g_static_scratch_ptr[MAX_DEVICES] = {};   // device address of the array, per device, looked up once
+int* g_static_counters_ptr[MAX_DEVICES] = {};
 
 }  // namespace
 
@@ -502,9 +532,17 @@ extern "C" int bl_attention_decode_no_alloc(const void* q, const void* k_cache, 
         float* p = nullptr;
         BL_CUDA(cudaGetSymbolAddress((void**)&p, g_static_scratch));
         if (p == nullptr) BL_FAIL("bl_attention_decode_no_alloc: the scratch array has no address on device %d", dev);
+        int* c = nullptr;
+        BL_CUDA(cudaGetSymbolAddress((void**)&c, g_static_counters));
+        if (c == nullptr) BL_FAIL("bl_attention_decode_no_alloc: the counter array has no address on device %d", dev);
         g_static_scratch_ptr[dev] = p;
+        g_static_counters_ptr[dev] = c;
     }
+    if (n_splits > 1 && (long long)n * KV * ((H / KV + 15) / 16) > (long long)BL_NO_ALLOC_COUNTERS)
+        BL_FAIL("bl_attention_decode_no_alloc: %d requests x %d head groups need more than the %d built-in counters",
+                n, KV * ((H / KV + 15) / 16), BL_NO_ALLOC_COUNTERS);
     return bl_attention_decode(q, k_cache, v_cache, cu_q, ctx_len, block_table, max_pages, reqs, n, n_splits,
-                               n_splits > 1 ? g_static_scratch_ptr[dev] : nullptr, out, H, KV, dh, page_size, window,
+                               n_splits > 1 ? g_static_scratch_ptr[dev] : nullptr,
+                               n_splits > 1 ? g_static_counters_ptr[dev] : nullptr, out, H, KV, dh, page_size, window,
                                scale, stream);
 }

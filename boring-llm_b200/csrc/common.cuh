@@ -57,11 +57,45 @@ __device__ __forceinline__ float bl_silu(float x) { return x / (1.0f + expf(-x))
 __device__ __forceinline__ void bl_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void bl_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Asks for the 128-byte line at `p` to be brought into L2 (no register, no wait).
+__device__ __forceinline__ void bl_prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" :: "l"(p)); }
+
+// Brings rows [row0, row0 + n_rows) of a row-major matrix with `row_bytes` per row into L2, spread over the
+// block's threads. Used before bl_pdl_wait() so that a kernel's weights stream from HBM while its
+// predecessor is still running.
+__device__ __forceinline__ void bl_prefetch_rows_l2(const void* base, size_t row0, int n_rows, size_t row_bytes,
+                                                    size_t rows_total) {
+    const int lines_per_row = (int)((row_bytes + 127) / 128);
+    for (int i = threadIdx.x; i < n_rows * lines_per_row; i += blockDim.x) {
+        const size_t r = row0 + i / lines_per_row;
+        if (r < rows_total)
+            bl_prefetch_l2(reinterpret_cast<const char*>(base) + r * row_bytes + (size_t)(i % lines_per_row) * 128);
+    }
+}
+
 bool bl_pdl_enabled();
+
+// The small kernels of a step all ask for the same split of an SM's memory between shared memory and L1.
+// Kernels that want different splits cannot share an SM, so a chain of them would drain the SMs at every
+// boundary and could never overlap under programmatic dependent launch. Set once per kernel.
+template <typename... KArgs>
+cudaError_t bl_same_carveout(void (*kernel)(KArgs...)) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+}
 
 template <typename... KArgs, typename... Args>
 cudaError_t bl_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                 Args... args) {
+    // one look-up per launch in a small table of kernels that already carry the carveout preference
+    static thread_local const void* seen[64];
+    static thread_local int n_seen = 0;
+    bool known = false;
+    for (int i = 0; i < n_seen; ++i) if (seen[i] == (const void*)kernel) { known = true; break; }
+    if (!known) {
+        cudaError_t e = bl_same_carveout(kernel);
+        if (e != cudaSuccess) return e;
+        if (n_seen < 64) seen[n_seen++] = (const void*)kernel;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
     cudaLaunchAttribute attr;

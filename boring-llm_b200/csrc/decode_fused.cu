@@ -44,15 +44,16 @@ __device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p, bool ok) {
 }
 
 template <int MT, int MODE>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, MT == 1 ? 3 : 1)
 fused_norm_gemm_kernel(const FusedParams p) {
     constexpr bool GLU = MODE == MODE_SWIGLU;
     constexpr int TOK = MT * 8;
-    constexpr int UNROLL = MT <= 2 ? 4 : 2;
+    constexpr int UNROLL = (GLU || MT > 2) ? 2 : 4;    // fewer registers where two matrices stream: three blocks fit an SM
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int K = p.K, XROW = K + 8;
     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                       // [TOK][K + 8]
     float* red = reinterpret_cast<float*>(smem_raw + (((size_t)TOK * XROW * 2 + 15) & ~(size_t)15));   // [GLU?2:1][WARPS][16][TOK + 1]
+    float* nws = red + (size_t)(GLU ? 2 : 1) * WARPS * 16 * (TOK + 1);                    // [K] norm weights, 32-bit
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int tile = blockIdx.x / p.m_groups;
     const int m0 = (blockIdx.x % p.m_groups) * TOK;
@@ -87,8 +88,36 @@ fused_norm_gemm_kernel(const FusedParams p) {
     };
     bl_pdl_trigger();
     fetch(warp * 32);                                  // W is on its way while the kernel before this one finishes
+    {
+        const size_t rows_total = MODE == MODE_SWIGLU ? (size_t)2 * p.N : (size_t)n_rows;
+        const size_t first = MODE == MODE_QKV ? (size_t)hh * p.dh + jt * 8 : (size_t)tile * 16;
+        const int span = MODE == MODE_QKV ? 8 : 16;
+        bl_prefetch_rows_l2(p.w, first, span, (size_t)K * 2, rows_total);
+        if (MODE == MODE_QKV) bl_prefetch_rows_l2(p.w, first + p.dh / 2, 8, (size_t)K * 2, rows_total);
+        if (MODE == MODE_SWIGLU) bl_prefetch_rows_l2(p.w, (size_t)p.N + first, 16, (size_t)K * 2, rows_total);
+    }
+    // everything that no earlier kernel of the step writes is fetched before the wait: the norm's weights, and for
+    // the q/k/v epilogue each thread's bias pair, position, page and rotation
+    for (int k = threadIdx.x; k < K; k += WARPS * 32) nws[k] = bl_load_any(p.norm_w, p.norm_w_dtype, k);
+    float e_b0 = 0.f, e_b1 = 0.f, e_cs = 1.f, e_sn = 0.f;
+    int e_pos = 0, e_page = -1;
+    if (MODE == MODE_QKV && threadIdx.x < 8 * TOK) {
+        const int c = threadIdx.x % 8, m = m0 + threadIdx.x / 8;
+        if (m < p.M) {
+            const int row_lo = hh * p.dh + jt * 8 + c;
+            if (p.bias) { e_b0 = bl_load_any(p.bias, p.bias_dtype, row_lo); e_b1 = bl_load_any(p.bias, p.bias_dtype, row_lo + p.dh / 2); }
+            e_pos = p.positions[m];
+            if (hh < p.H + p.KV) {
+                const float angle = (float)e_pos * p.inv_freq[jt * 8 + c];
+                e_cs = cosf(angle) * p.mscale; e_sn = sinf(angle) * p.mscale;
+            }
+            if (hh >= p.H && p.k_cache != nullptr)
+                e_page = p.block_table[(size_t)p.tok_req[m] * p.max_pages + e_pos / p.page_size];
+        }
+    }
     bl_pdl_wait();                                     // from here on the residual stream may be read
 
+    __syncthreads();                                   // the norm weights are in shared memory
     // normalise this block's rows into shared memory: warp w takes rows w, w + 8, ...
     for (int i = warp; i < TOK; i += WARPS) {
         const int m = m0 + i;
@@ -107,10 +136,9 @@ fused_norm_gemm_kernel(const FusedParams p) {
         const float inv = 1.0f / sqrtf(ss / (float)K + p.eps);
         for (int k = lane * 4; k < K; k += 128) {
             const float4 v = *reinterpret_cast<const float4*>(src + k);
-            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * inv * bl_load_any(p.norm_w, p.norm_w_dtype, k),
-                                                      v.y * inv * bl_load_any(p.norm_w, p.norm_w_dtype, k + 1));
-            __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * inv * bl_load_any(p.norm_w, p.norm_w_dtype, k + 2),
-                                                      v.w * inv * bl_load_any(p.norm_w, p.norm_w_dtype, k + 3));
+            const float4 nw = *reinterpret_cast<const float4*>(nws + k);
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * inv * nw.x, v.y * inv * nw.y);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * inv * nw.z, v.w * inv * nw.w);
             uint2 pk;
             pk.x = *reinterpret_cast<unsigned*>(&lo); pk.y = *reinterpret_cast<unsigned*>(&hi);
             *reinterpret_cast<uint2*>(dst + k) = pk;
@@ -168,34 +196,24 @@ fused_norm_gemm_kernel(const FusedParams p) {
         return v;
     };
     if (MODE == MODE_QKV) {
-        // one thread per (dimension pair c, token): both halves of the pair
+        // one thread per (dimension pair c, token): both halves of the pair; its constants are in registers
         const int half = p.dh / 2;
-        for (int i = threadIdx.x; i < 8 * TOK; i += WARPS * 32) {
-            const int c = i % 8, tok = i / 8, m = m0 + tok;
-            if (m >= p.M) continue;
-            const int row_lo = hh * p.dh + jt * 8 + c, row_hi = row_lo + half;
-            float v0 = total(0, c, tok), v1 = total(0, c + 8, tok);
-            if (p.bias) { v0 += bl_load_any(p.bias, p.bias_dtype, row_lo); v1 += bl_load_any(p.bias, p.bias_dtype, row_hi); }
-            const int pos = p.positions[m];
-            const int d0 = jt * 8 + c, d1 = d0 + half;
-            float y0 = v0, y1 = v1;
-            if (hh < p.H + p.KV) {
-                const float angle = (float)pos * p.inv_freq[d0];
-                const float cs = cosf(angle) * p.mscale, sn = sinf(angle) * p.mscale;
-                y0 = v0 * cs - v1 * sn;
-                y1 = v0 * sn + v1 * cs;
-            }
-            if (hh < p.H) {
-                __nv_bfloat16* q = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)m * p.H + hh) * p.dh;
-                q[d0] = __float2bfloat16_rn(y0); q[d1] = __float2bfloat16_rn(y1);
-            } else if (p.k_cache != nullptr) {
-                const int page = p.block_table[(size_t)p.tok_req[m] * p.max_pages + pos / p.page_size];
-                if (page < 0) continue;                      // never scheduled; keep memory safe anyway
-                const bool is_k = hh < p.H + p.KV;
-                const int kvh = is_k ? hh - p.H : hh - p.H - p.KV;
-                __nv_bfloat16* dst = (is_k ? p.k_cache : p.v_cache) +
-                    (((size_t)page * p.KV + kvh) * p.page_size + pos % p.page_size) * p.dh;
-                dst[d0] = __float2bfloat16_rn(y0); dst[d1] = __float2bfloat16_rn(y1);
+        if (threadIdx.x < 8 * TOK) {
+            const int c = threadIdx.x % 8, tok = threadIdx.x / 8, m = m0 + tok;
+            if (m < p.M) {
+                const float v0 = total(0, c, tok) + e_b0, v1 = total(0, c + 8, tok) + e_b1;
+                const int d0 = jt * 8 + c, d1 = d0 + half;
+                const float y0 = v0 * e_cs - v1 * e_sn, y1 = v0 * e_sn + v1 * e_cs;     // cos 1, sin 0 for value heads
+                if (hh < p.H) {
+                    __nv_bfloat16* q = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)m * p.H + hh) * p.dh;
+                    q[d0] = __float2bfloat16_rn(y0); q[d1] = __float2bfloat16_rn(y1);
+                } else if (e_page >= 0) {                     // a page < 0 is never scheduled; keep memory safe anyway
+                    const bool is_k = hh < p.H + p.KV;
+                    const int kvh = is_k ? hh - p.H : hh - p.H - p.KV;
+                    __nv_bfloat16* dst = (is_k ? p.k_cache : p.v_cache) +
+                        (((size_t)e_page * p.KV + kvh) * p.page_size + e_pos % p.page_size) * p.dh;
+                    dst[d0] = __float2bfloat16_rn(y0); dst[d1] = __float2bfloat16_rn(y1);
+                }
             }
         }
     } else {
@@ -218,7 +236,7 @@ fused_norm_gemm_kernel(const FusedParams p) {
 size_t smem_bytes(int mt, int K, bool glu) {
     const size_t tok = (size_t)mt * 8;
     const size_t xs = (tok * (K + 8) * 2 + 15) & ~(size_t)15;
-    return xs + (glu ? 2 : 1) * (size_t)WARPS * 16 * (tok + 1) * sizeof(float);
+    return xs + (glu ? 2 : 1) * (size_t)WARPS * 16 * (tok + 1) * sizeof(float) + (size_t)K * sizeof(float);
 }
 constexpr size_t SMEM_LIMIT = 200 * 1024;
 

@@ -216,3 +216,21 @@ extern "C" int bl_argmax(const float* logits, int* out_ids, int rows, int vocab,
     BL_CHECK_LAUNCH("bl_argmax");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// A time stamp between two kernels of a stream (or of a captured graph): one thread writes the GPU's
+// nanosecond timer. Launched the ordinary way, so it starts when everything before it has finished; the
+// differences between successive stamps are the durations of the kernels in between, in place, with the
+// memory state that the real step leaves. Role: the reference's marginal-cost decode profiler
+// (tools/profile_decode_marginal.py, src/model.br:1697-1701), which also measures stages inside the running step.
+__global__ void stamp_kernel(unsigned long long* buf, int slot) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    buf[slot] = t;
+}
+
+extern "C" int bl_stamp(unsigned long long* buf, int slot, void* stream) {
+    stamp_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(buf, slot);
+    BL_CHECK_LAUNCH("bl_stamp");
+    return 0;
+}

@@ -28,19 +28,20 @@ __device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p, bool ok) {
     return ok ? __ldg(reinterpret_cast<const uint4*>(p)) : make_uint4(0u, 0u, 0u, 0u);
 }
 
-// MT: groups of 8 tokens handled by one block (M tile = 8 * MT).
-template <int MT, int EPI, typename TO>
-__global__ void __launch_bounds__(WARPS * 32)
+// MT: groups of 8 tokens handled by one block (M tile = 8 * MT). NW: warps per block (8, or 16 for long K).
+template <int MT, int EPI, typename TO, int NW>
+__global__ void __launch_bounds__(NW * 32)
 gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no read-only cache */,
                    const __nv_bfloat16* __restrict__ w,
-                   const void* __restrict__ bias, int bias_dtype, TO* __restrict__ out,
+                   const void* __restrict__ bias, int bias_dtype, TO* out,
                    int M, int N, int K, int m_groups) {
     constexpr bool GLU = EPI == BL_EPI_SWIGLU;
-    __shared__ float red[GLU ? 2 : 1][WARPS][COLS][MT * 8 + 1];
+    constexpr int TOK = MT * 8;
+    __shared__ float red[GLU ? 2 : 1][NW][COLS][TOK + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = (blockIdx.x / m_groups) * COLS;
-    const int m0 = (blockIdx.x % m_groups) * (MT * 8);
+    const int m0 = (blockIdx.x % m_groups) * TOK;
     float acc[MT][4], acu[GLU ? MT : 1][4];
 #pragma unroll
     for (int j = 0; j < MT; ++j)
@@ -53,50 +54,71 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
     const __nv_bfloat16* u_lo = w + (size_t)(N + r_lo) * K;      // up rows follow the N gate rows
     const __nv_bfloat16* u_hi = w + (size_t)(N + r_hi) * K;
     // The loop bounds are the same for every lane of a warp (the MMA needs all 32 lanes); a lane whose 8 values
-    // lie past K loads zeros. UNROLL chunks of W are fetched before any is used, so that each warp keeps enough
-    // 16-byte loads in flight to cover the latency of HBM; the first fetch is issued before the kernel waits
-    // for its predecessor, since W does not depend on it.
-    constexpr int UNROLL = MT <= 2 ? 4 : 2;
-    uint4 a_lo[UNROLL], a_hi[UNROLL], g_lo[GLU ? UNROLL : 1], g_hi[GLU ? UNROLL : 1];
-    auto fetch = [&](int kc0) {
+    // lie past K loads zeros. Loads go out in batches of UNROLL chunks, and the next batch is on its way while
+    // the current one is multiplied: a trip to L2 costs far more than the arithmetic of a batch. The first
+    // batch of W, and the whole slice of W as an L2 prefetch, are issued before the kernel waits for its
+    // predecessor, since W does not depend on it.
+    constexpr int UNROLL = (GLU || MT > 2 || NW > 8) ? 2 : 4;
+    constexpr int STEP = UNROLL * NW * 32;
+    struct Batch { uint4 a_lo[UNROLL], a_hi[UNROLL], g_lo[GLU ? UNROLL : 1], g_hi[GLU ? UNROLL : 1], b[UNROLL][MT]; };
+    auto fetch_w = [&](Batch& bt, int kc0) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int k = kc0 + u * WARPS * 32 + 8 * t;
+            const int k = kc0 + u * NW * 32 + 8 * t;
             const bool k_ok = k < K;
-            a_lo[u] = ld16(w_lo + k, lo_ok && k_ok);
-            a_hi[u] = ld16(w_hi + k, hi_ok && k_ok);
-            if (GLU) { g_lo[u] = ld16(u_lo + k, lo_ok && k_ok); g_hi[u] = ld16(u_hi + k, hi_ok && k_ok); }
+            bt.a_lo[u] = ld16(w_lo + k, lo_ok && k_ok);
+            bt.a_hi[u] = ld16(w_hi + k, hi_ok && k_ok);
+            if (GLU) { bt.g_lo[u] = ld16(u_lo + k, lo_ok && k_ok); bt.g_hi[u] = ld16(u_hi + k, hi_ok && k_ok); }
         }
     };
-    bl_pdl_trigger();
-    fetch(warp * 32);
-    bl_pdl_wait();
-    for (int kc0 = warp * 32; kc0 < K; kc0 += UNROLL * WARPS * 32) {
-        uint4 b[UNROLL][MT];
+    auto fetch_x = [&](Batch& bt, int kc0) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int k = kc0 + u * WARPS * 32 + 8 * t;
+            const int k = kc0 + u * NW * 32 + 8 * t;
 #pragma unroll
             for (int j = 0; j < MT; ++j) {
                 const int tok = m0 + 8 * j + g;
-                b[u][j] = (tok < M && k < K) ? *reinterpret_cast<const uint4*>(x + (size_t)tok * K + k)
-                                             : make_uint4(0u, 0u, 0u, 0u);
+                bt.b[u][j] = (tok < M && k < K) ? *reinterpret_cast<const uint4*>(x + (size_t)tok * K + k)
+                                                : make_uint4(0u, 0u, 0u, 0u);
             }
         }
+    };
+    auto multiply = [&](const Batch& bt) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
 #pragma unroll
             for (int j = 0; j < MT; ++j) {
-                mma_bf16(acc[j], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b[u][j].x, b[u][j].y);
-                mma_bf16(acc[j], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b[u][j].z, b[u][j].w);
+                mma_bf16(acc[j], bt.a_lo[u].x, bt.a_hi[u].x, bt.a_lo[u].y, bt.a_hi[u].y, bt.b[u][j].x, bt.b[u][j].y);
+                mma_bf16(acc[j], bt.a_lo[u].z, bt.a_hi[u].z, bt.a_lo[u].w, bt.a_hi[u].w, bt.b[u][j].z, bt.b[u][j].w);
                 if (GLU) {
-                    mma_bf16(acu[j], g_lo[u].x, g_hi[u].x, g_lo[u].y, g_hi[u].y, b[u][j].x, b[u][j].y);
-                    mma_bf16(acu[j], g_lo[u].z, g_hi[u].z, g_lo[u].w, g_hi[u].w, b[u][j].z, b[u][j].w);
+                    mma_bf16(acu[j], bt.g_lo[u].x, bt.g_hi[u].x, bt.g_lo[u].y, bt.g_hi[u].y, bt.b[u][j].x, bt.b[u][j].y);
+                    mma_bf16(acu[j], bt.g_lo[u].z, bt.g_hi[u].z, bt.g_lo[u].w, bt.g_hi[u].w, bt.b[u][j].z, bt.b[u][j].w);
                 }
             }
         }
-        const int next = kc0 + UNROLL * WARPS * 32;
-        if (next < K) fetch(next);
+    };
+    Batch b0, b1;
+    bl_pdl_trigger();
+    fetch_w(b0, warp * 32);
+    bl_prefetch_rows_l2(w, n0, COLS, (size_t)K * 2, (size_t)(GLU ? 2 * N : N));
+    if (GLU) bl_prefetch_rows_l2(w, (size_t)N + n0, COLS, (size_t)K * 2, (size_t)2 * N);
+    // this thread's output element and, for the bias epilogue, its bias
+    const int e_c = threadIdx.x % COLS, e_tok = threadIdx.x / COLS;
+    const int e_n = n0 + e_c, e_m = m0 + e_tok;
+    const bool e_ok = threadIdx.x < COLS * TOK && e_n < N && e_m < M;
+    float e_add = 0.f;
+    if (EPI == BL_EPI_BIAS && e_ok) e_add = bl_load_any(bias, bias_dtype, e_n);
+    bl_pdl_wait();
+    if (EPI == BL_EPI_RESIDUAL && e_ok) e_add = bl_load(out + (size_t)e_m * N + e_n);   // on its way during the product
+    fetch_x(b0, warp * 32);
+    // two batches per trip of the loop, so that the buffers keep their names (and their registers)
+    for (int kc0 = warp * 32; kc0 < K; kc0 += 2 * STEP) {
+        const bool more1 = kc0 + STEP < K;
+        if (more1) { fetch_w(b1, kc0 + STEP); fetch_x(b1, kc0 + STEP); }
+        multiply(b0);
+        if (!more1) break;
+        if (kc0 + 2 * STEP < K) { fetch_w(b0, kc0 + 2 * STEP); fetch_x(b0, kc0 + 2 * STEP); }
+        multiply(b1);
     }
     // c0, c1: (column g, tokens 2t, 2t+1); c2, c3: (column g + 8, tokens 2t, 2t+1)
 #pragma unroll
@@ -109,27 +131,27 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < COLS * MT * 8; i += WARPS * 32) {
+    // the first COLS * TOK threads each own one output element (their residual or bias is already in a register)
+    for (int i = threadIdx.x; i < COLS * TOK; i += NW * 32) {
         const int c = i % COLS, tok = i / COLS;
         const int n = n0 + c, m = m0 + tok;
         if (n >= N || m >= M) continue;
         float v = 0.f, u = 0.f;
 #pragma unroll
-        for (int wp = 0; wp < WARPS; ++wp) { v += red[0][wp][c][tok]; if (GLU) u += red[1][wp][c][tok]; }
+        for (int wp = 0; wp < NW; ++wp) { v += red[0][wp][c][tok]; if (GLU) u += red[1][wp][c][tok]; }
         TO* dst = out + (size_t)m * N + n;
-        if (EPI == BL_EPI_BIAS) v += bl_load_any(bias, bias_dtype, n);
-        if (EPI == BL_EPI_RESIDUAL) v += bl_load(dst);
+        if (EPI == BL_EPI_BIAS || EPI == BL_EPI_RESIDUAL) v += (i == threadIdx.x) ? e_add : (EPI == BL_EPI_BIAS ? bl_load_any(bias, bias_dtype, n) : bl_load(dst));
         if (GLU) v = bl_silu(v) * u;
         bl_store(dst, v);
     }
 }
 
-template <int MT, typename TO>
-int launch(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K,
-           int epi, cudaStream_t s) {
+template <int MT, typename TO, int NW>
+int launch_nw(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K,
+              int epi, cudaStream_t s) {
     const int m_groups = (M + MT * 8 - 1) / (MT * 8);
     const int blocks = ((N + COLS - 1) / COLS) * m_groups;
-#define BL_GO(E) BL_CUDA(bl_launch_dependent(gemm_skinny_kernel<MT, E, TO>, dim3(blocks), dim3(WARPS * 32), 0, s, \
+#define BL_GO(E) BL_CUDA(bl_launch_dependent(gemm_skinny_kernel<MT, E, TO, NW>, dim3(blocks), dim3(NW * 32), 0, s, \
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, bias_dtype, (TO*)out, M, N, K, m_groups))
     switch (epi) {
         case BL_EPI_NONE: BL_GO(BL_EPI_NONE); break;
@@ -139,8 +161,15 @@ int launch(const void* x, const void* w, const void* bias, int bias_dtype, void*
         default: BL_FAIL("bl_gemm_skinny: unknown epilogue %d", epi);
     }
 #undef BL_GO
-    BL_CHECK_LAUNCH("bl_gemm_skinny");
     return 0;
+}
+
+// Long rows of W are cut over 16 warps instead of 8: fewer trips to memory one after the other per warp.
+template <int MT, typename TO>
+int launch(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K,
+           int epi, cudaStream_t s) {
+    if (K >= 2048 && MT == 1 && epi != BL_EPI_SWIGLU) return launch_nw<1, TO, 16>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
+    return launch_nw<MT, TO, 8>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
 }
 
 }  // namespace

@@ -16,6 +16,8 @@ extern "C" {
 // Capacity of the built-in scratch array, in floats (8 MiB). A call needs n * H * n_splits * (dh + 2) floats when
 // n_splits > 1 and none for a single slice; e.g. 64 requests x 14 heads x 16 slices x head size 64 = 946,176.
 #define BL_NO_ALLOC_SCRATCH_FLOATS (2 * 1024 * 1024)
+// Counters for merging the slices, one per (request, group of up to 16 query heads that share a key/value head).
+#define BL_NO_ALLOC_COUNTERS 16384
 
 // Same computation, arguments and result as bl_attention_decode (tensor-core attention for requests with one new
 // token each, their keys cut into n_splits slices that a second kernel merges), but without the scratch argument:
@@ -26,9 +28,11 @@ extern "C" {
 //   from bl_last_error() names the sizes); nothing is launched.
 // - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
 //   current) and keeps it; make that first call before any stream capture begins on that device.
-// - All calls on a device share the one array, and it keeps whatever the previous call left there. Nothing in it
-//   has to start at zero: every slot that the merge reads is written by the same call first. Two calls that overlap
-//   on the GPU (different streams, no ordering between them) race on it: order them.
+// - All calls on a device share the one array, and it keeps whatever the previous call left there. The partial
+//   results need no clearing: every slot that the merge reads is written by the same call first. The counters
+//   that tell the last-finishing block of a (request, head group) to merge must be zero when a call starts: they
+//   are zero when the library is loaded, and each call puts them back to zero itself. Two calls that overlap on
+//   the GPU (different streams, no ordering between them) race on both: order them.
 int bl_attention_decode_no_alloc(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
                                  const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
                                  int n_splits, void* out, int H, int KV, int dh, int page_size, int window,

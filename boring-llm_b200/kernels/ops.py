@@ -53,11 +53,48 @@ def _lib():
 launch_count = 0          # kernels launched through this module since import (the benchmark reads it)
 
 
+_trace = None             # a StepTrace while one is recording
+
+
 def _call(fn, *args):
     global launch_count
     launch_count += 1
     if fn(*args) != 0:
         raise KernelError(library.load().bl_last_error().decode())
+    if _trace is not None and fn.__name__ != "bl_stamp":
+        _trace.after(fn.__name__)
+
+
+class StepTrace:
+    """Time line of the kernels launched while it records: a time stamp kernel goes between every two of them
+    (also inside a CUDA graph that is being captured), and `durations()` turns the stamps of the last run or
+    replay into (kernel, microseconds) pairs. Stamps serialise the kernels, so overlap between neighbours
+    (programmatic dependent launch) is not in these figures: they are each kernel's own time in place."""
+
+    def __init__(self, device, capacity: int = 4096):
+        self.buf = torch.zeros(capacity, dtype=torch.int64, device=device)
+        self.names = []
+
+    def __enter__(self):
+        global _trace
+        _trace = self
+        self.names = []
+        _call(_lib().bl_stamp, ctypes.c_void_p(self.buf.data_ptr()), 0, _stream())
+        return self
+
+    def __exit__(self, *exc):
+        global _trace
+        _trace = None
+
+    def after(self, name: str) -> None:
+        self.names.append(name)
+        if len(self.names) < self.buf.numel():
+            library.load().bl_stamp(ctypes.c_void_p(self.buf.data_ptr()), len(self.names), _stream())
+
+    def durations(self):
+        torch.cuda.synchronize()
+        t = self.buf[:len(self.names) + 1].cpu().tolist()
+        return [(n, (t[i + 1] - t[i]) / 1000.0) for i, n in enumerate(self.names)]
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, shape=None):
@@ -224,9 +261,19 @@ def attention_decode(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_sp
         _need(scratch, "scratch", torch.float32)
         if scratch.numel() < need:
             raise KernelError(f"scratch: {scratch.numel()} floats, {need} needed")
+    counters = None
+    if need:
+        n_counters = n * KV * (-(-(H // KV) // 16))
+        counters = _decode_counters.get(q.device)
+        if counters is None or counters.numel() < n_counters:
+            # zero once; every launch leaves them at zero again
+            counters = _decode_counters[q.device] = torch.zeros(max(n_counters, 4096), dtype=torch.int32, device=q.device)
     _call(_lib().bl_attention_decode, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
-          block_table.shape[1], _p(reqs), n, n_splits, _p(scratch if need else None), _p(out), H, KV, dh, page_size,
-          window, ctypes.c_float(scale), _stream())
+          block_table.shape[1], _p(reqs), n, n_splits, _p(scratch if need else None), _p(counters), _p(out), H, KV, dh,
+          page_size, window, ctypes.c_float(scale), _stream())
+
+
+_decode_counters = {}
 
 
 def attention_decode_scratch(n: int, H: int, dh: int, n_splits: int) -> int:

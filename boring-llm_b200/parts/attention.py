@@ -18,6 +18,7 @@ FUSED_MAX_ROWS = 32       # steps with at most this many rows take the fused nor
 
 
 DECODE_TARGET_BLOCKS = 2 * 148     # blocks wanted in flight when one query's keys are cut into slices
+DECODE_MAX_SPLITS = 32               # more slices make the merge longer than they shorten the scan
 
 
 class Mixer(Part):
@@ -139,6 +140,6 @@ class GQAAttention(Mixer):
             n = ctx.decode_reqs.shape[0]
             groups = self.KV * (-(-(self.H // self.KV) // 16))
             longest = ctx.max_decode_ctx if self.window <= 0 else min(ctx.max_decode_ctx, self.window + 64)
-            n_splits = max(1, min(-(-longest // 64), -(-DECODE_TARGET_BLOCKS // (n * groups)), 256))
+            n_splits = max(1, min(-(-longest // 64), -(-DECODE_TARGET_BLOCKS // (n * groups)), DECODE_MAX_SPLITS))
             ops.attention_decode(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.decode_reqs, n_splits, out,
                                  self.H, self.window, self.scale)
