@@ -156,9 +156,7 @@ def decode_device_timed(eng, batch, steps, warmup):
     ctx0 = CONTEXT - (steps + warmup) - 1
     reqs = fill_requests(eng, batch, ctx0, seed=batch)
     toks = [r.output[-1] for r in reqs]
-    out = torch.empty(batch, dtype=torch.int32, device="cuda")
-    temp = torch.zeros(batch, device="cuda"); zi = torch.zeros(batch, dtype=torch.int32, device="cuda")
-    ones = torch.ones(batch, device="cuda")
+    rows = [(r.params, r.rng, r.tokens) for r in reqs]          # greedy
     total_ms, launches = 0.0, 0
     for it in range(warmup + steps):
         entries = [StepEntry(r.request_id, [t], [0]) for r, t in zip(reqs, toks)]
@@ -166,11 +164,9 @@ def decode_device_timed(eng, batch, steps, warmup):
         l0 = ops.launch_count
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        logits = eng.runner.step(entries)
-        ops.sample(logits, temp, zi, ones, temp, temp, out)
+        toks = eng.runner.step_and_sample(entries, rows, eng.sampler)     # copy in, every kernel of the step, sampler
         e1.record()
         torch.cuda.synchronize()
-        toks = out.cpu().tolist()
         if it >= warmup:
             total_ms += e0.elapsed_time(e1)
             launches += ops.launch_count - l0 + eng.runner.last_step_graph_kernels
@@ -188,16 +184,19 @@ def decode_end_to_end(eng, batch, steps, warmup):
         eng.step()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
+    h2d = d2h = 0
     for _ in range(steps):
         eng.step()
+        h2d += eng.runner.last_h2d_bytes
+        d2h += eng.runner.last_d2h_bytes
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     assert all(len(r.output) == 1 + warmup + steps for r in reqs)
     drop_requests(eng, reqs)
-    # per step: 3 ints per token + request metadata + block tables go up, one int32 per request comes back
-    pages = -(-CONTEXT // 16)
-    h2d = 4 * (3 * batch + (batch + 1) + 2 * batch + batch + batch * (-(-pages // 8) * 8)) + 4 * 5 * batch
-    return batch * steps / dt, h2d, 4 * batch
+    # per step, counted by the runner from the tensors it copies: token ids, positions, lengths, slots, sampling
+    # parameters (and block-table rows when a request got a new page) go up from pinned memory, one int32 per
+    # row of the captured batch comes back
+    return batch * steps / dt, h2d // steps, d2h // steps
 
 
 def prefill_timed(eng, reps=3):

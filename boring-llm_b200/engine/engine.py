@@ -67,9 +67,8 @@ class Engine:
         if sched is None:
             return []
         t0 = time.perf_counter()
-        logits = self.runner.step(sched.entries)
         rows = [(r.params, r.rng, r.tokens) for r, s in zip(sched.requests, sched.samples) if s]
-        sampled = self.sampler.sample(logits, rows) if rows else []
+        sampled = self.runner.step_and_sample(sched.entries, rows, self.sampler)
         self.stats_time["engine_steps"] += 1
         self.stats_time["step_seconds"] += time.perf_counter() - t0
         return self.scheduler.apply(sched, sampled)

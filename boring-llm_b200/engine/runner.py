@@ -51,7 +51,9 @@ class _DecodeGraph:
         G = len(runner.cache.paged_groups)
         W = runner._table_width
         B = rows
-        sizes = [("token_ids", B), ("positions", B), ("ctx_len", B), ("slots", B), ("tables", G * B * W),
+        sizes = [("token_ids", B), ("positions", B), ("ctx_len", B), ("slots", B),
+                 ("temperature", B), ("top_k", B), ("top_p", B), ("min_p", B), ("uniform", B),
+                 ("tables", G * B * W),
                  ("tok_req", B), ("cu_q", B + 1), ("logit_rows", B), ("decode_reqs", B)]
         total = sum(n for _, n in sizes)
         self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
@@ -64,8 +66,15 @@ class _DecodeGraph:
             self.h[name] = hn[o:o + n]
             self.d[name] = self.dev[o:o + n]
             o += n
-        self.dynamic_ints = 4 * B + G * B * W          # the leading fields change every step
+        self.dynamic_ints = 9 * B + G * B * W          # the leading fields change every step
+        self.small_ints = 9 * B                        # ... and the tables only when a request gets a new page
         self.h["tables"] = self.h["tables"].reshape(G, B, W)
+        for name in ("temperature", "top_p", "min_p", "uniform"):      # 32-bit floats in the same buffer
+            self.h[name] = self.h[name].view(np.float32)
+            self.d[name] = self.d[name].view(torch.float32)
+        self.h["top_p"][:] = 1.0
+        self.row_owner = [None] * B                    # (request, pages per group) whose table a row holds
+        self.tables_dirty = True
         ar = np.arange(B, dtype=np.int32)
         self.h["tok_req"][:] = ar; self.h["logit_rows"][:] = ar; self.h["decode_reqs"][:] = ar
         self.h["cu_q"][:] = np.arange(B + 1, dtype=np.int32)
@@ -90,10 +99,15 @@ class _DecodeGraph:
         from ..kernels import ops
         before = ops.launch_count
         self.graph = torch.cuda.CUDAGraph()
+        self.sampled = torch.zeros(B, dtype=torch.int32, device=runner.device)
         with torch.cuda.graph(self.graph):
             self.logits = runner.model.forward(self.ctx)
+            # one token per row from the step's own logits: greedy rows (temperature 0) cost one pass
+            ops.sample(self.logits, self.d["temperature"], self.d["top_k"], self.d["top_p"], self.d["min_p"],
+                       self.d["uniform"], self.sampled)
         self.kernels = ops.launch_count - before       # kernels of this library that one replay launches
         self.copied = torch.cuda.Event()
+        self.sampled_host = torch.zeros(B, dtype=torch.int32).pin_memory()
 
     def fill_padding(self, live: int) -> None:
         h = self.h
@@ -101,8 +115,13 @@ class _DecodeGraph:
         h["positions"][live:] = 0
         h["ctx_len"][live:] = 1
         h["slots"][live:] = self.trash_slot
-        h["tables"][:, live:, :] = -1
-        h["tables"][:, live:, 0] = self.trash_page
+        for r in range(live, self.rows):
+            if self.row_owner[r] != "padding":
+                h["tables"][:, r, :] = -1
+                h["tables"][:, r, 0] = self.trash_page
+                self.row_owner[r] = "padding"
+                self.tables_dirty = True
+        h["temperature"][live:] = 0.0
 
 
 class ModelRunner:
@@ -123,6 +142,7 @@ class ModelRunner:
         self.tokens_run = 0
         self.graph_steps = 0
         self.last_step_graph_kernels = 0               # kernels launched by the last step through a graph replay
+        self.last_h2d_bytes = self.last_d2h_bytes = 0  # bytes the last step copied to and from the device
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self._table_width = -(-(-(-options.ctx_size // options.page_size)) // 8) * 8
 
@@ -153,9 +173,11 @@ class ModelRunner:
         self._slot_index = i
         return self._pinned[i]
 
-    def _graphed_decode(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def _graphed_decode(self, entries: Sequence[StepEntry], sampling=None):
         """A step in which every request has exactly one token: replays the captured graph of the next
-        larger row count. Reservation, commit and the returned logits are those of the general path."""
+        larger row count. Reservation, commit and the returned logits are those of the general path.
+        With `sampling` (one (params, generator, history) per entry) the graph's own sampler picks the
+        tokens and they are returned as a list instead of the logits."""
         R = len(entries)
         rows = 1
         while rows < R:
@@ -173,14 +195,31 @@ class ModelRunner:
             h["ctx_len"][r] = rc.num_tokens + 1
             h["slots"][r] = rc.slot
             slot_list.append(rc.slot)
-            for gi, tab in enumerate(rc.tables):
-                row = h["tables"][gi, r]
-                row[:len(tab)] = tab
-                row[len(tab):] = -1
+            owner = (e.request_id, tuple(len(t) for t in rc.tables), tuple(t[0] if t else -1 for t in rc.tables))
+            if gr.row_owner[r] != owner:               # a new request in this row, a new page, or a page a window freed
+                for gi, tab in enumerate(rc.tables):
+                    row = h["tables"][gi, r]
+                    row[:len(tab)] = tab
+                    row[len(tab):] = -1
+                gr.row_owner[r] = owner if not any(g.spec.window > 0 for g in self.cache.paged_groups) else None
+                gr.tables_dirty = True
+            if sampling is not None:
+                prm, rng, _ = sampling[r]
+                h["temperature"][r] = prm.temperature
+                h["top_k"][r] = prm.top_k
+                h["top_p"][r] = prm.top_p
+                h["min_p"][r] = prm.min_p
+                if prm.temperature > 0:
+                    h["uniform"][r] = rng.next_f32()
+            else:
+                h["temperature"][r] = 0.0
         gr.fill_padding(R)
         gr.ctx.slot_list = slot_list + [gr.trash_slot] * (rows - R)
-        gr.dev[:gr.dynamic_ints].copy_(gr.host[:gr.dynamic_ints], non_blocking=True)
+        n_copy = gr.dynamic_ints if gr.tables_dirty else gr.small_ints
+        gr.tables_dirty = False
+        gr.dev[:n_copy].copy_(gr.host[:n_copy], non_blocking=True)
         gr.copied.record()
+        self.last_h2d_bytes, self.last_d2h_bytes = 4 * n_copy, (4 * rows if sampling is not None else 0)
         gr.graph.replay()
         self.last_step_graph_kernels = gr.kernels
         for e in entries:
@@ -188,10 +227,30 @@ class ModelRunner:
         self.steps += 1
         self.graph_steps += 1
         self.tokens_run += R
+        if sampling is not None:
+            gr.sampled_host.copy_(gr.sampled, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            toks = gr.sampled_host.numpy()
+            return [int(toks[r]) for r, e in enumerate(entries) if len(e.want)]
         wanted = [r for r, e in enumerate(entries) if len(e.want)]
         if len(wanted) == R:
             return gr.logits[:R]
         return gr.logits[torch.tensor(wanted, dtype=torch.long, device=self.device)] if wanted else gr.logits[:0]
+
+    def step_and_sample(self, entries: Sequence[StepEntry], rows, sampler) -> List[int]:
+        """A step followed by sampling: `rows` holds one (params, generator, history) per entry that wants
+        logits (each such entry wants exactly its last token). Decode-only steps without a repeat penalty
+        run the sampler inside the captured graph and bring back only the token ids."""
+        if (len(rows) == len(entries) and all(len(e.tokens) == 1 for e in entries) and self._graphs_usable(entries)
+                and all(r[0].repeat_penalty == 1.0 for r in rows)):
+            self._prepare(entries)
+            return self._graphed_decode(entries, rows)
+        logits = self.step(entries)
+        return sampler.sample(logits, rows) if rows else []
+
+    def _graphs_usable(self, entries) -> bool:
+        return (self.options.cuda_graphs and self.fast and self.dtype == torch.bfloat16
+                and getattr(self.model, "graph_safe", False) and len(entries) <= GRAPH_MAX_BATCH)
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs the entries' tokens as one batch; returns float32 logits `[wanted, vocab]` on the
@@ -199,6 +258,13 @@ class ModelRunner:
         are admitted; pages are reserved here, and an `OutOfPages` leaves everything as it was.
         The returned tensor may be a view of a buffer that the next step overwrites: use or copy it
         before stepping again."""
+        self._prepare(entries)
+        if self._graphs_usable(entries) and all(len(e.tokens) == 1 for e in entries):
+            return self._graphed_decode(entries)
+        return self._general_step(entries)
+
+    def _prepare(self, entries: Sequence[StepEntry]) -> None:
+        """Checks the entries, admits new requests and reserves pages for the whole batch or not at all."""
         page = self.options.page_size
         if not entries:
             raise StepError("a step needs at least one entry")
@@ -238,9 +304,8 @@ class ModelRunner:
             ok = self.cache.reserve(e.request_id, len(e.tokens))
             assert ok, "reservation was checked for the whole batch"
 
-        if (self.options.cuda_graphs and self.fast and self.dtype == torch.bfloat16
-                and getattr(self.model, "graph_safe", False) and len(entries) <= GRAPH_MAX_BATCH and all(len(e.tokens) == 1 for e in entries)):
-            return self._graphed_decode(entries)
+    def _general_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Any mix of portions and single tokens: metadata built for this batch, kernels launched one by one."""
         self.last_step_graph_kernels = 0
         R = len(entries)
         T = sum(len(e.tokens) for e in entries)
@@ -292,6 +357,7 @@ class ModelRunner:
         cu_q[R] = T
         dev = torch.empty(n_ints, dtype=torch.int32, device=self.device)
         dev.copy_(host[:n_ints], non_blocking=True)
+        self.last_h2d_bytes, self.last_d2h_bytes = 4 * n_ints, 0
         ev = torch.cuda.Event()
         ev.record()
         self._pinned_events[self._slot_index] = ev
