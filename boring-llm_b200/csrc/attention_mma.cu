@@ -65,24 +65,36 @@ struct Tiles {
     static constexpr int BYTES = 2 * STAGE * (int)sizeof(__nv_bfloat16);
 };
 
-// Copies keys [key0, key0 + 64) of one key/value head into a stage; keys outside [lo, hi] or on a page that the
-// table no longer holds become zeros (they are masked, and zeros keep the value product finite).
+// Copies keys [key0, key0 + 64) of one key/value head into a stage. The 16 keys of a page lie together in global
+// memory, so a page is copied as one contiguous run of 16-byte chunks (only the destination rows are padded).
+// Pages outside [lo, hi] or no longer in the table, and keys past hi on the last page, become zeros: they are
+// masked anyway, and zeros keep the value product finite whatever an old request left in a reused page.
 template <int DH>
 __device__ __forceinline__ void load_block(__nv_bfloat16* stage, const AttnParams& p, const int* table, int kvh,
                                            int key0, int lo, int hi) {
     constexpr int CH = DH / 8;                                    // 16-byte chunks per row
+    constexpr int CPP = PAGE * CH;                                // chunks per page
     constexpr int ROW = Tiles<DH>::ROW;
     __nv_bfloat16* ks = stage;
     __nv_bfloat16* vs = stage + KB * ROW;
-    for (int i = threadIdx.x; i < KB * CH; i += THREADS) {
-        const int r = i / CH, c = i % CH;
-        const int key = key0 + r;
-        int page = -1;
-        if (key >= lo && key <= hi) page = table[key / PAGE];
+    int pages[KB / PAGE];
+#pragma unroll
+    for (int q = 0; q < KB / PAGE; ++q) {
+        const int first = key0 + q * PAGE;
+        pages[q] = (first + PAGE - 1 >= lo && first <= hi) ? table[first / PAGE] : -1;
+    }
+#pragma unroll
+    for (int it = 0; it < (KB * CH + THREADS - 1) / THREADS; ++it) {
+        const int i = threadIdx.x + it * THREADS;
+        if (i >= KB * CH) break;
+        const int pg = i / CPP, j = i % CPP;
+        const int row = j / CH, c = j % CH;
+        const int page = pages[pg];
+        const int r = pg * PAGE + row;
         __nv_bfloat16* kd = ks + r * ROW + c * 8;
         __nv_bfloat16* vd = vs + r * ROW + c * 8;
-        if (page >= 0) {
-            const size_t off = (((size_t)page * p.KV + kvh) * PAGE + (key % PAGE)) * DH + c * 8;
+        if (page >= 0 && key0 + r <= hi) {
+            const size_t off = ((size_t)page * p.KV + kvh) * (PAGE * DH) + j * 8;
             cp_async16(kd, p.kc + off);
             cp_async16(vd, p.vc + off);
         } else {
@@ -118,16 +130,30 @@ __device__ __forceinline__ void block_step(const __nv_bfloat16* stage, int koff,
     }
     // scale, mask, running maximum
     float mx[2] = {-INFINITY, -INFINITY};
+    // most blocks lie wholly inside what both rows may see: no per-key test there
+    const int k_first = key_abs0 + koff, k_last = k_first + NT * 8 - 1;
+    const bool all_seen = k_last <= min(pos[0], pos[1]) && (window <= 0 || k_first + window > max(pos[0], pos[1]));
+    if (all_seen) {
 #pragma unroll
-    for (int n = 0; n < NT; ++n) {
+        for (int n = 0; n < NT; ++n) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const int j = key_abs0 + koff + n * 8 + 2 * t + (c & 1);
-            const int p = pos[c >> 1];
-            const bool seen = j <= p && (window <= 0 || j + window > p);
-            const float v = seen ? s[n][c] * scale_log2 : -INFINITY;
-            s[n][c] = v;
-            mx[c >> 1] = fmaxf(mx[c >> 1], v);
+            for (int c = 0; c < 4; ++c) {
+                s[n][c] *= scale_log2;
+                mx[c >> 1] = fmaxf(mx[c >> 1], s[n][c]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int j = k_first + n * 8 + 2 * t + (c & 1);
+                const int p = pos[c >> 1];
+                const bool seen = j <= p && (window <= 0 || j + window > p);
+                const float v = seen ? s[n][c] * scale_log2 : -INFINITY;
+                s[n][c] = v;
+                mx[c >> 1] = fmaxf(mx[c >> 1], v);
+            }
         }
     }
     float alpha[2], m_use[2];

@@ -157,41 +157,71 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const bool ready = mbar_wait(accum, 0, give_up, 3);
     fence_after_sync();
     if (ready && !*give_up) {
-        const int m = m0 + warp * 32 + lane;
+        // A thread of tcgen05.ld holds 32 consecutive columns of ONE row; written out like that, every store
+        // instruction of a warp would touch 32 different rows. So each warp passes its 32 x 32 chunk through a
+        // padded tile of shared memory (the stages are free by now) and writes it out four rows at a time,
+        // 128 contiguous bytes per row, with 16-byte accesses.
+        constexpr int PITCH = 36;                                               // floats per staged row (16-byte aligned, conflict-free)
+        float* tile = reinterpret_cast<float*>(aligned) + warp * 32 * PITCH;
         const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
-        if (GLU) {
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t g[32], u[32];
-                tmem_ld32(lane_addr + c * 32, g);
+        const int r_sub = lane >> 3, c4 = (lane & 7) * 4;                       // this lane's row (of four) and column quad when writing out
+        const bool vec_ok = (N % 4) == 0;
+        constexpr int CHUNKS = GLU ? 2 : BN / 32;
+#pragma unroll 1
+        for (int c = 0; c < CHUNKS; ++c) {
+            uint32_t r[32];
+            tmem_ld32(lane_addr + c * 32, r);
+            if (GLU) {
+                uint32_t u[32];
                 tmem_ld32(lane_addr + 64 + c * 32, u);
                 tmem_ld_wait();
-                if (m < M) {
-                    TO* dst = out + (size_t)m * N + n0 + c * 32;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (n0 + c * 32 + j < N) bl_store(dst + j, bl_silu(__uint_as_float(g[j])) * __uint_as_float(u[j]));
-                }
-            }
-        } else {
-#pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(lane_addr + c * 32, r);
+                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(bl_silu(__uint_as_float(r[j])) * __uint_as_float(u[j]));
+            } else {
                 tmem_ld_wait();
-                if (m < M) {
-                    TO* dst = out + (size_t)m * N + n0 + c * 32;
+            }
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int n = n0 + c * 32 + j;
-                        if (n >= N) continue;
-                        float v = __uint_as_float(r[j]);
-                        if (EPI == BL_EPI_BIAS) v += bl_load_any(bias, bias_dtype, n);
-                        if (EPI == BL_EPI_RESIDUAL) v += bl_load(dst + j);
-                        bl_store(dst + j, v);
+            for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<uint4*>(tile + lane * PITCH + 4 * j) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            __syncwarp();
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const int row = it * 4 + r_sub;
+                const int m = m0 + warp * 32 + row;
+                const int n = n0 + c * 32 + c4;
+                if (m >= M || n >= N) continue;
+                float4 v = *reinterpret_cast<const float4*>(tile + row * PITCH + c4);
+                TO* dst = out + (size_t)m * N + n;
+                if (vec_ok && n + 3 < N) {
+                    if (EPI == BL_EPI_BIAS) {
+                        v.x += bl_load_any(bias, bias_dtype, n); v.y += bl_load_any(bias, bias_dtype, n + 1);
+                        v.z += bl_load_any(bias, bias_dtype, n + 2); v.w += bl_load_any(bias, bias_dtype, n + 3);
+                    }
+                    if (sizeof(TO) == 4) {
+                        if (EPI == BL_EPI_RESIDUAL) {
+                            const float4 o = *reinterpret_cast<const float4*>(dst);
+                            v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                        }
+                        *reinterpret_cast<float4*>(dst) = v;
+                    } else {
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                        uint2 pk;
+                        pk.x = *reinterpret_cast<unsigned*>(&lo); pk.y = *reinterpret_cast<unsigned*>(&hi);
+                        *reinterpret_cast<uint2*>(dst) = pk;
+                    }
+                } else {
+                    const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (n + j >= N) break;
+                        float x1 = e[j];
+                        if (EPI == BL_EPI_BIAS) x1 += bl_load_any(bias, bias_dtype, n + j);
+                        if (EPI == BL_EPI_RESIDUAL) x1 += bl_load(dst + j);
+                        bl_store(dst + j, x1);
                     }
                 }
             }
+            __syncwarp();
         }
     }
     fence_before_sync();

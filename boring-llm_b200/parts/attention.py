@@ -17,7 +17,7 @@ from .rotary import RotaryTable
 FUSED_MAX_ROWS = 32       # steps with at most this many rows take the fused norm + product kernels
 
 
-DECODE_TARGET_BLOCKS = 2 * 148     # blocks wanted in flight when one query's keys are cut into slices
+DECODE_TARGET_BLOCKS = 4 * 148     # blocks wanted in flight when one query's keys are cut into slices
 DECODE_MAX_SPLITS = 32               # more slices make the merge longer than they shorten the scan
 
 
