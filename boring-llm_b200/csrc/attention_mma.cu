@@ -197,7 +197,7 @@ __device__ __forceinline__ void block_step(const __nv_bfloat16* stage, int koff,
 }
 
 template <int DH, bool DECODE>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, (!DECODE && DH <= 64) ? 4 : 1)
 attention_mma_kernel(const AttnParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -213,8 +213,10 @@ attention_mma_kernel(const AttnParams p) {
         split = blockIdx.x;
         tok0 = 0;
     } else {
-        r = p.work[2 * blockIdx.x];
-        tok0 = p.work[2 * blockIdx.x + 1];
+        // late tiles of a request see the most keys: they go first, so that the short ones fill the tail
+        const int tile = gridDim.x - 1 - blockIdx.x;
+        r = p.work[2 * tile];
+        tok0 = p.work[2 * tile + 1];
         head0 = blockIdx.y;
         kvh = head0 / G;
     }

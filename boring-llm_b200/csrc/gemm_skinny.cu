@@ -29,8 +29,10 @@ __device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p, bool ok) {
 }
 
 // MT: groups of 8 tokens handled by one block (M tile = 8 * MT). NW: warps per block (8, or 16 for long K).
-template <int MT, int EPI, typename TO, int NW>
-__global__ void __launch_bounds__(NW * 32)
+// DEEP: two batches of loads in flight per warp (few blocks, each short: hide the trips to memory); without it one
+// batch and half the registers, so that twice as many blocks fit an SM (many blocks: HBM throughput is what counts).
+template <int MT, int EPI, typename TO, int NW, bool DEEP>
+__global__ void __launch_bounds__(NW * 32, DEEP ? 1 : (NW == 8 ? 4 : 2))
 gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no read-only cache */,
                    const __nv_bfloat16* __restrict__ w,
                    const void* __restrict__ bias, int bias_dtype, TO* out,
@@ -97,7 +99,8 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
             }
         }
     };
-    Batch b0, b1;
+    Batch b0;
+    Batch b1;        // used only when DEEP
     bl_pdl_trigger();
     fetch_w(b0, warp * 32);
     bl_prefetch_rows_l2(w, n0, COLS, (size_t)K * 2, (size_t)(GLU ? 2 * N : N));
@@ -112,13 +115,20 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
     if (EPI == BL_EPI_RESIDUAL && e_ok) e_add = bl_load(out + (size_t)e_m * N + e_n);   // on its way during the product
     fetch_x(b0, warp * 32);
     // two batches per trip of the loop, so that the buffers keep their names (and their registers)
-    for (int kc0 = warp * 32; kc0 < K; kc0 += 2 * STEP) {
-        const bool more1 = kc0 + STEP < K;
-        if (more1) { fetch_w(b1, kc0 + STEP); fetch_x(b1, kc0 + STEP); }
-        multiply(b0);
-        if (!more1) break;
-        if (kc0 + 2 * STEP < K) { fetch_w(b0, kc0 + 2 * STEP); fetch_x(b0, kc0 + 2 * STEP); }
-        multiply(b1);
+    if (DEEP) {
+        for (int kc0 = warp * 32; kc0 < K; kc0 += 2 * STEP) {
+            const bool more1 = kc0 + STEP < K;
+            if (more1) { fetch_w(b1, kc0 + STEP); fetch_x(b1, kc0 + STEP); }
+            multiply(b0);
+            if (!more1) break;
+            if (kc0 + 2 * STEP < K) { fetch_w(b0, kc0 + 2 * STEP); fetch_x(b0, kc0 + 2 * STEP); }
+            multiply(b1);
+        }
+    } else {
+        for (int kc0 = warp * 32; kc0 < K; kc0 += STEP) {
+            multiply(b0);
+            if (kc0 + STEP < K) { fetch_w(b0, kc0 + STEP); fetch_x(b0, kc0 + STEP); }
+        }
     }
     // c0, c1: (column g, tokens 2t, 2t+1); c2, c3: (column g + 8, tokens 2t, 2t+1)
 #pragma unroll
@@ -146,12 +156,12 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
     }
 }
 
-template <int MT, typename TO, int NW>
+template <int MT, typename TO, int NW, bool DEEP>
 int launch_nw(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K,
               int epi, cudaStream_t s) {
     const int m_groups = (M + MT * 8 - 1) / (MT * 8);
     const int blocks = ((N + COLS - 1) / COLS) * m_groups;
-#define BL_GO(E) BL_CUDA(bl_launch_dependent(gemm_skinny_kernel<MT, E, TO, NW>, dim3(blocks), dim3(NW * 32), 0, s, \
+#define BL_GO(E) BL_CUDA(bl_launch_dependent(gemm_skinny_kernel<MT, E, TO, NW, DEEP>, dim3(blocks), dim3(NW * 32), 0, s, \
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, bias_dtype, (TO*)out, M, N, K, m_groups))
     switch (epi) {
         case BL_EPI_NONE: BL_GO(BL_EPI_NONE); break;
@@ -168,8 +178,11 @@ int launch_nw(const void* x, const void* w, const void* bias, int bias_dtype, vo
 template <int MT, typename TO>
 int launch(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K,
            int epi, cudaStream_t s) {
-    if (K >= 2048 && MT == 1 && epi != BL_EPI_SWIGLU) return launch_nw<1, TO, 16>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
-    return launch_nw<MT, TO, 8>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
+    const int m_groups = (M + MT * 8 - 1) / (MT * 8);
+    const int blocks = ((N + COLS - 1) / COLS) * m_groups;
+    if (blocks > 4 * 148) return launch_nw<MT, TO, 8, false>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
+    if (K >= 2048 && MT == 1 && epi != BL_EPI_SWIGLU) return launch_nw<1, TO, 16, true>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
+    return launch_nw<MT, TO, 8, true>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
 }
 
 }  // namespace
