@@ -12,7 +12,7 @@ import torch
 from ..kernels import ops
 from ..kernels.ops import EPI_NONE, EPI_BIAS, EPI_RESIDUAL, EPI_SWIGLU
 
-SKINNY_MAX_ROWS = 64      # up to here W streams through registers; above, 128-row tiles go to tcgen05
+SKINNY_MAX_ROWS = 64      # up to here W streams through registers (measured faster than 128-row tcgen05 tiles at 64 rows)
 
 
 def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
