@@ -99,6 +99,12 @@ void bl_set_dependent_launch(int on);
 // Writes the GPU's nanosecond timer to buf[slot] once everything before it on the stream has finished.
 int bl_stamp(unsigned long long* buf, int slot, void* stream);
 
+// The same product on pairs of SMs (tcgen05 cta_group::2, clusters of two blocks, 256 x 256 tiles): twice the
+// arithmetic per byte loaded into shared memory. Same contract as bl_gemm_tc.
+int bl_gemm_tc_pair(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype,
+                    int M, int N, int K, int epilogue, void* stream);
+int bl_gemm_tc_pair_status(int* status);
+
 #ifdef __cplusplus
 }
 #endif

@@ -48,6 +48,9 @@ __device__ __forceinline__ float bl_warp_max(float v) {
 
 // x / (1 + exp(-x)), as src/math.br:232-233.
 __device__ __forceinline__ float bl_silu(float x) { return x / (1.0f + expf(-x)); }
+// The same with the hardware's exp2 and reciprocal units (relative error around 1e-6): for epilogues whose result
+// is rounded to bfloat16 (2^-9) anyway and that evaluate it millions of times per step.
+__device__ __forceinline__ float bl_silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 // Programmatic dependent launch. A kernel launched with bl_launch_dependent() may start while its predecessor
 // on the stream is still running; whatever it does before bl_pdl_wait() must touch only data that no earlier

@@ -176,7 +176,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tmem_ld32(lane_addr + 64 + c * 32, u);
                 tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(bl_silu(__uint_as_float(r[j])) * __uint_as_float(u[j]));
+                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(bl_silu_fast(__uint_as_float(r[j])) * __uint_as_float(u[j]));
             } else {
                 tmem_ld_wait();
             }

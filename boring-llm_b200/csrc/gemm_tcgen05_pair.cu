@@ -1,0 +1,400 @@
+// Matrix product for many rows on PAIRS of SMs: out[M, N] = epilogue(x[M, K] . W[N, K]^T), bfloat16 operands,
+// 32-bit accumulation in tensor memory, tcgen05.mma with cta_group::2, persistent blocks.
+//
+// Two blocks of a cluster compute 256 x BN tiles of the output (BN 256, or 128 where 256 would leave SMs idle).
+// Each block loads its own 128 rows of x and HALF of the tile's rows of W per 64-wide k block, but the pair
+// multiplies 256 x BN x 64 with them: twice the arithmetic per byte that crosses from L2 into shared memory.
+// The leader block (cluster rank 0) issues the MMAs for both; the hardware reads x tiles and W halves from both
+// blocks' shared memory and writes each block's 128 rows of the accumulator into that block's tensor memory.
+//
+// One pair per two SMs stays resident and walks over tiles (tile t, t + pairs, ...). The round trip "stage free ->
+// TMA -> data landed -> MMA done -> stage free" takes a couple of microseconds, so five stages are kept in flight,
+// and the accumulator is double buffered in tensor memory (2 x 256 columns): while the eight epilogue warps drain
+// one tile, the issuer already fills the next, and the loaders never stop.
+//
+//   warp 0, one thread in EACH block (loader): waits for its own stage to be free, TMA-loads its x tile and its half
+//     of W. Both blocks' copies report their bytes to the LEADER's "full" barrier (the .cta_group::2 form of
+//     cp.async.bulk.tensor, barrier address with the peer bit cleared); the leader expects the bytes of both.
+//     No multicast: every block fetches its own tiles.
+//   warp 1, one thread in the leader (issuer): waits until both blocks have drained the accumulator buffer, then per
+//     k block waits for "full", issues four K = 16 MMAs (M 256, N BN) and commits with multicast to the "empty"
+//     barrier of that stage in BOTH blocks; after a tile, to both blocks' "accumulator full" barriers.
+//   warps 2..9 of each block (epilogue, two per quarter of the rows, taking chunks in turn): tcgen05.ld of the block's own 128 x BN accumulator, 32 x 32 chunks passed
+//     through shared memory, 16-byte stores, then an arrival on the leader's "accumulator empty" barrier. For
+//     SwiGLU the leader's half of W holds gate rows and the peer's half the matching up rows, so the first BN/2
+//     columns are gates and the rest their ups.
+// Every mbarrier wait is bounded (a status word records the first that ran out); the cluster barriers are hardware
+// barriers that both blocks always reach.
+#include "common.cuh"
+#include "api.h"
+#include <cuda.h>
+
+namespace {
+
+constexpr int BM = 128;                 // rows per block (256 per pair)
+constexpr int BK = 64, STAGES = 5;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int STAGE_BYTES_MAX = A_BYTES + 128 * BK * 2;              // with BN = 256 each block holds 128 rows of W
+constexpr int EPI_WARPS = 8, THREADS = 32 * (2 + EPI_WARPS);    // two warps per quarter of the accumulator's rows
+constexpr int PITCH = 36;                                            // floats per staged row of the epilogue
+constexpr int STAGING_BYTES = EPI_WARPS * 32 * PITCH * 4;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES_MAX + STAGING_BYTES + 1024 + 256;
+constexpr int TMEM_COLS = 512;                                       // two accumulators of up to 256 columns
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;      // clears the bit that selects the odd block of a pair
+
+__device__ int g_status2 = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (*give_up) return false;
+    }
+    *give_up = 1;
+    atomicCAS(&g_status2, 0, code);
+    return false;
+}
+// Both blocks of the pair issue this; the bytes are reported to the barrier of the EVEN block (the leader).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(dst), "l"(map), "r"(leader_bar & PEER_BIT_MASK), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {      // arrives on `bar` in both blocks
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 :: "r"(bar), "h"((unsigned short)3) : "memory");
+}
+// Arrives on the barrier at this address in the LEADER block (own block when it is the leader).
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(bar & PEER_BIT_MASK) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {        // K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
+    const uint32_t lo = ((addr >> 4) & 0x3FFFu) | (1u << 16);
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
+// D 32-bit, A and B bfloat16 and K-major, N >> 3 at bit 17, M = 256 over the pair (>> 4 at bit 24)
+__host__ __device__ constexpr uint32_t idesc_for(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+template <int EPI, typename TO, int BN>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const void* __restrict__ bias, int bias_dtype, TO* __restrict__ out, int M, int N, int K,
+                    int m_pairs, int n_tiles) {
+    constexpr bool GLU = EPI == BL_EPI_SWIGLU;
+    constexpr int B_BYTES = (BN / 2) * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int COLS = GLU ? BN / 2 : BN;                          // output columns per tile
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
+    float* staging = reinterpret_cast<float*>(aligned + STAGES * STAGE_BYTES_MAX);
+    const uint32_t bars = base + STAGES * STAGE_BYTES_MAX + STAGING_BYTES;
+    volatile int* give_up = reinterpret_cast<volatile int*>(aligned + STAGES * STAGE_BYTES_MAX + STAGING_BYTES + 192);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + STAGES * STAGE_BYTES_MAX + STAGING_BYTES + 200);
+    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, acc_full0 = bars + 16 * STAGES, acc_empty0 = acc_full0 + 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x / 2, n_pairs = gridDim.x / 2;
+    const int total_tiles = m_pairs * n_tiles;
+    const int kblocks = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        *give_up = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full0 + 8 * b, 1); mbar_init(acc_empty0 + 8 * b, 2 * EPI_WARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    fence_before_sync();
+    __syncthreads();
+    cluster_sync();                                                  // both blocks' barriers exist before anyone signals them
+    fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;                                              // k blocks loaded so far, over all tiles
+            for (int t = pair; t < total_tiles && !*give_up; t += n_pairs) {
+                const int m0 = ((t % m_pairs) * 2 + (int)rank) * BM;
+                const int n0 = (t / m_pairs) * COLS;
+                // this block's half of W. Plain: rows n0 + rank * BN/2. SwiGLU: gate rows (leader) or the up rows that match.
+                const int w_row0 = GLU ? (int)rank * N + n0 : n0 + (int)rank * (BN / 2);
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, give_up, 1)) break;
+                    const uint32_t a_dst = base + s * STAGE_BYTES_MAX, b_dst = a_dst + A_BYTES;
+                    if (leader) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);   // the bytes of both blocks
+                    tma_load_2d_pair(a_dst, &map_a, full0 + 8 * s, kb * BK, m0);
+                    tma_load_2d_pair(b_dst, &map_b, full0 + 8 * s, kb * BK, w_row0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (leader && lane == 0) {
+            int it = 0, local = 0;
+            for (int t = pair; t < total_tiles && !*give_up; t += n_pairs, ++local) {
+                const int buf = local & 1;
+                // both blocks must have drained this accumulator buffer (its first two uses find it free)
+                if (local >= 2 && !mbar_wait(acc_empty0 + 8 * buf, ((local / 2) & 1) ^ 1, give_up, 4)) break;
+                fence_after_sync();
+                const uint32_t d_tmem = tmem + buf * 256;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(full0 + 8 * s, (it / STAGES) & 1, give_up, 2)) break;
+                    fence_after_sync();
+                    const uint64_t a_desc = smem_desc(base + s * STAGE_BYTES_MAX);
+                    const uint64_t b_desc = smem_desc(base + s * STAGE_BYTES_MAX + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_bf16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc_for(BN), (kb | k) != 0);
+                    umma_commit_pair(empty0 + 8 * s);
+                }
+                umma_commit_pair(acc_full0 + 8 * buf);
+            }
+        }
+    } else {
+        const int ew = warp - 2;                                     // epilogue warp 0..7
+        const int quarter = warp & 3;                                // the 32 accumulator rows this warp may read
+        const int half = ew >> 2;                                    // of the two warps of a quarter: even or odd chunks
+        float* tile = staging + ew * 32 * PITCH;
+        const int r_sub = lane >> 3, c4 = (lane & 7) * 4;
+        const bool vec_ok = (N % 4) == 0;
+        constexpr int CHUNKS = COLS / 32;
+        int local = 0;
+        for (int t = pair; t < total_tiles; t += n_pairs, ++local) {
+            const int buf = local & 1;
+            const int m0 = ((t % m_pairs) * 2 + (int)rank) * BM;
+            const int n0 = (t / m_pairs) * COLS;
+            if (!mbar_wait(acc_full0 + 8 * buf, (local / 2) & 1, give_up, 3)) break;
+            fence_after_sync();
+            const uint32_t lane_addr = tmem + buf * 256 + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c = half; c < CHUNKS; c += 2) {
+                uint32_t r[32];
+                tmem_ld32(lane_addr + c * 32, r);
+                if (GLU) {
+                    uint32_t u[32];
+                    tmem_ld32(lane_addr + BN / 2 + c * 32, u);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(bl_silu_fast(__uint_as_float(r[j])) * __uint_as_float(u[j]));
+                } else {
+                    tmem_ld_wait();
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    *reinterpret_cast<uint4*>(tile + lane * PITCH + 4 * j) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                __syncwarp();
+#pragma unroll
+                for (int it2 = 0; it2 < 8; ++it2) {
+                    const int row = it2 * 4 + r_sub;
+                    const int m = m0 + quarter * 32 + row;
+                    const int n = n0 + c * 32 + c4;
+                    if (m >= M || n >= N) continue;
+                    float4 v = *reinterpret_cast<const float4*>(tile + row * PITCH + c4);
+                    TO* dst = out + (size_t)m * N + n;
+                    if (vec_ok && n + 3 < N) {
+                        if (EPI == BL_EPI_BIAS) {
+                            v.x += bl_load_any(bias, bias_dtype, n); v.y += bl_load_any(bias, bias_dtype, n + 1);
+                            v.z += bl_load_any(bias, bias_dtype, n + 2); v.w += bl_load_any(bias, bias_dtype, n + 3);
+                        }
+                        if (sizeof(TO) == 4) {
+                            if (EPI == BL_EPI_RESIDUAL) {
+                                const float4 o = *reinterpret_cast<const float4*>(dst);
+                                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                            }
+                            *reinterpret_cast<float4*>(dst) = v;
+                        } else {
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                            uint2 pk;
+                            pk.x = *reinterpret_cast<unsigned*>(&lo); pk.y = *reinterpret_cast<unsigned*>(&hi);
+                            *reinterpret_cast<uint2*>(dst) = pk;
+                        }
+                    } else {
+                        const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (n + j >= N) break;
+                            float x1 = e[j];
+                            if (EPI == BL_EPI_BIAS) x1 += bl_load_any(bias, bias_dtype, n + j);
+                            if (EPI == BL_EPI_RESIDUAL) x1 += bl_load(dst + j);
+                            bl_store(dst + j, x1);
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+            // this warp is done with the buffer: tell the issuer (in the leader block)
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(acc_empty0 + 8 * buf);
+        }
+    }
+    __syncwarp();
+    fence_before_sync();
+    __syncthreads();
+    cluster_sync();                                                  // neither block leaves while the other may still read its memory
+    if (warp == 0) {
+        fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+    EncodeTiled enc = encode_fn();
+    if (enc == nullptr) BL_FAIL("bl_gemm_tc_pair: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) BL_FAIL("bl_gemm_tc_pair: cuTensorMapEncodeTiled failed with code %d (rows %d, K %d)", (int)r, rows, K);
+    return 0;
+}
+
+template <int EPI, typename TO, int BN>
+int launch_bn(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K, int sms,
+              cudaStream_t s) {
+    static bool configured = false;
+    if (!configured) {
+        BL_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI, TO, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured = true;
+    }
+    const bool glu = EPI == BL_EPI_SWIGLU;
+    CUtensorMap a, b;
+    if (make_map(&a, x, M, K, BM)) return 1;
+    if (make_map(&b, w, glu ? 2 * N : N, K, BN / 2)) return 1;
+    const int cols = glu ? BN / 2 : BN;
+    const int m_pairs = (M + 2 * BM - 1) / (2 * BM), n_tiles = (N + cols - 1) / cols;
+    int pairs = m_pairs * n_tiles;
+    if (pairs > sms / 2) pairs = sms / 2;                            // one resident pair per two SMs walks over the tiles
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = s;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    BL_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<EPI, TO, BN>, a, b, bias, bias_dtype, (TO*)out, M, N, K, m_pairs, n_tiles));
+    return 0;
+}
+
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 2;
+    }
+    return n;
+}
+
+// 256-column tiles unless they would leave SM pairs without a tile while 128-column tiles would not.
+template <int EPI, typename TO>
+int launch(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K, cudaStream_t s) {
+    const int sms = sm_count();
+    const int cols256 = EPI == BL_EPI_SWIGLU ? 128 : 256;
+    const int m_pairs = (M + 2 * BM - 1) / (2 * BM);
+    const int tiles256 = m_pairs * ((N + cols256 - 1) / cols256);
+    if (tiles256 < sms / 2) return launch_bn<EPI, TO, 128>(x, w, bias, bias_dtype, out, M, N, K, sms, s);
+    return launch_bn<EPI, TO, 256>(x, w, bias, bias_dtype, out, M, N, K, sms, s);
+}
+
+}  // namespace
+
+// Same contract as bl_gemm_tc; meant for M of a few hundred rows and more (a pair covers 256 rows).
+extern "C" int bl_gemm_tc_pair(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype,
+                               int M, int N, int K, int epilogue, void* stream) {
+    if (M <= 0) return 0;
+    if (N <= 0 || K <= 0) BL_FAIL("bl_gemm_tc_pair: bad sizes N=%d K=%d", N, K);
+    if (K % 8 != 0) BL_FAIL("bl_gemm_tc_pair: K=%d is not a multiple of 8 (TMA rows must be 16-byte multiples)", K);
+    if (((uintptr_t)x | (uintptr_t)w) & 15) BL_FAIL("bl_gemm_tc_pair: x and W must be 16-byte aligned");
+    if (epilogue == BL_EPI_BIAS && (bias == nullptr || (bias_dtype != BL_F32 && bias_dtype != BL_BF16)))
+        BL_FAIL("bl_gemm_tc_pair: bias epilogue needs a float32 or bfloat16 bias");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == BL_F32) {
+        switch (epilogue) {
+            case BL_EPI_NONE: return launch<BL_EPI_NONE, float>(x, w, bias, bias_dtype, out, M, N, K, s);
+            case BL_EPI_BIAS: return launch<BL_EPI_BIAS, float>(x, w, bias, bias_dtype, out, M, N, K, s);
+            case BL_EPI_RESIDUAL: return launch<BL_EPI_RESIDUAL, float>(x, w, bias, bias_dtype, out, M, N, K, s);
+            case BL_EPI_SWIGLU: return launch<BL_EPI_SWIGLU, float>(x, w, bias, bias_dtype, out, M, N, K, s);
+        }
+    } else if (out_dtype == BL_BF16) {
+        switch (epilogue) {
+            case BL_EPI_NONE: return launch<BL_EPI_NONE, __nv_bfloat16>(x, w, bias, bias_dtype, out, M, N, K, s);
+            case BL_EPI_BIAS: return launch<BL_EPI_BIAS, __nv_bfloat16>(x, w, bias, bias_dtype, out, M, N, K, s);
+            case BL_EPI_SWIGLU: return launch<BL_EPI_SWIGLU, __nv_bfloat16>(x, w, bias, bias_dtype, out, M, N, K, s);
+            case BL_EPI_RESIDUAL: BL_FAIL("bl_gemm_tc_pair: the residual stream is 32-bit; output dtype must be float32");
+        }
+    } else {
+        BL_FAIL("bl_gemm_tc_pair: unknown output dtype %d", out_dtype);
+    }
+    BL_FAIL("bl_gemm_tc_pair: unknown epilogue %d", epilogue);
+}
+
+extern "C" int bl_gemm_tc_pair_status(int* status) {
+    int v = 0, zero = 0;
+    BL_CUDA(cudaMemcpyFromSymbol(&v, g_status2, sizeof(int)));
+    if (v != 0) BL_CUDA(cudaMemcpyToSymbol(g_status2, &zero, sizeof(int)));
+    *status = v;
+    return 0;
+}

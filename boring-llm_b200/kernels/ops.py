@@ -294,13 +294,27 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
           M, N, K, epilogue, _stream())
 
 
+def gemm_tc_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                 epilogue: int = EPI_NONE) -> None:
+    """`gemm_tc` on pairs of SMs (tcgen05 cta_group::2): 256 x 256 tiles, for a few hundred rows and more."""
+    M, K = x.shape
+    N = out.shape[1]
+    rows_w = 2 * N if epilogue == EPI_SWIGLU else N
+    _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16, (rows_w, K)); _need(out, "out", None, (M, N))
+    if bias is not None:
+        _need(bias, "bias", None, (N,))
+    _call(_lib().bl_gemm_tc_pair, _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0, _p(out), _dt(out),
+          M, N, K, epilogue, _stream())
+
+
 def check_status() -> None:
     """Raises if a tensor-core block gave up on one of its bounded waits since the last check. Synchronises."""
-    v = ctypes.c_int(0)
-    _call(_lib().bl_gemm_tc_status, ctypes.byref(v))
-    if v.value != 0:
-        who = {1: "the TMA loader", 2: "the MMA issuer", 3: "the epilogue"}.get(v.value, "a thread")
-        raise KernelError(f"bl_gemm_tc: {who} gave up on a bounded wait (code {v.value}); results of that launch are invalid")
+    for name, fn in (("bl_gemm_tc", _lib().bl_gemm_tc_status), ("bl_gemm_tc_pair", _lib().bl_gemm_tc_pair_status)):
+        v = ctypes.c_int(0)
+        _call(fn, ctypes.byref(v))
+        if v.value != 0:
+            who = {1: "the TMA loader", 2: "the MMA issuer", 3: "the epilogue"}.get(v.value, "a thread")
+            raise KernelError(f"{name}: {who} gave up on a bounded wait (code {v.value}); results of that launch are invalid")
 
 
 def norm_gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:

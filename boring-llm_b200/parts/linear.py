@@ -13,6 +13,7 @@ from ..kernels import ops
 from ..kernels.ops import EPI_NONE, EPI_BIAS, EPI_RESIDUAL, EPI_SWIGLU
 
 SKINNY_MAX_ROWS = 64      # up to here W streams through registers (measured faster than 128-row tcgen05 tiles at 64 rows)
+PAIR_MIN_ROWS = 256       # from here on pairs of SMs share 256 x 256 tiles (tcgen05 cta_group::2)
 
 
 def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -22,7 +23,9 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optio
     if ctx.fast and ops.gemm_skinny_supported(x, w):
         if x.shape[0] <= SKINNY_MAX_ROWS:
             ops.gemm_skinny(x, w, out, bias, epilogue)
-        else:
+        elif x.shape[0] < PAIR_MIN_ROWS:
             ops.gemm_tc(x, w, out, bias, epilogue)
+        else:
+            ops.gemm_tc_pair(x, w, out, bias, epilogue)
     else:
         ops.gemm_plain(x, w, out, bias, epilogue)

@@ -411,10 +411,13 @@ def test_attention_mma_is_refused_where_it_is_not_built():
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (1, 7, 8), (130, 200, 96), (257, 129, 264), (300, 608, 176),
                                    (2048, 1152, 896), (65, 896, 4864), (500, 320, 200)])
-def test_gemm_tc_epilogues(M, N, K):
-    """The tcgen05 product against 64-bit arithmetic and against its plain twin: tiles that overhang M, N and K,
-    one k block and seventy-six, every epilogue."""
+@pytest.mark.parametrize("pair", [False, True])
+def test_gemm_tc_epilogues(M, N, K, pair):
+    """The tcgen05 products (one block per 128 x 128 tile; a pair of blocks per 256 x 256 tile) against 64-bit
+    arithmetic and against their plain twin: tiles that overhang M, N and K, one k block and seventy-six, every
+    epilogue."""
     o = ops()
+    gemm_tc = o.gemm_tc_pair if pair else o.gemm_tc
     dtype = torch.bfloat16
     x = (data((M, K), 24) * 0.5).to(dtype)
     w = (data((2 * N, K), 25) * 0.25).to(dtype)
@@ -422,23 +425,23 @@ def test_gemm_tc_epilogues(M, N, K):
     xd, wd, bd = x.double().cpu(), w.double().cpu(), b.double().cpu()
     wn = w[:N].contiguous()
     out = torch.full((M, N), float("nan"), device=DEV)
-    o.gemm_tc(x, wn, out)
+    gemm_tc(x, wn, out)
     o.check_status()
     close(out, xd @ wd[:N].T, torch.float32, "none")
     twin = torch.empty(M, N, device=DEV)
     o.gemm_plain(x, wn, twin)
     close(out, twin.double(), torch.float32, "twin")
-    o.gemm_tc(x, wn, out, b, o.EPI_BIAS)
+    gemm_tc(x, wn, out, b, o.EPI_BIAS)
     close(out, xd @ wd[:N].T + bd, torch.float32, "bias")
     res = data((M, N), 27)
     acc = res.clone()
-    o.gemm_tc(x, wn, acc, None, o.EPI_RESIDUAL)
+    gemm_tc(x, wn, acc, None, o.EPI_RESIDUAL)
     close(acc, res.double().cpu() + xd @ wd[:N].T, torch.float32, "residual")
     act = torch.full((M, N), float("nan"), dtype=dtype, device=DEV)
-    o.gemm_tc(x, w, act, None, o.EPI_SWIGLU)
+    gemm_tc(x, w, act, None, o.EPI_SWIGLU)
     close(act, plain.silu(xd @ wd[:N].T) * (xd @ wd[N:].T), dtype, "swiglu")
     half = torch.empty(M, N, dtype=dtype, device=DEV)
-    o.gemm_tc(x, wn, half)
+    gemm_tc(x, wn, half)
     close(half, xd @ wd[:N].T, dtype, "bfloat16 output")
     o.check_status()
 
