@@ -253,11 +253,20 @@ attention_mma_kernel(const AttnParams p) {
         b_end = min(b_end, s0 + per);
         b_begin = min(s0, b_end);
     }
+    constexpr int STAGE = Tiles<DH>::STAGE;
+    const int nb = b_end - b_begin;
+    int issued = 0;                                   // blocks whose copies into shared memory have been started
     if (DECODE) {
-        // the cached keys and values of earlier tokens do not depend on the kernel before: start them on their
-        // way into L2 (the newest token's row is written there by that kernel; L2 stays coherent with it)
+        // The cached keys and values of earlier tokens do not depend on the kernel before: blocks that do not hold
+        // the newest token are copied into the two stages right away, and the rest of this slice is started on its
+        // way into L2 (the newest token's row is written there by that kernel; L2 stays coherent with it).
+        while (issued < 2 && issued < nb && (b_begin + issued + 1) * KB <= hi) {
+            load_block<DH>(smem + (issued & 1) * STAGE, p, table, kvh, (b_begin + issued) * KB, lo, hi);
+            cp_async_commit();
+            ++issued;
+        }
         constexpr int LINES = PAGE * DH * 2 / 128 > 0 ? PAGE * DH * 2 / 128 : 1;     // 128-byte lines per (page, head)
-        const int first_page = b_begin * (KB / PAGE), last_page = min(b_end * (KB / PAGE), hi / PAGE + 1);
+        const int first_page = (b_begin + issued) * (KB / PAGE), last_page = min(b_end * (KB / PAGE), hi / PAGE + 1);
         for (int i = threadIdx.x; i < (last_page - first_page) * LINES; i += THREADS) {
             const int pg = first_page + i / LINES;
             const int page = pg * PAGE + PAGE - 1 >= lo ? table[pg] : -1;
@@ -287,20 +296,25 @@ attention_mma_kernel(const AttnParams p) {
 #pragma unroll
     for (int n = 0; n < DH / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    constexpr int STAGE = Tiles<DH>::STAGE;
-    if (b_begin < b_end) load_block<DH>(smem, p, table, kvh, b_begin * KB, lo, hi);
-    cp_async_commit();
-    for (int b = b_begin; b < b_end; ++b) {
-        const int st = (b - b_begin) & 1;
-        if (b + 1 < b_end) load_block<DH>(smem + (st ^ 1) * STAGE, p, table, kvh, (b + 1) * KB, lo, hi);
+    while (issued < 2 && issued < nb) {               // two blocks in flight before the first is used
+        load_block<DH>(smem + (issued & 1) * STAGE, p, table, kvh, (b_begin + issued) * KB, lo, hi);
         cp_async_commit();
-        cp_async_wait<1>();
+        ++issued;
+    }
+    for (int i = 0; i < nb; ++i) {
+        const int b = b_begin + i, st = i & 1;
+        if (issued - (i + 1) >= 1) cp_async_wait<1>(); else cp_async_wait<0>();       // block i has landed
         __syncthreads();
         if (DECODE)
             block_step<DH, 2>(smem + st * STAGE, warp * 16, b * KB, qf, o, m, l, pos, p.window, p.scale_log2);
         else
             block_step<DH, 8>(smem + st * STAGE, 0, b * KB, qf, o, m, l, pos, p.window, p.scale_log2);
         __syncthreads();
+        if (issued < nb) {                            // the stage just used takes the block after next
+            load_block<DH>(smem + st * STAGE, p, table, kvh, (b_begin + issued) * KB, lo, hi);
+            cp_async_commit();
+            ++issued;
+        }
     }
     cp_async_wait<0>();
 #pragma unroll

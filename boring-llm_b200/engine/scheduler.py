@@ -56,6 +56,15 @@ class Request:
     def tokens(self) -> List[int]:
         return self.prompt + self.output
 
+    def token_slice(self, a: int, b: int) -> List[int]:
+        """tokens[a:b] without building the whole list (a decode step wants one token of thousands)."""
+        n = len(self.prompt)
+        if b <= n:
+            return self.prompt[a:b]
+        if a >= n:
+            return self.output[a - n:b - n]
+        return self.prompt[a:] + self.output[:b - n]
+
     @property
     def remaining(self) -> int:
         """Tokens known but not yet in the cache."""
@@ -182,7 +191,7 @@ class Scheduler:
             return None
         entries, reqs, samples = [], [], []
         for req, n in picked.values():
-            toks = req.tokens[req.num_computed:req.num_computed + n]
+            toks = req.token_slice(req.num_computed, req.num_computed + n)
             last = req.num_computed + n == len(req.prompt) + len(req.output)
             entries.append(StepEntry(req.request_id, toks, [n - 1] if last else []))
             reqs.append(req)

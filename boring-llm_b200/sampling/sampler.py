@@ -11,7 +11,8 @@ from .params import SamplingParams, XorShift64, penalty_window
 
 
 class Sampler:
-    """`sample(logits, rows)`: `rows` is a list of (params, generator, history) per logits row.
+    """`sample(logits, rows)`: `rows` is a list of (params, generator, history) per logits row; `history` is a
+    list of token ids or an object with a `tokens` attribute (read only when a penalty is on).
     Greedy rows do not advance their generator (src/sampling.br:496-497); every other row draws
     one number per token. The choice itself runs in `bl_sample` on the device."""
 
@@ -35,7 +36,8 @@ class Sampler:
                 f[3, i] = rng.next_f32()
             if p.repeat_penalty != 1.0:
                 pen[i] = p.repeat_penalty
-                pen_tokens.extend(penalty_window(history, p.repeat_last_n))
+                tokens = history.tokens if hasattr(history, "tokens") else history
+                pen_tokens.extend(penalty_window(tokens, p.repeat_last_n))
             pen_offsets.append(len(pen_tokens))
         if pen_tokens:
             logits = logits.clone()
