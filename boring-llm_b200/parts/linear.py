@@ -13,6 +13,7 @@ from ..kernels import ops
 from ..kernels.ops import EPI_NONE, EPI_BIAS, EPI_RESIDUAL, EPI_SWIGLU
 
 SKINNY_MAX_ROWS = 64      # up to here W streams through registers (measured faster than 128-row tcgen05 tiles at 64 rows)
+TC_MIN_COLUMNS_FEW_ROWS = 4096   # 33..64 rows: wide products have enough 128-column tiles for TMA to stream W at full rate
 PAIR_MIN_ROWS = 256       # from here on pairs of SMs share 256 x 256 tiles (tcgen05 cta_group::2)
 
 
@@ -21,7 +22,8 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optio
     """out = epilogue(x @ w.T). float32 operands always take the plain CUDA-core kernel (true 32-bit);
     bfloat16 operands take a tensor-core kernel chosen by the number of rows."""
     if ctx.fast and ops.gemm_skinny_supported(x, w):
-        if x.shape[0] <= SKINNY_MAX_ROWS:
+        M, N = x.shape[0], out.shape[1]
+        if M <= SKINNY_MAX_ROWS and not (M > 32 and N >= TC_MIN_COLUMNS_FEW_ROWS):
             ops.gemm_skinny(x, w, out, bias, epilogue)
         elif x.shape[0] < PAIR_MIN_ROWS:
             ops.gemm_tc(x, w, out, bias, epilogue)
