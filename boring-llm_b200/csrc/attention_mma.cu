@@ -334,45 +334,59 @@ attention_mma_kernel(const AttnParams p) {
         }
         return;
     }
-    // decode: merge the four warps (same 16 rows, different keys), then write the slice's result
+    // decode: merge the four warps (same 16 rows, different keys), then write the slice's result.
+    // Every thread scales its own accumulators to the rows' common maximum; the sums over the warps
+    // are then plain additions of 16-byte words. Rows are DH + 8 floats apart, which keeps the
+    // 8-byte stores of a half-warp and the 16-byte loads of a quarter-warp on distinct banks.
     __syncthreads();
-    float* so = reinterpret_cast<float*>(smem_raw);               // [4 warps][16 rows][DH]
-    float* sm = so + 4 * 16 * DH;                                 // [4][16] maxima
-    float* sl = sm + 4 * 16;                                      // [4][16] sums
+    constexpr int SO = DH + 8;
+    float* so = reinterpret_cast<float*>(smem_raw);               // [4 warps][16 rows][SO]
+    float* sm = so + 4 * 16 * SO;                                 // [4][16] maxima
+    float* sl = sm + 4 * 16;                                      // [4][16] sums, then sums at the common maximum
+    if (t == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) { sm[warp * 16 + g + 8 * h] = m[h]; sl[warp * 16 + g + 8 * h] = l[h]; }
+    }
+    __syncthreads();
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int row = g + 8 * h;
-        if (t == 0) { sm[warp * 16 + row] = m[h]; sl[warp * 16 + row] = l[h]; }
+        float M = -INFINITY;
 #pragma unroll
-        for (int n = 0; n < DH / 8; ++n) {
-            so[(warp * 16 + row) * DH + n * 8 + 2 * t] = o[n][2 * h];
-            so[(warp * 16 + row) * DH + n * 8 + 2 * t + 1] = o[n][2 * h + 1];
-        }
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm[w * 16 + row]);
+        const float f = m[h] == -INFINITY ? 0.f : exp2f(m[h] - M);
+        if (t == 0) sl[warp * 16 + row] = l[h] * f;
+        float* dst = so + (warp * 16 + row) * SO + 2 * t;
+#pragma unroll
+        for (int n = 0; n < DH / 8; ++n)
+            *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][2 * h] * f, o[n][2 * h + 1] * f);
     }
     __syncthreads();
     const int rows_here = min(16, (kvh + 1) * G - head0);
     const int q_tok = q_begin;
-    for (int i = threadIdx.x; i < rows_here * DH; i += THREADS) {
-        const int row = i / DH, d = i % DH;
-        float M = -INFINITY;
+    constexpr int D4 = DH / 4;
+    if (q_len > 0) {
+        for (int i = threadIdx.x; i < rows_here * D4; i += THREADS) {
+            const int row = i / D4, d = (i % D4) * 4;
+            float M = -INFINITY, L = 0.f;
+            float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm[w * 16 + row]);
-        float L = 0.f, O = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float mw = sm[w * 16 + row];
-            const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
-            L += sl[w * 16 + row] * f;
-            O += so[(w * 16 + row) * DH + d] * f;
-        }
-        const int hd = head0 + row;
-        if (q_len <= 0) continue;
-        if (p.n_splits == 1) {
-            p.out[((size_t)q_tok * p.H + hd) * DH + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
-        } else {
-            const size_t slot = ((size_t)blockIdx.z * p.H + hd) * p.n_splits + split;
-            p.part_o[slot * DH + d] = O;
-            if (d == 0) { p.part_ml[slot * 2] = M; p.part_ml[slot * 2 + 1] = L; }
+            for (int w = 0; w < 4; ++w) {
+                M = fmaxf(M, sm[w * 16 + row]);
+                L += sl[w * 16 + row];
+                const float4 a = *reinterpret_cast<const float4*>(so + (w * 16 + row) * SO + d);
+                O.x += a.x; O.y += a.y; O.z += a.z; O.w += a.w;
+            }
+            const int hd = head0 + row;
+            if (p.n_splits == 1) {
+                const float inv = L > 0.f ? 1.0f / L : 0.f;
+                *reinterpret_cast<uint2*>(p.out + ((size_t)q_tok * p.H + hd) * DH + d) =
+                    make_uint2(pack_bf16(O.x * inv, O.y * inv), pack_bf16(O.z * inv, O.w * inv));
+            } else {
+                const size_t slot = ((size_t)blockIdx.z * p.H + hd) * p.n_splits + split;
+                *reinterpret_cast<float4*>(p.part_o + slot * DH + d) = O;
+                if (d == 0) *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(M, L);
+            }
         }
     }
     if (p.n_splits == 1 || q_len <= 0) return;
@@ -393,6 +407,19 @@ attention_mma_kernel(const AttnParams p) {
     __threadfence();
     float* wts = reinterpret_cast<float*>(smem_raw);               // [rows_here][n_splits] weights 2^(m_s - M), then L per row
     float* sL = wts + 16 * p.n_splits;
+    // One thread per (row, four dimensions). Its first PRE slices are requested before the weights are
+    // worked out, so that the two round trips to L2 overlap.
+    const int mine = threadIdx.x;                                  // rows_here * D4 <= 16 * 64: up to 8 items a thread
+    const bool first_item = mine < rows_here * D4;
+    constexpr int PRE = 8;
+    float4 a0[PRE];
+    {
+        const int row = first_item ? mine / D4 : 0, d = first_item ? (mine % D4) * 4 : 0;
+        const float4* po = reinterpret_cast<const float4*>(p.part_o + (((size_t)blockIdx.z * p.H + head0 + row) * p.n_splits) * DH + d);
+#pragma unroll
+        for (int j = 0; j < PRE; ++j)
+            a0[j] = first_item && j < p.n_splits ? __ldcg(po + (size_t)j * D4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     for (int row = warp; row < rows_here; row += 4) {
         const float2* ml = reinterpret_cast<const float2*>(p.part_ml) + ((size_t)blockIdx.z * p.H + head0 + row) * p.n_splits;
         // every lane's (max, sum) pairs are loaded at once (up to 8 per lane: 256 slices), then used twice
@@ -424,17 +451,19 @@ attention_mma_kernel(const AttnParams p) {
         if (lane == 0) sL[row] = lsum;
     }
     __syncthreads();
-    // one thread per (row, four dimensions): sixteen 16-byte loads in flight, slices added in slice order
-    constexpr int D4 = DH / 4;
+    // sixteen 16-byte loads in flight, slices added in slice order
     for (int i = threadIdx.x; i < rows_here * D4; i += THREADS) {
         const int row = i / D4, d = (i % D4) * 4;
         const float4* po = reinterpret_cast<const float4*>(p.part_o + (((size_t)blockIdx.z * p.H + head0 + row) * p.n_splits) * DH + d);
         float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int s0 = 0; s0 < p.n_splits; s0 += 16) {
             float4 a[16];
+            const bool have = i == mine && s0 == 0;               // the first PRE slices are already here
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-                a[j] = s0 + j < p.n_splits ? __ldcg(po + (size_t)(s0 + j) * D4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < 16; ++j) {
+                if (j < PRE && have) a[j] = a0[j];
+                else a[j] = s0 + j < p.n_splits ? __ldcg(po + (size_t)(s0 + j) * D4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 const float f = s0 + j < p.n_splits ? wts[row * p.n_splits + s0 + j] : 0.f;
@@ -452,7 +481,7 @@ template <int DH, bool DECODE>
 int launch(const AttnParams& p, dim3 grid, cudaStream_t s) {
     static bool configured = false;                               // per template instance
     int bytes = Tiles<DH>::BYTES;                                  // the stages; reused by the merges
-    if (bytes < (int)((4 * 16 * DH + 128) * sizeof(float))) bytes = (int)((4 * 16 * DH + 128) * sizeof(float));
+    if (bytes < (int)((4 * 16 * (DH + 8) + 128) * sizeof(float))) bytes = (int)((4 * 16 * (DH + 8) + 128) * sizeof(float));
     if (bytes < (int)((16 * 256 + 16) * sizeof(float))) bytes = (int)((16 * 256 + 16) * sizeof(float));
     if (!configured) {
         BL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<DH, DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));

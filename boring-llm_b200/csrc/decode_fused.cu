@@ -44,7 +44,7 @@ __device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p, bool ok) {
 }
 
 template <int MT, int MODE>
-__global__ void __launch_bounds__(WARPS * 32, MT == 1 ? 3 : 1)
+__global__ void __launch_bounds__(WARPS * 32, MT == 1 ? (MODE == MODE_SWIGLU ? 3 : 2) : 1)
 fused_norm_gemm_kernel(const FusedParams p) {
     constexpr bool GLU = MODE == MODE_SWIGLU;
     constexpr int TOK = MT * 8;
@@ -126,22 +126,40 @@ fused_norm_gemm_kernel(const FusedParams p) {
             for (int k = lane * 4; k < K; k += 128) *reinterpret_cast<uint2*>(dst + k) = make_uint2(0u, 0u);
             continue;
         }
+        // The row is read in batches of NB 16-byte words per lane, all on their way at once; a row of up to
+        // NB * 128 values stays in registers between the sum of squares and the scaling.
         const float* src = p.x + (size_t)(p.row_idx ? p.row_idx[m] : m) * K;
+        constexpr int NB = 8;
+        float4 v[NB];
+        auto load_batch = [&](int k0) {
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                const int k = k0 + j * 128 + lane * 4;
+                v[j] = k < K ? *reinterpret_cast<const float4*>(src + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        };
+        const bool single = K <= NB * 128;
         float ss = 0.f;
-        for (int k = lane * 4; k < K; k += 128) {
-            const float4 v = *reinterpret_cast<const float4*>(src + k);
-            ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
+        for (int k0 = 0; k0 < K; k0 += NB * 128) {
+            load_batch(k0);
+#pragma unroll
+            for (int j = 0; j < NB; ++j) { ss += v[j].x * v[j].x; ss += v[j].y * v[j].y; ss += v[j].z * v[j].z; ss += v[j].w * v[j].w; }
         }
         ss = bl_warp_sum(ss);
         const float inv = 1.0f / sqrtf(ss / (float)K + p.eps);
-        for (int k = lane * 4; k < K; k += 128) {
-            const float4 v = *reinterpret_cast<const float4*>(src + k);
-            const float4 nw = *reinterpret_cast<const float4*>(nws + k);
-            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * inv * nw.x, v.y * inv * nw.y);
-            __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * inv * nw.z, v.w * inv * nw.w);
-            uint2 pk;
-            pk.x = *reinterpret_cast<unsigned*>(&lo); pk.y = *reinterpret_cast<unsigned*>(&hi);
-            *reinterpret_cast<uint2*>(dst + k) = pk;
+        for (int k0 = 0; k0 < K; k0 += NB * 128) {
+            if (!single) load_batch(k0);
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                const int k = k0 + j * 128 + lane * 4;
+                if (k >= K) continue;
+                const float4 nw = *reinterpret_cast<const float4*>(nws + k);
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v[j].x * inv * nw.x, v[j].y * inv * nw.y);
+                __nv_bfloat162 hi = __floats2bfloat162_rn(v[j].z * inv * nw.z, v[j].w * inv * nw.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<unsigned*>(&lo); pk.y = *reinterpret_cast<unsigned*>(&hi);
+                *reinterpret_cast<uint2*>(dst + k) = pk;
+            }
         }
     }
     __syncthreads();

@@ -60,7 +60,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
     // the current one is multiplied: a trip to L2 costs far more than the arithmetic of a batch. The first
     // batch of W, and the whole slice of W as an L2 prefetch, are issued before the kernel waits for its
     // predecessor, since W does not depend on it.
-    constexpr int UNROLL = (GLU || MT > 2 || NW > 8) ? 2 : 4;
+    constexpr int UNROLL = (GLU || MT > 2) ? 2 : 4;
     constexpr int STEP = UNROLL * NW * 32;
     struct Batch { uint4 a_lo[UNROLL], a_hi[UNROLL], g_lo[GLU ? UNROLL : 1], g_hi[GLU ? UNROLL : 1], b[UNROLL][MT]; };
     auto fetch_w = [&](Batch& bt, int kc0) {
