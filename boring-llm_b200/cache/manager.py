@@ -100,6 +100,8 @@ class RequestCache:
     slot: int
     num_tokens: int = 0
     tables: List[List[int]] = field(default_factory=list)
+    uid: int = 0          # unlike request_id never used twice by one manager
+    version: int = 0      # counts the changes of `tables`: (uid, version) names one state of the block tables
 
 
 class CacheManager:
@@ -147,6 +149,7 @@ class CacheManager:
         self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
         self._requests: Dict[object, RequestCache] = {}
         self._on_slot_assigned = on_slot_assigned
+        self._next_uid = 0
 
     # ---- requests -------------------------------------------------------------------------
     def has_free_slot(self) -> bool:
@@ -158,7 +161,8 @@ class CacheManager:
         if not self._free_slots:
             raise CacheError("no free request slot (check has_free_slot() before admitting)")
         slot = self._free_slots.pop()
-        rc = RequestCache(request_id, slot, 0, [[] for _ in self.paged_groups])
+        rc = RequestCache(request_id, slot, 0, [[] for _ in self.paged_groups], self._next_uid)
+        self._next_uid += 1
         self._requests[request_id] = rc
         if self._on_slot_assigned is not None:
             self._on_slot_assigned(slot)       # the storage zeroes the slot's state
@@ -169,6 +173,10 @@ class CacheManager:
             return self._requests[request_id]
         except KeyError:
             raise CacheError(f"request {request_id!r} is not live") from None
+
+    def find(self, request_id) -> Optional[RequestCache]:
+        """The live request's record, or None."""
+        return self._requests.get(request_id)
 
     def __contains__(self, request_id) -> bool:
         return request_id in self._requests
@@ -203,6 +211,8 @@ class CacheManager:
         for n, g, table in zip(need, self.paged_groups, rc.tables):
             for _ in range(n):
                 table.append(g.pool.take(request_id))
+            if n:
+                rc.version += 1
         return True
 
     def commit(self, request_id, n_new: int) -> None:
@@ -224,6 +234,7 @@ class CacheManager:
                 if table[i] >= 0:
                     g.pool.give_back(table[i], request_id)
                     table[i] = -1
+                    rc.version += 1
 
     def truncate(self, request_id, n_keep: int) -> None:
         """Keeps the first `n_keep` tokens (the reference truncates by setting a length,
@@ -240,6 +251,7 @@ class CacheManager:
                     raise CacheError("truncate: a window has already given pages of the kept prefix back")
             while len(table) > keep_pages:
                 p = table.pop()
+                rc.version += 1
                 if p >= 0:
                     g.pool.give_back(p, request_id)
         rc.num_tokens = n_keep

@@ -63,7 +63,38 @@ struct Tiles {
     static constexpr int ROW = DH + PAD;
     static constexpr int STAGE = 2 * KB * ROW;                    // elements: K tile then V tile
     static constexpr int BYTES = 2 * STAGE * (int)sizeof(__nv_bfloat16);
+    // decode: every warp has a ring of its own, one page of keys and values per stage
+    static constexpr int WSTAGE = 2 * PAGE * ROW;
+    static constexpr int WSTAGES = DH <= 128 ? 3 : 2;
+    static constexpr int DECODE_BYTES = 4 * WSTAGES * WSTAGE * (int)sizeof(__nv_bfloat16);
 };
+
+// Decode: one warp copies the page of keys [key0, key0 + 16) of one key/value head, and its values, into a stage
+// of its own. A page outside [lo, hi] or no longer in the table, and keys past hi, become zeros (see load_block).
+template <int DH>
+__device__ __forceinline__ void load_page(__nv_bfloat16* stage, const AttnParams& p, const int* table, int kvh,
+                                          int key0, int lo, int hi) {
+    constexpr int CH = DH / 8;
+    constexpr int ROW = Tiles<DH>::ROW;
+    const int lane = threadIdx.x & 31;
+    const int page = (key0 + PAGE - 1 >= lo && key0 <= hi) ? table[key0 / PAGE] : -1;
+    const size_t base = page >= 0 ? ((size_t)page * p.KV + kvh) * (PAGE * DH) : 0;
+#pragma unroll
+    for (int it = 0; it < (PAGE * CH + 31) / 32; ++it) {
+        const int i = lane + 32 * it;
+        if (i >= PAGE * CH) break;
+        const int row = i / CH, c = i % CH;
+        __nv_bfloat16* kd = stage + row * ROW + c * 8;
+        __nv_bfloat16* vd = kd + PAGE * ROW;
+        if (page >= 0 && key0 + row <= hi) {
+            cp_async16(kd, p.kc + base + i * 8);
+            cp_async16(vd, p.vc + base + i * 8);
+        } else {
+            *reinterpret_cast<uint4*>(kd) = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(vd) = make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+}
 
 // Copies keys [key0, key0 + 64) of one key/value head into a stage. The 16 keys of a page lie together in global
 // memory, so a page is copied as one contiguous run of 16-byte chunks (only the destination rows are padded).
@@ -104,15 +135,15 @@ __device__ __forceinline__ void load_block(__nv_bfloat16* stage, const AttnParam
     }
 }
 
-// One warp, 16 rows, NT n-tiles of 8 keys starting at key `koff` of the staged block.
-template <int DH, int NT>
+// One warp, 16 rows, NT n-tiles of 8 keys starting at key `koff` of the staged block (KROWS keys, then their values).
+template <int DH, int NT, int KROWS = KB>
 __device__ __forceinline__ void block_step(const __nv_bfloat16* stage, int koff, int key_abs0,
                                            const unsigned (&qf)[DH / 16][4], float (&o)[DH / 8][4],
                                            float (&m)[2], float (&l)[2], const int (&pos)[2], int window,
                                            float scale_log2) {
     constexpr int ROW = Tiles<DH>::ROW;
     const __nv_bfloat16* ks = stage;
-    const __nv_bfloat16* vs = stage + KB * ROW;
+    const __nv_bfloat16* vs = stage + KROWS * ROW;
     const int lane = threadIdx.x & 31, t = lane & 3;
     const int mi = lane >> 3, ri = lane & 7;                      // ldmatrix: which 8x8 matrix, which row of it
     float s[NT][4];
@@ -197,7 +228,7 @@ __device__ __forceinline__ void block_step(const __nv_bfloat16* stage, int koff,
 }
 
 template <int DH, bool DECODE>
-__global__ void __launch_bounds__(THREADS, (!DECODE && DH <= 64) ? 4 : 1)
+__global__ void __launch_bounds__(THREADS, DH <= 64 ? 4 : 1)
 attention_mma_kernel(const AttnParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -254,19 +285,21 @@ attention_mma_kernel(const AttnParams p) {
         b_begin = min(s0, b_end);
     }
     constexpr int STAGE = Tiles<DH>::STAGE;
+    constexpr int WSTAGE = Tiles<DH>::WSTAGE, WSTAGES = Tiles<DH>::WSTAGES;
     const int nb = b_end - b_begin;
     int issued = 0;                                   // blocks whose copies into shared memory have been started
+    __nv_bfloat16* wring = smem + warp * WSTAGES * WSTAGE;        // decode: this warp's ring
     if (DECODE) {
-        // The cached keys and values of earlier tokens do not depend on the kernel before: blocks that do not hold
-        // the newest token are copied into the two stages right away, and the rest of this slice is started on its
-        // way into L2 (the newest token's row is written there by that kernel; L2 stays coherent with it).
-        while (issued < 2 && issued < nb && (b_begin + issued + 1) * KB <= hi) {
-            load_block<DH>(smem + (issued & 1) * STAGE, p, table, kvh, (b_begin + issued) * KB, lo, hi);
+        // The cached keys and values of earlier tokens do not depend on the kernel before: pages that do not hold
+        // the newest token are copied into the warp's stages right away, and the rest of this slice is started on
+        // its way into L2 (the newest token's row is written there by that kernel; L2 stays coherent with it).
+        while (issued < WSTAGES && issued < nb && (b_begin + issued) * KB + warp * PAGE + PAGE <= hi) {
+            load_page<DH>(wring + issued * WSTAGE, p, table, kvh, (b_begin + issued) * KB + warp * PAGE, lo, hi);
             cp_async_commit();
             ++issued;
         }
         constexpr int LINES = PAGE * DH * 2 / 128 > 0 ? PAGE * DH * 2 / 128 : 1;     // 128-byte lines per (page, head)
-        const int first_page = (b_begin + issued) * (KB / PAGE), last_page = min(b_end * (KB / PAGE), hi / PAGE + 1);
+        const int first_page = (b_begin + min(nb, WSTAGES)) * (KB / PAGE), last_page = min(b_end * (KB / PAGE), hi / PAGE + 1);
         for (int i = threadIdx.x; i < (last_page - first_page) * LINES; i += THREADS) {
             const int pg = first_page + i / LINES;
             const int page = pg * PAGE + PAGE - 1 >= lo ? table[pg] : -1;
@@ -296,24 +329,45 @@ attention_mma_kernel(const AttnParams p) {
 #pragma unroll
     for (int n = 0; n < DH / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    while (issued < 2 && issued < nb) {               // two blocks in flight before the first is used
-        load_block<DH>(smem + (issued & 1) * STAGE, p, table, kvh, (b_begin + issued) * KB, lo, hi);
-        cp_async_commit();
-        ++issued;
-    }
-    for (int i = 0; i < nb; ++i) {
-        const int b = b_begin + i, st = i & 1;
-        if (issued - (i + 1) >= 1) cp_async_wait<1>(); else cp_async_wait<0>();       // block i has landed
-        __syncthreads();
-        if (DECODE)
-            block_step<DH, 2>(smem + st * STAGE, warp * 16, b * KB, qf, o, m, l, pos, p.window, p.scale_log2);
-        else
-            block_step<DH, 8>(smem + st * STAGE, 0, b * KB, qf, o, m, l, pos, p.window, p.scale_log2);
-        __syncthreads();
-        if (issued < nb) {                            // the stage just used takes the block after next
-            load_block<DH>(smem + st * STAGE, p, table, kvh, (b_begin + issued) * KB, lo, hi);
+    if (DECODE) {
+        // Every warp walks its own pages (page `warp` of each 64-key block) through its own ring: no barrier of the
+        // block inside the loop, and up to WSTAGES pages on their way per warp.
+        while (issued < WSTAGES && issued < nb) {
+            load_page<DH>(wring + issued * WSTAGE, p, table, kvh, (b_begin + issued) * KB + warp * PAGE, lo, hi);
             cp_async_commit();
             ++issued;
+        }
+        for (int i = 0; i < nb; ++i) {
+            const int pending = issued - (i + 1);     // copies started after page i's
+            if (pending >= 3) cp_async_wait<3>(); else if (pending == 2) cp_async_wait<2>();
+            else if (pending == 1) cp_async_wait<1>(); else cp_async_wait<0>();
+            __syncwarp();
+            __nv_bfloat16* st = wring + (i % WSTAGES) * WSTAGE;
+            block_step<DH, 2, PAGE>(st, 0, (b_begin + i) * KB + warp * PAGE, qf, o, m, l, pos, p.window, p.scale_log2);
+            __syncwarp();
+            if (issued < nb) {                        // the stage just used takes the page WSTAGES blocks on
+                load_page<DH>(st, p, table, kvh, (b_begin + issued) * KB + warp * PAGE, lo, hi);
+                cp_async_commit();
+                ++issued;
+            }
+        }
+    } else {
+        while (issued < 2 && issued < nb) {           // two blocks in flight before the first is used
+            load_block<DH>(smem + (issued & 1) * STAGE, p, table, kvh, (b_begin + issued) * KB, lo, hi);
+            cp_async_commit();
+            ++issued;
+        }
+        for (int i = 0; i < nb; ++i) {
+            const int b = b_begin + i, st = i & 1;
+            if (issued - (i + 1) >= 1) cp_async_wait<1>(); else cp_async_wait<0>();   // block i has landed
+            __syncthreads();
+            block_step<DH, 8>(smem + st * STAGE, 0, b * KB, qf, o, m, l, pos, p.window, p.scale_log2);
+            __syncthreads();
+            if (issued < nb) {                        // the stage just used takes the block after next
+                load_block<DH>(smem + st * STAGE, p, table, kvh, (b_begin + issued) * KB, lo, hi);
+                cp_async_commit();
+                ++issued;
+            }
         }
     }
     cp_async_wait<0>();
@@ -480,7 +534,7 @@ attention_mma_kernel(const AttnParams p) {
 template <int DH, bool DECODE>
 int launch(const AttnParams& p, dim3 grid, cudaStream_t s) {
     static bool configured = false;                               // per template instance
-    int bytes = Tiles<DH>::BYTES;                                  // the stages; reused by the merges
+    int bytes = DECODE ? Tiles<DH>::DECODE_BYTES : Tiles<DH>::BYTES;  // the stages; reused by the merges
     if (bytes < (int)((4 * 16 * (DH + 8) + 128) * sizeof(float))) bytes = (int)((4 * 16 * (DH + 8) + 128) * sizeof(float));
     if (bytes < (int)((16 * 256 + 16) * sizeof(float))) bytes = (int)((16 * 256 + 16) * sizeof(float));
     if (!configured) {

@@ -156,6 +156,116 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
     }
 }
 
+// The same product for very many columns (an output head): one warp owns 16 columns over the whole of K, so
+// nothing is summed across warps and no barrier is met; a warp streams its rows of W with two batches of
+// 16-byte loads in flight from start to end. Blocks of 8 warps cover 128 columns.
+template <int MT, int EPI, typename TO>
+__global__ void __launch_bounds__(256, MT <= 2 ? 2 : 1)
+gemm_skinny_cols_kernel(const __nv_bfloat16* x /* written by the kernel before: no read-only cache */,
+                        const __nv_bfloat16* __restrict__ w,
+                        const void* __restrict__ bias, int bias_dtype, TO* out,
+                        int M, int N, int K, int m_groups) {
+    static_assert(EPI != BL_EPI_SWIGLU, "two matrices per column: use the 16-column kernel");
+    constexpr int TOK = MT * 8;
+    constexpr int UNROLL = MT == 1 ? 4 : 2;
+    constexpr int STEP = UNROLL * 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = ((blockIdx.x / m_groups) * 8 + warp) * COLS;
+    const int m0 = (blockIdx.x % m_groups) * TOK;
+    float acc[MT][4];
+#pragma unroll
+    for (int j = 0; j < MT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+    const int r_lo = n0 + g, r_hi = n0 + g + 8;
+    const bool lo_ok = r_lo < N, hi_ok = r_hi < N;
+    const __nv_bfloat16* w_lo = w + (size_t)r_lo * K;
+    const __nv_bfloat16* w_hi = w + (size_t)r_hi * K;
+    struct Batch { uint4 a_lo[UNROLL], a_hi[UNROLL], b[UNROLL][MT]; };
+    auto fetch_w = [&](Batch& bt, int kc0) {
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = kc0 + u * 32 + 8 * t;
+            bt.a_lo[u] = ld16(w_lo + k, lo_ok && k < K);
+            bt.a_hi[u] = ld16(w_hi + k, hi_ok && k < K);
+        }
+    };
+    auto fetch_x = [&](Batch& bt, int kc0) {
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = kc0 + u * 32 + 8 * t;
+#pragma unroll
+            for (int j = 0; j < MT; ++j) {
+                const int tok = m0 + 8 * j + g;
+                bt.b[u][j] = (tok < M && k < K) ? *reinterpret_cast<const uint4*>(x + (size_t)tok * K + k)
+                                                : make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+    };
+    auto multiply = [&](const Batch& bt) {
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+            for (int j = 0; j < MT; ++j) {
+                mma_bf16(acc[j], bt.a_lo[u].x, bt.a_hi[u].x, bt.a_lo[u].y, bt.a_hi[u].y, bt.b[u][j].x, bt.b[u][j].y);
+                mma_bf16(acc[j], bt.a_lo[u].z, bt.a_hi[u].z, bt.a_lo[u].w, bt.a_hi[u].w, bt.b[u][j].z, bt.b[u][j].w);
+            }
+        }
+    };
+    Batch b0, b1;
+    bl_pdl_trigger();
+    fetch_w(b0, 0);
+    float e_lo = 0.f, e_hi = 0.f;
+    if (EPI == BL_EPI_BIAS) {
+        if (lo_ok) e_lo = bl_load_any(bias, bias_dtype, r_lo);
+        if (hi_ok) e_hi = bl_load_any(bias, bias_dtype, r_hi);
+    }
+    bl_pdl_wait();
+    fetch_x(b0, 0);
+    // the loop bounds are the same for every lane (the MMA needs all 32); two batches per trip keep the buffers' names
+    for (int kc0 = 0; kc0 < K; kc0 += 2 * STEP) {
+        const bool more1 = kc0 + STEP < K;
+        if (more1) { fetch_w(b1, kc0 + STEP); fetch_x(b1, kc0 + STEP); }
+        multiply(b0);
+        if (!more1) break;
+        if (kc0 + 2 * STEP < K) { fetch_w(b0, kc0 + 2 * STEP); fetch_x(b0, kc0 + 2 * STEP); }
+        multiply(b1);
+    }
+    // c0, c1: (column g, tokens 2t, 2t+1); c2, c3: (column g + 8, tokens 2t, 2t+1)
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int m = m0 + 8 * j + 2 * t + (i & 1);
+            const bool hi = i >= 2;
+            if (m >= M || !(hi ? hi_ok : lo_ok)) continue;
+            TO* dst = out + (size_t)m * N + (hi ? r_hi : r_lo);
+            float v = acc[j][i];
+            if (EPI == BL_EPI_BIAS) v += hi ? e_hi : e_lo;
+            if (EPI == BL_EPI_RESIDUAL) v += bl_load(dst);
+            bl_store(dst, v);
+        }
+    }
+}
+
+template <int MT, typename TO>
+int launch_cols(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K,
+                int epi, cudaStream_t s) {
+    const int m_groups = (M + MT * 8 - 1) / (MT * 8);
+    const int blocks = ((N + 8 * COLS - 1) / (8 * COLS)) * m_groups;
+#define BL_GO(E) BL_CUDA(bl_launch_dependent(gemm_skinny_cols_kernel<MT, E, TO>, dim3(blocks), dim3(256), 0, s, \
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, bias_dtype, (TO*)out, M, N, K, m_groups))
+    switch (epi) {
+        case BL_EPI_NONE: BL_GO(BL_EPI_NONE); break;
+        case BL_EPI_BIAS: BL_GO(BL_EPI_BIAS); break;
+        case BL_EPI_RESIDUAL: BL_GO(BL_EPI_RESIDUAL); break;
+        default: BL_FAIL("bl_gemm_skinny: the column kernel has no epilogue %d", epi);
+    }
+#undef BL_GO
+    return 0;
+}
+
 template <int MT, typename TO, int NW, bool DEEP>
 int launch_nw(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K,
               int epi, cudaStream_t s) {
@@ -180,6 +290,8 @@ int launch(const void* x, const void* w, const void* bias, int bias_dtype, void*
            int epi, cudaStream_t s) {
     const int m_groups = (M + MT * 8 - 1) / (MT * 8);
     const int blocks = ((N + COLS - 1) / COLS) * m_groups;
+    // the choice depends on N alone, so that a row's result is the same whatever else is in the batch
+    if ((N + COLS - 1) / COLS > 4 * 148 && epi != BL_EPI_SWIGLU) return launch_cols<MT, TO>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
     if (blocks > 4 * 148) return launch_nw<MT, TO, 8, false>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
     if (K >= 2048 && MT == 1 && epi != BL_EPI_SWIGLU) return launch_nw<1, TO, 16, true>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
     return launch_nw<MT, TO, 8, true>(x, w, bias, bias_dtype, out, M, N, K, epi, s);

@@ -73,7 +73,7 @@ class _DecodeGraph:
             self.h[name] = self.h[name].view(np.float32)
             self.d[name] = self.d[name].view(torch.float32)
         self.h["top_p"][:] = 1.0
-        self.row_owner = [None] * B                    # (request, pages per group) whose table a row holds
+        self.row_owner = [None] * B                    # (request uid, table version) whose table a row holds
         self.tables_dirty = True
         ar = np.arange(B, dtype=np.int32)
         self.h["tok_req"][:] = ar; self.h["logit_rows"][:] = ar; self.h["decode_reqs"][:] = ar
@@ -187,32 +187,33 @@ class ModelRunner:
             gr = self._graphs[rows] = _DecodeGraph(self, rows)
         gr.copied.synchronize()                        # the previous copy out of the pinned buffer is done
         h = gr.h
-        slot_list = []
-        for r, e in enumerate(entries):
-            rc = self.cache.get(e.request_id)
-            h["token_ids"][r] = int(e.tokens[0])
-            h["positions"][r] = rc.num_tokens
-            h["ctx_len"][r] = rc.num_tokens + 1
-            h["slots"][r] = rc.slot
-            slot_list.append(rc.slot)
-            owner = (e.request_id, tuple(len(t) for t in rc.tables), tuple(t[0] if t else -1 for t in rc.tables))
-            if gr.row_owner[r] != owner:               # a new request in this row, a new page, or a page a window freed
+        get = self.cache.get
+        rcs = [get(e.request_id) for e in entries]
+        slot_list = [rc.slot for rc in rcs]
+        h["token_ids"][:R] = [e.tokens[0] for e in entries]
+        h["positions"][:R] = [rc.num_tokens for rc in rcs]
+        np.add(h["positions"][:R], 1, out=h["ctx_len"][:R])
+        h["slots"][:R] = slot_list
+        owners = gr.row_owner
+        for r, rc in enumerate(rcs):
+            owner = (rc.uid, rc.version)
+            if owners[r] != owner:                     # a new request in this row, a new page, or a page a window freed
                 for gi, tab in enumerate(rc.tables):
                     row = h["tables"][gi, r]
                     row[:len(tab)] = tab
                     row[len(tab):] = -1
-                gr.row_owner[r] = owner if not any(g.spec.window > 0 for g in self.cache.paged_groups) else None
+                owners[r] = owner
                 gr.tables_dirty = True
-            if sampling is not None:
-                prm, rng, _ = sampling[r]
-                h["temperature"][r] = prm.temperature
-                h["top_k"][r] = prm.top_k
-                h["top_p"][r] = prm.top_p
-                h["min_p"][r] = prm.min_p
+        if sampling is not None:
+            h["temperature"][:R] = [s[0].temperature for s in sampling]
+            h["top_k"][:R] = [s[0].top_k for s in sampling]
+            h["top_p"][:R] = [s[0].top_p for s in sampling]
+            h["min_p"][:R] = [s[0].min_p for s in sampling]
+            for r, (prm, rng, _) in enumerate(sampling):
                 if prm.temperature > 0:
                     h["uniform"][r] = rng.next_f32()
-            else:
-                h["temperature"][r] = 0.0
+        else:
+            h["temperature"][:R] = 0.0
         gr.fill_padding(R)
         gr.ctx.slot_list = slot_list + [gr.trash_slot] * (rows - R)
         n_copy = gr.dynamic_ints if gr.tables_dirty else gr.small_ints
@@ -268,6 +269,8 @@ class ModelRunner:
         page = self.options.page_size
         if not entries:
             raise StepError("a step needs at least one entry")
+        if self._prepare_decode(entries):
+            return
         seen = set()
         for e in entries:
             if e.request_id in seen:
@@ -303,6 +306,30 @@ class ModelRunner:
         for e in entries:
             ok = self.cache.reserve(e.request_id, len(e.tokens))
             assert ok, "reservation was checked for the whole batch"
+
+    def _prepare_decode(self, entries: Sequence[StepEntry]) -> bool:
+        """The common case in one pass: every entry is one token of a different live request that still has
+        room on its last page. True: nothing is left to check or reserve. False: nothing was changed."""
+        find = self.cache.find
+        page, limit, vocab = self.options.page_size, self.options.ctx_size, self.vocab_size
+        seen = set()
+        for e in entries:
+            rc = find(e.request_id)
+            if rc is None or len(e.tokens) != 1 or rc.num_tokens >= limit:
+                return False
+            t = e.tokens[0]
+            if type(t) is not int or not 0 <= t < vocab:
+                return False
+            for w in e.want:
+                if w != 0:
+                    return False
+            room = rc.num_tokens < page * len(rc.tables[0]) if rc.tables else True
+            for tab in rc.tables[1:]:
+                room = room and rc.num_tokens < page * len(tab)
+            if not room:
+                return False
+            seen.add(e.request_id)
+        return len(seen) == len(entries)
 
     def _general_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Any mix of portions and single tokens: metadata built for this batch, kernels launched one by one."""

@@ -17,7 +17,7 @@ from .rotary import RotaryTable
 FUSED_MAX_ROWS = 32       # steps with at most this many rows take the fused norm + product kernels
 
 
-DECODE_TARGET_BLOCKS = 4 * 148     # blocks wanted in flight when one query's keys are cut into slices
+DECODE_SMS = 148                     # a launch of more blocks than fit the SMs at once would run a second, nearly empty round
 DECODE_MAX_SPLITS = 32               # more slices make the merge longer than they shorten the scan
 
 
@@ -140,6 +140,7 @@ class GQAAttention(Mixer):
             n = ctx.decode_reqs.shape[0]
             groups = self.KV * (-(-(self.H // self.KV) // 16))
             longest = ctx.max_decode_ctx if self.window <= 0 else min(ctx.max_decode_ctx, self.window + 64)
-            n_splits = max(1, min(-(-longest // 64), -(-DECODE_TARGET_BLOCKS // (n * groups)), DECODE_MAX_SPLITS))
+            resident = DECODE_SMS * (4 if self.dh <= 64 else 2 if self.dh <= 128 else 1)   # blocks the kernel fits at once
+            n_splits = max(1, min(-(-longest // 64), resident // (n * groups), DECODE_MAX_SPLITS))
             ops.attention_decode(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.decode_reqs, n_splits, out,
                                  self.H, self.window, self.scale)

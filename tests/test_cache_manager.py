@@ -166,3 +166,43 @@ def test_random_orders_never_lose_or_double_a_page(seed):
         m.free(rid)
     m.check()
     assert m.free_pages() == [m.num_pages] * len(m.paged_groups)
+
+
+def test_table_version_names_one_state_of_the_block_tables():
+    """(uid, version) changes exactly when a block table does; a request id used again gets a new uid."""
+    m = CacheManager([PagedKVSpec(1, 16, 0), PagedKVSpec(1, 16, 8)], page_size=4, capacity_tokens=64, max_requests=2)
+    a = m.add_request("a")
+    seen = {}
+
+    def check():
+        key = (a.uid, a.version)
+        state = tuple(tuple(t) for t in a.tables)
+        assert seen.setdefault(key, state) == state, "one name, two states"
+        return key
+
+    k0 = check()
+    assert m.reserve("a", 3)
+    k1 = check()
+    assert k1 != k0
+    m.commit("a", 3)
+    assert check() == k1                          # no page came or went
+    for _ in range(20):                           # token by token: new pages, and pages the window has passed
+        before = tuple(tuple(t) for t in a.tables)
+        kb = check()
+        assert m.reserve("a", 1)
+        m.commit("a", 1)
+        after = tuple(tuple(t) for t in a.tables)
+        assert (check() == kb) == (after == before)
+    m.free("a")
+    b = m.add_request("a")
+    assert b.uid != a.uid
+    assert m.find("a") is b and m.find("zz") is None
+    full = CacheManager([PagedKVSpec(1, 16, 0)], page_size=4, capacity_tokens=64, max_requests=1)
+    c = full.add_request("c")
+    assert full.reserve("c", 10)
+    full.commit("c", 10)
+    v = c.version
+    full.truncate("c", 9)                         # still three pages
+    assert c.version == v
+    full.truncate("c", 3)                         # two pages go back
+    assert c.version != v and len(c.tables[0]) == 1

@@ -312,7 +312,7 @@ def test_kernels_refuse_what_they_cannot_run():
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 7, 8), (8, 1152, 896), (5, 200, 96), (17, 129, 80), (33, 64, 264), (64, 4864 // 8, 176),
-                                   (100, 50, 64)])
+                                   (100, 50, 64), (3, 9500, 72), (20, 9481, 40), (40, 9600, 64)])
 def test_gemm_skinny_epilogues(M, N, K):
     o = ops()
     dtype = torch.bfloat16
