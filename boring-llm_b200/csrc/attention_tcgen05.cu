@@ -1,0 +1,463 @@
+// Paged causal grouped-query attention for prefill on the fifth-generation tensor cores (head size 64).
+//
+// A block is 128 consecutive new tokens of one request and one query head; thread r owns row r. It walks the
+// request's keys in blocks of 128 (eight 16-token pages) up to the diagonal:
+//   S = Q . K^T      tcgen05.mma, M 128 x N 128 x K 64, Q and the key block in shared memory (TMA, 128-byte
+//                    swizzle, K-major), S in tensor memory;
+//   softmax          every thread reads its row of S with tcgen05.ld (lane r of tensor memory is row r, so the
+//                    row maximum and sum need no shuffles), keeps the running maximum and sum in 32-bit, and
+//                    writes P = 2^(s - m) as bfloat16 into shared memory in the swizzled K-major layout;
+//   O_b = P . V      tcgen05.mma, M 128 x N 64 x K 128, V as it lies in its pages (keys x head size: the
+//                    MN-major form of the B operand), O_b in tensor memory;
+//   out = out * 2^(m_old - m) + O_b   in registers.
+// One thread issues the TMA copies and the MMAs; keys and values have two stages each, and the S of the next
+// block is computed while the threads add up the O_b of this one. Two blocks fit an SM (112 KB of shared
+// memory, 256 of 512 tensor-memory columns each), so one block's softmax overlaps the other's products.
+// Pages come from the request's block table, one TMA box (16 keys x 64) per page and tensor.
+//
+// Every wait on an mbarrier is bounded; when a bound runs out the block records a code in a status word, keeps
+// meeting its barriers without touching tensor memory, frees it and returns (bl_attention_prefill_tc_status).
+// Softmax is the online form of the reference's flash kernels (FlashAttnRegKernel, src/math_gpu.br:3309-3504);
+// scores are scaled after the dot product (src/math.br:319-322); a key j is visible to a query at position p
+// when j <= p and, with a window, j + window > p (:327-328).
+#include "common.cuh"
+#include "api.h"
+#include <cuda.h>
+
+namespace {
+
+constexpr int DH = 64;                 // head size
+constexpr int ROWS = 128;              // query rows per block
+constexpr int KBLK = 128;              // keys per block
+constexpr int PAGE = 16;
+constexpr int PAGES = KBLK / PAGE;     // TMA boxes per tensor and block
+constexpr int PAGE_BYTES = PAGE * DH * 2;
+constexpr int Q_BYTES = ROWS * DH * 2, KV_BYTES = KBLK * DH * 2, P_BYTES = ROWS * KBLK * 2;
+constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_P = OFF_V + 2 * KV_BYTES;
+constexpr int OFF_BARS = OFF_P + P_BYTES;
+constexpr int SMEM_BYTES = OFF_BARS + 256;
+constexpr int TMEM_COLS = 256;         // S: columns 0..127, O_b: columns 128..191
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+__device__ int g_status = 0;           // 0 = fine; else the code of the first wait that ran out
+
+struct Params {
+    __nv_bfloat16* out;
+    const int* cu_q; const int* ctx_len; const int* block_table; int max_pages;
+    const int* tiles;                  // [n][2] (request, first token of the 128-row tile within the request)
+    int H, KV, window; float scale_log2;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
+}
+// Bounded wait. False when the bound ran out or another thread of the block has given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (*give_up) return false;
+    }
+    *give_up = 1;
+    atomicCAS(&g_status, 0, code);
+    return false;
+}
+// Bounded wait that does not look at the give-up flag (a block that has given up waits for its own copies).
+__device__ __forceinline__ void mbar_wait_plain(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// what the threads wrote into shared memory becomes visible to the tensor cores and to TMA
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// 128-byte swizzle, rows of 128 bytes, groups of 8 rows 1024 bytes apart. The same descriptor serves a K-major
+// operand (rows = M or N, 64 elements of K per row) and an MN-major one (rows = K, 64 elements of N per row).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    const uint32_t lo = ((addr >> 4) & 0x3FFFu) | (1u << 16);                 // start address, leading offset 1 (unused: one 64-wide atom)
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);               // stride offset, version 1, SWIZZLE_128B
+    return ((uint64_t)hi << 32) | lo;
+}
+// kind::f16 instruction descriptors: D 32-bit, A and B bfloat16, N >> 3 at bit 17, M >> 4 at bit 24;
+// bit 16 set: B is MN-major (V lies keys x head size).
+constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(KBLK >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(DH >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+
+// 2^x on the special-function unit (about 2 ulp; 2^-inf = 0, tiny results flush to 0)
+__device__ __forceinline__ float bl_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+__global__ void __launch_bounds__(ROWS, 2)
+attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, const Params p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const uint32_t base = smem_u32(smem);
+    const uint32_t bars = base + OFF_BARS;
+    const uint32_t full_q = bars, full_k0 = bars + 8, full_v0 = bars + 24, s_done = bars + 40, o_done = bars + 48;
+    volatile int* give_up = reinterpret_cast<volatile int*>(smem + OFF_BARS + 64);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BARS + 72);
+    const int warp = threadIdx.x >> 5, row = threadIdx.x;
+    const bool leader = threadIdx.x == 0;
+
+    // late tiles of a request see the most keys: they go first, so that the short ones fill the tail
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int r = p.tiles[2 * tile], tok0 = p.tiles[2 * tile + 1];
+    const int head = blockIdx.y, kvh = head / (p.H / p.KV);
+    const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin, ctx = p.ctx_len[r];
+    const int* table = p.block_table + (size_t)r * p.max_pages;
+    const int rows_here = min(ROWS, q_len - tok0);                       // > 0 by construction of the tiles
+    const int p_first = ctx - q_len + tok0, p_last = p_first + rows_here - 1;
+    const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0, hi = p_last;
+    const int b_begin = lo / KBLK, nb = rows_here > 0 ? hi / KBLK + 1 - b_begin : 0;
+    const bool valid = row < rows_here;
+    const int pos = valid ? p_first + row : -1;                          // an invalid row sees nothing
+
+    if (leader) {
+        *give_up = (base & 1023u) ? 1 : 0;                               // the swizzled tiles need 1024-byte alignment
+        if (base & 1023u) atomicCAS(&g_status, 0, 9);
+        mbar_init(full_q, 1);
+        mbar_init(full_k0, 1); mbar_init(full_k0 + 8, 1);
+        mbar_init(full_v0, 1); mbar_init(full_v0 + 8, 1);
+        mbar_init(s_done, 1); mbar_init(o_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_s = tmem, tmem_o = tmem + KBLK;
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;               // this warp's 32 lanes of tensor memory
+
+    // Is page `pg` of key block `b` copied? Only pages that hold a key some row may see, and that the table still has.
+    auto page_of = [&](int b, int pg) -> int {
+        const int first = b * KBLK + pg * PAGE;
+        if (first > hi || first + PAGE - 1 < lo) return -1;
+        return table[first / PAGE];
+    };
+    // Warp 0 starts the copies of one tensor's block into a stage, one box per page: lane pg (0..7) holds the page
+    // number of page pg of the block in `page` (-1: not copied) and issues its own box, after lane 0 has told the
+    // barrier how many bytes to expect. Called by all 32 lanes of warp 0.
+    const int lane = threadIdx.x & 31;
+    auto load_pages = [&](const CUtensorMap* map, uint32_t dst, uint32_t bar, int page) {
+        const unsigned have = __ballot_sync(0xffffffffu, lane < PAGES && page >= 0);
+        if (lane == 0) {
+            if (have) mbar_expect_tx(bar, (uint32_t)__popc(have) * PAGE_BYTES); else mbar_arrive(bar);
+        }
+        __syncwarp();
+        if (lane < PAGES && page >= 0) tma_load_2d(dst + lane * PAGE_BYTES, map, bar, 0, (page * p.KV + kvh) * PAGE);
+        __syncwarp();
+    };
+    auto issue_s = [&](int i) {                                          // S = Q . K^T of the i-th block of this tile
+        const uint64_t a = smem_desc(base + OFF_Q), b = smem_desc(base + OFF_K + (i & 1) * KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < DH / 16; ++k) umma_bf16(tmem_s, a + 2 * k, b + 2 * k, IDESC_S, k != 0);
+        umma_commit(s_done);
+    };
+
+    bool ok = !*give_up;
+    int k_loads[2] = {0, 0}, v_loads[2] = {0, 0};                        // copies started per stage (warp 0 counts)
+    if (warp == 0 && nb > 0) {
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            const int page0 = lane < PAGES ? page_of(b_begin, lane) : -1;
+            const int page1 = lane < PAGES && nb > 1 ? page_of(b_begin + 1, lane) : -1;
+            if (leader) {
+                mbar_expect_tx(full_q, Q_BYTES);
+                tma_load_2d(base + OFF_Q, &map_q, full_q, head * DH, q_begin + tok0);
+            }
+            load_pages(&map_k, base + OFF_K, full_k0, page0); ++k_loads[0];
+            load_pages(&map_v, base + OFF_V, full_v0, page0); ++v_loads[0];
+            if (nb > 1) {
+                load_pages(&map_k, base + OFF_K + KV_BYTES, full_k0 + 8, page1); ++k_loads[1];
+                load_pages(&map_v, base + OFF_V + KV_BYTES, full_v0 + 8, page1); ++v_loads[1];
+            }
+            if (leader) {
+                ok = mbar_wait(full_q, 0, give_up, 1) && mbar_wait(full_k0, 0, give_up, 2);
+                if (ok) { fence_after_sync(); issue_s(0); }
+            }
+        }
+        __syncwarp();
+    }
+
+    float o[DH];
+#pragma unroll
+    for (int j = 0; j < DH; ++j) o[j] = 0.f;
+    float m = -INFINITY, l = 0.f;
+
+    for (int i = 0; i < nb; ++i) {
+        const int b = b_begin + i, st = i & 1;
+        const uint32_t par = (uint32_t)(i & 1), st_par = (uint32_t)((i >> 1) & 1);
+        // warp 0: the page numbers of the block after next are on their way while the scores are waited for
+        int page_next = -1;
+        if (warp == 0 && lane < PAGES && i + 2 < nb) page_next = page_of(b + 2, lane);
+        // ---- the scores of this block are in tensor memory
+        ok = mbar_wait(s_done, par, give_up, 3) && ok;
+        ok = __all_sync(0xffffffffu, ok);
+        fence_after_sync();
+        if (warp == 0 && ok && i + 2 < nb) {                             // the key stage is free: the block after next
+            load_pages(&map_k, base + OFF_K + st * KV_BYTES, full_k0 + 8 * st, page_next); ++k_loads[st];
+        }
+        const int k0 = b * KBLK;
+        // blocks that lie wholly inside what this row may see need no per-key test
+        const bool all_seen = k0 + KBLK - 1 <= pos && (p.window <= 0 || k0 + p.window > pos);
+        // Local key j of chunk c (keys k0 + 32 c + j) is visible when lo_c < j <= hi_c. Everything below is free of
+        // branches per key: a masked key becomes -inf before the maximum and before 2^x (2^-inf = 0).
+        const int hi_l = pos - k0, lo_l = p.window > 0 ? pos - p.window - k0 : -(1 << 30);
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < KBLK / 32; ++c) {                        // first pass: the row's maximum (of the raw scores)
+                uint32_t s[32];
+                tmem_ld32(tmem_s + lane_off + c * 32, s);
+                tmem_ld_wait();
+                if (all_seen) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(s[j]));
+                } else {
+                    const int hi_c = hi_l - c * 32, lo_c = lo_l - c * 32;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        mx[j & 3] = fmaxf(mx[j & 3], (j <= hi_c && j > lo_c) ? __uint_as_float(s[j]) : -INFINITY);
+                }
+            }
+        }
+        // the scale is positive: the maximum of the scaled scores is the scaled maximum
+        const float m_new = fmaxf(m, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;            // a row that has seen no key yet
+        const float alpha = bl_ex2(m - m_use);                           // 2^-inf = 0 on the first block
+        m = m_new;
+        float sm4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < KBLK / 32; ++c) {                        // second pass: P into shared memory
+                uint32_t s[32];
+                tmem_ld32(tmem_s + lane_off + c * 32, s);
+                tmem_ld_wait();
+                float e[32];
+                if (all_seen) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        e[j] = bl_ex2(fmaf(__uint_as_float(s[j]), p.scale_log2, -m_use));
+                        sm4[j & 3] += e[j];
+                    }
+                } else {
+                    const int hi_c = hi_l - c * 32, lo_c = lo_l - c * 32;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float x = fmaf(__uint_as_float(s[j]), p.scale_log2, -m_use);
+                        e[j] = bl_ex2((j <= hi_c && j > lo_c) ? x : -INFINITY);
+                        sm4[j & 3] += e[j];
+                    }
+                }
+                // 16-byte chunk cc of the row's 256 bytes: sub-tile cc / 8 (64 keys each), chunk cc % 8, swizzled by the row
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int cc = c * 4 + q4;
+                    unsigned char* dst = smem + OFF_P + (cc >> 3) * (ROWS * 128) + row * 128 + (((cc & 7) ^ (row & 7)) << 4);
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(e[8 * q4], e[8 * q4 + 1]), pack_bf16(e[8 * q4 + 2], e[8 * q4 + 3]),
+                                                                pack_bf16(e[8 * q4 + 4], e[8 * q4 + 5]), pack_bf16(e[8 * q4 + 6], e[8 * q4 + 7]));
+                }
+            }
+        }
+        const float sum = (sm4[0] + sm4[1]) + (sm4[2] + sm4[3]);
+        l = l * alpha + sum;
+        // ---- the values of this block: rows that were not copied, or that lie past the last key, become zeros
+        // (their P is 0, and 0 times whatever an old request left in a page must stay 0)
+        ok = mbar_wait(full_v0 + 8 * st, st_par, give_up, 4) && ok;
+        if (ok && k0 + KBLK - 1 > hi || ok && k0 < lo) {
+            for (int idx = threadIdx.x; idx < KBLK * 8; idx += ROWS) {   // (key row, 16-byte chunk); a row's chunks stay in the row
+                const int key = k0 + (idx >> 3);
+                const int first = key / PAGE * PAGE;
+                const bool copied = !(first > hi || first + PAGE - 1 < lo) && table[first / PAGE] >= 0;
+                if (!copied || key > hi)
+                    *reinterpret_cast<uint4*>(smem + OFF_V + st * KV_BYTES + (idx << 4)) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        fence_async_smem();
+        fence_before_sync();
+        __syncthreads();
+        ok = !*give_up && ok;
+        ok = __all_sync(0xffffffffu, ok);
+        if (leader && ok) {
+            fence_after_sync();
+            const uint64_t a0 = smem_desc(base + OFF_P), bv = smem_desc(base + OFF_V + st * KV_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < KBLK / 16; ++kk)                      // 16 keys a step: 32 bytes along P's rows, two 8-row groups of V
+                umma_bf16(tmem_o, a0 + (uint64_t)((kk >> 2) * (ROWS * 128 >> 4) + 2 * (kk & 3)), bv + (uint64_t)(kk * (2048 >> 4)),
+                          IDESC_PV, kk != 0);
+            umma_commit(o_done);
+            if (i + 1 < nb) {                                            // the next block's scores meanwhile
+                if (mbar_wait(full_k0 + 8 * (st ^ 1), (uint32_t)(((i + 1) >> 1) & 1), give_up, 5)) { fence_after_sync(); issue_s(i + 1); }
+            }
+        }
+        __syncwarp();
+        // ---- this block's share of the output
+        ok = mbar_wait(o_done, par, give_up, 6) && ok;
+        ok = __all_sync(0xffffffffu, ok);
+        fence_after_sync();
+        if (warp == 0 && ok && i + 2 < nb) {                             // the value stage is free
+            load_pages(&map_v, base + OFF_V + st * KV_BYTES, full_v0 + 8 * st, page_next); ++v_loads[st];
+        }
+        if (ok) {
+#pragma unroll
+            for (int c = 0; c < DH / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_o + lane_off + c * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o[c * 32 + j] = o[c * 32 + j] * alpha + __uint_as_float(v[j]);
+            }
+        }
+        fence_before_sync();                                             // the next P . V overwrites what was just read
+    }
+    if (ok && valid) {
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        __nv_bfloat16* dst = p.out + ((size_t)(q_begin + tok0 + row) * p.H + head) * DH;
+#pragma unroll
+        for (int j = 0; j < DH; j += 8)
+            *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16(o[j] * inv, o[j + 1] * inv), pack_bf16(o[j + 2] * inv, o[j + 3] * inv),
+                                                            pack_bf16(o[j + 4] * inv, o[j + 5] * inv), pack_bf16(o[j + 6] * inv, o[j + 7] * inv));
+    }
+    // a block that gave up lets its own copies land before its shared memory goes to the next block
+    if (leader && *give_up && !(base & 1023u)) {
+        mbar_wait_plain(full_q, 0);
+        for (int s2 = 0; s2 < 2; ++s2) {
+            if (k_loads[s2] > 0) mbar_wait_plain(full_k0 + 8 * s2, (uint32_t)((k_loads[s2] - 1) & 1));
+            if (v_loads[s2] > 0) mbar_wait_plain(full_v0 + 8 * s2, (uint32_t)((v_loads[s2] - 1) & 1));
+        }
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 0) {
+        fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)ptr;
+    }
+    return fn;
+}
+
+// A row-major [rows, cols] bfloat16 matrix as a 2-D tensor map with boxes of box_rows x 64 elements, 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, int box_rows) {
+    EncodeTiled enc = encode_fn();
+    if (enc == nullptr) BL_FAIL("bl_attention_prefill_tc: cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult res = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (res != CUDA_SUCCESS)
+        BL_FAIL("bl_attention_prefill_tc: cuTensorMapEncodeTiled failed with code %d (rows %lld, cols %d)", (int)res, rows, cols);
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int bl_attention_prefill_tc_supported(int dh, int page_size) { return dh == DH && page_size == PAGE; }
+
+// tiles[n_tiles][2] = (request, first token of a 128-token tile within the request's new tokens). T: rows of q and
+// out; n_pages: pages of the cache tensors (their first dimension).
+extern "C" int bl_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                                       const int* ctx_len, const int* block_table, int max_pages, const int* tiles,
+                                       int n_tiles, void* out, int T, int n_pages, int H, int KV, int dh, int page_size,
+                                       int window, float scale, void* stream) {
+    if (n_tiles <= 0) return 0;
+    if (dh != DH || page_size != PAGE)
+        BL_FAIL("bl_attention_prefill_tc: head size %d with pages of %d tokens is not built (64 with 16 only)", dh, page_size);
+    if (H <= 0 || KV <= 0 || H % KV != 0) BL_FAIL("bl_attention_prefill_tc: %d heads cannot share %d key/value heads", H, KV);
+    if (max_pages <= 0 || window < 0 || T <= 0 || n_pages <= 0) BL_FAIL("bl_attention_prefill_tc: bad sizes");
+    if (!(scale > 0.f)) BL_FAIL("bl_attention_prefill_tc: the scale of the scores must be positive (got %g)", (double)scale);
+    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15)
+        BL_FAIL("bl_attention_prefill_tc: q, the caches and out must be 16-byte aligned");
+    CUtensorMap mq, mk, mv;
+    if (make_map(&mq, q, T, H * DH, ROWS)) return 1;
+    if (make_map(&mk, k_cache, (long long)n_pages * KV * PAGE, DH, PAGE)) return 1;
+    if (make_map(&mv, v_cache, (long long)n_pages * KV * PAGE, DH, PAGE)) return 1;
+    Params p;
+    p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
+    p.tiles = tiles; p.H = H; p.KV = KV; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
+    static bool configured = false;
+    if (!configured) {
+        BL_CUDA(cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured = true;
+    }
+    // Launched in plain stream order: a block holds tensor memory from its first instructions on, and a dependent
+    // launch that started early could take that memory on an SM and then wait for this kernel.
+    attention_tc_kernel<<<dim3(n_tiles, H, 1), ROWS, SMEM_BYTES, (cudaStream_t)stream>>>(mq, mk, mv, p);
+    BL_CHECK_LAUNCH("bl_attention_prefill_tc");
+    return 0;
+}
+
+// Reads and clears the status word: 0 when no block has given up on a wait since the last call (1 q, 2 first keys,
+// 3 scores, 4 values, 5 next keys, 6 output, 9 shared memory not 1024-byte aligned). Synchronises the device.
+extern "C" int bl_attention_prefill_tc_status(int* status) {
+    int v = 0, zero = 0;
+    BL_CUDA(cudaMemcpyFromSymbol(&v, g_status, sizeof(int)));
+    if (v != 0) BL_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(int)));
+    *status = v;
+    return 0;
+}

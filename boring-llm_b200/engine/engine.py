@@ -70,6 +70,7 @@ class Engine:
         # the third item is the request itself: its token history is only put together if a penalty asks for it
         rows = [(r.params, r.rng, r) for r, s in zip(sched.requests, sched.samples) if s]
         sampled = self.runner.step_and_sample(sched.entries, rows, self.sampler)
+        self.runner.check_kernels()
         self.stats_time["engine_steps"] += 1
         self.stats_time["step_seconds"] += time.perf_counter() - t0
         return self.scheduler.apply(sched, sampled)

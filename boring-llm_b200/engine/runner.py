@@ -144,6 +144,7 @@ class ModelRunner:
         self.last_step_graph_kernels = 0               # kernels launched by the last step through a graph replay
         self.last_h2d_bytes = self.last_d2h_bytes = 0  # bytes the last step copied to and from the device
         self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._waits_unchecked = False                  # a step ran kernels with bounded waits since the last check
         self._table_width = -(-(-(-options.ctx_size // options.page_size)) // 8) * 8
 
     # ---- requests --------------------------------------------------------------------------------
@@ -342,8 +343,9 @@ class ModelRunner:
         width = max(1, max(len(t) for rc in rcs for t in (rc.tables or [[0]])))
         width = -(-width // 8) * 8
         tiles = [(r, t0) for r, e in enumerate(entries) if len(e.tokens) > 1 for t0 in range(0, len(e.tokens), 64)]
+        tiles128 = [t for t in tiles if t[1] % 128 == 0]
         singles = [r for r, e in enumerate(entries) if len(e.tokens) == 1]
-        n_ints = 3 * T + (R + 1) + 2 * R + N + G * R * width + 2 * len(tiles) + len(singles)
+        n_ints = 3 * T + (R + 1) + 2 * R + N + G * R * width + 2 * len(tiles) + 2 * len(tiles128) + len(singles)
         host = self._host_buffer(n_ints)
         h = host.numpy()
         o = 0
@@ -357,9 +359,11 @@ class ModelRunner:
         tables = h[o:o + G * R * width].reshape(G, R, width); o += G * R * width
         tables[...] = -1
         tile_arr = h[o:o + 2 * len(tiles)]; o += 2 * len(tiles)
+        tile128_arr = h[o:o + 2 * len(tiles128)]; o += 2 * len(tiles128)
         single_arr = h[o:o + len(singles)]; o += len(singles)
         if tiles:
             tile_arr[:] = np.asarray(tiles, dtype=np.int32).reshape(-1)
+            tile128_arr[:] = np.asarray(tiles128, dtype=np.int32).reshape(-1)
         if singles:
             single_arr[:] = np.asarray(singles, dtype=np.int32)
         t0 = 0
@@ -401,12 +405,24 @@ class ModelRunner:
             q_lens=q_lens, ctx_lens=ctx_lens, slot_list=slot_list, storage=self.storage, fast=self.fast)
         if tiles:
             ctx.prefill_tiles = take(2 * len(tiles)).view(len(tiles), 2)
+            ctx.prefill_tiles128 = take(2 * len(tiles128)).view(len(tiles128), 2)
+            ctx.prefill_tokens = sum(n for n in q_lens if n > 1)
         if singles:
             ctx.decode_reqs = take(len(singles))
             ctx.max_decode_ctx = max(ctx_lens[r] for r in singles)
         logits = self.model.forward(ctx)
+        self._waits_unchecked = self.fast and self.dtype == torch.bfloat16
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps += 1
         self.tokens_run += T
         return logits
+
+    def check_kernels(self) -> None:
+        """The tcgen05 kernels bound every wait on a barrier and record it when a bound runs out instead of
+        hanging; the results of such a launch are invalid. Raises then. Call after the step's results have been
+        read (it synchronises); costs nothing when no such kernel ran since the last call."""
+        if self._waits_unchecked:
+            self._waits_unchecked = False
+            from ..kernels import ops
+            ops.check_status()

@@ -18,6 +18,7 @@ FUSED_MAX_ROWS = 32       # steps with at most this many rows take the fused nor
 
 
 DECODE_SMS = 148                     # a launch of more blocks than fit the SMs at once would run a second, nearly empty round
+PREFILL_TC_MIN_TOKENS = 1024         # steps with fewer prompt tokens keep the 64-row tiles of the mma.sync kernel
 DECODE_MAX_SPLITS = 32               # more slices make the merge longer than they shorten the scan
 
 
@@ -127,15 +128,21 @@ class GQAAttention(Mixer):
 
     def attend(self, ctx, q, k_cache, v_cache, table, out):
         """Tensor-core kernels for bfloat16 where they are built (pages of 16, common head sizes): one launch for
-        the requests with several new tokens, one for those with a single token. Otherwise, and always in
+        the requests with several new tokens (the tcgen05 kernel for head size 64 when the step has many of them),
+        one for those with a single token. Otherwise, and always in
         float32, the plain kernel."""
         if not (ctx.fast and ops.attention_mma_supported(q.dtype, self.dh, k_cache.shape[2])):
             ops.attention_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, out,
                                 self.H, self.window, self.scale)
             return
         if ctx.prefill_tiles is not None:
-            ops.attention_prefill(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.prefill_tiles, out,
-                                  self.H, self.window, self.scale)
+            if (ctx.prefill_tiles128 is not None and ctx.prefill_tokens >= PREFILL_TC_MIN_TOKENS
+                    and ops.attention_prefill_tc_supported(q.dtype, self.dh, k_cache.shape[2])):
+                ops.attention_prefill_tc(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.prefill_tiles128, out,
+                                         self.H, self.window, self.scale)
+            else:
+                ops.attention_prefill(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.prefill_tiles, out,
+                                      self.H, self.window, self.scale)
         if ctx.decode_reqs is not None:
             n = ctx.decode_reqs.shape[0]
             groups = self.KV * (-(-(self.H // self.KV) // 16))

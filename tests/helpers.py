@@ -27,8 +27,14 @@ TINY = {
               num_attention_heads=5, num_key_value_heads=5, head_dim=48, intermediate_size=176, vocab_size=211,
               rope_theta=500000.0, rms_norm_eps=3e-6, tie_word_embeddings=False, max_position_embeddings=512,
               use_sliding_window=True, sliding_window=20, max_window_layers=1),
+    # 2 layers, head 64 (the head size of the tcgen05 prefill attention), 4 heads in 2 groups, hidden != heads * head,
+    # a window of 150 positions (more than one key block of 128) on the second layer
+    "D": dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=2, hidden_size=128,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=192, vocab_size=300,
+              rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=1024,
+              use_sliding_window=True, sliding_window=150, max_window_layers=1),
 }
-SEEDS = {"A": 0, "B": 1, "C": 2}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
 
 # Largest allowed |engine - plain| as a fraction of the largest |plain logit| of the compared rows.
 # float32: every product is a 32-bit FMA chain of a few hundred terms through a few layers (about 1e3 ulps

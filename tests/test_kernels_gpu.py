@@ -395,6 +395,40 @@ def test_attention_mma_window_edges(window):
     attention_case(o, mma_attention, torch.bfloat16, 4, 2, 64, [200, 131], [150, 1], window, 6)
 
 
+def tc_attention(q, kc, vc, tok_req, cu_q, ctx_len, table, out, H, window, scale):
+    """The tcgen05 prefill kernel for requests with several new tokens (tiles of 128 rows), the decode kernel for the rest."""
+    o = ops()
+    cu = cu_q.cpu().tolist()
+    q_lens = [b - a for a, b in zip(cu[:-1], cu[1:])]
+    tiles = [(r, t0) for r, n in enumerate(q_lens) if n > 1 for t0 in range(0, n, 128)]
+    singles = [r for r, n in enumerate(q_lens) if n == 1]
+    out.fill_(float("nan"))
+    if tiles:
+        o.attention_prefill_tc(q, kc, vc, cu_q, ctx_len, table, torch.tensor(tiles, dtype=torch.int32, device=DEV), out, H, window, scale)
+        o.check_status()
+    if singles:
+        o.attention_decode(q, kc, vc, cu_q, ctx_len, table, torch.tensor(singles, dtype=torch.int32, device=DEV), 1, out, H, window, scale)
+
+
+@pytest.mark.parametrize("H,KV", [(14, 2), (7, 1), (4, 4)])
+def test_attention_tcgen05_shapes(H, KV):
+    """Prefill attention on tcgen05: portions over an existing cache with offsets off every tile and page size,
+    whole prompts of several key blocks, rows past the end of a tile, several requests in one launch."""
+    o = ops()
+    assert o.attention_prefill_tc_supported(torch.bfloat16, 64, 16)
+    assert not o.attention_prefill_tc_supported(torch.bfloat16, 128, 16)
+    assert not o.attention_prefill_tc_supported(torch.float32, 64, 16)
+    attention_case(o, tc_attention, torch.bfloat16, H, KV, 64, [333, 70, 16, 33], [70, 70, 2, 17], 0, 2)
+    attention_case(o, tc_attention, torch.bfloat16, H, KV, 64, [64, 65, 128, 200, 129], [64, 1, 128, 1, 65], 0, 3)
+    attention_case(o, tc_attention, torch.bfloat16, H, KV, 64, [1000, 515, 257], [1000, 300, 129], 0, 4)
+
+
+@pytest.mark.parametrize("window", [1, 15, 16, 17, 100, 128, 200])
+def test_attention_tcgen05_window_edges(window):
+    o = ops()
+    attention_case(o, tc_attention, torch.bfloat16, 4, 2, 64, [200, 131, 700, 17], [150, 1, 500, 2], window, 6)
+
+
 def test_attention_mma_is_refused_where_it_is_not_built():
     from boring_llm_b200.kernels import KernelError
     o = ops()

@@ -12,7 +12,8 @@ import helpers
 pytestmark = pytest.mark.gpu
 
 # prompts + continuations, as lengths: a one-token prompt, lengths off every page edge, one over 4 pages
-LENGTHS = {"A": [7 + 8, 16 + 8, 33 + 8, 70], "B": [1 + 12, 5 + 12, 19 + 12, 64 + 12], "C": [3, 45, 64, 90]}
+LENGTHS = {"A": [7 + 8, 16 + 8, 33 + 8, 70], "B": [1 + 12, 5 + 12, 19 + 12, 64 + 12], "C": [3, 45, 64, 90],
+           "D": [300, 131, 260, 17]}
 
 
 def requests_for(name):
@@ -77,6 +78,34 @@ def test_all_ways_of_cutting_agree_with_the_plain_implementation(model_folders, 
         for mode, rows in by_mode.items():
             worst = max(np.abs(rows[k] - ref[k]).max() for k in ref)
             assert worst <= 2e-6 * scale, f"{name}: '{mode}' differs from 'whole' by {worst:.3e}"
+
+
+def test_tcgen05_prefill_attention_inside_the_engine(model_folders, expected, monkeypatch):
+    """Head size 64: every portion of more than one token goes through the tcgen05 attention kernel (its
+    threshold is set to 0 for the test): whole prompts of several key blocks, portions of changing size over
+    an existing cache, a window wider than a key block, portions beside single tokens on reused pages."""
+    from boring_llm_b200.kernels import ops
+    from boring_llm_b200.parts import attention
+    monkeypatch.setattr(attention, "PREFILL_TC_MIN_TOKENS", 0)
+    calls = []
+    real = ops.attention_prefill_tc
+    monkeypatch.setattr(ops, "attention_prefill_tc", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    d = model_folders("D", "bfloat16")
+    reqs = requests_for("D")
+    want = expected("D", "bfloat16")
+    for mode, cut in [("whole", helpers.cut_whole), ("changing portions", None)]:
+        steps, n0 = [], 0
+        for i, (rid, toks) in enumerate(reqs.items()):
+            sizes = cut(toks) if cut else helpers.cut_varying(toks, 23 + i)
+            s = helpers.solo_trace(rid, toks, sizes, n0)
+            steps += s; n0 += len(s)
+        outputs, runner = helpers.run_inprocess(d, "bfloat16", steps, max_tokens=320)
+        check_rows(helpers.collect_rows(steps, outputs), want, "bfloat16", f"D {mode}")
+    steps, peak = helpers.mixed_trace(reqs, seed=7, max_live=4)
+    outputs, runner = helpers.run_inprocess(d, "bfloat16", steps, max_tokens=peak)
+    check_rows(helpers.collect_rows(steps, outputs), want, "bfloat16", "D mixed")
+    assert len(calls) >= 2 * len(reqs), "the tcgen05 kernel did not run"
+    ops.check_status()
 
 
 @pytest.mark.parametrize("name", ["A", "B", "C"])
