@@ -10,13 +10,17 @@
 //   O_b = P . V      tcgen05.mma, M 128 x N 64 x K 128, V as it lies in its pages (keys x head size: the
 //                    MN-major form of the B operand), O_b in tensor memory;
 //   out = out * 2^(m_old - m) + O_b   in registers.
-// One thread issues the TMA copies and the MMAs; keys and values have two stages each, and the S of the next
-// block is computed while the threads add up the O_b of this one. Two blocks fit an SM (112 KB of shared
-// memory, 256 of 512 tensor-memory columns each), so one block's softmax overlaps the other's products.
+// Seven warps: four own the rows, one issues the MMAs (lane 0), two issue the TMA copies of keys and of values
+// (a box costs its issuing lane about 0.1 us, so the sixteen boxes of a block are kept off the MMAs' path).
+// They meet only at mbarriers. Keys, values, scores, P and the shares of the output all have two buffers: the
+// scores of block i + 2 and the product of block i run while the row warps work on block i + 1, whose
+// arithmetic (the 2^x of the special-function unit above all) is what bounds the kernel. One block per SM
+// (144 KB of shared memory, all 512 tensor-memory columns).
 // Pages come from the request's block table, one TMA box (16 keys x 64) per page and tensor.
 //
-// Every wait on an mbarrier is bounded; when a bound runs out the block records a code in a status word, keeps
-// meeting its barriers without touching tensor memory, frees it and returns (bl_attention_prefill_tc_status).
+// Every wait on an mbarrier is bounded; when a bound runs out the block records a code in a status word, its
+// warps leave their loops (the others see the flag at their next wait), its own copies are waited for, and it
+// frees its tensor memory and returns (bl_attention_prefill_tc_status).
 // Softmax is the online form of the reference's flash kernels (FlashAttnRegKernel, src/math_gpu.br:3309-3504);
 // scores are scaled after the dot product (src/math.br:319-322); a key j is visible to a query at position p
 // when j <= p and, with a window, j + window > p (:327-328).
@@ -32,11 +36,12 @@ constexpr int KBLK = 128;              // keys per block
 constexpr int PAGE = 16;
 constexpr int PAGES = KBLK / PAGE;     // TMA boxes per tensor and block
 constexpr int PAGE_BYTES = PAGE * DH * 2;
+constexpr int THREADS = ROWS + 96;     // four warps of rows, one that issues the MMAs, two that copy
 constexpr int Q_BYTES = ROWS * DH * 2, KV_BYTES = KBLK * DH * 2, P_BYTES = ROWS * KBLK * 2;
 constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_P = OFF_V + 2 * KV_BYTES;
-constexpr int OFF_BARS = OFF_P + P_BYTES;
+constexpr int OFF_BARS = OFF_P + 2 * P_BYTES;
 constexpr int SMEM_BYTES = OFF_BARS + 256;
-constexpr int TMEM_COLS = 256;         // S: columns 0..127, O_b: columns 128..191
+constexpr int TMEM_COLS = 512;         // scores: 2 x 128 columns; shares of the output: 2 x 64 columns from column 256
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 __device__ int g_status = 0;           // 0 = fine; else the code of the first wait that ran out
@@ -130,17 +135,19 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-__global__ void __launch_bounds__(ROWS, 2)
+__global__ void __launch_bounds__(THREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const Params p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t base = smem_u32(smem);
     const uint32_t bars = base + OFF_BARS;
-    const uint32_t full_q = bars, full_k0 = bars + 8, full_v0 = bars + 24, s_done = bars + 40, o_done = bars + 48;
-    volatile int* give_up = reinterpret_cast<volatile int*>(smem + OFF_BARS + 64);
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BARS + 72);
-    const int warp = threadIdx.x >> 5, row = threadIdx.x;
-    const bool leader = threadIdx.x == 0;
+    // barriers, 8 bytes each: q, keys[2], values[2], scores[2], outputs[2], P written[2]
+    const uint32_t full_q = bars, full_k0 = bars + 8, full_v0 = bars + 24, s_done0 = bars + 40, o_done0 = bars + 56,
+                   p_ready0 = bars + 72;
+    volatile int* give_up = reinterpret_cast<volatile int*>(smem + OFF_BARS + 96);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BARS + 104);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, row = threadIdx.x;
+    const bool issuer = warp == ROWS / 32;                               // the first four warps own rows, the fifth issues the MMAs
 
     // late tiles of a request see the most keys: they go first, so that the short ones fill the tail
     const int tile = gridDim.x - 1 - blockIdx.x;
@@ -152,19 +159,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int p_first = ctx - q_len + tok0, p_last = p_first + rows_here - 1;
     const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0, hi = p_last;
     const int b_begin = lo / KBLK, nb = rows_here > 0 ? hi / KBLK + 1 - b_begin : 0;
-    const bool valid = row < rows_here;
-    const int pos = valid ? p_first + row : -1;                          // an invalid row sees nothing
 
-    if (leader) {
+    if (threadIdx.x == 0) {
         *give_up = (base & 1023u) ? 1 : 0;                               // the swizzled tiles need 1024-byte alignment
         if (base & 1023u) atomicCAS(&g_status, 0, 9);
         mbar_init(full_q, 1);
-        mbar_init(full_k0, 1); mbar_init(full_k0 + 8, 1);
-        mbar_init(full_v0, 1); mbar_init(full_v0 + 8, 1);
-        mbar_init(s_done, 1); mbar_init(o_done, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(full_k0 + 8 * i, 1); mbar_init(full_v0 + 8 * i, 1);
+            mbar_init(s_done0 + 8 * i, 1); mbar_init(o_done0 + 8 * i, 1);
+            mbar_init(p_ready0 + 8 * i, ROWS);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) {
+    if (issuer) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      :: "r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
@@ -174,90 +181,128 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_s = tmem, tmem_o = tmem + KBLK;
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;               // this warp's 32 lanes of tensor memory
-
-    // Is page `pg` of key block `b` copied? Only pages that hold a key some row may see, and that the table still has.
-    auto page_of = [&](int b, int pg) -> int {
-        const int first = b * KBLK + pg * PAGE;
-        if (first > hi || first + PAGE - 1 < lo) return -1;
-        return table[first / PAGE];
-    };
-    // Warp 0 starts the copies of one tensor's block into a stage, one box per page: lane pg (0..7) holds the page
-    // number of page pg of the block in `page` (-1: not copied) and issues its own box, after lane 0 has told the
-    // barrier how many bytes to expect. Called by all 32 lanes of warp 0.
-    const int lane = threadIdx.x & 31;
-    auto load_pages = [&](const CUtensorMap* map, uint32_t dst, uint32_t bar, int page) {
-        const unsigned have = __ballot_sync(0xffffffffu, lane < PAGES && page >= 0);
-        if (lane == 0) {
-            if (have) mbar_expect_tx(bar, (uint32_t)__popc(have) * PAGE_BYTES); else mbar_arrive(bar);
-        }
-        __syncwarp();
-        if (lane < PAGES && page >= 0) tma_load_2d(dst + lane * PAGE_BYTES, map, bar, 0, (page * p.KV + kvh) * PAGE);
-        __syncwarp();
-    };
-    auto issue_s = [&](int i) {                                          // S = Q . K^T of the i-th block of this tile
-        const uint64_t a = smem_desc(base + OFF_Q), b = smem_desc(base + OFF_K + (i & 1) * KV_BYTES);
-#pragma unroll
-        for (int k = 0; k < DH / 16; ++k) umma_bf16(tmem_s, a + 2 * k, b + 2 * k, IDESC_S, k != 0);
-        umma_commit(s_done);
-    };
-
+    // scores of block i: columns (i & 1) * 128 ..; its share of the output: columns 256 + (i & 1) * 64 ..
     bool ok = !*give_up;
-    int k_loads[2] = {0, 0}, v_loads[2] = {0, 0};                        // copies started per stage (warp 0 counts)
-    if (warp == 0 && nb > 0) {
+
+    if (warp >= ROWS / 32 + 1) {
+        // ================= warps 5 and 6: the copies of the keys (and q) and of the values, a page per lane 0..7.
+        // Issuing a box costs its lane about 0.1 us, one lane after the other: two warps keep the sixteen boxes of a
+        // block off the path of the MMAs.
+        const bool keys = warp == ROWS / 32 + 1;
+        const CUtensorMap* map = keys ? &map_k : &map_v;
+        const uint32_t full0 = keys ? full_k0 : full_v0, free0 = keys ? s_done0 : o_done0, off = keys ? OFF_K : OFF_V;
+        auto page_of = [&](int b, int pg) -> int {                       // -1: no row may see a key of this page
+            const int first = b * KBLK + pg * PAGE;
+            if (first > hi || first + PAGE - 1 < lo) return -1;
+            return table[first / PAGE];
+        };
+        int loads[2] = {0, 0};                                           // copies started per stage
         ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-            const int page0 = lane < PAGES ? page_of(b_begin, lane) : -1;
-            const int page1 = lane < PAGES && nb > 1 ? page_of(b_begin + 1, lane) : -1;
-            if (leader) {
-                mbar_expect_tx(full_q, Q_BYTES);
-                tma_load_2d(base + OFF_Q, &map_q, full_q, head * DH, q_begin + tok0);
+        if (ok && keys && lane == 0) {
+            mbar_expect_tx(full_q, Q_BYTES);
+            tma_load_2d(base + OFF_Q, &map_q, full_q, head * DH, q_begin + tok0);
+        }
+        int page = lane < PAGES && nb > 0 ? page_of(b_begin, lane) : -1;
+        for (int i = 0; ok && i < nb; ++i) {
+            const int st = i & 1;
+            const int page_next = lane < PAGES && i + 1 < nb ? page_of(b_begin + i + 1, lane) : -1;   // on its way during this block's copies
+            if (i >= 2) {                                                // the stage is free once block i - 2 has been multiplied
+                if (lane == 0) ok = mbar_wait(free0 + 8 * st, (uint32_t)(((i - 2) >> 1) & 1), give_up, keys ? 3 : 7);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
             }
-            load_pages(&map_k, base + OFF_K, full_k0, page0); ++k_loads[0];
-            load_pages(&map_v, base + OFF_V, full_v0, page0); ++v_loads[0];
-            if (nb > 1) {
-                load_pages(&map_k, base + OFF_K + KV_BYTES, full_k0 + 8, page1); ++k_loads[1];
-                load_pages(&map_v, base + OFF_V + KV_BYTES, full_v0 + 8, page1); ++v_loads[1];
+            const uint32_t bar = full0 + 8 * st, dst = base + off + st * KV_BYTES;
+            const unsigned have = __ballot_sync(0xffffffffu, lane < PAGES && page >= 0);
+            if (lane == 0) {
+                if (have) mbar_expect_tx(bar, (uint32_t)__popc(have) * PAGE_BYTES); else mbar_arrive(bar);
             }
-            if (leader) {
-                ok = mbar_wait(full_q, 0, give_up, 1) && mbar_wait(full_k0, 0, give_up, 2);
-                if (ok) { fence_after_sync(); issue_s(0); }
+            __syncwarp();
+            if (lane < PAGES && page >= 0) tma_load_2d(dst + lane * PAGE_BYTES, map, bar, 0, (page * p.KV + kvh) * PAGE);
+            __syncwarp();
+            ++loads[st];
+            page = page_next;
+        }
+        // a block that gave up lets its own copies land before its shared memory goes to the next block
+        if (lane == 0 && *give_up && !(base & 1023u)) {
+            if (keys) mbar_wait_plain(full_q, 0);
+            for (int s2 = 0; s2 < 2; ++s2)
+                if (loads[s2] > 0) mbar_wait_plain(full0 + 8 * s2, (uint32_t)((loads[s2] - 1) & 1));
+        }
+    } else if (issuer) {
+        // ================= the fifth warp: lane 0 issues the MMAs
+        auto issue_s = [&](int i) {                                      // S = Q . K^T of the i-th block of this tile
+            const uint64_t a = smem_desc(base + OFF_Q), b = smem_desc(base + OFF_K + (i & 1) * KV_BYTES);
+#pragma unroll
+            for (int k = 0; k < DH / 16; ++k) umma_bf16(tmem + (i & 1) * KBLK, a + 2 * k, b + 2 * k, IDESC_S, k != 0);
+            umma_commit(s_done0 + 8 * (i & 1));
+        };
+        if (lane == 0 && ok && nb > 0) {
+            ok = mbar_wait(full_q, 0, give_up, 1) && mbar_wait(full_k0, 0, give_up, 2);
+            if (ok) { fence_after_sync(); issue_s(0); }
+            if (ok && nb > 1) {
+                ok = mbar_wait(full_k0 + 8, 0, give_up, 2);
+                if (ok) { fence_after_sync(); issue_s(1); }
+            }
+            for (int i = 0; ok && i < nb; ++i) {
+                const int st = i & 1;
+                const uint32_t par = (uint32_t)((i >> 1) & 1);
+                // P of block i is in shared memory (and its scores have been read): O_i = P . V
+                ok = mbar_wait(p_ready0 + 8 * st, par, give_up, 4) && mbar_wait(full_v0 + 8 * st, par, give_up, 5);
+                if (!ok) break;
+                fence_after_sync();
+                const uint64_t a0 = smem_desc(base + OFF_P + st * P_BYTES), bv = smem_desc(base + OFF_V + st * KV_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < KBLK / 16; ++kk)                  // 16 keys a step: 32 bytes along P's rows, two 8-row groups of V
+                    umma_bf16(tmem + 2 * KBLK + st * DH, a0 + (uint64_t)((kk >> 2) * (ROWS * 128 >> 4) + 2 * (kk & 3)),
+                              bv + (uint64_t)(kk * (2048 >> 4)), IDESC_PV, kk != 0);
+                umma_commit(o_done0 + 8 * st);
+                if (i + 2 < nb) {                                        // the scores of block i + 2 go where those of block i were
+                    ok = mbar_wait(full_k0 + 8 * st, par ^ 1, give_up, 6);
+                    if (ok) { fence_after_sync(); issue_s(i + 2); }
+                }
             }
         }
         __syncwarp();
-    }
-
-    float o[DH];
+    } else {
+        // ================= four warps: thread `row` owns one query row
+        const bool valid = row < rows_here;
+        const int pos = valid ? p_first + row : -1;                      // an invalid row sees nothing
+        const uint32_t lane_off = (uint32_t)(warp * 32) << 16;           // this warp's 32 lanes of tensor memory
+        float o[DH];
 #pragma unroll
-    for (int j = 0; j < DH; ++j) o[j] = 0.f;
-    float m = -INFINITY, l = 0.f;
-
-    for (int i = 0; i < nb; ++i) {
-        const int b = b_begin + i, st = i & 1;
-        const uint32_t par = (uint32_t)(i & 1), st_par = (uint32_t)((i >> 1) & 1);
-        // warp 0: the page numbers of the block after next are on their way while the scores are waited for
-        int page_next = -1;
-        if (warp == 0 && lane < PAGES && i + 2 < nb) page_next = page_of(b + 2, lane);
-        // ---- the scores of this block are in tensor memory
-        ok = mbar_wait(s_done, par, give_up, 3) && ok;
-        ok = __all_sync(0xffffffffu, ok);
-        fence_after_sync();
-        if (warp == 0 && ok && i + 2 < nb) {                             // the key stage is free: the block after next
-            load_pages(&map_k, base + OFF_K + st * KV_BYTES, full_k0 + 8 * st, page_next); ++k_loads[st];
-        }
-        const int k0 = b * KBLK;
-        // blocks that lie wholly inside what this row may see need no per-key test
-        const bool all_seen = k0 + KBLK - 1 <= pos && (p.window <= 0 || k0 + p.window > pos);
-        // Local key j of chunk c (keys k0 + 32 c + j) is visible when lo_c < j <= hi_c. Everything below is free of
-        // branches per key: a masked key becomes -inf before the maximum and before 2^x (2^-inf = 0).
-        const int hi_l = pos - k0, lo_l = p.window > 0 ? pos - p.window - k0 : -(1 << 30);
-        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        if (ok) {
+        for (int j = 0; j < DH; ++j) o[j] = 0.f;
+        float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
+        // out = out * alpha + O_i, read from tensor memory one block late (the product runs meanwhile)
+        auto add_output = [&](int i, float alpha) {
+            const uint32_t t_o = tmem + 2 * KBLK + (i & 1) * DH + lane_off;
+#pragma unroll
+            for (int c = 0; c < DH / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(t_o + c * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o[c * 32 + j] = o[c * 32 + j] * alpha + __uint_as_float(v[j]);
+            }
+        };
+        for (int i = 0; i < nb; ++i) {
+            const int b = b_begin + i, st = i & 1;
+            const uint32_t par = (uint32_t)((i >> 1) & 1);
+            ok = mbar_wait(s_done0 + 8 * st, par, give_up, 8) && ok;
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            fence_after_sync();
+            const uint32_t t_s = tmem + st * KBLK + lane_off;
+            const int k0 = b * KBLK;
+            // blocks that lie wholly inside what this row may see need no per-key test
+            const bool all_seen = k0 + KBLK - 1 <= pos && (p.window <= 0 || k0 + p.window > pos);
+            // Local key j of chunk c (keys k0 + 32 c + j) is visible when lo_c < j <= hi_c. Everything below is free of
+            // branches per key: a masked key becomes -inf before the maximum and before 2^x (2^-inf = 0).
+            const int hi_l = pos - k0, lo_l = p.window > 0 ? pos - p.window - k0 : -(1 << 30);
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll 1
             for (int c = 0; c < KBLK / 32; ++c) {                        // first pass: the row's maximum (of the raw scores)
                 uint32_t s[32];
-                tmem_ld32(tmem_s + lane_off + c * 32, s);
+                tmem_ld32(t_s + c * 32, s);
                 tmem_ld_wait();
                 if (all_seen) {
 #pragma unroll
@@ -269,18 +314,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         mx[j & 3] = fmaxf(mx[j & 3], (j <= hi_c && j > lo_c) ? __uint_as_float(s[j]) : -INFINITY);
                 }
             }
-        }
-        // the scale is positive: the maximum of the scaled scores is the scaled maximum
-        const float m_new = fmaxf(m, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2);
-        const float m_use = m_new == -INFINITY ? 0.f : m_new;            // a row that has seen no key yet
-        const float alpha = bl_ex2(m - m_use);                           // 2^-inf = 0 on the first block
-        m = m_new;
-        float sm4[4] = {0.f, 0.f, 0.f, 0.f};
-        if (ok) {
+            // the scale is positive: the maximum of the scaled scores is the scaled maximum
+            const float m_new = fmaxf(m, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;        // a row that has seen no key yet
+            const float alpha = bl_ex2(m - m_use);                       // 2^-inf = 0 on the first block
+            m = m_new;
+            float sm4[4] = {0.f, 0.f, 0.f, 0.f};
+            unsigned char* p_tile = smem + OFF_P + st * P_BYTES;
 #pragma unroll 1
             for (int c = 0; c < KBLK / 32; ++c) {                        // second pass: P into shared memory
                 uint32_t s[32];
-                tmem_ld32(tmem_s + lane_off + c * 32, s);
+                tmem_ld32(t_s + c * 32, s);
                 tmem_ld_wait();
                 float e[32];
                 if (all_seen) {
@@ -302,82 +346,59 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
                     const int cc = c * 4 + q4;
-                    unsigned char* dst = smem + OFF_P + (cc >> 3) * (ROWS * 128) + row * 128 + (((cc & 7) ^ (row & 7)) << 4);
+                    unsigned char* dst = p_tile + (cc >> 3) * (ROWS * 128) + row * 128 + (((cc & 7) ^ (row & 7)) << 4);
                     *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(e[8 * q4], e[8 * q4 + 1]), pack_bf16(e[8 * q4 + 2], e[8 * q4 + 3]),
                                                                 pack_bf16(e[8 * q4 + 4], e[8 * q4 + 5]), pack_bf16(e[8 * q4 + 6], e[8 * q4 + 7]));
                 }
             }
-        }
-        const float sum = (sm4[0] + sm4[1]) + (sm4[2] + sm4[3]);
-        l = l * alpha + sum;
-        // ---- the values of this block: rows that were not copied, or that lie past the last key, become zeros
-        // (their P is 0, and 0 times whatever an old request left in a page must stay 0)
-        ok = mbar_wait(full_v0 + 8 * st, st_par, give_up, 4) && ok;
-        if (ok && k0 + KBLK - 1 > hi || ok && k0 < lo) {
-            for (int idx = threadIdx.x; idx < KBLK * 8; idx += ROWS) {   // (key row, 16-byte chunk); a row's chunks stay in the row
-                const int key = k0 + (idx >> 3);
-                const int first = key / PAGE * PAGE;
-                const bool copied = !(first > hi || first + PAGE - 1 < lo) && table[first / PAGE] >= 0;
-                if (!copied || key > hi)
-                    *reinterpret_cast<uint4*>(smem + OFF_V + st * KV_BYTES + (idx << 4)) = make_uint4(0u, 0u, 0u, 0u);
+            l = l * alpha + ((sm4[0] + sm4[1]) + (sm4[2] + sm4[3]));
+            // the values of this block: rows that were not copied, or that lie past the last key, become zeros
+            // (their P is 0, and 0 times whatever an old request left in a page must stay 0)
+            if (k0 + KBLK - 1 > hi || k0 < lo) {
+                ok = mbar_wait(full_v0 + 8 * st, par, give_up, 10) && ok;
+                if (ok) {
+                    for (int idx = threadIdx.x; idx < KBLK * 8; idx += ROWS) {   // (key row, 16-byte chunk); a row's chunks stay in the row
+                        const int key = k0 + (idx >> 3);
+                        const int first = key / PAGE * PAGE;
+                        const bool copied = !(first > hi || first + PAGE - 1 < lo) && table[first / PAGE] >= 0;
+                        if (!copied || key > hi)
+                            *reinterpret_cast<uint4*>(smem + OFF_V + st * KV_BYTES + (idx << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
             }
-        }
-        fence_async_smem();
-        fence_before_sync();
-        __syncthreads();
-        ok = !*give_up && ok;
-        ok = __all_sync(0xffffffffu, ok);
-        if (leader && ok) {
-            fence_after_sync();
-            const uint64_t a0 = smem_desc(base + OFF_P), bv = smem_desc(base + OFF_V + st * KV_BYTES);
-#pragma unroll
-            for (int kk = 0; kk < KBLK / 16; ++kk)                      // 16 keys a step: 32 bytes along P's rows, two 8-row groups of V
-                umma_bf16(tmem_o, a0 + (uint64_t)((kk >> 2) * (ROWS * 128 >> 4) + 2 * (kk & 3)), bv + (uint64_t)(kk * (2048 >> 4)),
-                          IDESC_PV, kk != 0);
-            umma_commit(o_done);
-            if (i + 1 < nb) {                                            // the next block's scores meanwhile
-                if (mbar_wait(full_k0 + 8 * (st ^ 1), (uint32_t)(((i + 1) >> 1) & 1), give_up, 5)) { fence_after_sync(); issue_s(i + 1); }
+            fence_async_smem();
+            fence_before_sync();
+            mbar_arrive(p_ready0 + 8 * st);
+            // the share of the block before: its product has had a whole softmax to finish
+            if (i > 0) {
+                ok = mbar_wait(o_done0 + 8 * (st ^ 1), (uint32_t)(((i - 1) >> 1) & 1), give_up, 11) && ok;
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                fence_after_sync();
+                add_output(i - 1, alpha_prev);
             }
+            alpha_prev = alpha;
         }
-        __syncwarp();
-        // ---- this block's share of the output
-        ok = mbar_wait(o_done, par, give_up, 6) && ok;
-        ok = __all_sync(0xffffffffu, ok);
-        fence_after_sync();
-        if (warp == 0 && ok && i + 2 < nb) {                             // the value stage is free
-            load_pages(&map_v, base + OFF_V + st * KV_BYTES, full_v0 + 8 * st, page_next); ++v_loads[st];
-        }
-        if (ok) {
+        if (nb > 0) {
+            ok = mbar_wait(o_done0 + 8 * ((nb - 1) & 1), (uint32_t)(((nb - 1) >> 1) & 1), give_up, 12) && ok;
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                fence_after_sync();
+                add_output(nb - 1, alpha_prev);
+                if (valid) {
+                    const float inv = l > 0.f ? 1.0f / l : 0.f;
+                    __nv_bfloat16* dst = p.out + ((size_t)(q_begin + tok0 + row) * p.H + head) * DH;
 #pragma unroll
-            for (int c = 0; c < DH / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem_o + lane_off + c * 32, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) o[c * 32 + j] = o[c * 32 + j] * alpha + __uint_as_float(v[j]);
+                    for (int j = 0; j < DH; j += 8)
+                        *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16(o[j] * inv, o[j + 1] * inv), pack_bf16(o[j + 2] * inv, o[j + 3] * inv),
+                                                                        pack_bf16(o[j + 4] * inv, o[j + 5] * inv), pack_bf16(o[j + 6] * inv, o[j + 7] * inv));
+                }
             }
-        }
-        fence_before_sync();                                             // the next P . V overwrites what was just read
-    }
-    if (ok && valid) {
-        const float inv = l > 0.f ? 1.0f / l : 0.f;
-        __nv_bfloat16* dst = p.out + ((size_t)(q_begin + tok0 + row) * p.H + head) * DH;
-#pragma unroll
-        for (int j = 0; j < DH; j += 8)
-            *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16(o[j] * inv, o[j + 1] * inv), pack_bf16(o[j + 2] * inv, o[j + 3] * inv),
-                                                            pack_bf16(o[j + 4] * inv, o[j + 5] * inv), pack_bf16(o[j + 6] * inv, o[j + 7] * inv));
-    }
-    // a block that gave up lets its own copies land before its shared memory goes to the next block
-    if (leader && *give_up && !(base & 1023u)) {
-        mbar_wait_plain(full_q, 0);
-        for (int s2 = 0; s2 < 2; ++s2) {
-            if (k_loads[s2] > 0) mbar_wait_plain(full_k0 + 8 * s2, (uint32_t)((k_loads[s2] - 1) & 1));
-            if (v_loads[s2] > 0) mbar_wait_plain(full_v0 + 8 * s2, (uint32_t)((v_loads[s2] - 1) & 1));
         }
     }
     fence_before_sync();
     __syncthreads();
-    if (warp == 0) {
+    if (issuer) {
         fence_after_sync();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(TMEM_COLS) : "memory");
     }
@@ -447,13 +468,15 @@ extern "C" int bl_attention_prefill_tc(const void* q, const void* k_cache, const
     }
     // Launched in plain stream order: a block holds tensor memory from its first instructions on, and a dependent
     // launch that started early could take that memory on an SM and then wait for this kernel.
-    attention_tc_kernel<<<dim3(n_tiles, H, 1), ROWS, SMEM_BYTES, (cudaStream_t)stream>>>(mq, mk, mv, p);
+    attention_tc_kernel<<<dim3(n_tiles, H, 1), THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(mq, mk, mv, p);
     BL_CHECK_LAUNCH("bl_attention_prefill_tc");
     return 0;
 }
 
-// Reads and clears the status word: 0 when no block has given up on a wait since the last call (1 q, 2 first keys,
-// 3 scores, 4 values, 5 next keys, 6 output, 9 shared memory not 1024-byte aligned). Synchronises the device.
+// Reads and clears the status word: 0 when no block has given up on a wait since the last call. Codes name the
+// wait: 1 q, 2 first keys, 3 / 7 a stage of keys / values to become free, 4 P, 5 values, 6 keys of the block after
+// next, 8 scores, 10 values (row warps), 11 / 12 a share of the output, 9 shared memory not 1024-byte aligned.
+// Synchronises the device.
 extern "C" int bl_attention_prefill_tc_status(int* status) {
     int v = 0, zero = 0;
     BL_CUDA(cudaMemcpyFromSymbol(&v, g_status, sizeof(int)));

@@ -88,18 +88,76 @@ __global__ void rmsnorm_kernel(const float* x /* written by the kernel before: n
         bl_store(y + (size_t)r * d + i, x[src + i] * inv * bl_load_any(w, w_dtype, i));
 }
 
+// The same with one warp per row and 16-byte loads, for widths that are a multiple of 4: a row of up to 1,024
+// values stays in registers between the sum of squares and the scaling; nothing is shared between warps, so
+// there is no barrier. A lane adds its squares in index order and the warp's sum is a fixed butterfly: the
+// result of a row depends only on d.
+template <typename TY>
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_kernel(const float* x /* written by the kernel before: no read-only cache */,
+                    const int* __restrict__ row_idx, const void* __restrict__ w, int w_dtype, TY* __restrict__ y,
+                    int rows, int d, float eps) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const float* src = x + (size_t)(row_idx ? row_idx[r] : r) * d;
+    constexpr int NB = 8;
+    float4 v[NB];
+    auto load_batch = [&](int k0) {
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            const int k = k0 + j * 128 + lane * 4;
+            v[j] = k < d ? *reinterpret_cast<const float4*>(src + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    const bool single = d <= NB * 128;
+    float ss = 0.f;
+    for (int k0 = 0; k0 < d; k0 += NB * 128) {
+        load_batch(k0);
+#pragma unroll
+        for (int j = 0; j < NB; ++j) { ss += v[j].x * v[j].x; ss += v[j].y * v[j].y; ss += v[j].z * v[j].z; ss += v[j].w * v[j].w; }
+    }
+    ss = bl_warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    TY* dst = y + (size_t)r * d;
+    for (int k0 = 0; k0 < d; k0 += NB * 128) {
+        if (!single) load_batch(k0);
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            const int k = k0 + j * 128 + lane * 4;
+            if (k >= d) continue;
+            const float o0 = v[j].x * inv * bl_load_any(w, w_dtype, k), o1 = v[j].y * inv * bl_load_any(w, w_dtype, k + 1);
+            const float o2 = v[j].z * inv * bl_load_any(w, w_dtype, k + 2), o3 = v[j].w * inv * bl_load_any(w, w_dtype, k + 3);
+            if (sizeof(TY) == 4) {
+                *reinterpret_cast<float4*>(dst + k) = make_float4(o0, o1, o2, o3);
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(o0, o1), hi = __floats2bfloat162_rn(o2, o3);
+                uint2 pk;
+                pk.x = *reinterpret_cast<unsigned*>(&lo); pk.y = *reinterpret_cast<unsigned*>(&hi);
+                *reinterpret_cast<uint2*>(dst + k) = pk;
+            }
+        }
+    }
+}
+
 extern "C" int bl_rmsnorm(const float* x, const int* row_idx, const void* w, int w_dtype, void* y,
                           int y_dtype, int rows, int d, float eps, void* stream) {
     if (rows <= 0) return 0;
     if (d <= 0) BL_FAIL("bl_rmsnorm: bad width %d", d);
     if (w_dtype != BL_F32 && w_dtype != BL_BF16) BL_FAIL("bl_rmsnorm: unknown weight dtype %d", w_dtype);
+    if (y_dtype != BL_F32 && y_dtype != BL_BF16) BL_FAIL("bl_rmsnorm: unknown output dtype %d", y_dtype);
     cudaStream_t s = (cudaStream_t)stream;
-    if (y_dtype == BL_F32)
+    const bool wide = d % 4 == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0;      // 16-byte loads and stores of whole rows
+    if (wide && y_dtype == BL_F32)
+        BL_CUDA(bl_launch_dependent(rmsnorm_rows_kernel<float>, dim3((rows + 7) / 8), dim3(256), 0, s, x, row_idx, w, w_dtype, (float*)y, rows, d, eps));
+    else if (wide)
+        BL_CUDA(bl_launch_dependent(rmsnorm_rows_kernel<__nv_bfloat16>, dim3((rows + 7) / 8), dim3(256), 0, s, x, row_idx, w, w_dtype, (__nv_bfloat16*)y, rows, d, eps));
+    else if (y_dtype == BL_F32)
         BL_CUDA(bl_launch_dependent(rmsnorm_kernel<float>, dim3(rows), dim3(128), 0, s, x, row_idx, w, w_dtype, (float*)y, d, eps));
-    else if (y_dtype == BL_BF16)
-        BL_CUDA(bl_launch_dependent(rmsnorm_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, s, x, row_idx, w, w_dtype, (__nv_bfloat16*)y, d, eps));
     else
-        BL_FAIL("bl_rmsnorm: unknown output dtype %d", y_dtype);
+        BL_CUDA(bl_launch_dependent(rmsnorm_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, s, x, row_idx, w, w_dtype, (__nv_bfloat16*)y, d, eps));
     BL_CHECK_LAUNCH("bl_rmsnorm");
     return 0;
 }
@@ -126,6 +184,14 @@ __global__ void rope_kv_write_kernel(const float* qkv /* written by the kernel b
         if (page < 0) write = false;       // the host never schedules this; keep memory safe anyway
         page_base = ((size_t)(page < 0 ? 0 : page) * KV) * page_size * dh + (size_t)(pos % page_size) * dh;
     }
+    // the rotation of pair j is the same for every head of the token: worked out once, into shared memory
+    extern __shared__ float cs_sn[];                     // [rot_half] cos, then [rot_half] sin
+    for (int j = threadIdx.x; j < rot_half; j += blockDim.x) {
+        const float angle = (float)pos * inv_freq[j];
+        cs_sn[j] = cosf(angle) * mscale;
+        cs_sn[rot_half + j] = sinf(angle) * mscale;
+    }
+    __syncthreads();
     const int n_rot_items = (H + KV) * half;
     for (int it = threadIdx.x; it < n_rot_items; it += blockDim.x) {
         const int head = it / half, j = it % half;
@@ -134,9 +200,8 @@ __global__ void rope_kv_write_kernel(const float* qkv /* written by the kernel b
         float c = 1.f, s = 0.f;
         if (j < rot_half) {
             i0 = j; i1 = j + rot_half;
-            const float angle = (float)pos * inv_freq[j];
-            c = cosf(angle) * mscale;
-            s = sinf(angle) * mscale;
+            c = cs_sn[j];
+            s = cs_sn[rot_half + j];
         } else {                                         // dimensions past the rotated ones pass through
             i0 = 2 * j; i1 = 2 * j + 1;
         }
@@ -170,10 +235,10 @@ extern "C" int bl_rope_kv_write(const float* qkv, const int* positions, const in
     if ((k_cache == nullptr) != (v_cache == nullptr)) BL_FAIL("bl_rope_kv_write: key and value cache must both be given or both be null");
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == BL_F32)
-        BL_CUDA(bl_launch_dependent(rope_kv_write_kernel<float>, dim3(T), dim3(128), 0, s, qkv, positions, tok_req, block_table,
+        BL_CUDA(bl_launch_dependent(rope_kv_write_kernel<float>, dim3(T), dim3(128), (size_t)rot_half * 8, s, qkv, positions, tok_req, block_table,
             max_pages, inv_freq, rot_half, mscale, (float*)q_out, (float*)k_cache, (float*)v_cache, H, KV, dh, page_size));
     else if (dtype == BL_BF16)
-        BL_CUDA(bl_launch_dependent(rope_kv_write_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, s, qkv, positions, tok_req,
+        BL_CUDA(bl_launch_dependent(rope_kv_write_kernel<__nv_bfloat16>, dim3(T), dim3(128), (size_t)rot_half * 8, s, qkv, positions, tok_req,
             block_table, max_pages, inv_freq, rot_half, mscale, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
             (__nv_bfloat16*)v_cache, H, KV, dh, page_size));
     else
