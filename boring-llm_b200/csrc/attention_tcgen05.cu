@@ -1,7 +1,7 @@
 // Paged causal grouped-query attention for prefill on the fifth-generation tensor cores (head size 64).
 //
-// A block is 128 consecutive new tokens of one request and one query head; thread r owns row r. It walks the
-// request's keys in blocks of 128 (eight 16-token pages) up to the diagonal:
+// A block is 256 consecutive new tokens of one request (two row tiles of 128) and one query head; a thread owns
+// one row. It walks the request's keys in blocks of 128 (eight 16-token pages) up to the diagonal; per tile:
 //   S = Q . K^T      tcgen05.mma, M 128 x N 128 x K 64, Q and the key block in shared memory (TMA, 128-byte
 //                    swizzle, K-major), S in tensor memory;
 //   softmax          every thread reads its row of S with tcgen05.ld (lane r of tensor memory is row r, so the
@@ -10,12 +10,13 @@
 //   O_b = P . V      tcgen05.mma, M 128 x N 64 x K 128, V as it lies in its pages (keys x head size: the
 //                    MN-major form of the B operand), O_b in tensor memory;
 //   out = out * 2^(m_old - m) + O_b   in registers.
-// Seven warps: four own the rows, one issues the MMAs (lane 0), two issue the TMA copies of keys and of values
-// (a box costs its issuing lane about 0.1 us, so the sixteen boxes of a block are kept off the MMAs' path).
-// They meet only at mbarriers. Keys, values, scores, P and the shares of the output all have two buffers: the
-// scores of block i + 2 and the product of block i run while the row warps work on block i + 1, whose
-// arithmetic (the 2^x of the special-function unit above all) is what bounds the kernel. One block per SM
-// (144 KB of shared memory, all 512 tensor-memory columns).
+// Eleven warps: four per row tile own the rows, one issues the MMAs of both tiles (lane 0), two issue the TMA
+// copies of keys and of values (a box costs its issuing lane about 0.1 us, so the sixteen boxes of a block are
+// kept off the MMAs' path). They meet only at mbarriers. Keys and values (shared by the two tiles), P and the
+// shares of the output have two buffers each, the scores one per tile: while one tile's warps wait for their
+// next scores the other tile's warps have the SM's arithmetic (the 2^x of the special-function unit above all,
+// which bounds the kernel), and the products run beside both. One block per SM (224 KB of shared memory, all
+// 512 tensor-memory columns).
 // Pages come from the request's block table, one TMA box (16 keys x 64) per page and tensor.
 //
 // Every wait on an mbarrier is bounded; when a bound runs out the block records a code in a status word, its
@@ -36,12 +37,13 @@ constexpr int KBLK = 128;              // keys per block
 constexpr int PAGE = 16;
 constexpr int PAGES = KBLK / PAGE;     // TMA boxes per tensor and block
 constexpr int PAGE_BYTES = PAGE * DH * 2;
-constexpr int THREADS = ROWS + 96;     // four warps of rows, one that issues the MMAs, two that copy
-constexpr int Q_BYTES = ROWS * DH * 2, KV_BYTES = KBLK * DH * 2, P_BYTES = ROWS * KBLK * 2;
+constexpr int TILES = 2;               // row tiles of 128 per block: two groups of four warps take turns on the SM
+constexpr int THREADS = TILES * ROWS + 96;   // the row warps, one warp that issues the MMAs, two that copy
+constexpr int Q_BYTES = TILES * ROWS * DH * 2, KV_BYTES = KBLK * DH * 2, P_BYTES = ROWS * KBLK * 2;
 constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_P = OFF_V + 2 * KV_BYTES;
-constexpr int OFF_BARS = OFF_P + 2 * P_BYTES;
+constexpr int OFF_BARS = OFF_P + 2 * TILES * P_BYTES;                // P: [tile][stage]
 constexpr int SMEM_BYTES = OFF_BARS + 256;
-constexpr int TMEM_COLS = 512;         // scores: 2 x 128 columns; shares of the output: 2 x 64 columns from column 256
+constexpr int TMEM_COLS = 512;         // scores: 128 columns per tile; shares of the output: [tile][stage] x 64 columns from column 256
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 __device__ int g_status = 0;           // 0 = fine; else the code of the first wait that ran out
@@ -63,7 +65,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
 }
-// Bounded wait. False when the bound ran out or another thread of the block has given up.
+// Bounded wait. False when the bound ran out or another thread of the block has given up. SLEEP: the waiter is one
+// of the copy or issue warps, which wait most of the time; it naps between tries so that its spinning does not
+// take issue slots from the row warps of its scheduler.
+template <bool SLEEP = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
         uint32_t ok;
@@ -71,6 +76,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
         if (*give_up) return false;
+        if (SLEEP) __nanosleep(40);
     }
     *give_up = 1;
     atomicCAS(&g_status, 0, code);
@@ -141,13 +147,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t base = smem_u32(smem);
     const uint32_t bars = base + OFF_BARS;
-    // barriers, 8 bytes each: q, keys[2], values[2], scores[2], outputs[2], P written[2]
-    const uint32_t full_q = bars, full_k0 = bars + 8, full_v0 = bars + 24, s_done0 = bars + 40, o_done0 = bars + 56,
-                   p_ready0 = bars + 72;
-    volatile int* give_up = reinterpret_cast<volatile int*>(smem + OFF_BARS + 96);
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BARS + 104);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, row = threadIdx.x;
-    const bool issuer = warp == ROWS / 32;                               // the first four warps own rows, the fifth issues the MMAs
+    // barriers, 8 bytes each. [stage] is the stage of keys and values (block i uses stage i & 1), [t] the row tile.
+    const uint32_t full_q = bars;
+    const uint32_t full_k0 = bars + 8;          // [stage] keys copied
+    const uint32_t full_v0 = bars + 24;         // [stage] values copied
+    const uint32_t k_free0 = bars + 40;         // [stage] every tile's scores of the block are done: the keys may go
+    const uint32_t v_free0 = bars + 56;         // [stage] every tile's product of the block is done: the values may go
+    const uint32_t s_done0 = bars + 72;         // [t] the tile's scores are in tensor memory
+    const uint32_t o_done0 = bars + 88;         // [t][stage] the tile's share of the output is in tensor memory
+    const uint32_t p_ready0 = bars + 120;       // [t][stage] the tile's P is in shared memory (and its scores have been read)
+    volatile int* give_up = reinterpret_cast<volatile int*>(smem + OFF_BARS + 160);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BARS + 168);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int ROW_WARPS = TILES * ROWS / 32;
+    const bool issuer = warp == ROW_WARPS;                               // after the row warps: the MMA issuer, then two copy warps
 
     // late tiles of a request see the most keys: they go first, so that the short ones fill the tail
     const int tile = gridDim.x - 1 - blockIdx.x;
@@ -155,7 +168,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int head = blockIdx.y, kvh = head / (p.H / p.KV);
     const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin, ctx = p.ctx_len[r];
     const int* table = p.block_table + (size_t)r * p.max_pages;
-    const int rows_here = min(ROWS, q_len - tok0);                       // > 0 by construction of the tiles
+    const int rows_here = min(TILES * ROWS, q_len - tok0);               // > 0 by construction of the tiles
+    const int n_tiles = rows_here > ROWS ? 2 : 1;                        // a short last tile leaves the second half idle
     const int p_first = ctx - q_len + tok0, p_last = p_first + rows_here - 1;
     const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0, hi = p_last;
     const int b_begin = lo / KBLK, nb = rows_here > 0 ? hi / KBLK + 1 - b_begin : 0;
@@ -166,8 +180,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         mbar_init(full_q, 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(full_k0 + 8 * i, 1); mbar_init(full_v0 + 8 * i, 1);
-            mbar_init(s_done0 + 8 * i, 1); mbar_init(o_done0 + 8 * i, 1);
-            mbar_init(p_ready0 + 8 * i, ROWS);
+            mbar_init(k_free0 + 8 * i, n_tiles); mbar_init(v_free0 + 8 * i, n_tiles);
+            mbar_init(s_done0 + 8 * i, 1);
+            for (int j = 0; j < 2; ++j) { mbar_init(o_done0 + 16 * i + 8 * j, 1); mbar_init(p_ready0 + 16 * i + 8 * j, ROWS); }
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -181,16 +196,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    // scores of block i: columns (i & 1) * 128 ..; its share of the output: columns 256 + (i & 1) * 64 ..
+    // tensor memory: scores of tile t in columns 128 t ..; the share of the output of tile t and block i in columns
+    // 256 + 128 t + 64 (i & 1) ..
     bool ok = !*give_up;
 
-    if (warp >= ROWS / 32 + 1) {
-        // ================= warps 5 and 6: the copies of the keys (and q) and of the values, a page per lane 0..7.
+    if (warp > ROW_WARPS) {
+        // ================= two warps: the copies of the keys (and q) and of the values, a page per lane 0..7.
         // Issuing a box costs its lane about 0.1 us, one lane after the other: two warps keep the sixteen boxes of a
         // block off the path of the MMAs.
-        const bool keys = warp == ROWS / 32 + 1;
+        const bool keys = warp == ROW_WARPS + 1;
         const CUtensorMap* map = keys ? &map_k : &map_v;
-        const uint32_t full0 = keys ? full_k0 : full_v0, free0 = keys ? s_done0 : o_done0, off = keys ? OFF_K : OFF_V;
+        const uint32_t full0 = keys ? full_k0 : full_v0, free0 = keys ? k_free0 : v_free0, off = keys ? OFF_K : OFF_V;
         auto page_of = [&](int b, int pg) -> int {                       // -1: no row may see a key of this page
             const int first = b * KBLK + pg * PAGE;
             if (first > hi || first + PAGE - 1 < lo) return -1;
@@ -207,7 +223,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int st = i & 1;
             const int page_next = lane < PAGES && i + 1 < nb ? page_of(b_begin + i + 1, lane) : -1;   // on its way during this block's copies
             if (i >= 2) {                                                // the stage is free once block i - 2 has been multiplied
-                if (lane == 0) ok = mbar_wait(free0 + 8 * st, (uint32_t)(((i - 2) >> 1) & 1), give_up, keys ? 3 : 7);
+                if (lane == 0) ok = mbar_wait<true>(free0 + 8 * st, (uint32_t)(((i - 2) >> 1) & 1), give_up, keys ? 3 : 7);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
             }
@@ -229,52 +245,63 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (loads[s2] > 0) mbar_wait_plain(full0 + 8 * s2, (uint32_t)((loads[s2] - 1) & 1));
         }
     } else if (issuer) {
-        // ================= the fifth warp: lane 0 issues the MMAs
-        auto issue_s = [&](int i) {                                      // S = Q . K^T of the i-th block of this tile
-            const uint64_t a = smem_desc(base + OFF_Q), b = smem_desc(base + OFF_K + (i & 1) * KV_BYTES);
+        // ================= one warp: lane 0 issues the MMAs of both tiles
+        auto issue_s = [&](int t, int i) {                               // S_t = Q_t . K^T of the i-th block
+            const uint64_t a = smem_desc(base + OFF_Q + t * (ROWS * DH * 2)), b = smem_desc(base + OFF_K + (i & 1) * KV_BYTES);
 #pragma unroll
-            for (int k = 0; k < DH / 16; ++k) umma_bf16(tmem + (i & 1) * KBLK, a + 2 * k, b + 2 * k, IDESC_S, k != 0);
-            umma_commit(s_done0 + 8 * (i & 1));
+            for (int k = 0; k < DH / 16; ++k) umma_bf16(tmem + t * KBLK, a + 2 * k, b + 2 * k, IDESC_S, k != 0);
+            umma_commit(s_done0 + 8 * t);
+            umma_commit(k_free0 + 8 * (i & 1));
         };
         if (lane == 0 && ok && nb > 0) {
-            ok = mbar_wait(full_q, 0, give_up, 1) && mbar_wait(full_k0, 0, give_up, 2);
-            if (ok) { fence_after_sync(); issue_s(0); }
-            if (ok && nb > 1) {
-                ok = mbar_wait(full_k0 + 8, 0, give_up, 2);
-                if (ok) { fence_after_sync(); issue_s(1); }
+            ok = mbar_wait<true>(full_q, 0, give_up, 1) && mbar_wait<true>(full_k0, 0, give_up, 2);
+            if (ok) {
+                fence_after_sync();
+                for (int t = 0; t < n_tiles; ++t) issue_s(t, 0);
             }
             for (int i = 0; ok && i < nb; ++i) {
                 const int st = i & 1;
                 const uint32_t par = (uint32_t)((i >> 1) & 1);
-                // P of block i is in shared memory (and its scores have been read): O_i = P . V
-                ok = mbar_wait(p_ready0 + 8 * st, par, give_up, 4) && mbar_wait(full_v0 + 8 * st, par, give_up, 5);
-                if (!ok) break;
-                fence_after_sync();
-                const uint64_t a0 = smem_desc(base + OFF_P + st * P_BYTES), bv = smem_desc(base + OFF_V + st * KV_BYTES);
+                for (int t = 0; ok && t < n_tiles; ++t) {
+                    // P_t of block i is in shared memory and the tile's scores have been read
+                    ok = mbar_wait<true>(p_ready0 + 16 * t + 8 * st, par, give_up, 4);
+                    if (!ok) break;
+                    fence_after_sync();
+                    if (i + 1 < nb) {                                    // the next scores first: the tile's row warps wait for them
+                        ok = mbar_wait<true>(full_k0 + 8 * (st ^ 1), (uint32_t)(((i + 1) >> 1) & 1), give_up, 6);
+                        if (!ok) break;
+                        fence_after_sync();
+                        issue_s(t, i + 1);
+                    }
+                    ok = mbar_wait<true>(full_v0 + 8 * st, par, give_up, 5);
+                    if (!ok) break;
+                    fence_after_sync();
+                    const uint64_t a0 = smem_desc(base + OFF_P + (2 * t + st) * P_BYTES), bv = smem_desc(base + OFF_V + st * KV_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < KBLK / 16; ++kk)                  // 16 keys a step: 32 bytes along P's rows, two 8-row groups of V
-                    umma_bf16(tmem + 2 * KBLK + st * DH, a0 + (uint64_t)((kk >> 2) * (ROWS * 128 >> 4) + 2 * (kk & 3)),
-                              bv + (uint64_t)(kk * (2048 >> 4)), IDESC_PV, kk != 0);
-                umma_commit(o_done0 + 8 * st);
-                if (i + 2 < nb) {                                        // the scores of block i + 2 go where those of block i were
-                    ok = mbar_wait(full_k0 + 8 * st, par ^ 1, give_up, 6);
-                    if (ok) { fence_after_sync(); issue_s(i + 2); }
+                    for (int kk = 0; kk < KBLK / 16; ++kk)              // 16 keys a step: 32 bytes along P's rows, two 8-row groups of V
+                        umma_bf16(tmem + TILES * KBLK + (2 * t + st) * DH, a0 + (uint64_t)((kk >> 2) * (ROWS * 128 >> 4) + 2 * (kk & 3)),
+                                  bv + (uint64_t)(kk * (2048 >> 4)), IDESC_PV, kk != 0);
+                    umma_commit(o_done0 + 16 * t + 8 * st);
+                    umma_commit(v_free0 + 8 * st);
                 }
             }
         }
         __syncwarp();
-    } else {
-        // ================= four warps: thread `row` owns one query row
-        const bool valid = row < rows_here;
-        const int pos = valid ? p_first + row : -1;                      // an invalid row sees nothing
-        const uint32_t lane_off = (uint32_t)(warp * 32) << 16;           // this warp's 32 lanes of tensor memory
+    } else if (warp / (ROWS / 32) < n_tiles) {
+        // ================= four warps per tile: a thread owns one query row
+        const int t = warp / (ROWS / 32);
+        const int row = threadIdx.x - t * ROWS;                          // row of the tile = lane of tensor memory
+        const bool valid = t * ROWS + row < rows_here;
+        const int pos = valid ? p_first + t * ROWS + row : -1;           // an invalid row sees nothing
+        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;     // this warp's 32 lanes of tensor memory
+        const uint32_t t_s = tmem + t * KBLK + lane_off;
         float o[DH];
 #pragma unroll
         for (int j = 0; j < DH; ++j) o[j] = 0.f;
         float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
         // out = out * alpha + O_i, read from tensor memory one block late (the product runs meanwhile)
         auto add_output = [&](int i, float alpha) {
-            const uint32_t t_o = tmem + 2 * KBLK + (i & 1) * DH + lane_off;
+            const uint32_t t_o = tmem + TILES * KBLK + (2 * t + (i & 1)) * DH + lane_off;
 #pragma unroll
             for (int c = 0; c < DH / 32; ++c) {
                 uint32_t v[32];
@@ -286,12 +313,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         };
         for (int i = 0; i < nb; ++i) {
             const int b = b_begin + i, st = i & 1;
-            const uint32_t par = (uint32_t)((i >> 1) & 1);
-            ok = mbar_wait(s_done0 + 8 * st, par, give_up, 8) && ok;
+            ok = mbar_wait(s_done0 + 8 * t, (uint32_t)(i & 1), give_up, 8) && ok;
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             fence_after_sync();
-            const uint32_t t_s = tmem + st * KBLK + lane_off;
             const int k0 = b * KBLK;
             // blocks that lie wholly inside what this row may see need no per-key test
             const bool all_seen = k0 + KBLK - 1 <= pos && (p.window <= 0 || k0 + p.window > pos);
@@ -320,7 +345,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const float alpha = bl_ex2(m - m_use);                       // 2^-inf = 0 on the first block
             m = m_new;
             float sm4[4] = {0.f, 0.f, 0.f, 0.f};
-            unsigned char* p_tile = smem + OFF_P + st * P_BYTES;
+            unsigned char* p_tile = smem + OFF_P + (2 * t + st) * P_BYTES;
 #pragma unroll 1
             for (int c = 0; c < KBLK / 32; ++c) {                        // second pass: P into shared memory
                 uint32_t s[32];
@@ -353,11 +378,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             l = l * alpha + ((sm4[0] + sm4[1]) + (sm4[2] + sm4[3]));
             // the values of this block: rows that were not copied, or that lie past the last key, become zeros
-            // (their P is 0, and 0 times whatever an old request left in a page must stay 0)
+            // (their P is 0, and 0 times whatever an old request left in a page must stay 0). Both tiles write the
+            // same zeros: neither has to wait for the other.
             if (k0 + KBLK - 1 > hi || k0 < lo) {
-                ok = mbar_wait(full_v0 + 8 * st, par, give_up, 10) && ok;
+                ok = mbar_wait(full_v0 + 8 * st, (uint32_t)((i >> 1) & 1), give_up, 10) && ok;
                 if (ok) {
-                    for (int idx = threadIdx.x; idx < KBLK * 8; idx += ROWS) {   // (key row, 16-byte chunk); a row's chunks stay in the row
+                    for (int idx = row; idx < KBLK * 8; idx += ROWS) {   // (key row, 16-byte chunk); a row's chunks stay in the row
                         const int key = k0 + (idx >> 3);
                         const int first = key / PAGE * PAGE;
                         const bool copied = !(first > hi || first + PAGE - 1 < lo) && table[first / PAGE] >= 0;
@@ -368,10 +394,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             fence_async_smem();
             fence_before_sync();
-            mbar_arrive(p_ready0 + 8 * st);
+            mbar_arrive(p_ready0 + 16 * t + 8 * st);
             // the share of the block before: its product has had a whole softmax to finish
             if (i > 0) {
-                ok = mbar_wait(o_done0 + 8 * (st ^ 1), (uint32_t)(((i - 1) >> 1) & 1), give_up, 11) && ok;
+                ok = mbar_wait(o_done0 + 16 * t + 8 * (st ^ 1), (uint32_t)(((i - 1) >> 1) & 1), give_up, 11) && ok;
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 fence_after_sync();
@@ -380,14 +406,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             alpha_prev = alpha;
         }
         if (nb > 0) {
-            ok = mbar_wait(o_done0 + 8 * ((nb - 1) & 1), (uint32_t)(((nb - 1) >> 1) & 1), give_up, 12) && ok;
+            ok = mbar_wait(o_done0 + 16 * t + 8 * ((nb - 1) & 1), (uint32_t)(((nb - 1) >> 1) & 1), give_up, 12) && ok;
             ok = __all_sync(0xffffffffu, ok);
             if (ok) {
                 fence_after_sync();
                 add_output(nb - 1, alpha_prev);
                 if (valid) {
                     const float inv = l > 0.f ? 1.0f / l : 0.f;
-                    __nv_bfloat16* dst = p.out + ((size_t)(q_begin + tok0 + row) * p.H + head) * DH;
+                    __nv_bfloat16* dst = p.out + ((size_t)(q_begin + tok0 + t * ROWS + row) * p.H + head) * DH;
 #pragma unroll
                     for (int j = 0; j < DH; j += 8)
                         *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16(o[j] * inv, o[j + 1] * inv), pack_bf16(o[j + 2] * inv, o[j + 3] * inv),
@@ -440,7 +466,7 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, int bo
 
 extern "C" int bl_attention_prefill_tc_supported(int dh, int page_size) { return dh == DH && page_size == PAGE; }
 
-// tiles[n_tiles][2] = (request, first token of a 128-token tile within the request's new tokens). T: rows of q and
+// tiles[n_tiles][2] = (request, first token of a 256-token tile within the request's new tokens). T: rows of q and
 // out; n_pages: pages of the cache tensors (their first dimension).
 extern "C" int bl_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
                                        const int* ctx_len, const int* block_table, int max_pages, const int* tiles,
@@ -455,7 +481,7 @@ extern "C" int bl_attention_prefill_tc(const void* q, const void* k_cache, const
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15)
         BL_FAIL("bl_attention_prefill_tc: q, the caches and out must be 16-byte aligned");
     CUtensorMap mq, mk, mv;
-    if (make_map(&mq, q, T, H * DH, ROWS)) return 1;
+    if (make_map(&mq, q, T, H * DH, TILES * ROWS)) return 1;
     if (make_map(&mk, k_cache, (long long)n_pages * KV * PAGE, DH, PAGE)) return 1;
     if (make_map(&mv, v_cache, (long long)n_pages * KV * PAGE, DH, PAGE)) return 1;
     Params p;

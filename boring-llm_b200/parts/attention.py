@@ -136,9 +136,9 @@ class GQAAttention(Mixer):
                                 self.H, self.window, self.scale)
             return
         if ctx.prefill_tiles is not None:
-            if (ctx.prefill_tiles128 is not None and ctx.prefill_tokens >= PREFILL_TC_MIN_TOKENS
+            if (ctx.prefill_tiles256 is not None and ctx.prefill_tokens >= PREFILL_TC_MIN_TOKENS
                     and ops.attention_prefill_tc_supported(q.dtype, self.dh, k_cache.shape[2])):
-                ops.attention_prefill_tc(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.prefill_tiles128, out,
+                ops.attention_prefill_tc(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.prefill_tiles256, out,
                                          self.H, self.window, self.scale)
             else:
                 ops.attention_prefill(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.prefill_tiles, out,

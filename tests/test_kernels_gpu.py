@@ -396,11 +396,11 @@ def test_attention_mma_window_edges(window):
 
 
 def tc_attention(q, kc, vc, tok_req, cu_q, ctx_len, table, out, H, window, scale):
-    """The tcgen05 prefill kernel for requests with several new tokens (tiles of 128 rows), the decode kernel for the rest."""
+    """The tcgen05 prefill kernel for requests with several new tokens (tiles of 256 rows), the decode kernel for the rest."""
     o = ops()
     cu = cu_q.cpu().tolist()
     q_lens = [b - a for a, b in zip(cu[:-1], cu[1:])]
-    tiles = [(r, t0) for r, n in enumerate(q_lens) if n > 1 for t0 in range(0, n, 128)]
+    tiles = [(r, t0) for r, n in enumerate(q_lens) if n > 1 for t0 in range(0, n, 256)]
     singles = [r for r, n in enumerate(q_lens) if n == 1]
     out.fill_(float("nan"))
     if tiles:
