@@ -164,11 +164,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     // late tiles of a request see the most keys: they go first, so that the short ones fill the tail
     const int tile = gridDim.x - 1 - blockIdx.x;
-    const int r = p.tiles[2 * tile], tok0 = p.tiles[2 * tile + 1];
+    const int r = p.tiles[3 * tile], tok0 = p.tiles[3 * tile + 1], row_limit = p.tiles[3 * tile + 2];
     const int head = blockIdx.y, kvh = head / (p.H / p.KV);
     const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin, ctx = p.ctx_len[r];
     const int* table = p.block_table + (size_t)r * p.max_pages;
-    const int rows_here = min(TILES * ROWS, q_len - tok0);               // > 0 by construction of the tiles
+    const int rows_here = min(min(TILES * ROWS, row_limit), q_len - tok0);   // > 0 by construction of the tiles
     const int n_tiles = rows_here > ROWS ? 2 : 1;                        // a short last tile leaves the second half idle
     const int p_first = ctx - q_len + tok0, p_last = p_first + rows_here - 1;
     const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0, hi = p_last;
@@ -466,8 +466,9 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, int bo
 
 extern "C" int bl_attention_prefill_tc_supported(int dh, int page_size) { return dh == DH && page_size == PAGE; }
 
-// tiles[n_tiles][2] = (request, first token of a 256-token tile within the request's new tokens). T: rows of q and
-// out; n_pages: pages of the cache tensors (their first dimension).
+// tiles[n_tiles][3] = (request, first token of the block's rows within the request's new tokens, rows of the block:
+// 256, or 128 for a block that takes one row tile only). T: rows of q and out; n_pages: pages of the cache tensors
+// (their first dimension).
 extern "C" int bl_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
                                        const int* ctx_len, const int* block_table, int max_pages, const int* tiles,
                                        int n_tiles, void* out, int T, int n_pages, int H, int KV, int dh, int page_size,

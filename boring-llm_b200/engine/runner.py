@@ -343,9 +343,8 @@ class ModelRunner:
         width = max(1, max(len(t) for rc in rcs for t in (rc.tables or [[0]])))
         width = -(-width // 8) * 8
         tiles = [(r, t0) for r, e in enumerate(entries) if len(e.tokens) > 1 for t0 in range(0, len(e.tokens), 64)]
-        tiles256 = [t for t in tiles if t[1] % 256 == 0]
         singles = [r for r, e in enumerate(entries) if len(e.tokens) == 1]
-        n_ints = 3 * T + (R + 1) + 2 * R + N + G * R * width + 2 * len(tiles) + 2 * len(tiles256) + len(singles)
+        n_ints = 3 * T + (R + 1) + 2 * R + N + G * R * width + 2 * len(tiles) + len(singles)
         host = self._host_buffer(n_ints)
         h = host.numpy()
         o = 0
@@ -359,11 +358,9 @@ class ModelRunner:
         tables = h[o:o + G * R * width].reshape(G, R, width); o += G * R * width
         tables[...] = -1
         tile_arr = h[o:o + 2 * len(tiles)]; o += 2 * len(tiles)
-        tile128_arr = h[o:o + 2 * len(tiles256)]; o += 2 * len(tiles256)
         single_arr = h[o:o + len(singles)]; o += len(singles)
         if tiles:
             tile_arr[:] = np.asarray(tiles, dtype=np.int32).reshape(-1)
-            tile128_arr[:] = np.asarray(tiles256, dtype=np.int32).reshape(-1)
         if singles:
             single_arr[:] = np.asarray(singles, dtype=np.int32)
         t0 = 0
@@ -405,7 +402,6 @@ class ModelRunner:
             q_lens=q_lens, ctx_lens=ctx_lens, slot_list=slot_list, storage=self.storage, fast=self.fast)
         if tiles:
             ctx.prefill_tiles = take(2 * len(tiles)).view(len(tiles), 2)
-            ctx.prefill_tiles256 = take(2 * len(tiles256)).view(len(tiles256), 2)
             ctx.prefill_tokens = sum(n for n in q_lens if n > 1)
         if singles:
             ctx.decode_reqs = take(len(singles))

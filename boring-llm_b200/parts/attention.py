@@ -22,6 +22,36 @@ PREFILL_TC_MIN_TOKENS = 1024         # steps with fewer prompt tokens keep the 6
 DECODE_MAX_SPLITS = 32               # more slices make the merge longer than they shorten the scan
 
 
+def tc_attention_blocks(q_lens, ctx_lens, heads: int, sms: int = DECODE_SMS):
+    """The launch list of the tcgen05 prefill attention: (request, first token, rows) per block and head, lightest
+    first (the kernel starts from the end of the list). A block takes two row tiles of 128 that share their keys
+    and values and take turns on the SM: best when there are more blocks than SMs. A launch that would leave
+    SMs idle lasts as long as its block with the most keys, and that block runs nearly twice as fast with one
+    row tile alone: so, heaviest first, blocks give their second tile to a block of its own until the SMs are
+    filled. Key blocks are estimated without the window (an upper bound)."""
+    PAIR, ALONE = 3.4, 1.85                              # microseconds per 128-key block, measured
+    blocks = []                                          # [cost, request, first token, rows]
+    for r, (n, c) in enumerate(zip(q_lens, ctx_lens)):
+        if n <= 1:
+            continue
+        for t0 in range(0, n, 256):
+            rows = min(256, n - t0)
+            key_blocks = -(-(c - n + t0 + rows) // 128)
+            blocks.append([key_blocks * (PAIR if rows > 128 else ALONE), r, t0, 256 if rows > 128 else 128])
+    blocks.sort(reverse=True)
+    i, total = 0, len(blocks)
+    while total * heads < sms and i < len(blocks):
+        cost, r, t0, rows = blocks[i]
+        if rows == 256:
+            key_blocks = round(cost / PAIR)
+            blocks[i] = [-(-(key_blocks * 128 - 128) // 128) * ALONE, r, t0, 128]      # the first tile ends 128 keys earlier
+            blocks.append([key_blocks * ALONE, r, t0 + 128, 128])
+            total += 1
+        i += 1
+    blocks.sort()
+    return [[r, t0, rows] for _, r, t0, rows in blocks]
+
+
 class Mixer(Part):
     """Interface of a mixer.
 
@@ -136,9 +166,13 @@ class GQAAttention(Mixer):
                                 self.H, self.window, self.scale)
             return
         if ctx.prefill_tiles is not None:
-            if (ctx.prefill_tiles256 is not None and ctx.prefill_tokens >= PREFILL_TC_MIN_TOKENS
+            if (ctx.prefill_tokens >= PREFILL_TC_MIN_TOKENS
                     and ops.attention_prefill_tc_supported(q.dtype, self.dh, k_cache.shape[2])):
-                ops.attention_prefill_tc(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.prefill_tiles256, out,
+                key = ("tcgen05 attention blocks", self.H)
+                if key not in ctx.memo:                 # once per step: the other layers find it here
+                    ctx.memo[key] = torch.tensor(tc_attention_blocks(ctx.q_lens, ctx.ctx_lens, self.H),
+                                                 dtype=torch.int32, device=ctx.device)
+                ops.attention_prefill_tc(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.memo[key], out,
                                          self.H, self.window, self.scale)
             else:
                 ops.attention_prefill(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.prefill_tiles, out,

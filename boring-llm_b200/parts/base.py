@@ -95,10 +95,10 @@ class StepContext:
     storage: object                    # cache.CacheStorage
     fast: bool = True                  # False: plain kernels only (the twins)
     prefill_tiles: Optional[torch.Tensor] = None   # [n, 2] (request, first token of a 64-token tile) for q_len > 1
-    prefill_tiles256: Optional[torch.Tensor] = None   # the same in tiles of 256 tokens
     prefill_tokens: int = 0                        # tokens of the requests with q_len > 1
     decode_reqs: Optional[torch.Tensor] = None     # [n] requests with exactly one new token
     max_decode_ctx: int = 0                        # longest context among them (an upper bound is enough)
+    memo: dict = field(default_factory=dict)       # what a part works out once per step and its other layers reuse
 
     @property
     def max_q_len(self) -> int:

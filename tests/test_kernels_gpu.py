@@ -400,7 +400,10 @@ def tc_attention(q, kc, vc, tok_req, cu_q, ctx_len, table, out, H, window, scale
     o = ops()
     cu = cu_q.cpu().tolist()
     q_lens = [b - a for a, b in zip(cu[:-1], cu[1:])]
-    tiles = [(r, t0) for r, n in enumerate(q_lens) if n > 1 for t0 in range(0, n, 256)]
+    from boring_llm_b200.parts.attention import tc_attention_blocks
+    ctx_lens = ctx_len.cpu().tolist()
+    # few blocks: the heavy ones are split into single row tiles; `sms=1` keeps every pair together
+    tiles = tc_attention_blocks(q_lens, ctx_lens, H) if len(q_lens) % 2 else tc_attention_blocks(q_lens, ctx_lens, H, sms=1)
     singles = [r for r, n in enumerate(q_lens) if n == 1]
     out.fill_(float("nan"))
     if tiles:
