@@ -4,10 +4,12 @@
 //            walks the request's keys in blocks of 64 (four 16-token pages) up to the diagonal;
 //   decode:  a block is one single-token request, one key/value head and one slice of its keys; the 16 MMA
 //            rows are the query heads that share that key/value head (every key and value is read once
-//            for all of them), the four warps take a page each of every 64-key block, and slices of long
-//            contexts are merged by a second small kernel from partial (max, sum, output) triples.
+//            for all of them); each of the four warps streams a page of every 64-key block through a
+//            cp.async ring of its own, with no barrier of the block in the loop; the slices of long contexts
+//            are merged from partial (max, sum, output) triples by whichever block of the (request, head
+//            group) finishes last.
 // Keys and values come from the request's pages through its block table with 16-byte cp.async copies into
-// padded shared-memory tiles, double buffered. Softmax is the online form of the reference's flash kernels
+// padded shared-memory tiles. Softmax is the online form of the reference's flash kernels
 // (FlashAttnRegKernel, src/math_gpu.br:3309-3504: running max m, sum l, rescale by exp(m - m_new)); the
 // split of one query's keys and its merge follow FlashDecodeKernel / FlashDecodeCombineKernel
 // (:3520-3679) and the sharing of key/value reads across a group follows FlashDecodeWarpTail128Kernel

@@ -17,7 +17,7 @@ from .rotary import RotaryTable
 FUSED_MAX_ROWS = 32       # steps with at most this many rows take the fused norm + product kernels
 
 
-DECODE_SMS = 148                     # a launch of more blocks than fit the SMs at once would run a second, nearly empty round
+DECODE_SMS = 148                     # SMs of a B200: launches are sized to fill them once
 PREFILL_TC_MIN_TOKENS = 1024         # steps with fewer prompt tokens keep the 64-row tiles of the mma.sync kernel
 DECODE_MAX_SPLITS = 32               # more slices make the merge longer than they shorten the scan
 
