@@ -186,6 +186,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // q, the newest keys and values, the output buffer and the tensor memory of the SM belong to the kernels before
+    // this one until here; the block's preamble above may run while they finish
+    bl_pdl_wait();
     if (issuer) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -196,6 +199,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    bl_pdl_trigger();                                                    // the next kernel may start its own preamble (it waits before it touches data)
     // tensor memory: scores of tile t in columns 128 t ..; the share of the output of tile t and block i in columns
     // 256 + 128 t + 64 (i & 1) ..
     bool ok = !*give_up;
@@ -493,9 +497,10 @@ extern "C" int bl_attention_prefill_tc(const void* q, const void* k_cache, const
         BL_CUDA(cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         configured = true;
     }
-    // Launched in plain stream order: a block holds tensor memory from its first instructions on, and a dependent
-    // launch that started early could take that memory on an SM and then wait for this kernel.
-    attention_tc_kernel<<<dim3(n_tiles, H, 1), THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(mq, mk, mv, p);
+    // A block waits (griddepcontrol.wait) before it allocates tensor memory or touches data, so it may be launched
+    // while the kernel before it still runs.
+    BL_CUDA(bl_launch_dependent(attention_tc_kernel, dim3(n_tiles, H, 1), dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)stream,
+                                mq, mk, mv, p));
     BL_CHECK_LAUNCH("bl_attention_prefill_tc");
     return 0;
 }

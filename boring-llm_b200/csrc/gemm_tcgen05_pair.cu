@@ -8,7 +8,7 @@
 // blocks' shared memory and writes each block's 128 rows of the accumulator into that block's tensor memory.
 //
 // One pair per two SMs stays resident and walks over tiles (tile t, t + pairs, ...). The round trip "stage free ->
-// TMA -> data landed -> MMA done -> stage free" takes a couple of microseconds, so five stages are kept in flight,
+// TMA -> data landed -> MMA done -> stage free" takes a couple of microseconds, so five to seven stages are kept in flight,
 // and the accumulator is double buffered in tensor memory (2 x 256 columns): while the eight epilogue warps drain
 // one tile, the issuer already fills the next, and the loaders never stop.
 //
@@ -32,13 +32,20 @@
 namespace {
 
 constexpr int BM = 128;                 // rows per block (256 per pair)
-constexpr int BK = 64, STAGES = 5;
+constexpr int BK = 64;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int STAGE_BYTES_MAX = A_BYTES + 128 * BK * 2;              // with BN = 256 each block holds 128 rows of W
+// A stage holds the block's 128 rows of x and its half of the tile's rows of W. The ring is as deep as shared memory
+// allows: five stages of 32 KB for 256-wide tiles, seven of 24 KB for 128-wide ones (their products are the short
+// ones, where the latency of a stage's round trip is what limits the kernel).
+constexpr int stage_bytes(int bn) { return A_BYTES + (bn / 2) * BK * 2; }
+constexpr int stages_for(int bn) { return bn == 256 ? 5 : 7; }
+constexpr int RING_BYTES = stages_for(128) * stage_bytes(128) > stages_for(256) * stage_bytes(256)
+                               ? stages_for(128) * stage_bytes(128) : stages_for(256) * stage_bytes(256);
+constexpr int MAX_STAGES = 7;
 constexpr int EPI_WARPS = 8, THREADS = 32 * (2 + EPI_WARPS);    // two warps per quarter of the accumulator's rows
 constexpr int PITCH = 36;                                            // floats per staged row of the epilogue
 constexpr int STAGING_BYTES = EPI_WARPS * 32 * PITCH * 4;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES_MAX + STAGING_BYTES + 1024 + 256;
+constexpr int SMEM_BYTES = RING_BYTES + STAGING_BYTES + 1024 + 256;
 constexpr int TMEM_COLS = 512;                                       // two accumulators of up to 256 columns
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;      // clears the bit that selects the odd block of a pair
@@ -113,16 +120,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const void* __restrict__ bias, int bias_dtype, TO* __restrict__ out, int M, int N, int K,
                     int m_pairs, int n_tiles) {
     constexpr bool GLU = EPI == BL_EPI_SWIGLU;
-    constexpr int B_BYTES = (BN / 2) * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int STAGE_BYTES = stage_bytes(BN), STAGES = stages_for(BN);
+    static_assert(STAGES <= MAX_STAGES && STAGES * STAGE_BYTES <= RING_BYTES && STAGE_BYTES % 1024 == 0, "ring does not fit");
     constexpr int COLS = GLU ? BN / 2 : BN;                          // output columns per tile
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
-    float* staging = reinterpret_cast<float*>(aligned + STAGES * STAGE_BYTES_MAX);
-    const uint32_t bars = base + STAGES * STAGE_BYTES_MAX + STAGING_BYTES;
-    volatile int* give_up = reinterpret_cast<volatile int*>(aligned + STAGES * STAGE_BYTES_MAX + STAGING_BYTES + 192);
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + STAGES * STAGE_BYTES_MAX + STAGING_BYTES + 200);
-    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, acc_full0 = bars + 16 * STAGES, acc_empty0 = acc_full0 + 16;
+    float* staging = reinterpret_cast<float*>(aligned + RING_BYTES);
+    const uint32_t bars = base + RING_BYTES + STAGING_BYTES;
+    volatile int* give_up = reinterpret_cast<volatile int*>(aligned + RING_BYTES + STAGING_BYTES + 192);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(aligned + RING_BYTES + STAGING_BYTES + 200);
+    const uint32_t full0 = bars, empty0 = bars + 8 * MAX_STAGES, acc_full0 = bars + 16 * MAX_STAGES, acc_empty0 = acc_full0 + 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint32_t rank;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
@@ -137,6 +145,22 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full0 + 8 * b, 1); mbar_init(acc_empty0 + 8 * b, 2 * EPI_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    __syncthreads();
+    cluster_sync();                                                  // both blocks' barriers exist before anyone signals them
+    // W does not depend on the kernel before this one: the loader starts this block's half of W for the first ring of
+    // k blocks before the dependent-launch wait, so that those copies (the first touch of this layer's weights) run
+    // while the predecessor finishes. The stage's barrier expects the bytes of x and W together; x follows after the wait.
+    int early = 0;                                                   // loader: k blocks whose W is already on its way
+    if (warp == 0 && lane == 0 && pair < total_tiles) {
+        const int n0 = (pair / m_pairs) * COLS;
+        const int w_row0 = GLU ? (int)rank * N + n0 : n0 + (int)rank * (BN / 2);
+        for (; early < STAGES && early < kblocks; ++early) {
+            if (leader) mbar_expect_tx(full0 + 8 * early, 2 * STAGE_BYTES);   // the bytes of both blocks
+            tma_load_2d_pair(base + early * STAGE_BYTES + A_BYTES, &map_b, full0 + 8 * early, early * BK, w_row0);
+        }
+    }
+    __syncwarp();
+    bl_pdl_wait();                                                   // x, the residual stream and tensor memory belong to the predecessor until here
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -145,9 +169,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     fence_before_sync();
     __syncthreads();
-    cluster_sync();                                                  // both blocks' barriers exist before anyone signals them
+    cluster_sync();                                                  // both blocks hold their tensor memory before the leader writes into it
     fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    bl_pdl_trigger();                                                // the next kernel may start its own preamble (it waits before it touches data)
 
     if (warp == 0) {
         if (lane == 0) {
@@ -160,10 +185,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, give_up, 1)) break;
-                    const uint32_t a_dst = base + s * STAGE_BYTES_MAX, b_dst = a_dst + A_BYTES;
-                    if (leader) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);   // the bytes of both blocks
+                    const uint32_t a_dst = base + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
+                    if (it >= early) {                                // (the first ring's W was started before the wait)
+                        if (leader) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);   // the bytes of both blocks
+                        tma_load_2d_pair(b_dst, &map_b, full0 + 8 * s, kb * BK, w_row0);
+                    }
                     tma_load_2d_pair(a_dst, &map_a, full0 + 8 * s, kb * BK, m0);
-                    tma_load_2d_pair(b_dst, &map_b, full0 + 8 * s, kb * BK, w_row0);
                 }
             }
         }
@@ -180,8 +207,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const int s = it % STAGES;
                     if (!mbar_wait(full0 + 8 * s, (it / STAGES) & 1, give_up, 2)) break;
                     fence_after_sync();
-                    const uint64_t a_desc = smem_desc(base + s * STAGE_BYTES_MAX);
-                    const uint64_t b_desc = smem_desc(base + s * STAGE_BYTES_MAX + A_BYTES);
+                    const uint64_t a_desc = smem_desc(base + s * STAGE_BYTES);
+                    const uint64_t b_desc = smem_desc(base + s * STAGE_BYTES + A_BYTES);
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k)
                         umma_bf16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc_for(BN), (kb | k) != 0);
@@ -314,6 +341,7 @@ int launch_bn(const void* x, const void* w, const void* bias, int bias_dtype, vo
     static bool configured = false;
     if (!configured) {
         BL_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI, TO, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        BL_CUDA(bl_same_carveout(gemm_tc_pair_kernel<EPI, TO, BN>));
         configured = true;
     }
     const bool glu = EPI == BL_EPI_SWIGLU;
@@ -329,10 +357,14 @@ int launch_bn(const void* x, const void* w, const void* bias, int bias_dtype, vo
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = SMEM_BYTES;
     cfg.stream = s;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr; cfg.numAttrs = 1;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    // The block waits (griddepcontrol.wait) before it allocates tensor memory or touches x and out, so it may be
+    // launched while its predecessor still runs: its preamble and the first copies of W overlap the predecessor's tail.
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = bl_pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr; cfg.numAttrs = 2;
     BL_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<EPI, TO, BN>, a, b, bias, bias_dtype, (TO*)out, M, N, K, m_pairs, n_tiles));
     return 0;
 }
