@@ -55,6 +55,12 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" :: "n"(N)); }
+// 2^x on the special-function unit (about 2 ulp; 2^-inf = 0, tiny results flush to 0)
+__device__ __forceinline__ float bl_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
@@ -161,7 +167,8 @@ __device__ __forceinline__ void block_step(const __nv_bfloat16* stage, int koff,
             mma_bf16(s[2 * np + 1], qf[kk], b[2], b[3]);
         }
     }
-    // scale, mask, running maximum
+    // mask, running maximum. The maximum is taken over the raw scores (the scale is positive) and scaled once;
+    // 2^(s * scale - m) is then one multiply-add and one special-function instruction per score.
     float mx[2] = {-INFINITY, -INFINITY};
     // most blocks lie wholly inside what both rows may see: no per-key test there
     const int k_first = key_abs0 + koff, k_last = k_first + NT * 8 - 1;
@@ -170,10 +177,7 @@ __device__ __forceinline__ void block_step(const __nv_bfloat16* stage, int koff,
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                s[n][c] *= scale_log2;
-                mx[c >> 1] = fmaxf(mx[c >> 1], s[n][c]);
-            }
+            for (int c = 0; c < 4; ++c) mx[c >> 1] = fmaxf(mx[c >> 1], s[n][c]);
         }
     } else {
 #pragma unroll
@@ -183,30 +187,32 @@ __device__ __forceinline__ void block_step(const __nv_bfloat16* stage, int koff,
                 const int j = k_first + n * 8 + 2 * t + (c & 1);
                 const int p = pos[c >> 1];
                 const bool seen = j <= p && (window <= 0 || j + window > p);
-                const float v = seen ? s[n][c] * scale_log2 : -INFINITY;
+                const float v = seen ? s[n][c] : -INFINITY;
                 s[n][c] = v;
                 mx[c >> 1] = fmaxf(mx[c >> 1], v);
             }
         }
     }
-    float alpha[2], m_use[2];
+    float m_use[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-        const float m_new = fmaxf(m[h], mx[h]);
+        const float m_new = fmaxf(m[h], mx[h] * scale_log2);
         m_use[h] = m_new == -INFINITY ? 0.f : m_new;              // a row that has seen no key yet
-        alpha[h] = exp2f(m[h] - m_use[h]);                         // exp2(-inf) = 0 on the first block
-        m[h] = m_new;
-        l[h] *= alpha[h];
-    }
+        if (m_new != m[h]) {                                       // (after the first blocks the maximum seldom moves)
+            const float alpha = bl_ex2(m[h] - m_use[h]);           // 2^-inf = 0 on the first block
+            m[h] = m_new;
+            l[h] *= alpha;
 #pragma unroll
-    for (int n = 0; n < DH / 8; ++n) { o[n][0] *= alpha[0]; o[n][1] *= alpha[0]; o[n][2] *= alpha[1]; o[n][3] *= alpha[1]; }
+            for (int n = 0; n < DH / 8; ++n) { o[n][2 * h] *= alpha; o[n][2 * h + 1] *= alpha; }
+        }
+    }
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            const float e = exp2f(s[n][c] - m_use[c >> 1]);
+            const float e = bl_ex2(fmaf(s[n][c], scale_log2, -m_use[c >> 1]));   // a masked score is -inf: 2^-inf = 0
             s[n][c] = e;
             l[c >> 1] += e;
         }
@@ -561,7 +567,8 @@ int dispatch(int dh, const AttnParams& p, dim3 grid, cudaStream_t s) {
     }
 }
 
-int check(int H, int KV, int dh, int page_size, int max_pages, int window) {
+int check(int H, int KV, int dh, int page_size, int max_pages, int window, float scale) {
+    if (!(scale > 0.f)) BL_FAIL("bl_attention_mma: the scale of the scores must be positive (got %g)", (double)scale);
     if (H <= 0 || KV <= 0 || H % KV != 0) BL_FAIL("bl_attention_mma: %d heads cannot share %d key/value heads", H, KV);
     if (page_size != PAGE) BL_FAIL("bl_attention_mma: pages of %d tokens are not built (16 only); use the plain kernel", page_size);
     if (max_pages <= 0 || window < 0) BL_FAIL("bl_attention_mma: bad table width or window");
@@ -582,7 +589,7 @@ extern "C" int bl_attention_prefill(const void* q, const void* k_cache, const vo
                                     int n_tiles, void* out, int H, int KV, int dh, int page_size, int window,
                                     float scale, void* stream) {
     if (n_tiles <= 0) return 0;
-    if (check(H, KV, dh, page_size, max_pages, window)) return 1;
+    if (check(H, KV, dh, page_size, max_pages, window, scale)) return 1;
     AttnParams p;
     p.q = (const __nv_bfloat16*)q; p.kc = (const __nv_bfloat16*)k_cache; p.vc = (const __nv_bfloat16*)v_cache;
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
@@ -602,7 +609,7 @@ extern "C" int bl_attention_decode(const void* q, const void* k_cache, const voi
                                    int n_splits, float* scratch, int* counters, void* out, int H, int KV, int dh,
                                    int page_size, int window, float scale, void* stream) {
     if (n <= 0) return 0;
-    if (check(H, KV, dh, page_size, max_pages, window)) return 1;
+    if (check(H, KV, dh, page_size, max_pages, window, scale)) return 1;
     if (n_splits < 1 || n_splits > 256) BL_FAIL("bl_attention_decode: %d slices (1..256)", n_splits);
     if (n_splits > 1 && (scratch == nullptr || counters == nullptr))
         BL_FAIL("bl_attention_decode: slices need scratch memory and zeroed counters");
