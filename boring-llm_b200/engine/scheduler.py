@@ -38,7 +38,7 @@ class AdmissionError(ValueError):
     """A request that can never run: empty prompt, or no room for even one new token."""
 
 
-@dataclass
+@dataclass(eq=False)          # a request is itself: lists of requests are searched by identity, not by comparing fields
 class Request:
     request_id: object
     prompt: List[int]
@@ -162,13 +162,13 @@ class Scheduler:
         for req in list(self.running):
             if budget <= 0:
                 break
-            if req in self.running and req.output and req.remaining == 1:
+            if req.state == RUNNING and req.output and req.remaining == 1:
                 try_take(req, 1)
         # 2. running requests inside their prompt (or re-computing after a preemption)
         for req in list(self.running):
             if budget <= 0:
                 break
-            if req in self.running and id(req) not in picked and req.remaining > 0:
+            if req.state == RUNNING and id(req) not in picked and req.remaining > 0:
                 try_take(req, min(req.remaining, chunk, budget))
         # 3. admissions in arrival order; none in a step that had to preempt
         while self.waiting and budget > 0 and not preempted and self.cache.has_free_slot():
