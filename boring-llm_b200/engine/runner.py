@@ -228,6 +228,8 @@ class ModelRunner:
             self.cache.commit(e.request_id, 1)
         self.steps += 1
         self.graph_steps += 1
+        if self.graph_steps % 256 == 0:                # graphs of more than a few rows hold tcgen05 products: look at their
+            self._waits_unchecked = True               # status word now and then (a look costs a device synchronisation)
         self.tokens_run += R
         if sampling is not None:
             gr.sampled_host.copy_(gr.sampled, non_blocking=True)
