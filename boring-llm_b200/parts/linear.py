@@ -13,7 +13,7 @@ from ..kernels import ops
 from ..kernels.ops import EPI_NONE, EPI_BIAS, EPI_RESIDUAL, EPI_SWIGLU
 
 SKINNY_MAX_ROWS = 64      # up to here W streams through registers (measured faster than 128-row tcgen05 tiles at 64 rows)
-TC_MIN_COLUMNS_FEW_ROWS = 4096   # 33..64 rows: wide products have enough 128-column tiles for TMA to stream W at full rate
+TC_MIN_COLUMNS_FEW_ROWS = 4096   # 17..64 rows: wide products have enough 128-column tiles for TMA to stream W at full rate
 TC_MIN_COLUMNS_VERY_FEW_ROWS = 32768   # 9..32 rows: only an output head is wide enough (measured: equal at 8 rows, 3% of a step at 32)
 PAIR_MIN_ROWS = 256       # from here on pairs of SMs share 256 x 256 tiles (tcgen05 cta_group::2)
 
@@ -24,7 +24,7 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optio
     bfloat16 operands take a tensor-core kernel chosen by the number of rows."""
     if ctx.fast and ops.gemm_skinny_supported(x, w):
         M, N = x.shape[0], out.shape[1]
-        few_rows_tc = (M > 32 and N >= TC_MIN_COLUMNS_FEW_ROWS) or (M > 8 and N >= TC_MIN_COLUMNS_VERY_FEW_ROWS)
+        few_rows_tc = (M > 16 and N >= TC_MIN_COLUMNS_FEW_ROWS) or (M > 8 and N >= TC_MIN_COLUMNS_VERY_FEW_ROWS)
         if M <= SKINNY_MAX_ROWS and not few_rows_tc:
             ops.gemm_skinny(x, w, out, bias, epilogue)
         elif x.shape[0] < PAIR_MIN_ROWS:
