@@ -164,7 +164,20 @@ extern "C" int bl_rmsnorm(const float* x, const int* row_idx, const void* w, int
 
 // ---------------------------------------------------------------------------------------------
 // One block per token. Work items: (head, pair) for q and k heads, then the v elements.
-template <typename TT>
+// four values as the output type: one 16-byte (float) or 8-byte (bfloat16) store
+__device__ __forceinline__ void bl_store4(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void bl_store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 pk;
+    pk.x = *reinterpret_cast<unsigned*>(&lo); pk.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = pk;
+}
+
+// VEC: every head is rotated in full (rot_half = head size / 2, a multiple of 4) and the buffers are 16-byte
+// aligned: a work item is four neighbouring pairs of a head, read and written with one vector access each.
+template <typename TT, bool VEC>
 __global__ void rope_kv_write_kernel(const float* qkv /* written by the kernel before */, const int* __restrict__ positions,
                                      const int* __restrict__ tok_req, const int* __restrict__ block_table,
                                      int max_pages, const float* __restrict__ inv_freq, int rot_half,
@@ -185,13 +198,37 @@ __global__ void rope_kv_write_kernel(const float* qkv /* written by the kernel b
         page_base = ((size_t)(page < 0 ? 0 : page) * KV) * page_size * dh + (size_t)(pos % page_size) * dh;
     }
     // the rotation of pair j is the same for every head of the token: worked out once, into shared memory
-    extern __shared__ float cs_sn[];                     // [rot_half] cos, then [rot_half] sin
+    extern __shared__ __align__(16) float cs_sn[];                     // [rot_half] cos, then [rot_half] sin
     for (int j = threadIdx.x; j < rot_half; j += blockDim.x) {
         const float angle = (float)pos * inv_freq[j];
         cs_sn[j] = cosf(angle) * mscale;
         cs_sn[rot_half + j] = sinf(angle) * mscale;
     }
     __syncthreads();
+    if (VEC) {
+        const int groups = half / 4;                     // groups of four pairs per head
+        for (int it = threadIdx.x; it < (H + KV) * groups; it += blockDim.x) {
+            const int head = it / groups, j = (it % groups) * 4;
+            const float* src = row + (size_t)head * dh;
+            const float4 x0 = *reinterpret_cast<const float4*>(src + j), x1 = *reinterpret_cast<const float4*>(src + j + half);
+            const float4 c = *reinterpret_cast<const float4*>(cs_sn + j), sn = *reinterpret_cast<const float4*>(cs_sn + half + j);
+            TT* dst = head < H ? q_out + (size_t)t * H * dh + (size_t)head * dh
+                               : k_cache + page_base + (size_t)(head - H) * page_size * dh;
+            if (head < H || write) {
+                bl_store4(dst + j, x0.x * c.x - x1.x * sn.x, x0.y * c.y - x1.y * sn.y, x0.z * c.z - x1.z * sn.z, x0.w * c.w - x1.w * sn.w);
+                bl_store4(dst + j + half, x0.x * sn.x + x1.x * c.x, x0.y * sn.y + x1.y * c.y, x0.z * sn.z + x1.z * c.z, x0.w * sn.w + x1.w * c.w);
+            }
+        }
+        if (write) {
+            const float* vsrc = row + (size_t)(H + KV) * dh;
+            for (int it = threadIdx.x; it < KV * dh / 4; it += blockDim.x) {
+                const int head = (it * 4) / dh, i = (it * 4) % dh;
+                const float4 v = *reinterpret_cast<const float4*>(vsrc + it * 4);
+                bl_store4(v_cache + page_base + (size_t)head * page_size * dh + i, v.x, v.y, v.z, v.w);
+            }
+        }
+        return;
+    }
     const int n_rot_items = (H + KV) * half;
     for (int it = threadIdx.x; it < n_rot_items; it += blockDim.x) {
         const int head = it / half, j = it % half;
@@ -234,15 +271,16 @@ extern "C" int bl_rope_kv_write(const float* qkv, const int* positions, const in
     if (rot_half < 0 || rot_half > dh / 2) BL_FAIL("bl_rope_kv_write: %d rotated pairs do not fit a head of %d", rot_half, dh);
     if ((k_cache == nullptr) != (v_cache == nullptr)) BL_FAIL("bl_rope_kv_write: key and value cache must both be given or both be null");
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == BL_F32)
-        BL_CUDA(bl_launch_dependent(rope_kv_write_kernel<float>, dim3(T), dim3(128), (size_t)rot_half * 8, s, qkv, positions, tok_req, block_table,
-            max_pages, inv_freq, rot_half, mscale, (float*)q_out, (float*)k_cache, (float*)v_cache, H, KV, dh, page_size));
-    else if (dtype == BL_BF16)
-        BL_CUDA(bl_launch_dependent(rope_kv_write_kernel<__nv_bfloat16>, dim3(T), dim3(128), (size_t)rot_half * 8, s, qkv, positions, tok_req,
-            block_table, max_pages, inv_freq, rot_half, mscale, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
-            (__nv_bfloat16*)v_cache, H, KV, dh, page_size));
-    else
-        BL_FAIL("bl_rope_kv_write: unknown dtype %d", dtype);
+    const size_t elem = dtype == BL_F32 ? 4 : 2;
+    const bool vec = rot_half * 2 == dh && rot_half % 4 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)inv_freq & 3) == 0 &&
+                     ((uintptr_t)q_out % (4 * elem)) == 0 && ((uintptr_t)k_cache % (4 * elem)) == 0 && ((uintptr_t)v_cache % (4 * elem)) == 0;
+    const size_t smem = (size_t)rot_half * 8;
+#define BL_ROPE(TT, VEC) BL_CUDA(bl_launch_dependent(rope_kv_write_kernel<TT, VEC>, dim3(T), dim3(128), smem, s, qkv, positions, tok_req, \
+        block_table, max_pages, inv_freq, rot_half, mscale, (TT*)q_out, (TT*)k_cache, (TT*)v_cache, H, KV, dh, page_size))
+    if (dtype == BL_F32) { if (vec) BL_ROPE(float, true); else BL_ROPE(float, false); }
+    else if (dtype == BL_BF16) { if (vec) BL_ROPE(__nv_bfloat16, true); else BL_ROPE(__nv_bfloat16, false); }
+    else BL_FAIL("bl_rope_kv_write: unknown dtype %d", dtype);
+#undef BL_ROPE
     BL_CHECK_LAUNCH("bl_rope_kv_write");
     return 0;
 }
