@@ -144,6 +144,7 @@ class ModelRunner:
         self.last_step_graph_kernels = 0               # kernels launched by the last step through a graph replay
         self.last_h2d_bytes = self.last_d2h_bytes = 0  # bytes the last step copied to and from the device
         self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._graph_safe: Optional[bool] = None
         self._waits_unchecked = False                  # a step ran kernels with bounded waits since the last check
         self._table_width = -(-(-(-options.ctx_size // options.page_size)) // 8) * 8
 
@@ -253,8 +254,10 @@ class ModelRunner:
         return sampler.sample(logits, rows) if rows else []
 
     def _graphs_usable(self, entries) -> bool:
+        if self._graph_safe is None:                   # the model's parts do not change after it is built
+            self._graph_safe = bool(getattr(self.model, "graph_safe", False))
         return (self.options.cuda_graphs and self.fast and self.dtype == torch.bfloat16
-                and getattr(self.model, "graph_safe", False) and len(entries) <= GRAPH_MAX_BATCH)
+                and self._graph_safe and len(entries) <= GRAPH_MAX_BATCH)
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs the entries' tokens as one batch; returns float32 logits `[wanted, vocab]` on the
