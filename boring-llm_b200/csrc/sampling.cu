@@ -165,9 +165,31 @@ sample_kernel(const float* logits /* written by the kernel before */, int vocab,
     // the first maximum (lowest id among equals): the greedy token and the softmax's reference point
     float best = -INFINITY;
     int bidx = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += THREADS) {
-        const float v = row[i];
-        if (bidx == 0x7fffffff || v > best) { best = v; bidx = i; }
+    if ((vocab & 3) == 0 && ((uintptr_t)row & 15) == 0) {          // 16-byte loads, four in flight per thread
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const int n4 = vocab >> 2;
+        for (int i0 = threadIdx.x; i0 < n4; i0 += 4 * THREADS) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * THREADS;
+                v[u] = i < n4 ? row4[i] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {                           // ascending ids within the thread: the first maximum stays
+                const int i = (i0 + u * THREADS) * 4;
+                if (i >= vocab) break;
+                if (bidx == 0x7fffffff || v[u].x > best) { best = v[u].x; bidx = i; }
+                if (v[u].y > best) { best = v[u].y; bidx = i + 1; }
+                if (v[u].z > best) { best = v[u].z; bidx = i + 2; }
+                if (v[u].w > best) { best = v[u].w; bidx = i + 3; }
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += THREADS) {
+            const float v = row[i];
+            if (bidx == 0x7fffffff || v > best) { best = v; bidx = i; }
+        }
     }
     for (int o = 16; o > 0; o >>= 1) {
         const float v2 = __shfl_xor_sync(0xffffffffu, best, o);
