@@ -91,6 +91,12 @@ int bl_gemm_tc(const void* x, const void* w, const void* bias, int bias_dtype, v
 // *status = 0 unless a block of bl_gemm_tc gave up on a bounded wait since the last call (synchronises the device).
 int bl_gemm_tc_status(int* status);
 
+// Few rows (up to 32) times very many columns (an output head), no epilogue: W is the M side of tcgen05.mma and
+// streams through a deep TMA ring once, x stays in shared memory, blocks are persistent (gemm_tcgen05_cols.cu).
+int bl_gemm_tc_cols_supported(int M, int N, int K);
+int bl_gemm_tc_cols(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, void* stream);
+int bl_gemm_tc_cols_status(int* status);
+
 // Fused kernels for steps with few rows (decode_fused.cu): the RMS norm in front of a product, and the split,
 // rotation and cache write behind the q/k/v product, folded into the product.
 int bl_norm_gemm_supported(int K);

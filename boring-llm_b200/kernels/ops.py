@@ -327,10 +327,27 @@ def gemm_tc_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Opti
           M, N, K, epilogue, _stream())
 
 
+def gemm_tc_cols_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether `gemm_tc_cols` takes these operands: bfloat16, up to 32 rows, 16-byte aligned, x fits shared memory."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and bool(library.load().bl_gemm_tc_cols_supported(x.shape[0], w.shape[0], x.shape[1])))
+
+
+def gemm_tc_cols(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x @ w.T for few rows and very many columns (an output head): the tcgen05 kernel that streams W once
+    through a deep TMA ring with W as the M side of the product."""
+    M, K = x.shape
+    N = w.shape[0]
+    _need(x, "x", torch.bfloat16, (M, K)); _need(w, "w", torch.bfloat16, (N, K)); _need(out, "out", None, (M, N))
+    _call(_lib().bl_gemm_tc_cols, _p(x), _p(w), _p(out), _dt(out), M, N, K, _stream())
+
+
 def check_status() -> None:
     """Raises if a tensor-core block gave up on one of its bounded waits since the last check. Synchronises."""
     for name, fn in (("bl_gemm_tc", _lib().bl_gemm_tc_status), ("bl_gemm_tc_pair", _lib().bl_gemm_tc_pair_status),
-                     ("bl_attention_prefill_tc", _lib().bl_attention_prefill_tc_status)):
+                     ("bl_attention_prefill_tc", _lib().bl_attention_prefill_tc_status),
+                     ("bl_gemm_tc_cols", _lib().bl_gemm_tc_cols_status)):
         v = ctypes.c_int(0)
         _call(fn, ctypes.byref(v))
         if v.value != 0:

@@ -346,6 +346,32 @@ def test_gemm_skinny_epilogues(M, N, K):
     close(out, twin.double(), torch.float32, "twin")
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 151936 // 16, 896), (16, 1000, 200), (17, 333, 72), (32, 4100, 896), (5, 130, 8)])
+def test_gemm_tc_cols(M, N, K):
+    """The output-head product (W as the M side of tcgen05.mma, persistent blocks, deep ring): tiles that overhang
+    N and K, one row and thirty-two, against 64-bit arithmetic; a row does not depend on the other rows."""
+    o = ops()
+    x = (data((M, K), 31) * 0.5).to(torch.bfloat16)
+    w = (data((N, K), 32) * 0.25).to(torch.bfloat16)
+    assert o.gemm_tc_cols_supported(x, w)
+    want = x.double().cpu() @ w.double().cpu().T
+    for dtype in (torch.float32, torch.bfloat16):
+        out = torch.full((M, N), float("nan"), dtype=dtype, device=DEV)
+        o.gemm_tc_cols(x, w, out)
+        o.check_status()
+        close(out, want, dtype, f"cols {dtype}")
+    out = torch.empty(M, N, device=DEV)
+    o.gemm_tc_cols(x, w, out)
+    one = torch.empty(1, N, device=DEV)
+    o.gemm_tc_cols(x[M - 1:M].contiguous(), w, one)
+    assert torch.equal(one[0], out[M - 1])
+    twin = torch.empty(M, N, device=DEV)
+    o.gemm_plain(x, w, twin)
+    close(out, twin.double(), torch.float32, "twin")
+    assert not o.gemm_tc_cols_supported(torch.zeros(33, K, dtype=torch.bfloat16, device=DEV), w)
+    o.check_status()
+
+
 def test_gemm_skinny_refuses_unaligned_k():
     from boring_llm_b200.kernels import KernelError
     o = ops()
