@@ -91,7 +91,7 @@ int bl_gemm_tc(const void* x, const void* w, const void* bias, int bias_dtype, v
 // *status = 0 unless a block of bl_gemm_tc gave up on a bounded wait since the last call (synchronises the device).
 int bl_gemm_tc_status(int* status);
 
-// Few rows (up to 32) times very many columns (an output head), no epilogue: W is the M side of tcgen05.mma and
+// Few rows (up to 64) times very many columns (an output head), no epilogue: W is the M side of tcgen05.mma and
 // streams through a deep TMA ring once, x stays in shared memory, blocks are persistent (gemm_tcgen05_cols.cu).
 int bl_gemm_tc_cols_supported(int M, int N, int K);
 int bl_gemm_tc_cols(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, void* stream);

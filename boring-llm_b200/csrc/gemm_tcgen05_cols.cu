@@ -1,5 +1,5 @@
 // Matrix product for FEW rows and VERY MANY columns (an output head at decode time) on the fifth-generation tensor
-// cores: out[M, N] = x[M, K] . W[N, K]^T with M up to 32, bfloat16 operands, 32-bit accumulation in tensor memory.
+// cores: out[M, N] = x[M, K] . W[N, K]^T with M up to 64, bfloat16 operands, 32-bit accumulation in tensor memory.
 //
 // The roles of the operands are swapped: 128 rows of W are the M side of tcgen05.mma and the (padded) rows of x its
 // N side, so a tile of the accumulator is 128 columns of the output x NT tokens and every byte of W passes through
@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_cols_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     TO* __restrict__ out, int M, int N, int K, int stages) {
     constexpr int X_TILE = NT * BK * 2;                                       // one k block of x
+    constexpr int TMEM_COLS = NT <= 32 ? 64 : 128;                            // two accumulators of NT columns
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t base = smem_u32(smem);
     const int kblocks = (K + BK - 1) / BK;
@@ -142,7 +143,7 @@ gemm_tc_cols_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     if (warp == 1) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     :: "r"(smem_u32((const void*)tmem_slot)), "r"(64) : "memory");
+                     :: "r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     fence_before_sync();
@@ -229,7 +230,7 @@ gemm_tc_cols_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     __syncthreads();
     if (warp == 1) {
         fence_after_sync();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(64) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -305,23 +306,25 @@ int launch(const void* x, const void* w, void* out, int M, int N, int K, cudaStr
 
 }  // namespace
 
-// Whether bl_gemm_tc_cols takes these sizes: up to 32 rows, K a multiple of 8, and x beside at least three stages
+// Whether bl_gemm_tc_cols takes these sizes: up to 64 rows, K a multiple of 8, and x beside at least three stages
 // of W in shared memory.
 extern "C" int bl_gemm_tc_cols_supported(int M, int N, int K) {
-    return M >= 1 && M <= 32 && N >= 1 && K >= 8 && K % 8 == 0 && stages_for(M <= 16 ? 16 : 32, K) > 0;
+    return M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0 && stages_for(M <= 16 ? 16 : (M <= 32 ? 32 : 64), K) > 0;
 }
 
-// bfloat16 x[M, K] (M <= 32) and W[N, K], both 16-byte aligned; out[M, N] float32 or bfloat16; no epilogue.
+// bfloat16 x[M, K] (M <= 64) and W[N, K], both 16-byte aligned; out[M, N] float32 or bfloat16; no epilogue.
 extern "C" int bl_gemm_tc_cols(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, void* stream) {
     if (M <= 0) return 0;
     if (!bl_gemm_tc_cols_supported(M, N, K))
-        BL_FAIL("bl_gemm_tc_cols: M=%d N=%d K=%d is not built (up to 32 rows, K a multiple of 8, x must fit shared memory beside the ring)", M, N, K);
+        BL_FAIL("bl_gemm_tc_cols: M=%d N=%d K=%d is not built (up to 64 rows, K a multiple of 8, x must fit shared memory beside the ring)", M, N, K);
     if (((uintptr_t)x | (uintptr_t)w) & 15) BL_FAIL("bl_gemm_tc_cols: x and W must be 16-byte aligned");
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == BL_F32)
-        return M <= 16 ? launch<16, float>(x, w, out, M, N, K, s) : launch<32, float>(x, w, out, M, N, K, s);
+        return M <= 16 ? launch<16, float>(x, w, out, M, N, K, s)
+             : M <= 32 ? launch<32, float>(x, w, out, M, N, K, s) : launch<64, float>(x, w, out, M, N, K, s);
     if (out_dtype == BL_BF16)
-        return M <= 16 ? launch<16, __nv_bfloat16>(x, w, out, M, N, K, s) : launch<32, __nv_bfloat16>(x, w, out, M, N, K, s);
+        return M <= 16 ? launch<16, __nv_bfloat16>(x, w, out, M, N, K, s)
+             : M <= 32 ? launch<32, __nv_bfloat16>(x, w, out, M, N, K, s) : launch<64, __nv_bfloat16>(x, w, out, M, N, K, s);
     BL_FAIL("bl_gemm_tc_cols: unknown output dtype %d", out_dtype);
 }
 

@@ -328,7 +328,7 @@ def gemm_tc_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Opti
 
 
 def gemm_tc_cols_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether `gemm_tc_cols` takes these operands: bfloat16, up to 32 rows, 16-byte aligned, x fits shared memory."""
+    """Whether `gemm_tc_cols` takes these operands: bfloat16, up to 64 rows, 16-byte aligned, x fits shared memory."""
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
             and bool(library.load().bl_gemm_tc_cols_supported(x.shape[0], w.shape[0], x.shape[1])))

@@ -346,10 +346,10 @@ def test_gemm_skinny_epilogues(M, N, K):
     close(out, twin.double(), torch.float32, "twin")
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 151936 // 16, 896), (16, 1000, 200), (17, 333, 72), (32, 4100, 896), (5, 130, 8)])
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 151936 // 16, 896), (16, 1000, 200), (17, 333, 72), (32, 4100, 896), (5, 130, 8), (33, 700, 136), (64, 2100, 896)])
 def test_gemm_tc_cols(M, N, K):
     """The output-head product (W as the M side of tcgen05.mma, persistent blocks, deep ring): tiles that overhang
-    N and K, one row and thirty-two, against 64-bit arithmetic; a row does not depend on the other rows."""
+    N and K, one row and sixty-four, against 64-bit arithmetic; a row does not depend on the other rows."""
     o = ops()
     x = (data((M, K), 31) * 0.5).to(torch.bfloat16)
     w = (data((N, K), 32) * 0.25).to(torch.bfloat16)
@@ -368,7 +368,7 @@ def test_gemm_tc_cols(M, N, K):
     twin = torch.empty(M, N, device=DEV)
     o.gemm_plain(x, w, twin)
     close(out, twin.double(), torch.float32, "twin")
-    assert not o.gemm_tc_cols_supported(torch.zeros(33, K, dtype=torch.bfloat16, device=DEV), w)
+    assert not o.gemm_tc_cols_supported(torch.zeros(65, K, dtype=torch.bfloat16, device=DEV), w)
     o.check_status()
 
 
