@@ -452,6 +452,14 @@ def test_attention_tcgen05_shapes(H, KV):
     attention_case(o, tc_attention, torch.bfloat16, H, KV, 64, [1000, 515, 257], [1000, 300, 129], 0, 4)
 
 
+def test_attention_tcgen05_long_prompt():
+    """Twenty key blocks and ten row blocks: the rings of keys, values, P and output shares wrap around many times,
+    and a planted key at position 0 decides the last row."""
+    o = ops()
+    attention_case(o, tc_attention, torch.bfloat16, 4, 2, 64, [2500, 1400], [2500, 700], 0, 8)
+    attention_case(o, tc_attention, torch.bfloat16, 2, 1, 64, [3000], [1300], 1100, 9)
+
+
 @pytest.mark.parametrize("window", [1, 15, 16, 17, 100, 128, 200])
 def test_attention_tcgen05_window_edges(window):
     o = ops()
