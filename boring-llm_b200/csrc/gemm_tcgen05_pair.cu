@@ -230,6 +230,20 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int buf = local & 1;
             const int m0 = ((t % m_pairs) * 2 + (int)rank) * BM;
             const int n0 = (t / m_pairs) * COLS;
+            // The residual epilogue reads what it adds to. Those reads do not depend on the product: the eight 16-byte
+            // words a lane needs for a chunk are requested before the chunk's accumulator is fetched (for the first
+            // chunk: before the accumulator is even waited for), so that their trip to L2 is not paid row by row.
+            constexpr bool PRELOAD = EPI == BL_EPI_RESIDUAL && sizeof(TO) == 4;
+            float4 res[8];
+            auto preload = [&](int c) {
+#pragma unroll
+                for (int it2 = 0; it2 < 8; ++it2) {
+                    const int m = m0 + quarter * 32 + it2 * 4 + r_sub, n = n0 + c * 32 + c4;
+                    res[it2] = (vec_ok && m < M && n + 3 < N) ? *reinterpret_cast<const float4*>(out + (size_t)m * N + n)
+                                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            };
+            if (PRELOAD && half < CHUNKS) preload(half);
             if (!mbar_wait(acc_full0 + 8 * buf, (local / 2) & 1, give_up, 3)) break;
             fence_after_sync();
             const uint32_t lane_addr = tmem + buf * 256 + ((uint32_t)(quarter * 32) << 16);
@@ -250,6 +264,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int j = 0; j < 8; ++j)
                     *reinterpret_cast<uint4*>(tile + lane * PITCH + 4 * j) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
                 __syncwarp();
+                float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);              // a lane writes the same four columns in all eight rows
+                if (EPI == BL_EPI_BIAS && vec_ok && n0 + c * 32 + c4 + 3 < N) {
+                    const int n = n0 + c * 32 + c4;
+                    b4 = make_float4(bl_load_any(bias, bias_dtype, n), bl_load_any(bias, bias_dtype, n + 1),
+                                     bl_load_any(bias, bias_dtype, n + 2), bl_load_any(bias, bias_dtype, n + 3));
+                }
 #pragma unroll
                 for (int it2 = 0; it2 < 8; ++it2) {
                     const int row = it2 * 4 + r_sub;
@@ -259,15 +279,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     float4 v = *reinterpret_cast<const float4*>(tile + row * PITCH + c4);
                     TO* dst = out + (size_t)m * N + n;
                     if (vec_ok && n + 3 < N) {
-                        if (EPI == BL_EPI_BIAS) {
-                            v.x += bl_load_any(bias, bias_dtype, n); v.y += bl_load_any(bias, bias_dtype, n + 1);
-                            v.z += bl_load_any(bias, bias_dtype, n + 2); v.w += bl_load_any(bias, bias_dtype, n + 3);
-                        }
+                        if (EPI == BL_EPI_BIAS) { v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w; }
                         if (sizeof(TO) == 4) {
-                            if (EPI == BL_EPI_RESIDUAL) {
-                                const float4 o = *reinterpret_cast<const float4*>(dst);
-                                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                            }
+                            if (EPI == BL_EPI_RESIDUAL) { v.x += res[it2].x; v.y += res[it2].y; v.z += res[it2].z; v.w += res[it2].w; }
                             *reinterpret_cast<float4*>(dst) = v;
                         } else {
                             __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
@@ -288,6 +302,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                 }
                 __syncwarp();
+                if (PRELOAD && c + 2 < CHUNKS) preload(c + 2);           // on its way while the next accumulator chunk is fetched
             }
             // this warp is done with the buffer: tell the issuer (in the leader block)
             fence_before_sync();
