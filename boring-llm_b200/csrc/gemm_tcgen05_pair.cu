@@ -17,7 +17,7 @@
 //     cp.async.bulk.tensor, barrier address with the peer bit cleared); the leader expects the bytes of both.
 //     No multicast: every block fetches its own tiles.
 //   warp 1, one thread in the leader (issuer): waits until both blocks have drained the accumulator buffer, then per
-//     k block waits for "full", issues four K = 16 MMAs (M 256, N BN) and commits with multicast to the "empty"
+//     stage waits for "full", issues four K = 16 MMAs (M 256, N BN) per k block of the stage and commits with multicast to the "empty"
 //     barrier of that stage in BOTH blocks; after a tile, to both blocks' "accumulator full" barriers.
 //   warps 2..9 of each block (epilogue, two per quarter of the rows, taking chunks in turn): tcgen05.ld of the block's own 128 x BN accumulator, 32 x 32 chunks passed
 //     through shared memory, 16-byte stores, then an arrival on the leader's "accumulator empty" barrier. For
@@ -35,10 +35,13 @@ constexpr int BM = 128;                 // rows per block (256 per pair)
 constexpr int BK = 64;
 constexpr int A_BYTES = BM * BK * 2;
 // A stage holds the block's 128 rows of x and its half of the tile's rows of W. The ring is as deep as shared memory
-// allows: five stages of 32 KB for 256-wide tiles, seven of 24 KB for 128-wide ones (their products are the short
-// ones, where the latency of a stage's round trip is what limits the kernel).
-constexpr int stage_bytes(int bn) { return A_BYTES + (bn / 2) * BK * 2; }
-constexpr int stages_for(int bn) { return bn == 256 ? 5 : 7; }
+// allows: five stages of 32 KB for 256-wide tiles, three of 48 KB (two k blocks each) for 128-wide ones.
+// (KS k blocks of 64 per stage: two for the 128-wide tiles, whose main loop is bound by the hand-over of stages
+// between loader, issuer and tensor cores and not by the tensor cores themselves: fewer, larger steps)
+constexpr int ksub(int bn) { return bn == 256 ? 1 : 2; }
+constexpr int b_bytes(int bn) { return (bn / 2) * BK * 2; }
+constexpr int stage_bytes(int bn) { return ksub(bn) * (A_BYTES + b_bytes(bn)); }
+constexpr int stages_for(int bn) { return bn == 256 ? 5 : 3; }
 constexpr int RING_BYTES = stages_for(128) * stage_bytes(128) > stages_for(256) * stage_bytes(256)
                                ? stages_for(128) * stage_bytes(128) : stages_for(256) * stage_bytes(256);
 constexpr int MAX_STAGES = 7;
@@ -120,7 +123,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const void* __restrict__ bias, int bias_dtype, TO* __restrict__ out, int M, int N, int K,
                     int m_pairs, int n_tiles) {
     constexpr bool GLU = EPI == BL_EPI_SWIGLU;
-    constexpr int STAGE_BYTES = stage_bytes(BN), STAGES = stages_for(BN);
+    constexpr int STAGE_BYTES = stage_bytes(BN), STAGES = stages_for(BN), KS = ksub(BN), B_BYTES = b_bytes(BN);
     static_assert(STAGES <= MAX_STAGES && STAGES * STAGE_BYTES <= RING_BYTES && STAGE_BYTES % 1024 == 0, "ring does not fit");
     constexpr int COLS = GLU ? BN / 2 : BN;                          // output columns per tile
     extern __shared__ unsigned char smem_raw[];
@@ -137,7 +140,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const bool leader = rank == 0;
     const int pair = blockIdx.x / 2, n_pairs = gridDim.x / 2;
     const int total_tiles = m_pairs * n_tiles;
-    const int kblocks = (K + BK - 1) / BK;
+    const int kblocks = ((K + BK - 1) / BK + KS - 1) / KS;           // steps of KS k blocks (a block past K arrives as zeros)
 
     if (threadIdx.x == 0) {
         *give_up = 0;
@@ -156,7 +159,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int w_row0 = GLU ? (int)rank * N + n0 : n0 + (int)rank * (BN / 2);
         for (; early < STAGES && early < kblocks; ++early) {
             if (leader) mbar_expect_tx(full0 + 8 * early, 2 * STAGE_BYTES);   // the bytes of both blocks
-            tma_load_2d_pair(base + early * STAGE_BYTES + A_BYTES, &map_b, full0 + 8 * early, early * BK, w_row0);
+#pragma unroll
+            for (int u = 0; u < KS; ++u)
+                tma_load_2d_pair(base + early * STAGE_BYTES + KS * A_BYTES + u * B_BYTES, &map_b, full0 + 8 * early, (early * KS + u) * BK, w_row0);
         }
     }
     __syncwarp();
@@ -185,12 +190,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, give_up, 1)) break;
-                    const uint32_t a_dst = base + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
+                    const uint32_t a_dst = base + s * STAGE_BYTES, b_dst = a_dst + KS * A_BYTES;   // stage: KS tiles of x, then KS of W
                     if (it >= early) {                                // (the first ring's W was started before the wait)
                         if (leader) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);   // the bytes of both blocks
-                        tma_load_2d_pair(b_dst, &map_b, full0 + 8 * s, kb * BK, w_row0);
+#pragma unroll
+                        for (int u = 0; u < KS; ++u) tma_load_2d_pair(b_dst + u * B_BYTES, &map_b, full0 + 8 * s, (kb * KS + u) * BK, w_row0);
                     }
-                    tma_load_2d_pair(a_dst, &map_a, full0 + 8 * s, kb * BK, m0);
+#pragma unroll
+                    for (int u = 0; u < KS; ++u) tma_load_2d_pair(a_dst + u * A_BYTES, &map_a, full0 + 8 * s, (kb * KS + u) * BK, m0);
                 }
             }
         }
@@ -207,11 +214,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const int s = it % STAGES;
                     if (!mbar_wait(full0 + 8 * s, (it / STAGES) & 1, give_up, 2)) break;
                     fence_after_sync();
-                    const uint64_t a_desc = smem_desc(base + s * STAGE_BYTES);
-                    const uint64_t b_desc = smem_desc(base + s * STAGE_BYTES + A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        umma_bf16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc_for(BN), (kb | k) != 0);
+                    for (int u = 0; u < KS; ++u) {
+                        const uint64_t a_desc = smem_desc(base + s * STAGE_BYTES + u * A_BYTES);
+                        const uint64_t b_desc = smem_desc(base + s * STAGE_BYTES + KS * A_BYTES + u * B_BYTES);
+#pragma unroll
+                        for (int k = 0; k < BK / 16; ++k)
+                            umma_bf16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc_for(BN), (kb | u | k) != 0);
+                    }
                     umma_commit_pair(empty0 + 8 * s);
                 }
                 umma_commit_pair(acc_full0 + 8 * buf);
