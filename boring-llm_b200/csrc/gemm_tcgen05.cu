@@ -11,6 +11,8 @@
 // gate rows of W and last 64 the matching up rows). Two blocks fit an SM (96 KB of stages, 128 of 512
 // tensor-memory columns each), so one block's epilogue overlaps the other's main loop.
 //
+// The kernel takes part in programmatic dependent launch: barriers and the first ring of W before the wait, tensor
+// memory, x and out after it.
 // Every wait on an mbarrier is bounded: when a bound runs out the block records a code in a status word,
 // drains its own copies, frees its tensor memory and returns; bl_gemm_tc_status() reports it on the host.
 // Role in the reference: the compiler's "native" tensor schedule for prefill matmuls
@@ -107,6 +109,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         mbar_init(accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    __syncthreads();
+    // W does not depend on the kernel before this one: the loader starts W for the first ring of k blocks before the
+    // dependent-launch wait (the stage's barrier expects x and W together; x follows after the wait)
+    auto load_w = [&](int s, int kb) {
+        const uint32_t b_dst = base + s * STAGE_BYTES + A_BYTES;
+        if (GLU) {                                                              // 64 gate rows, then the 64 up rows that match
+            tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BK, n0);
+            tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, kb * BK, N + n0);
+        } else {
+            tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BK, n0);
+        }
+    };
+    int early = 0;
+    if (warp == 0 && lane == 0) {
+        for (; early < STAGES && early < kblocks; ++early) {
+            mbar_expect_tx(full0 + 8 * early, STAGE_BYTES);
+            load_w(early, early);
+        }
+    }
+    __syncwarp();
+    bl_pdl_wait();                                                              // x, out and the SM's tensor memory belong to the predecessor until here
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -117,22 +140,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    bl_pdl_trigger();                                                           // the next kernel may start its preamble (it waits before it touches data)
 
     if (warp == 0 && lane == 0) {
         // loader: wait until the MMAs that read a stage are done, then refill it
-        int issued = 0;
+        int issued = early;
         for (int kb = 0; kb < kblocks; ++kb) {
             const int s = kb % STAGES;
             if (kb >= STAGES && !mbar_wait(empty0 + 8 * s, ((kb / STAGES) & 1) ^ 1, give_up, 1)) break;
-            const uint32_t a_dst = base + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
-            mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-            tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * BK, m0);
-            if (GLU) {                                                          // 64 gate rows, then the 64 up rows that match
-                tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BK, n0);
-                tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, kb * BK, N + n0);
-            } else {
-                tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BK, n0);
+            if (kb >= early) {
+                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                load_w(s, kb);
             }
+            tma_load_2d(base + s * STAGE_BYTES, &map_a, full0 + 8 * s, kb * BK, m0);
             issued = kb + 1;
         }
         if (*give_up)                                                           // let our own copies land before leaving
@@ -273,7 +293,9 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const void* bias, int bia
     }
     const int cols_per_tile = EPI == BL_EPI_SWIGLU ? BN / 2 : BN;
     dim3 grid((N + cols_per_tile - 1) / cols_per_tile, (M + BM - 1) / BM);
-    gemm_tc_kernel<EPI, TO><<<grid, 128, SMEM_BYTES, s>>>(a, b, bias, bias_dtype, (TO*)out, M, N, K);
+    // a block waits (griddepcontrol.wait) before it allocates tensor memory or touches x and out, so it may be launched
+    // while its predecessor still runs
+    BL_CUDA(bl_launch_dependent(gemm_tc_kernel<EPI, TO>, grid, dim3(128), (size_t)SMEM_BYTES, s, a, b, bias, bias_dtype, (TO*)out, M, N, K));
     BL_CHECK_LAUNCH("bl_gemm_tc");
     return 0;
 }
