@@ -14,7 +14,7 @@ from .linear import linear, EPI_BIAS, EPI_NONE, EPI_RESIDUAL
 from .norm import RMSNorm
 from .rotary import RotaryTable
 
-FUSED_MAX_ROWS = 32       # steps with at most this many rows take the fused norm + product kernels
+FUSED_MAX_ROWS = 64       # steps with at most this many rows take the fused norm + product kernels
 
 
 DECODE_SMS = 148                     # SMs of a B200: launches are sized to fill them once
