@@ -66,7 +66,7 @@ int bl_attention_prefill(const void* q, const void* k_cache, const void* v_cache
                          const int* ctx_len, const int* block_table, int max_pages, const int* tiles, int n_tiles,
                          void* out, int H, int KV, int dh, int page_size, int window, float scale, void* stream);
 // The same on tcgen05 tensor cores with TMA-fed tiles and scores and outputs in tensor memory (attention_tcgen05.cu):
-// head size 64 and pages of 16 only. tiles[n_tiles][3] = (request, first token, rows of the block: 128 or 256). T: rows of
+// head size 64 and pages of 16 only. tiles[n_tiles][2] = (request, first token of a 128-row tile). T: rows of
 // q and out; n_pages: pages in k_cache / v_cache. *status = 0 unless a block gave up on a bounded wait since the last
 // call (synchronises the device).
 int bl_attention_prefill_tc_supported(int dh, int page_size);

@@ -1,22 +1,22 @@
 // Paged causal grouped-query attention for prefill on the fifth-generation tensor cores (head size 64).
 //
-// A block is 256 consecutive new tokens of one request (two row tiles of 128) and one query head; a thread owns
-// one row. It walks the request's keys in blocks of 128 (eight 16-token pages) up to the diagonal; per tile:
+// A block is a tile of 128 consecutive new tokens of one request and one query head. It walks the request's keys
+// in blocks of 128 (eight 16-token pages) up to the diagonal:
 //   S = Q . K^T      tcgen05.mma, M 128 x N 128 x K 64, Q and the key block in shared memory (TMA, 128-byte
 //                    swizzle, K-major), S in tensor memory;
-//   softmax          every thread reads its row of S with tcgen05.ld (lane r of tensor memory is row r, so the
-//                    row maximum and sum need no shuffles), keeps the running maximum and sum in 32-bit, and
-//                    writes P = 2^(s - m) as bfloat16 into shared memory in the swizzled K-major layout;
+//   softmax          a thread reads its row of S with tcgen05.ld (lane r of tensor memory is row r, so the row
+//                    maximum and sum need no shuffles), keeps the running maximum and sum in 32-bit, and writes
+//                    P = 2^(s - m) as bfloat16 into shared memory in the swizzled K-major layout;
 //   O_b = P . V      tcgen05.mma, M 128 x N 64 x K 128, V as it lies in its pages (keys x head size: the
 //                    MN-major form of the B operand), O_b in tensor memory;
 //   out = out * 2^(m_old - m) + O_b   in registers.
-// Eleven warps: four per row tile own the rows, one issues the MMAs of both tiles (lane 0), two issue the TMA
-// copies of keys and of values (a box costs its issuing lane about 0.1 us, so the sixteen boxes of a block are
-// kept off the MMAs' path). They meet only at mbarriers. Keys and values (shared by the two tiles), P and the
-// shares of the output have two buffers each, the scores one per tile: while one tile's warps wait for their
-// next scores the other tile's warps have the SM's arithmetic (the 2^x of the special-function unit above all,
-// which bounds the kernel), and the products run beside both. One block per SM (224 KB of shared memory, all
-// 512 tensor-memory columns).
+// Eleven warps: eight own the rows, in two groups of four that take the even and the odd key blocks (each with a
+// running maximum, sum and output of its own, merged at the end as the slices of a split are); one issues the
+// MMAs (lane 0), two issue the TMA copies of keys and of values (a box costs its issuing lane about 0.1 us, so
+// the sixteen boxes of a block are kept off the MMAs' path). They meet only at mbarriers. Scores, keys, values, P
+// and the shares of the output have two buffers each, one per group: while one group waits for its product and
+// its next scores the other has the SM's arithmetic (the 2^x of the special-function unit above all, which
+// bounds the kernel). One block per SM.
 // Pages come from the request's block table, one TMA box (16 keys x 64) per page and tensor.
 //
 // Every wait on an mbarrier is bounded; when a bound runs out the block records a code in a status word, its
@@ -37,13 +37,13 @@ constexpr int KBLK = 128;              // keys per block
 constexpr int PAGE = 16;
 constexpr int PAGES = KBLK / PAGE;     // TMA boxes per tensor and block
 constexpr int PAGE_BYTES = PAGE * DH * 2;
-constexpr int TILES = 2;               // row tiles of 128 per block: two groups of four warps take turns on the SM
-constexpr int THREADS = TILES * ROWS + 96;   // the row warps, one warp that issues the MMAs, two that copy
-constexpr int Q_BYTES = TILES * ROWS * DH * 2, KV_BYTES = KBLK * DH * 2, P_BYTES = ROWS * KBLK * 2;
+constexpr int THREADS = 2 * ROWS + 96;       // eight row warps (two groups of four), one warp that issues the MMAs, two that copy
+constexpr int Q_BYTES = ROWS * DH * 2, KV_BYTES = KBLK * DH * 2, P_BYTES = ROWS * KBLK * 2;
 constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_P = OFF_V + 2 * KV_BYTES;
-constexpr int OFF_BARS = OFF_P + 2 * TILES * P_BYTES;                // P: [tile][stage]
+constexpr int OFF_XCH = OFF_P + 4 * P_BYTES;                         // the groups' maxima and sums at the merge: 4 x 128 floats
+constexpr int OFF_BARS = OFF_XCH + 4 * ROWS * 4;
 constexpr int SMEM_BYTES = OFF_BARS + 256;
-constexpr int TMEM_COLS = 512;         // scores: 128 columns per tile; shares of the output: [tile][stage] x 64 columns from column 256
+constexpr int TMEM_COLS = 512;         // scores: 2 x 128 columns; shares of the output: 2 x 64 columns from column 256
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 __device__ int g_status = 0;           // 0 = fine; else the code of the first wait that ran out
@@ -70,6 +70,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // take issue slots from the row warps of its scheduler.
 template <bool SLEEP = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
+#pragma unroll 1
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
         uint32_t ok;
         asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
@@ -84,6 +85,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 // Bounded wait that does not look at the give-up flag (a block that has given up waits for its own copies).
 __device__ __forceinline__ void mbar_wait_plain(uint32_t bar, uint32_t parity) {
+#pragma unroll 1
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
         uint32_t ok;
         asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
@@ -113,6 +115,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                  : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The same wait, tied to the registers of the load it completes: nothing that reads them may be moved above it.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                   "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :: "memory");
+}
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 // what the threads wrote into shared memory becomes visible to the tensor cores and to TMA
@@ -147,29 +158,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t base = smem_u32(smem);
     const uint32_t bars = base + OFF_BARS;
-    // barriers, 8 bytes each. [stage] is the stage of keys and values (block i uses stage i & 1), [t] the row tile.
+    // barriers, 8 bytes each; [i & 1] of block i for all pairs
     const uint32_t full_q = bars;
-    const uint32_t full_k0 = bars + 8;          // [stage] keys copied
-    const uint32_t full_v0 = bars + 24;         // [stage] values copied
-    const uint32_t k_free0 = bars + 40;         // [stage] every tile's scores of the block are done: the keys may go
-    const uint32_t v_free0 = bars + 56;         // [stage] every tile's product of the block is done: the values may go
-    const uint32_t s_done0 = bars + 72;         // [t] the tile's scores are in tensor memory
-    const uint32_t o_done0 = bars + 88;         // [t][stage] the tile's share of the output is in tensor memory
-    const uint32_t p_ready0 = bars + 120;       // [t][stage] the tile's P is in shared memory (and its scores have been read)
-    volatile int* give_up = reinterpret_cast<volatile int*>(smem + OFF_BARS + 160);
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BARS + 168);
+    const uint32_t full_k0 = bars + 8;          // keys copied
+    const uint32_t full_v0 = bars + 24;         // values copied
+    const uint32_t s_done0 = bars + 40;         // scores in tensor memory (and the keys' stage free again)
+    const uint32_t o_done0 = bars + 56;         // [group][own block & 1]: share of the output in tensor memory (and the values' stage free again)
+    const uint32_t p_ready0 = bars + 88;        // P in shared memory, scores read: 128 arrivals
+    const uint32_t l_ready = bars + 104;        // both groups have posted their maxima, sums and half of their output
+    volatile int* give_up = reinterpret_cast<volatile int*>(smem + OFF_BARS + 112);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BARS + 120);
+    float* xch = reinterpret_cast<float*>(smem + OFF_XCH);               // [2 groups][maximum, sum][128 rows]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr int ROW_WARPS = TILES * ROWS / 32;
+    constexpr int ROW_WARPS = 2 * ROWS / 32;                             // two groups of one thread per row
     const bool issuer = warp == ROW_WARPS;                               // after the row warps: the MMA issuer, then two copy warps
 
     // late tiles of a request see the most keys: they go first, so that the short ones fill the tail
     const int tile = gridDim.x - 1 - blockIdx.x;
-    const int r = p.tiles[3 * tile], tok0 = p.tiles[3 * tile + 1], row_limit = p.tiles[3 * tile + 2];
+    const int r = p.tiles[2 * tile], tok0 = p.tiles[2 * tile + 1];
     const int head = blockIdx.y, kvh = head / (p.H / p.KV);
     const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin, ctx = p.ctx_len[r];
     const int* table = p.block_table + (size_t)r * p.max_pages;
-    const int rows_here = min(min(TILES * ROWS, row_limit), q_len - tok0);   // > 0 by construction of the tiles
-    const int n_tiles = rows_here > ROWS ? 2 : 1;                        // a short last tile leaves the second half idle
+    const int rows_here = min(ROWS, q_len - tok0);                       // > 0 by construction of the tiles
     const int p_first = ctx - q_len + tok0, p_last = p_first + rows_here - 1;
     const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0, hi = p_last;
     const int b_begin = lo / KBLK, nb = rows_here > 0 ? hi / KBLK + 1 - b_begin : 0;
@@ -178,11 +188,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         *give_up = (base & 1023u) ? 1 : 0;                               // the swizzled tiles need 1024-byte alignment
         if (base & 1023u) atomicCAS(&g_status, 0, 9);
         mbar_init(full_q, 1);
+        mbar_init(l_ready, 2 * ROWS);
         for (int i = 0; i < 2; ++i) {
             mbar_init(full_k0 + 8 * i, 1); mbar_init(full_v0 + 8 * i, 1);
-            mbar_init(k_free0 + 8 * i, n_tiles); mbar_init(v_free0 + 8 * i, n_tiles);
-            mbar_init(s_done0 + 8 * i, 1);
-            for (int j = 0; j < 2; ++j) { mbar_init(o_done0 + 16 * i + 8 * j, 1); mbar_init(p_ready0 + 16 * i + 8 * j, ROWS); }
+            mbar_init(s_done0 + 8 * i, 1); mbar_init(o_done0 + 16 * i, 1); mbar_init(o_done0 + 16 * i + 8, 1);
+            mbar_init(p_ready0 + 8 * i, ROWS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -200,8 +210,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     fence_after_sync();
     const uint32_t tmem = *tmem_slot;
     bl_pdl_trigger();                                                    // the next kernel may start its own preamble (it waits before it touches data)
-    // tensor memory: scores of tile t in columns 128 t ..; the share of the output of tile t and block i in columns
-    // 256 + 128 t + 64 (i & 1) ..
+    // tensor memory: scores of block i in columns 128 (i & 1) ..; its share of the output in columns
+    // 256 + 64 (2 (i & 1) + (i >> 1 & 1)) ..: two per group, so that a group may add one while its next product runs
     bool ok = !*give_up;
 
     if (warp > ROW_WARPS) {
@@ -210,7 +220,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         // block off the path of the MMAs.
         const bool keys = warp == ROW_WARPS + 1;
         const CUtensorMap* map = keys ? &map_k : &map_v;
-        const uint32_t full0 = keys ? full_k0 : full_v0, free0 = keys ? k_free0 : v_free0, off = keys ? OFF_K : OFF_V;
+        const uint32_t full0 = keys ? full_k0 : full_v0, off = keys ? OFF_K : OFF_V;
         auto page_of = [&](int b, int pg) -> int {                       // -1: no row may see a key of this page
             const int first = b * KBLK + pg * PAGE;
             if (first > hi || first + PAGE - 1 < lo) return -1;
@@ -227,7 +237,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int st = i & 1;
             const int page_next = lane < PAGES && i + 1 < nb ? page_of(b_begin + i + 1, lane) : -1;   // on its way during this block's copies
             if (i >= 2) {                                                // the stage is free once block i - 2 has been multiplied
-                if (lane == 0) ok = mbar_wait<true>(free0 + 8 * st, (uint32_t)(((i - 2) >> 1) & 1), give_up, keys ? 3 : 7);
+                const int own = (i - 2) >> 1;                            // which of its group's blocks that one was
+                if (lane == 0)
+                    ok = keys ? mbar_wait<true>(s_done0 + 8 * st, (uint32_t)(own & 1), give_up, 3)
+                              : mbar_wait<true>(o_done0 + 16 * st + 8 * (own & 1), (uint32_t)((own >> 1) & 1), give_up, 7);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
             }
@@ -249,75 +262,83 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (loads[s2] > 0) mbar_wait_plain(full0 + 8 * s2, (uint32_t)((loads[s2] - 1) & 1));
         }
     } else if (issuer) {
-        // ================= one warp: lane 0 issues the MMAs of both tiles
-        auto issue_s = [&](int t, int i) {                               // S_t = Q_t . K^T of the i-th block
-            const uint64_t a = smem_desc(base + OFF_Q + t * (ROWS * DH * 2)), b = smem_desc(base + OFF_K + (i & 1) * KV_BYTES);
+        // ================= one warp: lane 0 issues the MMAs
+        auto issue_s = [&](int i) {                                      // S = Q . K^T of the i-th block of this tile
+            const uint64_t a = smem_desc(base + OFF_Q), b = smem_desc(base + OFF_K + (i & 1) * KV_BYTES);
 #pragma unroll
-            for (int k = 0; k < DH / 16; ++k) umma_bf16(tmem + t * KBLK, a + 2 * k, b + 2 * k, IDESC_S, k != 0);
-            umma_commit(s_done0 + 8 * t);
-            umma_commit(k_free0 + 8 * (i & 1));
+            for (int k = 0; k < DH / 16; ++k) umma_bf16(tmem + (i & 1) * KBLK, a + 2 * k, b + 2 * k, IDESC_S, k != 0);
+            umma_commit(s_done0 + 8 * (i & 1));
         };
         if (lane == 0 && ok && nb > 0) {
             ok = mbar_wait<true>(full_q, 0, give_up, 1) && mbar_wait<true>(full_k0, 0, give_up, 2);
-            if (ok) {
-                fence_after_sync();
-                for (int t = 0; t < n_tiles; ++t) issue_s(t, 0);
+            if (ok) { fence_after_sync(); issue_s(0); }
+            if (ok && nb > 1) {
+                ok = mbar_wait<true>(full_k0 + 8, 0, give_up, 2);
+                if (ok) { fence_after_sync(); issue_s(1); }
             }
             for (int i = 0; ok && i < nb; ++i) {
-                const int st = i & 1;
-                const uint32_t par = (uint32_t)((i >> 1) & 1);
-                for (int t = 0; ok && t < n_tiles; ++t) {
-                    // P_t of block i is in shared memory and the tile's scores have been read
-                    ok = mbar_wait<true>(p_ready0 + 16 * t + 8 * st, par, give_up, 4);
+                const int st = i & 1, own = i >> 1;
+                const uint32_t par = (uint32_t)(own & 1);
+                // the group has read the scores of block i (and written P): first the scores of its next block, which
+                // it waits for, into the same columns; then O_i = P . V, which it adds one block late
+                ok = mbar_wait(p_ready0 + 8 * st, par, give_up, 4);
+                if (!ok) break;
+                if (i + 2 < nb) {
+                    ok = mbar_wait(full_k0 + 8 * st, par ^ 1, give_up, 6);
                     if (!ok) break;
                     fence_after_sync();
-                    if (i + 1 < nb) {                                    // the next scores first: the tile's row warps wait for them
-                        ok = mbar_wait<true>(full_k0 + 8 * (st ^ 1), (uint32_t)(((i + 1) >> 1) & 1), give_up, 6);
-                        if (!ok) break;
-                        fence_after_sync();
-                        issue_s(t, i + 1);
-                    }
-                    ok = mbar_wait<true>(full_v0 + 8 * st, par, give_up, 5);
-                    if (!ok) break;
-                    fence_after_sync();
-                    const uint64_t a0 = smem_desc(base + OFF_P + (2 * t + st) * P_BYTES), bv = smem_desc(base + OFF_V + st * KV_BYTES);
-#pragma unroll
-                    for (int kk = 0; kk < KBLK / 16; ++kk)              // 16 keys a step: 32 bytes along P's rows, two 8-row groups of V
-                        umma_bf16(tmem + TILES * KBLK + (2 * t + st) * DH, a0 + (uint64_t)((kk >> 2) * (ROWS * 128 >> 4) + 2 * (kk & 3)),
-                                  bv + (uint64_t)(kk * (2048 >> 4)), IDESC_PV, kk != 0);
-                    umma_commit(o_done0 + 16 * t + 8 * st);
-                    umma_commit(v_free0 + 8 * st);
+                    issue_s(i + 2);
                 }
+                ok = mbar_wait(full_v0 + 8 * st, par, give_up, 5);
+                if (!ok) break;
+                fence_after_sync();
+                const uint64_t a0 = smem_desc(base + OFF_P + (2 * st + (own & 1)) * P_BYTES), bv = smem_desc(base + OFF_V + st * KV_BYTES);
+                const uint32_t t_o = tmem + 2 * KBLK + (2 * st + (own & 1)) * DH;
+#pragma unroll
+                for (int kk = 0; kk < KBLK / 16; ++kk)                  // 16 keys a step: 32 bytes along P's rows, two 8-row groups of V
+                    umma_bf16(t_o, a0 + (uint64_t)((kk >> 2) * (ROWS * 128 >> 4) + 2 * (kk & 3)),
+                              bv + (uint64_t)(kk * (2048 >> 4)), IDESC_PV, kk != 0);
+                umma_commit(o_done0 + 16 * st + 8 * (own & 1));
             }
         }
         __syncwarp();
-    } else if (warp / (ROWS / 32) < n_tiles) {
-        // ================= four warps per tile: a thread owns one query row
-        const int t = warp / (ROWS / 32);
-        const int row = threadIdx.x - t * ROWS;                          // row of the tile = lane of tensor memory
-        const bool valid = t * ROWS + row < rows_here;
-        const int pos = valid ? p_first + t * ROWS + row : -1;           // an invalid row sees nothing
+    } else {
+        // ================= eight warps in two groups of four: group g takes the key blocks i = g, g + 2, ... of the
+        // tile, a thread of it one query row, with a running maximum, sum and output of the group's own (merged at the
+        // end). While one group is in its exponentials the other reads scores, rescales or waits for its product.
+        const int grp = warp >> 2;
+        const int row = (warp & 3) * 32 + lane;                          // row of the tile = lane of tensor memory
+        const bool valid = row < rows_here;
+        const int pos = valid ? p_first + row : -1;                      // an invalid row sees nothing
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;     // this warp's 32 lanes of tensor memory
-        const uint32_t t_s = tmem + t * KBLK + lane_off;
+        const uint32_t t_s = tmem + grp * KBLK + lane_off, t_o = tmem + 2 * KBLK + 2 * grp * DH + lane_off;
+        const uint32_t s_done = s_done0 + 8 * grp, o_done = o_done0 + 16 * grp, p_ready = p_ready0 + 8 * grp, full_v = full_v0 + 8 * grp;
+        unsigned char* p_group = smem + OFF_P + 2 * grp * P_BYTES;       // the group's two P buffers: its blocks alternate
         float o[DH];
 #pragma unroll
         for (int j = 0; j < DH; ++j) o[j] = 0.f;
         float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
-        // out = out * alpha + O_i, read from tensor memory one block late (the product runs meanwhile)
-        auto add_output = [&](int i, float alpha) {
-            const uint32_t t_o = tmem + TILES * KBLK + (2 * t + (i & 1)) * DH + lane_off;
+        // out = out * alpha + O of the group's own-th block, whose product has had a whole softmax to finish
+        auto add_output = [&](int own, float alpha) -> bool {
+            bool fine = mbar_wait(o_done + 8 * (own & 1), (uint32_t)((own >> 1) & 1), give_up, 11);
+            fine = __all_sync(0xffffffffu, fine);
+            if (!fine) return false;
+            fence_after_sync();
 #pragma unroll
-            for (int c = 0; c < DH / 32; ++c) {
+            for (int h = 0; h < DH / 32; ++h) {
                 uint32_t v[32];
-                tmem_ld32(t_o + c * 32, v);
-                tmem_ld_wait();
+                tmem_ld32(t_o + (own & 1) * DH + h * 32, v);
+                tmem_ld_wait(v);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) o[c * 32 + j] = o[c * 32 + j] * alpha + __uint_as_float(v[j]);
+                for (int j = 0; j < 32; ++j) o[h * 32 + j] = o[h * 32 + j] * alpha + __uint_as_float(v[j]);
             }
+            return true;
         };
-        for (int i = 0; i < nb; ++i) {
-            const int b = b_begin + i, st = i & 1;
-            ok = mbar_wait(s_done0 + 8 * t, (uint32_t)(i & 1), give_up, 8) && ok;
+        int last = -1;                                                   // the group's last block
+        for (int i = grp; i < nb; i += 2) {
+            const int b = b_begin + i;
+            const uint32_t par = (uint32_t)((i >> 1) & 1);
+            ok = mbar_wait(s_done, par, give_up, 8) && ok;
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             fence_after_sync();
@@ -327,21 +348,27 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             // Local key j of chunk c (keys k0 + 32 c + j) is visible when lo_c < j <= hi_c. Everything below is free of
             // branches per key: a masked key becomes -inf before the maximum and before 2^x (2^-inf = 0).
             const int hi_l = pos - k0, lo_l = p.window > 0 ? pos - p.window - k0 : -(1 << 30);
+            // a masked key becomes -inf before the maximum and before 2^x (2^-inf = 0): no branch per key
+            auto mask = [&](uint32_t (&s)[32], int c) {
+                const int hi_c = hi_l - c * 32, lo_c = lo_l - c * 32;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) s[j] = (j <= hi_c && j > lo_c) ? s[j] : 0xff800000u;
+            };
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            auto chunk_max = [&](uint32_t (&s)[32], int c) {
+                if (!all_seen) mask(s, c);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(s[j]));
+            };
+            // First pass, the maximum of the raw scores; 32 scores a load, the next load on its way meanwhile. The
+            // loops over pairs of chunks stay rolled: both groups, at different places of this code, must find it in
+            // the instruction cache.
+            uint32_t sa[32], sb[32];
+            tmem_ld32(t_s, sa);
 #pragma unroll 1
-            for (int c = 0; c < KBLK / 32; ++c) {                        // first pass: the row's maximum (of the raw scores)
-                uint32_t s[32];
-                tmem_ld32(t_s + c * 32, s);
-                tmem_ld_wait();
-                if (all_seen) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(s[j]));
-                } else {
-                    const int hi_c = hi_l - c * 32, lo_c = lo_l - c * 32;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        mx[j & 3] = fmaxf(mx[j & 3], (j <= hi_c && j > lo_c) ? __uint_as_float(s[j]) : -INFINITY);
-                }
+            for (int cp = 0; cp < 2; ++cp) {                             // chunks 2 cp (in sa) and 2 cp + 1 (in sb)
+                tmem_ld_wait(sa); tmem_ld32(t_s + (2 * cp + 1) * 32, sb); chunk_max(sa, 2 * cp);
+                tmem_ld_wait(sb); tmem_ld32(t_s + 64, sa); chunk_max(sb, 2 * cp + 1);   // chunk 2: next here, first of the second pass
             }
             // the scale is positive: the maximum of the scaled scores is the scaled maximum
             const float m_new = fmaxf(m, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2);
@@ -349,80 +376,85 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const float alpha = bl_ex2(m - m_use);                       // 2^-inf = 0 on the first block
             m = m_new;
             float sm4[4] = {0.f, 0.f, 0.f, 0.f};
-            unsigned char* p_tile = smem + OFF_P + (2 * t + st) * P_BYTES;
-#pragma unroll 1
-            for (int c = 0; c < KBLK / 32; ++c) {                        // second pass: P into shared memory
-                uint32_t s[32];
-                tmem_ld32(t_s + c * 32, s);
-                tmem_ld_wait();
-                float e[32];
-                if (all_seen) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        e[j] = bl_ex2(fmaf(__uint_as_float(s[j]), p.scale_log2, -m_use));
-                        sm4[j & 3] += e[j];
-                    }
-                } else {
-                    const int hi_c = hi_l - c * 32, lo_c = lo_l - c * 32;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float x = fmaf(__uint_as_float(s[j]), p.scale_log2, -m_use);
-                        e[j] = bl_ex2((j <= hi_c && j > lo_c) ? x : -INFINITY);
-                        sm4[j & 3] += e[j];
-                    }
-                }
-                // 16-byte chunk cc of the row's 256 bytes: sub-tile cc / 8 (64 keys each), chunk cc % 8, swizzled by the row
+            // Second pass, chunks 3 (still in sb), 2, 1, 0: P = 2^(s * scale - m) as bfloat16 into shared memory. Keys
+            // 0..63 and 64..127 are two sub-tiles; 16-byte chunk cc (0..7) of the row's 128 bytes is swizzled by the row.
+            unsigned char* p_row = p_group + ((i >> 1) & 1) * P_BYTES + row * 128;
+            auto chunk_exp = [&](uint32_t (&s)[32], int c) {
+                if (!all_seen) mask(s, c);
+                unsigned char* sub = p_row + (c >> 1) * (ROWS * 128);
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const int cc = c * 4 + q4;
-                    unsigned char* dst = p_tile + (cc >> 3) * (ROWS * 128) + row * 128 + (((cc & 7) ^ (row & 7)) << 4);
-                    *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(e[8 * q4], e[8 * q4 + 1]), pack_bf16(e[8 * q4 + 2], e[8 * q4 + 3]),
-                                                                pack_bf16(e[8 * q4 + 4], e[8 * q4 + 5]), pack_bf16(e[8 * q4 + 6], e[8 * q4 + 7]));
+                    float e[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        e[j] = bl_ex2(fmaf(__uint_as_float(s[8 * q4 + j]), p.scale_log2, -m_use));
+                        sm4[j & 3] += e[j];
+                    }
+                    const int cc = (c & 1) * 4 + q4;
+                    *reinterpret_cast<uint4*>(sub + ((cc ^ (row & 7)) << 4)) =
+                        make_uint4(pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
                 }
+            };
+#pragma unroll 1
+            for (int cp = 1; cp >= 0; --cp) {                            // chunks 2 cp + 1 (in sb) and 2 cp (on its way into sa)
+                chunk_exp(sb, 2 * cp + 1);
+                tmem_ld_wait(sa);
+                if (cp) tmem_ld32(t_s + 32, sb);
+                chunk_exp(sa, 2 * cp);
+                if (cp) { tmem_ld_wait(sb); tmem_ld32(t_s, sa); }
             }
             l = l * alpha + ((sm4[0] + sm4[1]) + (sm4[2] + sm4[3]));
             // the values of this block: rows that were not copied, or that lie past the last key, become zeros
-            // (their P is 0, and 0 times whatever an old request left in a page must stay 0). Both tiles write the
-            // same zeros: neither has to wait for the other.
+            // (their P is 0, and 0 times whatever an old request left in a page must stay 0)
             if (k0 + KBLK - 1 > hi || k0 < lo) {
-                ok = mbar_wait(full_v0 + 8 * st, (uint32_t)((i >> 1) & 1), give_up, 10) && ok;
+                ok = mbar_wait(full_v, par, give_up, 10) && ok;
                 if (ok) {
-                    for (int idx = row; idx < KBLK * 8; idx += ROWS) {   // (key row, 16-byte chunk); a row's chunks stay in the row
+                    for (int idx = threadIdx.x & (ROWS - 1); idx < KBLK * 8; idx += ROWS) {   // (key row, 16-byte chunk); a row's chunks stay in the row
                         const int key = k0 + (idx >> 3);
                         const int first = key / PAGE * PAGE;
                         const bool copied = !(first > hi || first + PAGE - 1 < lo) && table[first / PAGE] >= 0;
                         if (!copied || key > hi)
-                            *reinterpret_cast<uint4*>(smem + OFF_V + st * KV_BYTES + (idx << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                            *reinterpret_cast<uint4*>(smem + OFF_V + grp * KV_BYTES + (idx << 4)) = make_uint4(0u, 0u, 0u, 0u);
                     }
                 }
             }
             fence_async_smem();
             fence_before_sync();
-            mbar_arrive(p_ready0 + 16 * t + 8 * st);
-            // the share of the block before: its product has had a whole softmax to finish
-            if (i > 0) {
-                ok = mbar_wait(o_done0 + 16 * t + 8 * (st ^ 1), (uint32_t)(((i - 1) >> 1) & 1), give_up, 11) && ok;
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                fence_after_sync();
-                add_output(i - 1, alpha_prev);
-            }
+            mbar_arrive(p_ready);
+            // while the issuer starts this block's product and the next scores: the share of the block before
+            if (last >= 0 && !add_output(last >> 1, alpha_prev)) { ok = false; break; }
             alpha_prev = alpha;
+            last = i;
         }
-        if (nb > 0) {
-            ok = mbar_wait(o_done0 + 16 * t + 8 * ((nb - 1) & 1), (uint32_t)(((nb - 1) >> 1) & 1), give_up, 12) && ok;
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok) {
-                fence_after_sync();
-                add_output(nb - 1, alpha_prev);
-                if (valid) {
-                    const float inv = l > 0.f ? 1.0f / l : 0.f;
-                    __nv_bfloat16* dst = p.out + ((size_t)(q_begin + tok0 + t * ROWS + row) * p.H + head) * DH;
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok && last >= 0) ok = add_output(last >> 1, alpha_prev);
+        // The groups merge: each finishes half of the head's dimensions, and hands the other half of its output,
+        // with its maximum and sum, to the other group through its own P buffer (all its products are done).
+        {
+            float* mine = reinterpret_cast<float*>(p_group);                              // [row][33]
+            const float* theirs = reinterpret_cast<const float*>(smem + OFF_P + 2 * (grp ^ 1) * P_BYTES);
 #pragma unroll
-                    for (int j = 0; j < DH; j += 8)
-                        *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16(o[j] * inv, o[j + 1] * inv), pack_bf16(o[j + 2] * inv, o[j + 3] * inv),
-                                                                        pack_bf16(o[j + 4] * inv, o[j + 5] * inv), pack_bf16(o[j + 6] * inv, o[j + 7] * inv));
-                }
+            for (int j = 0; j < DH / 2; ++j) mine[row * 33 + j] = grp ? o[j] : o[DH / 2 + j];
+            xch[(grp * 2) * ROWS + row] = m;
+            xch[(grp * 2 + 1) * ROWS + row] = l;
+            mbar_arrive(l_ready);
+            ok = mbar_wait(l_ready, 0, give_up, 14) && ok;
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok && valid) {
+                const float m_o = xch[((grp ^ 1) * 2) * ROWS + row], l_o = xch[((grp ^ 1) * 2 + 1) * ROWS + row];
+                const float mm = fmaxf(m, m_o), m_use = mm == -INFINITY ? 0.f : mm;
+                const float a = bl_ex2(m - m_use), a_o = bl_ex2(m_o - m_use);
+                const float total = l * a + l_o * a_o;
+                const float inv = total > 0.f ? 1.0f / total : 0.f;
+                const float wa = a * inv, wo = a_o * inv;
+                float r[DH / 2];
+#pragma unroll
+                for (int j = 0; j < DH / 2; ++j) r[j] = (grp ? o[DH / 2 + j] : o[j]) * wa + theirs[row * 33 + j] * wo;
+                __nv_bfloat16* dst = p.out + ((size_t)(q_begin + tok0 + row) * p.H + head) * DH + grp * (DH / 2);
+#pragma unroll
+                for (int j = 0; j < DH / 2; j += 8)
+                    *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16(r[j], r[j + 1]), pack_bf16(r[j + 2], r[j + 3]),
+                                                                    pack_bf16(r[j + 4], r[j + 5]), pack_bf16(r[j + 6], r[j + 7]));
             }
         }
     }
@@ -470,9 +502,8 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, int bo
 
 extern "C" int bl_attention_prefill_tc_supported(int dh, int page_size) { return dh == DH && page_size == PAGE; }
 
-// tiles[n_tiles][3] = (request, first token of the block's rows within the request's new tokens, rows of the block:
-// 256, or 128 for a block that takes one row tile only). T: rows of q and out; n_pages: pages of the cache tensors
-// (their first dimension).
+// tiles[n_tiles][2] = (request, first token of the tile's 128 rows within the request's new tokens); the last
+// entries start first. T: rows of q and out; n_pages: pages of the cache tensors (their first dimension).
 extern "C" int bl_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
                                        const int* ctx_len, const int* block_table, int max_pages, const int* tiles,
                                        int n_tiles, void* out, int T, int n_pages, int H, int KV, int dh, int page_size,
@@ -486,7 +517,7 @@ extern "C" int bl_attention_prefill_tc(const void* q, const void* k_cache, const
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15)
         BL_FAIL("bl_attention_prefill_tc: q, the caches and out must be 16-byte aligned");
     CUtensorMap mq, mk, mv;
-    if (make_map(&mq, q, T, H * DH, TILES * ROWS)) return 1;
+    if (make_map(&mq, q, T, H * DH, ROWS)) return 1;
     if (make_map(&mk, k_cache, (long long)n_pages * KV * PAGE, DH, PAGE)) return 1;
     if (make_map(&mv, v_cache, (long long)n_pages * KV * PAGE, DH, PAGE)) return 1;
     Params p;
@@ -507,7 +538,8 @@ extern "C" int bl_attention_prefill_tc(const void* q, const void* k_cache, const
 
 // Reads and clears the status word: 0 when no block has given up on a wait since the last call. Codes name the
 // wait: 1 q, 2 first keys, 3 / 7 a stage of keys / values to become free, 4 P, 5 values, 6 keys of the block after
-// next, 8 scores, 10 values (row warps), 11 / 12 a share of the output, 9 shared memory not 1024-byte aligned.
+// next, 8 scores, 10 values (row warps), 11 a share of the output, 14 the other group at the merge, 9 shared
+// memory not 1024-byte aligned.
 // Synchronises the device.
 extern "C" int bl_attention_prefill_tc_status(int* status) {
     int v = 0, zero = 0;

@@ -248,15 +248,14 @@ def attention_prefill_tc_supported(dtype: torch.dtype, dh: int, page_size: int) 
 
 def attention_prefill_tc(q, k_cache, v_cache, cu_q, ctx_len, block_table, tiles, out, H: int, window: int,
                          scale: float) -> None:
-    """The tcgen05 form of `attention_prefill` (head size 64, pages of 16). tiles: int32 [n, 3] = (request,
-    first token among the request's new tokens, rows of the block: 256, or 128 for one row tile alone); the
-    last entries are launched first."""
+    """The tcgen05 form of `attention_prefill` (head size 64, pages of 16). tiles: int32 [n, 2] = (request,
+    first token of a tile of 128 among the request's new tokens); the last entries are launched first."""
     T = q.shape[0]
     n_pages, KV, page_size, dh = k_cache.shape
     _need(q, "q", torch.bfloat16, (T, H * dh)); _need(k_cache, "k_cache", torch.bfloat16)
     _need(v_cache, "v_cache", torch.bfloat16, k_cache.shape); _need(out, "out", torch.bfloat16, (T, H * dh))
     _need(cu_q, "cu_q", torch.int32); _need(ctx_len, "ctx_len", torch.int32); _need(block_table, "block_table", torch.int32)
-    _need(tiles, "tiles", torch.int32, (tiles.shape[0], 3))
+    _need(tiles, "tiles", torch.int32, (tiles.shape[0], 2))
     _call(_lib().bl_attention_prefill_tc, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
           block_table.shape[1], _p(tiles), tiles.shape[0], _p(out), T, n_pages, H, KV, dh, page_size, window,
           ctypes.c_float(scale), _stream())

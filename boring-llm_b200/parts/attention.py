@@ -22,34 +22,19 @@ PREFILL_TC_MIN_TOKENS = 1024         # steps with fewer prompt tokens keep the 6
 DECODE_MAX_SPLITS = 32               # more slices make the merge longer than they shorten the scan
 
 
-def tc_attention_blocks(q_lens, ctx_lens, heads: int, sms: int = DECODE_SMS):
-    """The launch list of the tcgen05 prefill attention: (request, first token, rows) per block and head, lightest
-    first (the kernel starts from the end of the list). A block takes two row tiles of 128 that share their keys
-    and values and take turns on the SM: best when there are more blocks than SMs. A launch that would leave
-    SMs idle lasts as long as its block with the most keys, and that block runs nearly twice as fast with one
-    row tile alone: so, heaviest first, blocks give their second tile to a block of its own until the SMs are
-    filled. Key blocks are estimated without the window (an upper bound)."""
-    PAIR, ALONE = 3.4, 1.85                              # microseconds per 128-key block, measured
-    blocks = []                                          # [cost, request, first token, rows]
+def tc_attention_blocks(q_lens, ctx_lens):
+    """The launch list of the tcgen05 prefill attention: (request, first token) of every tile of 128 new tokens of
+    the requests with more than one, the tile with the fewest keys first (the kernel starts from the end of the
+    list, so that the long tiles run first and the short ones fill the tail). Key blocks are counted without the
+    window (an upper bound)."""
+    tiles = []                                           # [key blocks, request, first token]
     for r, (n, c) in enumerate(zip(q_lens, ctx_lens)):
         if n <= 1:
             continue
-        for t0 in range(0, n, 256):
-            rows = min(256, n - t0)
-            key_blocks = -(-(c - n + t0 + rows) // 128)
-            blocks.append([key_blocks * (PAIR if rows > 128 else ALONE), r, t0, 256 if rows > 128 else 128])
-    blocks.sort(reverse=True)
-    i, total = 0, len(blocks)
-    while total * heads < sms and i < len(blocks):
-        cost, r, t0, rows = blocks[i]
-        if rows == 256:
-            key_blocks = round(cost / PAIR)
-            blocks[i] = [-(-(key_blocks * 128 - 128) // 128) * ALONE, r, t0, 128]      # the first tile ends 128 keys earlier
-            blocks.append([key_blocks * ALONE, r, t0 + 128, 128])
-            total += 1
-        i += 1
-    blocks.sort()
-    return [[r, t0, rows] for _, r, t0, rows in blocks]
+        for t0 in range(0, n, 128):
+            tiles.append([-(-(c - n + min(t0 + 128, n)) // 128), r, t0])
+    tiles.sort()
+    return [[r, t0] for _, r, t0 in tiles]
 
 
 class Mixer(Part):
@@ -168,9 +153,9 @@ class GQAAttention(Mixer):
         if ctx.prefill_tiles is not None:
             if (ctx.prefill_tokens >= PREFILL_TC_MIN_TOKENS
                     and ops.attention_prefill_tc_supported(q.dtype, self.dh, k_cache.shape[2])):
-                key = ("tcgen05 attention blocks", self.H)
+                key = "tcgen05 attention tiles"
                 if key not in ctx.memo:                 # once per step: the other layers find it here
-                    ctx.memo[key] = torch.tensor(tc_attention_blocks(ctx.q_lens, ctx.ctx_lens, self.H),
+                    ctx.memo[key] = torch.tensor(tc_attention_blocks(ctx.q_lens, ctx.ctx_lens),
                                                  dtype=torch.int32, device=ctx.device)
                 ops.attention_prefill_tc(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.memo[key], out,
                                          self.H, self.window, self.scale)

@@ -422,14 +422,13 @@ def test_attention_mma_window_edges(window):
 
 
 def tc_attention(q, kc, vc, tok_req, cu_q, ctx_len, table, out, H, window, scale):
-    """The tcgen05 prefill kernel for requests with several new tokens (tiles of 256 rows), the decode kernel for the rest."""
+    """The tcgen05 prefill kernel for requests with several new tokens (tiles of 128 rows), the decode kernel for the rest."""
     o = ops()
     cu = cu_q.cpu().tolist()
     q_lens = [b - a for a, b in zip(cu[:-1], cu[1:])]
     from boring_llm_b200.parts.attention import tc_attention_blocks
     ctx_lens = ctx_len.cpu().tolist()
-    # few blocks: the heavy ones are split into single row tiles; `sms=1` keeps every pair together
-    tiles = tc_attention_blocks(q_lens, ctx_lens, H) if len(q_lens) % 2 else tc_attention_blocks(q_lens, ctx_lens, H, sms=1)
+    tiles = tc_attention_blocks(q_lens, ctx_lens)
     singles = [r for r, n in enumerate(q_lens) if n == 1]
     out.fill_(float("nan"))
     if tiles:
