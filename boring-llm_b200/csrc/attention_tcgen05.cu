@@ -6,17 +6,21 @@
 //                    swizzle, K-major), S in tensor memory;
 //   softmax          a thread reads its row of S with tcgen05.ld (lane r of tensor memory is row r, so the row
 //                    maximum and sum need no shuffles), keeps the running maximum and sum in 32-bit, and writes
-//                    P = 2^(s - m) as bfloat16 into shared memory in the swizzled K-major layout;
+//                    P = 2^(s - m) as bfloat16 pairs back into tensor memory (tcgen05.st), where the second
+//                    product takes its A operand from: P never passes through shared memory, whose bandwidth
+//                    the products' other operands and the TMA copies need;
 //   O_b = P . V      tcgen05.mma, M 128 x N 64 x K 128, V as it lies in its pages (keys x head size: the
 //                    MN-major form of the B operand), O_b in tensor memory;
 //   out = out * 2^(m_old - m) + O_b   in registers.
 // Eleven warps: eight own the rows, in two groups of four that take the even and the odd key blocks (each with a
 // running maximum, sum and output of its own, merged at the end as the slices of a split are); one issues the
 // MMAs (lane 0), two issue the TMA copies of keys and of values (a box costs its issuing lane about 0.1 us, so
-// the sixteen boxes of a block are kept off the MMAs' path). They meet only at mbarriers. Scores, keys, values, P
-// and the shares of the output have two buffers each, one per group: while one group waits for its product and
-// its next scores the other has the SM's arithmetic (the 2^x of the special-function unit above all, which
-// bounds the kernel). One block per SM.
+// the sixteen boxes of a block are kept off the MMAs' path). They meet only at mbarriers. Each group has its own
+// scores, P, share of the output (256 of the 512 tensor-memory columns) and stage of keys and values: while one
+// group waits for its product and its next scores the other has the SM's arithmetic (the 2^x of the
+// special-function unit above all, which bounds the kernel). The loops over a row's scores stay rolled in pairs of
+// 32-score loads, and the bounded waits are not unrolled: warps at different places of the code must all find it
+// in the instruction cache. One block per SM.
 // Pages come from the request's block table, one TMA box (16 keys x 64) per page and tensor.
 //
 // Every wait on an mbarrier is bounded; when a bound runs out the block records a code in a status word, its
@@ -38,12 +42,14 @@ constexpr int PAGE = 16;
 constexpr int PAGES = KBLK / PAGE;     // TMA boxes per tensor and block
 constexpr int PAGE_BYTES = PAGE * DH * 2;
 constexpr int THREADS = 2 * ROWS + 96;       // eight row warps (two groups of four), one warp that issues the MMAs, two that copy
-constexpr int Q_BYTES = ROWS * DH * 2, KV_BYTES = KBLK * DH * 2, P_BYTES = ROWS * KBLK * 2;
-constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_P = OFF_V + 2 * KV_BYTES;
-constexpr int OFF_XCH = OFF_P + 4 * P_BYTES;                         // the groups' maxima and sums at the merge: 4 x 128 floats
+constexpr int Q_BYTES = ROWS * DH * 2, KV_BYTES = KBLK * DH * 2;
+constexpr int MERGE_BYTES = ROWS * 33 * 4;                           // half of a group's output at the merge, rows padded to 33 floats
+constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_MERGE = OFF_V + 2 * KV_BYTES;
+constexpr int OFF_XCH = OFF_MERGE + 2 * MERGE_BYTES;                         // the groups' maxima and sums at the merge: 4 x 128 floats
 constexpr int OFF_BARS = OFF_XCH + 4 * ROWS * 4;
 constexpr int SMEM_BYTES = OFF_BARS + 256;
-constexpr int TMEM_COLS = 512;         // scores: 2 x 128 columns; shares of the output: 2 x 64 columns from column 256
+constexpr int TMEM_COLS = 512;         // per group: scores 128 columns, P (bfloat16 pairs) 64, share of the output 64
+constexpr int COL_P = 2 * KBLK, COL_O = COL_P + 2 * (KBLK / 2);
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 __device__ int g_status = 0;           // 0 = fine; else the code of the first wait that ran out
@@ -101,6 +107,18 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                  :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the same with the A operand in tensor memory (lane = row, a 32-bit column = two bfloat16 along K)
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+                 :: "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 :: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                    "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
 }
@@ -114,7 +132,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr) : "memory");
 }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // The same wait, tied to the registers of the load it completes: nothing that reads them may be moved above it.
 __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;"
@@ -163,8 +180,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const uint32_t full_k0 = bars + 8;          // keys copied
     const uint32_t full_v0 = bars + 24;         // values copied
     const uint32_t s_done0 = bars + 40;         // scores in tensor memory (and the keys' stage free again)
-    const uint32_t o_done0 = bars + 56;         // [group][own block & 1]: share of the output in tensor memory (and the values' stage free again)
-    const uint32_t p_ready0 = bars + 88;        // P in shared memory, scores read: 128 arrivals
+    const uint32_t o_done0 = bars + 56;         // share of the output in tensor memory (and P and the values' stage free again)
+    const uint32_t p_ready0 = bars + 88;        // P in tensor memory, scores read: 128 arrivals
     const uint32_t l_ready = bars + 104;        // both groups have posted their maxima, sums and half of their output
     volatile int* give_up = reinterpret_cast<volatile int*>(smem + OFF_BARS + 112);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BARS + 120);
@@ -191,7 +208,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         mbar_init(l_ready, 2 * ROWS);
         for (int i = 0; i < 2; ++i) {
             mbar_init(full_k0 + 8 * i, 1); mbar_init(full_v0 + 8 * i, 1);
-            mbar_init(s_done0 + 8 * i, 1); mbar_init(o_done0 + 16 * i, 1); mbar_init(o_done0 + 16 * i + 8, 1);
+            mbar_init(s_done0 + 8 * i, 1); mbar_init(o_done0 + 8 * i, 1);
             mbar_init(p_ready0 + 8 * i, ROWS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -210,8 +227,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     fence_after_sync();
     const uint32_t tmem = *tmem_slot;
     bl_pdl_trigger();                                                    // the next kernel may start its own preamble (it waits before it touches data)
-    // tensor memory: scores of block i in columns 128 (i & 1) ..; its share of the output in columns
-    // 256 + 64 (2 (i & 1) + (i >> 1 & 1)) ..: two per group, so that a group may add one while its next product runs
+    // tensor memory: scores of block i in columns 128 (i & 1) .., its P in columns 256 + 64 (i & 1) .., its share of
+    // the output in columns 384 + 64 (i & 1) ..
     bool ok = !*give_up;
 
     if (warp > ROW_WARPS) {
@@ -240,7 +257,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 const int own = (i - 2) >> 1;                            // which of its group's blocks that one was
                 if (lane == 0)
                     ok = keys ? mbar_wait<true>(s_done0 + 8 * st, (uint32_t)(own & 1), give_up, 3)
-                              : mbar_wait<true>(o_done0 + 16 * st + 8 * (own & 1), (uint32_t)((own >> 1) & 1), give_up, 7);
+                              : mbar_wait<true>(o_done0 + 8 * st, (uint32_t)(own & 1), give_up, 7);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
             }
@@ -279,8 +296,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             for (int i = 0; ok && i < nb; ++i) {
                 const int st = i & 1, own = i >> 1;
                 const uint32_t par = (uint32_t)(own & 1);
-                // the group has read the scores of block i (and written P): first the scores of its next block, which
-                // it waits for, into the same columns; then O_i = P . V, which it adds one block late
+                // the group has read the scores of block i, written P and taken the share of its block before: first the
+                // scores of its next block, which it waits for, into the same columns; then O_i = P . V
                 ok = mbar_wait(p_ready0 + 8 * st, par, give_up, 4);
                 if (!ok) break;
                 if (i + 2 < nb) {
@@ -292,13 +309,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 ok = mbar_wait(full_v0 + 8 * st, par, give_up, 5);
                 if (!ok) break;
                 fence_after_sync();
-                const uint64_t a0 = smem_desc(base + OFF_P + (2 * st + (own & 1)) * P_BYTES), bv = smem_desc(base + OFF_V + st * KV_BYTES);
-                const uint32_t t_o = tmem + 2 * KBLK + (2 * st + (own & 1)) * DH;
+                const uint64_t bv = smem_desc(base + OFF_V + st * KV_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < KBLK / 16; ++kk)                  // 16 keys a step: 32 bytes along P's rows, two 8-row groups of V
-                    umma_bf16(t_o, a0 + (uint64_t)((kk >> 2) * (ROWS * 128 >> 4) + 2 * (kk & 3)),
-                              bv + (uint64_t)(kk * (2048 >> 4)), IDESC_PV, kk != 0);
-                umma_commit(o_done0 + 16 * st + 8 * (own & 1));
+                for (int kk = 0; kk < KBLK / 16; ++kk)                  // 16 keys a step: 8 columns of P, two 8-row groups of V
+                    umma_bf16_ts(tmem + COL_O + st * DH, tmem + COL_P + st * (KBLK / 2) + kk * 8,
+                                 bv + (uint64_t)(kk * (2048 >> 4)), IDESC_PV, kk != 0);
+                umma_commit(o_done0 + 8 * st);
             }
         }
         __syncwarp();
@@ -311,23 +327,23 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const bool valid = row < rows_here;
         const int pos = valid ? p_first + row : -1;                      // an invalid row sees nothing
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;     // this warp's 32 lanes of tensor memory
-        const uint32_t t_s = tmem + grp * KBLK + lane_off, t_o = tmem + 2 * KBLK + 2 * grp * DH + lane_off;
-        const uint32_t s_done = s_done0 + 8 * grp, o_done = o_done0 + 16 * grp, p_ready = p_ready0 + 8 * grp, full_v = full_v0 + 8 * grp;
-        unsigned char* p_group = smem + OFF_P + 2 * grp * P_BYTES;       // the group's two P buffers: its blocks alternate
+        const uint32_t t_s = tmem + grp * KBLK + lane_off, t_p = tmem + COL_P + grp * (KBLK / 2) + lane_off,
+                       t_o = tmem + COL_O + grp * DH + lane_off;
+        const uint32_t s_done = s_done0 + 8 * grp, o_done = o_done0 + 8 * grp, p_ready = p_ready0 + 8 * grp, full_v = full_v0 + 8 * grp;
         float o[DH];
 #pragma unroll
         for (int j = 0; j < DH; ++j) o[j] = 0.f;
         float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
-        // out = out * alpha + O of the group's own-th block, whose product has had a whole softmax to finish
+        // out = out * alpha + O of the group's own-th block
         auto add_output = [&](int own, float alpha) -> bool {
-            bool fine = mbar_wait(o_done + 8 * (own & 1), (uint32_t)((own >> 1) & 1), give_up, 11);
+            bool fine = mbar_wait(o_done, (uint32_t)(own & 1), give_up, 11);
             fine = __all_sync(0xffffffffu, fine);
             if (!fine) return false;
             fence_after_sync();
 #pragma unroll
             for (int h = 0; h < DH / 32; ++h) {
                 uint32_t v[32];
-                tmem_ld32(t_o + (own & 1) * DH + h * 32, v);
+                tmem_ld32(t_o + h * 32, v);
                 tmem_ld_wait(v);
 #pragma unroll
                 for (int j = 0; j < 32; ++j) o[h * 32 + j] = o[h * 32 + j] * alpha + __uint_as_float(v[j]);
@@ -375,25 +391,24 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const float m_use = m_new == -INFINITY ? 0.f : m_new;        // a row that has seen no key yet
             const float alpha = bl_ex2(m - m_use);                       // 2^-inf = 0 on the first block
             m = m_new;
+            // The share of the group's block before: its product frees P and the columns of the output, which the
+            // product of this block will take. It has had the time of this block's scores and first pass.
+            if (last >= 0 && !add_output(last >> 1, alpha_prev)) { ok = false; break; }
             float sm4[4] = {0.f, 0.f, 0.f, 0.f};
-            // Second pass, chunks 3 (still in sb), 2, 1, 0: P = 2^(s * scale - m) as bfloat16 into shared memory. Keys
-            // 0..63 and 64..127 are two sub-tiles; 16-byte chunk cc (0..7) of the row's 128 bytes is swizzled by the row.
-            unsigned char* p_row = p_group + ((i >> 1) & 1) * P_BYTES + row * 128;
+            // Second pass, chunks 3 (still in sb), 2, 1, 0: P = 2^(s * scale - m) as bfloat16 into tensor memory, the A
+            // operand of the second product: lane = row, two keys to a 32-bit column, 16 columns a chunk.
             auto chunk_exp = [&](uint32_t (&s)[32], int c) {
                 if (!all_seen) mask(s, c);
-                unsigned char* sub = p_row + (c >> 1) * (ROWS * 128);
+                uint32_t pk[16];
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    float e[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        e[j] = bl_ex2(fmaf(__uint_as_float(s[8 * q4 + j]), p.scale_log2, -m_use));
-                        sm4[j & 3] += e[j];
-                    }
-                    const int cc = (c & 1) * 4 + q4;
-                    *reinterpret_cast<uint4*>(sub + ((cc ^ (row & 7)) << 4)) =
-                        make_uint4(pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
+                for (int j = 0; j < 16; ++j) {
+                    const float e0 = bl_ex2(fmaf(__uint_as_float(s[2 * j]), p.scale_log2, -m_use));
+                    const float e1 = bl_ex2(fmaf(__uint_as_float(s[2 * j + 1]), p.scale_log2, -m_use));
+                    sm4[j & 1] += e0;
+                    sm4[2 + (j & 1)] += e1;
+                    pk[j] = pack_bf16(e0, e1);
                 }
+                tmem_st16(t_p + 16 * c, pk);
             };
 #pragma unroll 1
             for (int cp = 1; cp >= 0; --cp) {                            // chunks 2 cp + 1 (in sb) and 2 cp (on its way into sa)
@@ -419,20 +434,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 }
             }
             fence_async_smem();
+            tmem_st_wait();
             fence_before_sync();
             mbar_arrive(p_ready);
-            // while the issuer starts this block's product and the next scores: the share of the block before
-            if (last >= 0 && !add_output(last >> 1, alpha_prev)) { ok = false; break; }
             alpha_prev = alpha;
             last = i;
         }
         ok = __all_sync(0xffffffffu, ok);
         if (ok && last >= 0) ok = add_output(last >> 1, alpha_prev);
         // The groups merge: each finishes half of the head's dimensions, and hands the other half of its output,
-        // with its maximum and sum, to the other group through its own P buffer (all its products are done).
+        // with its maximum and sum, to the other group through shared memory.
         {
-            float* mine = reinterpret_cast<float*>(p_group);                              // [row][33]
-            const float* theirs = reinterpret_cast<const float*>(smem + OFF_P + 2 * (grp ^ 1) * P_BYTES);
+            float* mine = reinterpret_cast<float*>(smem + OFF_MERGE + grp * MERGE_BYTES);          // [row][33]
+            const float* theirs = reinterpret_cast<const float*>(smem + OFF_MERGE + (grp ^ 1) * MERGE_BYTES);
 #pragma unroll
             for (int j = 0; j < DH / 2; ++j) mine[row * 33 + j] = grp ? o[j] : o[DH / 2 + j];
             xch[(grp * 2) * ROWS + row] = m;
