@@ -252,11 +252,13 @@ attention_mma_kernel(const AttnParams p) {
         split = blockIdx.x;
         tok0 = 0;
     } else {
-        // late tiles of a request see the most keys: they go first, so that the short ones fill the tail
-        const int tile = gridDim.x - 1 - blockIdx.x;
+        // Blocks start in the order of their index: all heads of the last tile, then all heads of the tile before.
+        // Late tiles of a request see the most keys: they go first, so that the short ones fill the tail (with the
+        // heads outermost, the long tiles of the last heads would start when the SMs are nearly through).
+        const int tile = gridDim.x / p.H - 1 - blockIdx.x / p.H;
         r = p.work[2 * tile];
         tok0 = p.work[2 * tile + 1];
-        head0 = blockIdx.y;
+        head0 = blockIdx.x % p.H;
         kvh = head0 / G;
     }
     // the step's index arrays are written before its first kernel: they may be read before the wait
@@ -597,7 +599,8 @@ extern "C" int bl_attention_prefill(const void* q, const void* k_cache, const vo
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
     p.work = tiles; p.part_o = nullptr; p.part_ml = nullptr; p.counters = nullptr; p.n_splits = 1; p.H = H; p.KV = KV; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
-    return dispatch<false>(dh, p, dim3(n_tiles, H, 1), (cudaStream_t)stream);
+    if ((long long)n_tiles * H > 2147483647LL) BL_FAIL("bl_attention_prefill: %d tiles x %d heads are more blocks than a launch takes", n_tiles, H);
+    return dispatch<false>(dh, p, dim3(n_tiles * H, 1, 1), (cudaStream_t)stream);
 }
 
 // Floats of scratch that bl_attention_decode needs for n requests and n_splits slices (0 when n_splits is 1).

@@ -190,10 +190,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     constexpr int ROW_WARPS = 2 * ROWS / 32;                             // two groups of one thread per row
     const bool issuer = warp == ROW_WARPS;                               // after the row warps: the MMA issuer, then two copy warps
 
-    // late tiles of a request see the most keys: they go first, so that the short ones fill the tail
-    const int tile = gridDim.x - 1 - blockIdx.x;
+    // Blocks start in the order of their index: all heads of the list's last tile, then all heads of the tile before.
+    // The list is sorted by keys, so the launch runs longest tile first and the short ones fill the tail (with the
+    // heads outermost, the long tiles of the last heads would start when the SMs are nearly through).
+    const int tile = gridDim.x / p.H - 1 - blockIdx.x / p.H;
     const int r = p.tiles[2 * tile], tok0 = p.tiles[2 * tile + 1];
-    const int head = blockIdx.y, kvh = head / (p.H / p.KV);
+    const int head = blockIdx.x % p.H, kvh = head / (p.H / p.KV);
     const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin, ctx = p.ctx_len[r];
     const int* table = p.block_table + (size_t)r * p.max_pages;
     const int rows_here = min(ROWS, q_len - tok0);                       // > 0 by construction of the tiles
@@ -544,7 +546,8 @@ extern "C" int bl_attention_prefill_tc(const void* q, const void* k_cache, const
     }
     // A block waits (griddepcontrol.wait) before it allocates tensor memory or touches data, so it may be launched
     // while the kernel before it still runs.
-    BL_CUDA(bl_launch_dependent(attention_tc_kernel, dim3(n_tiles, H, 1), dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)stream,
+    if ((long long)n_tiles * H > 2147483647LL) BL_FAIL("bl_attention_prefill_tc: %d tiles x %d heads are more blocks than a launch takes", n_tiles, H);
+    BL_CUDA(bl_launch_dependent(attention_tc_kernel, dim3(n_tiles * H, 1, 1), dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)stream,
                                 mq, mk, mv, p));
     BL_CHECK_LAUNCH("bl_attention_prefill_tc");
     return 0;

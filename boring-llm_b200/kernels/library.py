@@ -135,6 +135,8 @@ def build(verbose: bool = True, force: bool = False) -> str:
 def load() -> ctypes.CDLL:
     """The loaded library (built first if needed)."""
     global _lib
+    if _lib is not None:                       # the common case, hundreds of times a step: no lock
+        return _lib
     with _lock:
         if _lib is None:
             path = build()
