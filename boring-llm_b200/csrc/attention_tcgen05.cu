@@ -401,14 +401,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             // operand of the second product: lane = row, two keys to a 32-bit column, 16 columns a chunk.
             auto chunk_exp = [&](uint32_t (&s)[32], int c) {
                 if (!all_seen) mask(s, c);
+                // in batches, so that the special-function unit's queue stays full: 32 scaled differences, 32 x 2^x
+                // back to back (volatile keeps them together), then the sums and the pairs
+                float x[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) x[j] = fmaf(__uint_as_float(s[j]), p.scale_log2, -m_use);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) asm volatile("ex2.approx.ftz.f32 %0, %0;" : "+f"(x[j]));
                 uint32_t pk[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const float e0 = bl_ex2(fmaf(__uint_as_float(s[2 * j]), p.scale_log2, -m_use));
-                    const float e1 = bl_ex2(fmaf(__uint_as_float(s[2 * j + 1]), p.scale_log2, -m_use));
-                    sm4[j & 1] += e0;
-                    sm4[2 + (j & 1)] += e1;
-                    pk[j] = pack_bf16(e0, e1);
+                    sm4[j & 1] += x[2 * j];
+                    sm4[2 + (j & 1)] += x[2 * j + 1];
+                    pk[j] = pack_bf16(x[2 * j], x[2 * j + 1]);
                 }
                 tmem_st16(t_p + 16 * c, pk);
             };
