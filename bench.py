@@ -148,8 +148,10 @@ def drop_requests(eng, reqs):
 
 
 def decode_device_timed(eng, batch, steps, warmup):
-    """Tokens per second of `steps` decode steps of `batch` requests ending at the full context, timed on
-    the device step by step; returns (tokens/s, ms per step, kernel launches in the timed steps)."""
+    """Tokens per second of `steps` decode steps of `batch` requests ending at the full context, timed on the
+    device around all of them; returns (tokens/s, ms per step, kernel launches in the timed steps). Every step
+    copies its inputs in, runs every kernel and the sampler, and brings its token ids back; the step after is
+    launched before they are read (its tokens are fed back on the device), as `Engine.step` does."""
     import torch
     from boring_llm_b200.engine.runner import StepEntry
     from boring_llm_b200.kernels import ops
@@ -157,18 +159,31 @@ def decode_device_timed(eng, batch, steps, warmup):
     reqs = fill_requests(eng, batch, ctx0, seed=batch)
     toks = [r.output[-1] for r in reqs]
     rows = [(r.params, r.rng, r.tokens) for r in reqs]          # greedy
-    total_ms, launches = 0.0, 0
-    for it in range(warmup + steps):
-        entries = [StepEntry(r.request_id, [t], [0]) for r, t in zip(reqs, toks)]
-        l0 = ops.launch_count                                      # (the previous step ended with a device sync)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        toks = eng.runner.step_and_sample(entries, rows, eng.sampler)     # copy in, every kernel of the step, sampler
-        e1.record()
-        torch.cuda.synchronize()
-        if it >= warmup:
-            total_ms += e0.elapsed_time(e1)
-            launches += ops.launch_count - l0 + eng.runner.last_step_graph_kernels
+    run = eng.runner
+    for _ in range(warmup):
+        toks = run.step_and_sample([StepEntry(r.request_id, [t], [0]) for r, t in zip(reqs, toks)], rows, eng.sampler)
+    torch.cuda.synchronize()
+    l0, graph_kernels = ops.launch_count, 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    first = [StepEntry(r.request_id, [t], [0]) for r, t in zip(reqs, toks)]
+    pending = run.launch_decode(first, rows)
+    if pending is None:                                            # no captured graphs: one step after the other
+        toks = run.step_and_sample(first, rows, eng.sampler)
+        for _ in range(steps - 1):
+            toks = run.step_and_sample([StepEntry(r.request_id, [t], [0]) for r, t in zip(reqs, toks)], rows, eng.sampler)
+    else:
+        graph_kernels = run.last_step_graph_kernels
+        for _ in range(steps - 1):
+            ahead = run.launch_decode([StepEntry(r.request_id, [0], [0]) for r in reqs], rows, from_device=True)
+            graph_kernels += run.last_step_graph_kernels
+            toks = run.collect_decode(pending)
+            pending = ahead
+        toks = run.collect_decode(pending)
+    e1.record()
+    torch.cuda.synchronize()
+    total_ms = e0.elapsed_time(e1)
+    launches = ops.launch_count - l0 + graph_kernels
     drop_requests(eng, reqs)
     return batch * steps / (total_ms / 1e3), total_ms / steps, launches
 
@@ -191,6 +206,7 @@ def decode_end_to_end(eng, batch, steps, warmup):
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     assert all(len(r.output) == 1 + warmup + steps for r in reqs)
+    eng.drain()                                                    # the step that was launched ahead of the last one read
     drop_requests(eng, reqs)
     # per step, counted by the runner from the tensors it copies: token ids, positions, lengths, slots, sampling
     # parameters (and block-table rows when a request got a new page) go up from pinned memory, one int32 per

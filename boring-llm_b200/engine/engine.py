@@ -17,7 +17,7 @@ from ..models.loading import load_model
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .runner import ModelRunner, StepEntry
-from .scheduler import Request, Scheduler
+from .scheduler import RUNNING, Request, Scheduler
 
 
 class Engine:
@@ -42,6 +42,7 @@ class Engine:
         self.scheduler = Scheduler(self.runner.cache, options)
         self.sampler = Sampler(options.device)
         self._ids = itertools.count()
+        self._inflight = None                 # (scheduled step, PendingDecode): launched, tokens not read yet
         self.stats_time = {"engine_steps": 0, "step_seconds": 0.0}
 
     @classmethod
@@ -62,14 +63,49 @@ class Engine:
         return self.scheduler.add(rid, prompt, params)
 
     def step(self) -> List[Request]:
-        """One scheduler step. Returns the requests that finished in it."""
-        sched = self.scheduler.schedule()
-        if sched is None:
-            return []
+        """One scheduler step. Returns the requests that finished in it.
+
+        While the running requests only decode, the step after this one is launched before this one's tokens are
+        read (`EngineOptions.lookahead`): the device feeds the sampled tokens back itself, the host reads them one
+        step behind, and the GPU does not wait for the host between steps. A request that ends with an end token
+        has then already got a row in the step after; that row's result is dropped (the reference's loop,
+        src/model.br:2293-2304, feeds no token after the end token either: nothing of the row is kept)."""
         t0 = time.perf_counter()
-        # the third item is the request itself: its token history is only put together if a penalty asks for it
-        rows = [(r.params, r.rng, r) for r, s in zip(sched.requests, sched.samples) if s]
-        sampled = self.runner.step_and_sample(sched.entries, rows, self.sampler)
+        if self._inflight is None:
+            sched = self.scheduler.schedule()
+            if sched is None:
+                return []
+            # the third item is the request itself: its token history is only put together if a penalty asks for it
+            rows = [(r.params, r.rng, r) for r, s in zip(sched.requests, sched.samples) if s]
+            pending = self.runner.launch_decode(sched.entries, rows) if self.options.lookahead else None
+            if pending is None:
+                sampled = self.runner.step_and_sample(sched.entries, rows, self.sampler)
+                return self._finish_step(sched, sampled, t0)
+            self._inflight = (sched, pending)
+        sched, pending = self._inflight
+        ahead = self.scheduler.lookahead(sched)
+        nxt = None
+        if ahead is not None:
+            rows = [(r.params, r.rng, r) for r in ahead.requests]
+            p2 = self.runner.launch_decode(ahead.entries, rows, from_device=True)
+            if p2 is not None:
+                nxt = (ahead, p2)
+        sampled = self.runner.collect_decode(pending)
+        done = self._finish_step(sched, sampled, t0)
+        if nxt is not None and not any(r.state == RUNNING for r in nxt[0].requests):
+            nxt = None                            # every row of the step ahead has ended: nobody reads it
+        self._inflight = nxt
+        return done
+
+    def drain(self) -> List[Request]:
+        """Reads the step that was launched ahead, if there is one, so that the host's view is complete.
+        Returns the requests that finished in it."""
+        if self._inflight is None:
+            return []
+        (sched, pending), self._inflight = self._inflight, None
+        return self._finish_step(sched, self.runner.collect_decode(pending), time.perf_counter())
+
+    def _finish_step(self, sched, sampled, t0) -> List[Request]:
         self.runner.check_kernels()
         self.stats_time["engine_steps"] += 1
         self.stats_time["step_seconds"] += time.perf_counter() - t0

@@ -41,6 +41,14 @@ class StepError(ValueError):
 GRAPH_MAX_BATCH = 64          # decode steps of up to this many requests replay a captured CUDA graph
 
 
+class PendingDecode:
+    """A decode step that has been launched and whose sampled tokens have not been read yet."""
+    __slots__ = ("graph", "buffer", "rows")
+
+    def __init__(self, graph: "_DecodeGraph", buffer: int, rows: List[int]):
+        self.graph, self.buffer, self.rows = graph, buffer, rows
+
+
 class _DecodeGraph:
     """A captured decode step for a fixed number of rows. All per-step inputs live in one int32 device
     buffer that a single copy refreshes before each replay; rows beyond the live requests point at the
@@ -107,7 +115,11 @@ class _DecodeGraph:
                        self.d["uniform"], self.sampled)
         self.kernels = ops.launch_count - before       # kernels of this library that one replay launches
         self.copied = torch.cuda.Event()
-        self.sampled_host = torch.zeros(B, dtype=torch.int32).pin_memory()
+        # two steps may be in flight (the next is launched before this one's tokens are read): two buffers take turns
+        self.sampled_host = [torch.zeros(B, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.sampled_ready = [torch.cuda.Event() for _ in range(2)]
+        self.next_buffer = 0
+        self.last_live = 0                             # live rows of the last replay (whose tokens `sampled` holds)
 
     def fill_padding(self, live: int) -> None:
         h = self.h
@@ -175,11 +187,14 @@ class ModelRunner:
         self._slot_index = i
         return self._pinned[i]
 
-    def _graphed_decode(self, entries: Sequence[StepEntry], sampling=None):
+    def _graphed_decode(self, entries: Sequence[StepEntry], sampling=None, from_device: bool = False, wait: bool = True):
         """A step in which every request has exactly one token: replays the captured graph of the next
         larger row count. Reservation, commit and the returned logits are those of the general path.
         With `sampling` (one (params, generator, history) per entry) the graph's own sampler picks the
-        tokens and they are returned as a list instead of the logits."""
+        tokens and they are returned as a list instead of the logits; with `wait` false a `PendingDecode`
+        is returned instead, for `collect_decode`. With `from_device` the rows' tokens are the ones the
+        replay before this one sampled (same requests in the same rows): they are taken on the device,
+        so the step can be launched before the host has seen them."""
         R = len(entries)
         rows = 1
         while rows < R:
@@ -192,7 +207,11 @@ class ModelRunner:
         get = self.cache.get
         rcs = [get(e.request_id) for e in entries]
         slot_list = [rc.slot for rc in rcs]
-        h["token_ids"][:R] = [e.tokens[0] for e in entries]
+        if from_device:
+            if sampling is None or gr.last_live != R:
+                raise StepError("tokens can be taken on the device only from the sampled rows of the replay before")
+        else:
+            h["token_ids"][:R] = [e.tokens[0] for e in entries]
         h["positions"][:R] = [rc.num_tokens for rc in rcs]
         np.add(h["positions"][:R], 1, out=h["ctx_len"][:R])
         h["slots"][:R] = slot_list
@@ -222,8 +241,11 @@ class ModelRunner:
         gr.tables_dirty = False
         gr.dev[:n_copy].copy_(gr.host[:n_copy], non_blocking=True)
         gr.copied.record()
+        if from_device:                                # after the copy, which brought stale ids along
+            gr.d["token_ids"][:R].copy_(gr.sampled[:R])
         self.last_h2d_bytes, self.last_d2h_bytes = 4 * n_copy, (4 * rows if sampling is not None else 0)
         gr.graph.replay()
+        gr.last_live = R if sampling is not None else 0
         self.last_step_graph_kernels = gr.kernels
         for e in entries:
             self.cache.commit(e.request_id, 1)
@@ -233,23 +255,41 @@ class ModelRunner:
             self._waits_unchecked = True               # status word now and then (a look costs a device synchronisation)
         self.tokens_run += R
         if sampling is not None:
-            gr.sampled_host.copy_(gr.sampled, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-            toks = gr.sampled_host.numpy()
-            return [int(toks[r]) for r, e in enumerate(entries) if len(e.want)]
+            k = gr.next_buffer
+            gr.next_buffer = k ^ 1
+            gr.sampled_host[k].copy_(gr.sampled, non_blocking=True)
+            gr.sampled_ready[k].record()
+            pending = PendingDecode(gr, k, [r for r, e in enumerate(entries) if len(e.want)])
+            return self.collect_decode(pending) if wait else pending
         wanted = [r for r, e in enumerate(entries) if len(e.want)]
         if len(wanted) == R:
             return gr.logits[:R]
         return gr.logits[torch.tensor(wanted, dtype=torch.long, device=self.device)] if wanted else gr.logits[:0]
 
+    def collect_decode(self, pending: PendingDecode) -> List[int]:
+        """Waits for a launched decode step's tokens (not for whatever was launched after it)."""
+        gr = pending.graph
+        gr.sampled_ready[pending.buffer].synchronize()
+        toks = gr.sampled_host[pending.buffer].numpy()
+        return [int(toks[r]) for r in pending.rows]
+
+    def launch_decode(self, entries: Sequence[StepEntry], rows, from_device: bool = False) -> Optional[PendingDecode]:
+        """Launches a decode-only step with its sampler and returns without waiting for it, or returns None if
+        the step is not one that the captured graphs take (then nothing has been done). At most two such
+        steps may be uncollected at a time. See `_graphed_decode` for `from_device`."""
+        if not (len(rows) == len(entries) and all(len(e.tokens) == 1 for e in entries) and self._graphs_usable(entries)
+                and all(r[0].repeat_penalty == 1.0 for r in rows)):
+            return None
+        self._prepare(entries)
+        return self._graphed_decode(entries, rows, from_device=from_device, wait=False)
+
     def step_and_sample(self, entries: Sequence[StepEntry], rows, sampler) -> List[int]:
         """A step followed by sampling: `rows` holds one (params, generator, history) per entry that wants
         logits (each such entry wants exactly its last token). Decode-only steps without a repeat penalty
         run the sampler inside the captured graph and bring back only the token ids."""
-        if (len(rows) == len(entries) and all(len(e.tokens) == 1 for e in entries) and self._graphs_usable(entries)
-                and all(r[0].repeat_penalty == 1.0 for r in rows)):
-            self._prepare(entries)
-            return self._graphed_decode(entries, rows)
+        pending = self.launch_decode(entries, rows)
+        if pending is not None:
+            return self.collect_decode(pending)
         logits = self.step(entries)
         return sampler.sample(logits, rows) if rows else []
 

@@ -198,6 +198,30 @@ class Scheduler:
             samples.append(last)
         return ScheduledStep(entries, reqs, samples)
 
+    def lookahead(self, prev: ScheduledStep) -> Optional[ScheduledStep]:
+        """The decode step that follows `prev`, put together BEFORE `prev`'s tokens are known, so that it can be
+        launched while `prev` still runs (its input tokens are then taken on the device; the entries carry
+        token 0 in their place). Only when that step is certain but for end-of-generation tokens: `prev` was a
+        decode step of all running requests in their order, nobody waits, none of them ends by length with
+        `prev`'s token, and the pages for one more token each are there. Otherwise None, and nothing is changed
+        but pages that the requests' next tokens need anyway. A request that `prev` ends with an end token still
+        has its row in the step: `apply` skips it."""
+        if self.waiting or len(prev.requests) != len(self.running):
+            return None
+        for req, run, e, samp in zip(prev.requests, self.running, prev.entries, prev.samples):
+            if req is not run or req.state != RUNNING or not samp or len(e.tokens) != 1:
+                return None
+            n_out = len(req.output) + 1                       # once prev's token is there
+            if n_out >= req.max_new or len(req.prompt) + n_out >= self.options.ctx_size:
+                return None
+        if len(prev.requests) > self.options.max_num_batched_tokens:
+            return None
+        for req in prev.requests:
+            if not self.cache.reserve(req.request_id, 1):
+                return None
+        return ScheduledStep([StepEntry(req.request_id, [0], [0]) for req in prev.requests], list(prev.requests),
+                             [True] * len(prev.requests))
+
     def apply(self, step: ScheduledStep, sampled: Sequence[int]) -> List[Request]:
         """Records a finished step: `sampled` holds one token for every entry with `samples` true, in
         order. Returns the requests that finished. An end-of-generation token is returned but not
@@ -205,7 +229,9 @@ class Scheduler:
         done = []
         it = iter(sampled)
         for e, req, samp in zip(step.entries, step.requests, step.samples):
-            if req.state != RUNNING:
+            if req.state != RUNNING:                          # ended or preempted since the step was put together
+                if samp:
+                    next(it, None)                            # its row's token belongs to nobody
                 continue
             req.num_computed += len(e.tokens)
             if not samp:

@@ -114,3 +114,42 @@ def test_end_token_and_context_limit(model_folders):
         eng.generate([list(range(48))], n_predict=1)
     with pytest.raises(ValueError, match="vocabulary"):
         eng.generate([[1, 2, 999]], n_predict=1)
+
+
+def test_lookahead_gives_the_same_tokens_as_stepping_in_turn(model_folders):
+    """Decode steps launched one ahead (their tokens fed back on the device) against the same engine without:
+    greedy and sampled, with requests that end on an end token while their row is already in the step ahead,
+    ends by length at different steps, and a request that arrives while a step is in flight."""
+    from boring_llm_b200 import Engine
+    from boring_llm_b200.sampling.params import SamplingParams
+    d = model_folders("B", "bfloat16", 0.02)
+    prompts = [helpers.random_tokens(320, n, 700 + n) for n in (9, 21, 14, 30)]
+    kw = dict(dtype="bfloat16", ctx_size=128, max_num_seqs=4, max_tokens=1024, prefill_chunk=16)
+    ahead, turn = Engine(d, lookahead=True, **kw), Engine(d, lookahead=False, **kw)
+    free = turn.generate(prompts, n_predict=20, ignore_eos=True)
+    assert ahead.generate(prompts, n_predict=20, ignore_eos=True) == free
+    assert ahead.runner.graph_steps > 0 and ahead._inflight is None
+    # every request stops at a token of its own free run, at different steps
+    for cut in (2, 7, 13):
+        stops = [o[cut] for o in free]
+        want = turn.generate(prompts, n_predict=20, eos_token_ids=stops)
+        got = ahead.generate(prompts, n_predict=20, eos_token_ids=stops)
+        assert got == want and any(len(o) < 20 for o in got)
+    for seed in (1, 2):
+        want = turn.generate(prompts, n_predict=17, temperature=0.9, seed=seed, top_k=40, top_p=0.95, ignore_eos=True)
+        assert ahead.generate(prompts, n_predict=17, temperature=0.9, seed=seed, top_k=40, top_p=0.95, ignore_eos=True) == want
+    # different lengths: the batch shrinks while a step is ahead; then a request arrives in the middle
+    outs = {}
+    for eng in (turn, ahead):
+        reqs = [eng.add_request(p, SamplingParams(n_predict=5 + 4 * i, ignore_eos=True)) for i, p in enumerate(prompts[:3])]
+        for _ in range(6):
+            eng.step()
+        reqs.append(eng.add_request(prompts[3], SamplingParams(n_predict=9, ignore_eos=True)))
+        eng.run_until_done()
+        outs[eng] = [list(r.output) for r in reqs]
+        assert [len(o) for o in outs[eng]] == [5, 9, 13, 9]
+        eng.runner.cache.check()
+        s = eng.stats()
+        assert s["live_requests"] == 0 and s["pages_in_use"] == [0]
+        for p, o in zip(prompts, outs[eng]):                    # (the arrival meets the others one step apart in the two
+            check_greedy(d, p, o, "bfloat16")                   # engines, in kernels that round differently: no equality)

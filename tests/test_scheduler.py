@@ -205,3 +205,86 @@ def test_random_arrivals_with_few_pages_every_request_finishes_like_its_solo_run
         assert r.output == solo(r.prompt, min(r.params.n_predict, opts.ctx_size - len(r.prompt)))
     assert cache.free_pages() == [cache.num_pages] and not cache.live_requests()
     cache.check()
+
+
+def drive_ahead(sched, cache, limit=5000):
+    """The engine's loop with one decode step launched ahead (its tokens unknown when it is put together): the
+    stand-in 'device' computes a step's tokens only when the step is collected, from the history as it is then."""
+    inflight, kinds = None, []
+    for _ in range(limit):
+        if inflight is None:
+            if not sched.has_work():
+                break
+            inflight = sched.schedule()
+            if inflight is None:
+                break
+            for e in inflight.entries:
+                cache.commit(e.request_id, len(e.tokens))
+            kinds.append("scheduled")
+        st = inflight
+        ahead = sched.lookahead(st) if all(len(e.tokens) == 1 for e in st.entries) else None
+        if ahead is not None:
+            assert [e.tokens for e in ahead.entries] == [[0]] * len(st.entries) and ahead.requests == st.requests
+            for e in ahead.entries:
+                cache.commit(e.request_id, 1)
+            kinds.append("ahead")
+        # the device's answer for st: a row whose request has ended gets a token too (nobody reads it)
+        sampled = [next_token(req.tokens) if req.state == "running" else -1
+                   for req, samp in zip(st.requests, st.samples) if samp]
+        sched.apply(st, sampled)
+        cache.check()
+        if ahead is not None and not any(r.state == "running" for r in ahead.requests):
+            ahead = None
+        inflight = ahead
+    else:
+        raise AssertionError("the scheduler did not finish")
+    return kinds
+
+
+def test_lookahead_steps_give_every_request_its_solo_tokens():
+    sched, cache, _ = make(tokens=512, seqs=4, budget=64, chunk=16, ctx=128)
+    prompts = [[(3 * i + j) % VOCAB for j in range(n)] for i, n in enumerate((5, 20, 33))]
+    lens = (9, 14, 6)
+    reqs = [sched.add(i, p, SamplingParams(n_predict=n, ignore_eos=True)) for i, (p, n) in enumerate(zip(prompts, lens))]
+    kinds = drive_ahead(sched, cache)
+    assert kinds.count("ahead") >= 3                      # while all three decoded and none was about to end
+    for r, p, n in zip(reqs, prompts, lens):
+        assert r.output == solo(p, n) and r.finish_reason == "length"
+    assert cache.stats()["live_requests"] == 0 and cache.stats()["pages_in_use"] == [0]
+
+
+def test_lookahead_row_of_a_request_that_ends_on_an_end_token_is_dropped():
+    sched, cache, _ = make(tokens=512, seqs=4, budget=64, chunk=16, ctx=128)
+    prompts = [[(5 * i + j) % VOCAB for j in range(n)] for i, n in enumerate((7, 12))]
+    free = [solo(p, 12) for p in prompts]
+    stop = free[0][4]                                      # request 0 ends at its fifth token, request 1 goes on
+    reqs = [sched.add(0, prompts[0], SamplingParams(n_predict=12, eos_token_ids=(stop,))),
+            sched.add(1, prompts[1], SamplingParams(n_predict=12, ignore_eos=True))]
+    kinds = drive_ahead(sched, cache)
+    assert "ahead" in kinds
+    assert reqs[0].output == free[0][:free[0].index(stop) + 1] and reqs[0].finish_reason == "stop"
+    assert reqs[1].output == free[1]
+    assert cache.stats()["live_requests"] == 0 and cache.stats()["pages_in_use"] == [0]
+
+
+def test_lookahead_is_refused_when_the_next_step_is_not_certain():
+    sched, cache, _ = make(tokens=512, seqs=4, budget=64, chunk=16, ctx=128)
+    a = sched.add("a", [1, 2, 3], SamplingParams(n_predict=3, ignore_eos=True))
+    st = sched.schedule()                                  # the prompt: not a decode step
+    assert sched.lookahead(st) is None
+    cache.commit("a", 3); sched.apply(st, [next_token(a.tokens)])
+    st = sched.schedule()
+    cache.commit("a", 1)
+    assert sched.lookahead(st) is not None                 # token 2 of 3 follows for sure
+    sched.apply(st, [next_token(a.tokens)])
+    st = sched.schedule()
+    cache.commit("a", 1)
+    assert sched.lookahead(st) is None                     # this step's token is the last one
+    sched.add("b", [4, 5], SamplingParams(n_predict=4, ignore_eos=True))
+    sched.apply(st, [next_token(a.tokens)])
+    assert a.finish_reason == "length"
+    st = sched.schedule()
+    cache.commit("b", 2); sched.apply(st, [7])
+    st = sched.schedule(); cache.commit("b", 1)
+    sched.add("c", [9], SamplingParams(n_predict=2, ignore_eos=True))
+    assert sched.lookahead(st) is None                     # somebody waits: the next step will not be this batch
