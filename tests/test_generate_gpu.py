@@ -144,6 +144,10 @@ def test_lookahead_gives_the_same_tokens_as_stepping_in_turn(model_folders):
         reqs = [eng.add_request(p, SamplingParams(n_predict=5 + 4 * i, ignore_eos=True)) for i, p in enumerate(prompts[:3])]
         for _ in range(6):
             eng.step()
+        if eng is ahead:                                        # a step is in flight: reading it adds one token to each
+            before = [len(r.output) + (r.state == "running") for r in reqs]
+            assert eng._inflight is not None and eng.drain() == [] and eng._inflight is None
+            assert [len(r.output) for r in reqs] == before
         reqs.append(eng.add_request(prompts[3], SamplingParams(n_predict=9, ignore_eos=True)))
         eng.run_until_done()
         outs[eng] = [list(r.output) for r in reqs]
