@@ -22,7 +22,7 @@ PREFILL_TC_MIN_TOKENS = 1024         # steps with fewer prompt tokens keep the 6
 DECODE_MAX_SPLITS = 32               # more slices make the merge longer than they shorten the scan
 
 
-def tc_attention_blocks(q_lens, ctx_lens):
+def tc_attention_tiles(q_lens, ctx_lens):
     """The launch list of the tcgen05 prefill attention: (request, first token) of every tile of 128 new tokens of
     the requests with more than one, the tile with the fewest keys first (the kernel starts from the end of the
     list, so that the long tiles run first and the short ones fill the tail). Key blocks are counted without the
@@ -155,7 +155,7 @@ class GQAAttention(Mixer):
                     and ops.attention_prefill_tc_supported(q.dtype, self.dh, k_cache.shape[2])):
                 key = "tcgen05 attention tiles"
                 if key not in ctx.memo:                 # once per step: the other layers find it here
-                    ctx.memo[key] = torch.tensor(tc_attention_blocks(ctx.q_lens, ctx.ctx_lens),
+                    ctx.memo[key] = torch.tensor(tc_attention_tiles(ctx.q_lens, ctx.ctx_lens),
                                                  dtype=torch.int32, device=ctx.device)
                 ops.attention_prefill_tc(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.memo[key], out,
                                          self.H, self.window, self.scale)

@@ -426,9 +426,9 @@ def tc_attention(q, kc, vc, tok_req, cu_q, ctx_len, table, out, H, window, scale
     o = ops()
     cu = cu_q.cpu().tolist()
     q_lens = [b - a for a, b in zip(cu[:-1], cu[1:])]
-    from boring_llm_b200.parts.attention import tc_attention_blocks
+    from boring_llm_b200.parts.attention import tc_attention_tiles
     ctx_lens = ctx_len.cpu().tolist()
-    tiles = tc_attention_blocks(q_lens, ctx_lens)
+    tiles = tc_attention_tiles(q_lens, ctx_lens)
     singles = [r for r, n in enumerate(q_lens) if n == 1]
     out.fill_(float("nan"))
     if tiles:
