@@ -29,11 +29,11 @@
 // Softmax is the online form of the reference's flash kernels (FlashAttnRegKernel, src/math_gpu.br:3309-3504);
 // scores are scaled after the dot product (src/math.br:319-322); a key j is visible to a query at position p
 // when j <= p and, with a window, j + window > p (:327-328).
-#include "common.cuh"
-#include "api.h"
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 namespace {
+
+constexpr const char* WHO = "bl_attention_prefill_tc";
 
 constexpr int DH = 64;                 // head size
 constexpr int ROWS = 128;              // query rows per block
@@ -61,16 +61,6 @@ struct Params {
     int H, KV, window; float scale_log2;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
-}
 // Bounded wait. False when the bound ran out or another thread of the block has given up. SLEEP: the waiter is one
 // of the copy or issue warps, which wait most of the time; it naps between tries so that its spinning does not
 // take issue slots from the row warps of its scheduler.
@@ -99,14 +89,6 @@ __device__ __forceinline__ void mbar_wait_plain(uint32_t bar, uint32_t parity) {
         if (ok) return;
     }
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-                 :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
 // the same with the A operand in tensor memory (lane = row, a 32-bit column = two bfloat16 along K)
 __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
@@ -119,19 +101,6 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
                     "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr) : "memory");
-}
 // The same wait, tied to the registers of the load it completes: nothing that reads them may be moved above it.
 __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;"
@@ -141,18 +110,9 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
                    "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
                  :: "memory");
 }
-__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 // what the threads wrote into shared memory becomes visible to the tensor cores and to TMA
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// 128-byte swizzle, rows of 128 bytes, groups of 8 rows 1024 bytes apart. The same descriptor serves a K-major
-// operand (rows = M or N, 64 elements of K per row) and an MN-major one (rows = K, 64 elements of N per row).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    const uint32_t lo = ((addr >> 4) & 0x3FFFu) | (1u << 16);                 // start address, leading offset 1 (unused: one 64-wide atom)
-    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);               // stride offset, version 1, SWIZZLE_128B
-    return ((uint64_t)hi << 32) | lo;
-}
 // kind::f16 instruction descriptors: D 32-bit, A and B bfloat16, N >> 3 at bit 17, M >> 4 at bit 24;
 // bit 16 set: B is MN-major (V lies keys x head size).
 constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(KBLK >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
@@ -487,38 +447,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
 }
 
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-    static EncodeTiled fn = nullptr;
-    if (fn == nullptr) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)ptr;
-    }
-    return fn;
-}
-
-// A row-major [rows, cols] bfloat16 matrix as a 2-D tensor map with boxes of box_rows x 64 elements, 128-byte swizzle.
-int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, int box_rows) {
-    EncodeTiled enc = encode_fn();
-    if (enc == nullptr) BL_FAIL("bl_attention_prefill_tc: cuTensorMapEncodeTiled is not available from the driver");
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult res = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (res != CUDA_SUCCESS)
-        BL_FAIL("bl_attention_prefill_tc: cuTensorMapEncodeTiled failed with code %d (rows %lld, cols %d)", (int)res, rows, cols);
-    return 0;
-}
-
 }  // namespace
 
 extern "C" int bl_attention_prefill_tc_supported(int dh, int page_size) { return dh == DH && page_size == PAGE; }
@@ -538,9 +466,9 @@ extern "C" int bl_attention_prefill_tc(const void* q, const void* k_cache, const
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15)
         BL_FAIL("bl_attention_prefill_tc: q, the caches and out must be 16-byte aligned");
     CUtensorMap mq, mk, mv;
-    if (make_map(&mq, q, T, H * DH, ROWS)) return 1;
-    if (make_map(&mk, k_cache, (long long)n_pages * KV * PAGE, DH, PAGE)) return 1;
-    if (make_map(&mv, v_cache, (long long)n_pages * KV * PAGE, DH, PAGE)) return 1;
+    if (bl_make_map_bf16(WHO, &mq, q, T, H * DH, ROWS, 64)) return 1;
+    if (bl_make_map_bf16(WHO, &mk, k_cache, (long long)n_pages * KV * PAGE, DH, PAGE, 64)) return 1;
+    if (bl_make_map_bf16(WHO, &mv, v_cache, (long long)n_pages * KV * PAGE, DH, PAGE, 64)) return 1;
     Params p;
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
     p.tiles = tiles; p.H = H; p.KV = KV; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;

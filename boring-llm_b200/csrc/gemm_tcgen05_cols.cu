@@ -16,11 +16,11 @@
 // records a code in a status word, lets its own copies land, frees its tensor memory and returns.
 // Formula y = x . W^T (src/math.br:66-82); role in the reference: the output projection of forward_step
 // (src/model.br:1360-1362).
-#include "common.cuh"
-#include "api.h"
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 namespace {
+
+constexpr const char* WHO = "bl_gemm_tc_cols";
 
 constexpr int BN = 128;                 // output columns (rows of W) per tile
 constexpr int BK = 64;
@@ -32,16 +32,6 @@ constexpr int SMEM_LIMIT = 227 * 1024;
 
 __device__ int g_status3 = 0;           // 0 = fine; else the code of the first wait that ran out
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
-}
 // Bounded wait. False when the bound ran out or another thread of the block has given up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
@@ -64,17 +54,6 @@ __device__ __forceinline__ void mbar_wait_plain(uint32_t bar, uint32_t parity) {
         if (ok) return;
     }
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-                 :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
-}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -82,16 +61,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
                    "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                  : "r"(taddr) : "memory");
 }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// K-major operand tile with 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    const uint32_t lo = ((addr >> 4) & 0x3FFFu) | (1u << 16);
-    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
-    return ((uint64_t)hi << 32) | lo;
-}
 // kind::f16: D 32-bit, A and B bfloat16 and K-major, N >> 3 at bit 17, M >> 4 at bit 24
 constexpr uint32_t idesc_for(int nt) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(nt >> 3) << 17) | ((uint32_t)(BN >> 4) << 24);
@@ -234,37 +204,6 @@ gemm_tc_cols_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
 }
 
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-    static EncodeTiled fn = nullptr;
-    if (fn == nullptr) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)ptr;
-    }
-    return fn;
-}
-
-// A row-major [rows, K] bfloat16 matrix as a 2-D tensor map with boxes of box_rows x 64 elements, 128-byte swizzle.
-int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
-    EncodeTiled enc = encode_fn();
-    if (enc == nullptr) BL_FAIL("bl_gemm_tc_cols: cuTensorMapEncodeTiled is not available from the driver");
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) BL_FAIL("bl_gemm_tc_cols: cuTensorMapEncodeTiled failed with code %d (rows %d, K %d)", (int)r, rows, K);
-    return 0;
-}
-
 int sm_count() {
     static int n = 0;
     if (n == 0) {
@@ -295,8 +234,8 @@ int launch(const void* x, const void* w, void* out, int M, int N, int K, cudaStr
         configured = true;
     }
     CUtensorMap mx, mw;
-    if (make_map(&mx, x, M, K, NT)) return 1;
-    if (make_map(&mw, w, N, K, BN)) return 1;
+    if (bl_make_map_bf16(WHO, &mx, x, M, K, NT, BK)) return 1;
+    if (bl_make_map_bf16(WHO, &mw, w, N, K, BN, BK)) return 1;
     const int n_tiles = (N + BN - 1) / BN;
     const int blocks = n_tiles < sm_count() ? n_tiles : sm_count();
     BL_CUDA(bl_launch_dependent(gemm_tc_cols_kernel<NT, TO>, dim3(blocks), dim3(THREADS), (size_t)bytes, s, mx, mw, (TO*)out, M, N, K, stages));

@@ -25,11 +25,11 @@
 //     columns are gates and the rest their ups.
 // Every mbarrier wait is bounded (a status word records the first that ran out); the cluster barriers are hardware
 // barriers that both blocks always reach.
-#include "common.cuh"
-#include "api.h"
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 namespace {
+
+constexpr const char* WHO = "bl_gemm_tc_pair";
 
 constexpr int BM = 128;                 // rows per block (256 per pair)
 constexpr int BK = 64;
@@ -55,13 +55,6 @@ constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;      // clears the bit that sele
 
 __device__ int g_status2 = 0;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
         uint32_t ok;
@@ -91,26 +84,8 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {      // arrives
 __device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(bar & PEER_BIT_MASK) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {        // K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
-    const uint32_t lo = ((addr >> 4) & 0x3FFFu) | (1u << 16);
-    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
-    return ((uint64_t)hi << 32) | lo;
 }
 // D 32-bit, A and B bfloat16 and K-major, N >> 3 at bit 17, M = 256 over the pair (>> 4 at bit 24)
 __host__ __device__ constexpr uint32_t idesc_for(int bn) {
@@ -330,36 +305,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-    static EncodeTiled fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)p;
-    }
-    return fn;
-}
-
-int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
-    EncodeTiled enc = encode_fn();
-    if (enc == nullptr) BL_FAIL("bl_gemm_tc_pair: cuTensorMapEncodeTiled is not available from the driver");
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) BL_FAIL("bl_gemm_tc_pair: cuTensorMapEncodeTiled failed with code %d (rows %d, K %d)", (int)r, rows, K);
-    return 0;
-}
-
 template <int EPI, typename TO, int BN>
 int launch_bn(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K, int sms,
               cudaStream_t s) {
@@ -371,8 +316,8 @@ int launch_bn(const void* x, const void* w, const void* bias, int bias_dtype, vo
     }
     const bool glu = EPI == BL_EPI_SWIGLU;
     CUtensorMap a, b;
-    if (make_map(&a, x, M, K, BM)) return 1;
-    if (make_map(&b, w, glu ? 2 * N : N, K, BN / 2)) return 1;
+    if (bl_make_map_bf16(WHO, &a, x, M, K, BM, BK)) return 1;
+    if (bl_make_map_bf16(WHO, &b, w, glu ? 2 * N : N, K, BN / 2, BK)) return 1;
     const int cols = glu ? BN / 2 : BN;
     const int m_pairs = (M + 2 * BM - 1) / (2 * BM), n_tiles = (N + cols - 1) / cols;
     int pairs = m_pairs * n_tiles;
