@@ -89,11 +89,12 @@ __device__ __forceinline__ void mbar_wait_plain(uint32_t bar, uint32_t parity) {
         if (ok) return;
     }
 }
-// the same with the A operand in tensor memory (lane = row, a 32-bit column = two bfloat16 along K)
+// D (+)= A . B with the A operand in tensor memory (lane = row, a 32-bit column = two bfloat16 along K)
 __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
                  :: "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// 16 columns of this warp's 32 lanes of tensor memory, written: thread t's register j to lane t, column j
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
                  "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
@@ -101,7 +102,7 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
                     "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-// The same wait, tied to the registers of the load it completes: nothing that reads them may be moved above it.
+// tcgen05.wait::ld tied to the registers of the load it completes: nothing that reads them may be moved above it.
 __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;"
                  : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
