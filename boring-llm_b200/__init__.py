@@ -5,7 +5,7 @@ manager, one step function over mixed batches, a scheduler, sampling, and hand-w
 from .config import (ConfigError, EngineOptions, Qwen2Config, load_config, register_architecture,
                      registered_architectures)
 from .weights import WeightsError
-from .models import build_model, load_model, write_random_model
+from .models import build_model, load_model, load_random_model, write_random_model
 
 __version__ = "0.1.0"
 

@@ -644,10 +644,6 @@ static __device__ __align__(256) float g_static_scratch[BL_NO_ALLOC_SCRATCH_FLOA
 // them at zero again.
 static __device__ __align__(256) int g_static_counters[BL_NO_ALLOC_COUNTERS];
 
-constexpr int MAX_DEVICES = 64;
-float* g_static_scratch_ptr[MAX_DEVICES] = {};   // device address of the array, per device, looked up once
-int* g_static_counters_ptr[MAX_DEVICES] = {};
-
 }  // namespace
 
 extern "C" int bl_attention_decode_no_alloc(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
@@ -655,33 +651,31 @@ extern "C" int bl_attention_decode_no_alloc(const void* q, const void* k_cache, 
                                             const int* reqs, int n, int n_splits, void* out, int H, int KV, int dh,
                                             int page_size, int window, float scale, void* stream) {
     if (n <= 0) return 0;
-    if (n_splits < 1) BL_FAIL("bl_attention_decode_no_alloc: %d slices", n_splits);
+    // every argument is checked before any arithmetic on it (a caller's KV = 0 must be an error, not a division)
+    if (check(H, KV, dh, page_size, max_pages, window, scale)) return 1;
+    if (n_splits < 1 || n_splits > 256) BL_FAIL("bl_attention_decode_no_alloc: %d slices (1..256)", n_splits);
     const long long need = bl_attention_decode_scratch_floats(n, H, dh, n_splits);
     if (need > (long long)BL_NO_ALLOC_SCRATCH_FLOATS)
         BL_FAIL("bl_attention_decode_no_alloc: %d requests x %d heads x %d slices x head size %d need %lld floats of "
                 "scratch, the built-in array holds %d; use fewer slices or the allocating entry point",
                 n, H, n_splits, dh, need, BL_NO_ALLOC_SCRATCH_FLOATS);
-    int dev = -1;
-    BL_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= MAX_DEVICES) BL_FAIL("bl_attention_decode_no_alloc: device %d is outside 0..%d", dev, MAX_DEVICES - 1);
-    if (g_static_scratch_ptr[dev] == nullptr) {
-        // In host code the array's name stands for a host-side shadow, not for device memory: a kernel handed
-        // `g_static_scratch` itself would fault or touch the wrong memory. The device address has to be asked for,
-        // with this device current, and it differs from device to device.
-        float* p = nullptr;
-        BL_CUDA(cudaGetSymbolAddress((void**)&p, g_static_scratch));
-        if (p == nullptr) BL_FAIL("bl_attention_decode_no_alloc: the scratch array has no address on device %d", dev);
-        int* c = nullptr;
-        BL_CUDA(cudaGetSymbolAddress((void**)&c, g_static_counters));
-        if (c == nullptr) BL_FAIL("bl_attention_decode_no_alloc: the counter array has no address on device %d", dev);
-        g_static_scratch_ptr[dev] = p;
-        g_static_counters_ptr[dev] = c;
-    }
-    if (n_splits > 1 && (long long)n * KV * ((H / KV + 15) / 16) > (long long)BL_NO_ALLOC_COUNTERS)
+    const long long n_counters = (long long)n * KV * ((H / KV + 15) / 16);
+    if (n_splits > 1 && n_counters > (long long)BL_NO_ALLOC_COUNTERS)
         BL_FAIL("bl_attention_decode_no_alloc: %d requests x %d head groups need more than the %d built-in counters",
                 n, KV * ((H / KV + 15) / 16), BL_NO_ALLOC_COUNTERS);
+    float* scratch = nullptr;
+    int* counters = nullptr;
+    if (n_splits > 1) {
+        // In host code the array's name stands for a host-side shadow, not for device memory: a kernel handed
+        // `g_static_scratch` itself would fault or touch the wrong memory. The device address has to be asked for,
+        // with the device that will run the kernel current, and it differs from device to device. It is asked for
+        // on every call (a table look-up inside the runtime, no allocation): nothing is cached here, so there is
+        // nothing that two threads could fill at once or that a device reset could leave stale.
+        BL_CUDA(cudaGetSymbolAddress((void**)&scratch, g_static_scratch));
+        BL_CUDA(cudaGetSymbolAddress((void**)&counters, g_static_counters));
+        if (scratch == nullptr || counters == nullptr)
+            BL_FAIL("bl_attention_decode_no_alloc: the built-in arrays have no address on the current device");
+    }
     return bl_attention_decode(q, k_cache, v_cache, cu_q, ctx_len, block_table, max_pages, reqs, n, n_splits,
-                               n_splits > 1 ? g_static_scratch_ptr[dev] : nullptr,
-                               n_splits > 1 ? g_static_counters_ptr[dev] : nullptr, out, H, KV, dh, page_size, window,
-                               scale, stream);
+                               scratch, counters, out, H, KV, dh, page_size, window, scale, stream);
 }

@@ -26,8 +26,11 @@ extern "C" {
 //
 // - A call whose sizes need more than BL_NO_ALLOC_SCRATCH_FLOATS floats is refused (returns non-zero, the message
 //   from bl_last_error() names the sizes); nothing is launched.
-// - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
-//   current) and keeps it; make that first call before any stream capture begins on that device.
+// - Every call asks the runtime for the array's device address (cudaGetSymbolAddress, for the device that is
+//   current at the call): nothing is cached between calls, so calls from several host threads do not race on
+//   any host-side state of this entry point, and an address from before a cudaDeviceReset is never reused. The
+//   first look-up on a device may make the runtime load the library's image there; make that first call before
+//   any stream capture begins on that device.
 // - All calls on a device share the one array, and it keeps whatever the previous call left there. The partial
 //   results need no clearing: every slot that the merge reads is written by the same call first. The counters
 //   that tell the last-finishing block of a (request, head group) to merge must be zero when a call starts: they

@@ -13,7 +13,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ..config import EngineOptions
-from ..models.loading import load_model
+from ..models.loading import load_model, load_random_model
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .runner import ModelRunner, StepEntry
@@ -49,6 +49,14 @@ class Engine:
     def from_model(cls, config, model, options: EngineOptions) -> "Engine":
         """An engine around a model that is already built and loaded on the device."""
         return cls((config, model), options)
+
+    @classmethod
+    def from_random(cls, config, seed: int, options: Optional[EngineOptions] = None, std: float = 0.02,
+                    weight_dtype=None) -> "Engine":
+        """An engine around a model with seeded random weights, made on the device without a file (the same
+        tensors as `write_random_model` writes for this configuration, seed and standard deviation)."""
+        options = options if options is not None else EngineOptions()
+        return cls(load_random_model(config, seed, options.dtype, options.device, std, weight_dtype), options)
 
     # ---- requests ----------------------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, request_id=None) -> Request:

@@ -42,8 +42,24 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda:0") -> Tuple[objec
 
 def write_random_model(model_dir: str, config, seed: int, dtype="bfloat16", std: float = 0.02) -> None:
     """Writes config.json and model.safetensors of a randomly initialised model: matrices N(0, std),
-    norm weights 1 + N(0, std), biases N(0, std), stored as `dtype`."""
+    norm weights 1 + N(0, std), biases N(0, std), stored as `dtype`. The same tensors, bit for bit, as
+    `load_random_model` puts on the device without a file."""
     model = build_model(config)
     tensors = random_tensors(model.tensor_specs(), seed, torch_dtype(dtype), std,
                              vocab_size=getattr(config, "vocab_size", 0))
     write_model_folder(model_dir, config.to_dict(), tensors)
+
+
+def load_random_model(config, seed: int, dtype="bfloat16", device="cuda:0", std: float = 0.02, weight_dtype=None):
+    """(configuration, model on the device) with seeded random weights made on the device, tensor by tensor,
+    without a file: what `write_random_model(dir, config, seed, weight_dtype, std)` followed by
+    `load_model(dir, dtype, device)` gives, for models of any size. `weight_dtype` (default: `dtype`) is the
+    type the values are rounded to before the engine takes them: "bfloat16" under a float32 engine gives the
+    bfloat16 model's exact weights widened to 32-bit, which separates the rounding of weights from that of
+    activations."""
+    model = build_model(config)
+    dev = torch.device(device)
+    tensors = random_tensors(model.tensor_specs(), seed, torch_dtype(dtype if weight_dtype is None else weight_dtype),
+                             std, vocab_size=getattr(config, "vocab_size", 0), device=dev)
+    model.load(tensors, torch_dtype(dtype), dev)
+    return config, model

@@ -86,34 +86,10 @@ def load_checkpoint(model_dir: str, expected: Dict[str, TensorSpec],
     return out
 
 
-def random_tensors(expected: Dict[str, TensorSpec], seed: int, dtype: torch.dtype = torch.bfloat16,
-                   std: float = 0.02, vocab_size: int = 0) -> Dict[str, torch.Tensor]:
-    """Seeded random weights: matrices N(0, std), norm weights 1 + N(0, std), biases N(0, std),
-    drawn in 32-bit in name order from one generator, then rounded once to `dtype`.
-
-    The reference has random weights only in its fixture generator
-    (tools/make_arch_test_ggufs.py:214-227); the distributions here are the ones this
-    engine's test and benchmark configurations name.
-    """
-    g = torch.Generator(device="cpu")
-    g.manual_seed(int(seed))
-    out = {}
-    for name in sorted(expected):
-        spec = expected[name]
-        if spec.kind == INT_TABLE:
-            hi = max(vocab_size, 2)
-            out[name] = torch.randint(0, hi, spec.shape, generator=g, dtype=torch.int32)
-            continue
-        t = torch.randn(spec.shape, generator=g, dtype=torch.float32) * std
-        if spec.kind == NORM:
-            t = t + 1.0
-        out[name] = t.to(dtype)
-    return out
-
-
-def write_model_folder(model_dir: str, config_dict: dict, tensors: Dict[str, torch.Tensor]) -> None:
+def write_model_folder(model_dir: str, config_dict: dict, tensors) -> None:
+    """config.json and model.safetensors from a configuration and a mapping `{name: tensor}`."""
     os.makedirs(model_dir, exist_ok=True)
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(config_dict, f, indent=2)
         f.write("\n")
-    write_safetensors(os.path.join(model_dir, "model.safetensors"), tensors, {"format": "pt"})
+    write_safetensors(os.path.join(model_dir, "model.safetensors"), {k: tensors[k].cpu() for k in tensors}, {"format": "pt"})

@@ -86,7 +86,7 @@ def rope_neox(x, positions, inv_freq):
     x0' = x0 cos - x1 sin, x1' = x0 sin + x1 cos. x: [seq, heads, d_head]."""
     half = x.shape[-1] // 2
     ang32 = positions.astype(np.float32)[:, None] * inv_freq[None, :]        # float32 product
-    ang = torch.from_numpy(ang32.astype(np.float64)).to(x.dtype)
+    ang = torch.from_numpy(ang32.astype(np.float64)).to(dtype=x.dtype, device=x.device)
     c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     a, b = x[..., :half], x[..., half:]
     return torch.cat([a * c - b * s, a * s + b * c], dim=-1)
@@ -101,7 +101,7 @@ def gqa_attention(q, k, v, scale, window=0, p_stored=None):
     KV = k.shape[1]
     group = H // KV
     out = torch.zeros_like(q)
-    idx = torch.arange(seq)
+    idx = torch.arange(seq, device=q.device)
     allowed = idx[None, :] <= idx[:, None]
     if window > 0:
         allowed &= idx[None, :] + window > idx[:, None]
@@ -133,7 +133,7 @@ def round_bf16(x):
     return x.to(torch.bfloat16).to(x.dtype)
 
 
-def forward(cfg, W, tokens, dtype=torch.float64, stored=None):
+def forward(cfg, W, tokens, dtype=torch.float64, stored=None, rows=None):
     """Logits of every position of one whole sequence: src/model.br:1280-1362 with every optional
     branch neutral, as the reference runs GGUF arch `qwen2`.
 
@@ -142,6 +142,8 @@ def forward(cfg, W, tokens, dtype=torch.float64, stored=None):
     the SwiGLU product); everything inside a formula (products' sums, softmax, norms' statistics,
     rotation, the residual stream, logits) stays in `dtype`. With it the comparison is about the
     formulas and the cache, not about how well a random model happens to be conditioned.
+
+    `rows`: positions whose logits are returned (default: all). The tensors of `W` may live on any device.
     """
     st = stored if stored is not None else (lambda t: t)
     W = {k: v.to(dtype) for k, v in W.items()}
@@ -168,6 +170,8 @@ def forward(cfg, W, tokens, dtype=torch.float64, stored=None):
         h = st(rms_norm(x, W[p + "post_attention_layernorm.weight"], eps))       # :1340
         act = st(silu(linear(h, W[p + "mlp.gate_proj.weight"])) * linear(h, W[p + "mlp.up_proj.weight"]))
         x = x + linear(act, W[p + "mlp.down_proj.weight"])                       # :1346-1356, src/math.br:246-261
+    if rows is not None:
+        x = x[list(rows)]
     y = st(rms_norm(x, W["model.norm.weight"], eps))                             # :1360
     out_w = W["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else W["lm_head.weight"]
     return linear(y, out_w)                                                      # :1361

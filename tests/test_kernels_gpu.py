@@ -564,6 +564,7 @@ def test_norm_qkv_rope_fused(H, KV, dh, d, bias):
     ctx_lens, q_lens = [5, 40, 17, 300], [5, 9, 1, 1]
     s = paged_setup(ctx_lens, q_lens, KV, dh, page, bf, 9)
     s2 = paged_setup(ctx_lens, q_lens, KV, dh, page, bf, 9)
+    before_k, before_v = s2["kc"].clone(), s2["vc"].clone()
     T = s["T"]
     x = data((T, d), 41) * 2
     nw = (data((d,), 42) * 0.25 + 1).to(bf)
@@ -582,8 +583,18 @@ def test_norm_qkv_rope_fused(H, KV, dh, d, bias):
     q = torch.full((T, H * dh), float("nan"), dtype=bf, device=DEV)
     o.norm_qkv_rope(x, nw, 1e-6, w, b, s2["positions"], s2["tok_req"], s2["table"], inv, 1.0, q, s2["kc"], s2["vc"], H, KV, dh)
     close(q, q_ref.double(), bf, "q")
-    close(s2["kc"], s["kc"].double(), bf, "key pages")          # junk in untouched rows is identical on both sides
-    close(s2["vc"], s["vc"].double(), bf, "value pages")
+    # the rows that the step's tokens own, one by one (the pools are full of +-1e4 junk, which would set the scale of
+    # a comparison of whole pools so high that a key in the wrong row, or no key at all, would pass) ...
+    touched = torch.zeros(s["kc"].shape[0], page, dtype=torch.bool)
+    for t in range(T):
+        pg = int(s["table_np"][s["tok_req_np"][t], s["positions_np"][t] // page]); row = int(s["positions_np"][t]) % page
+        close(s2["kc"][pg, :, row, :], s["kc"][pg, :, row, :].double(), bf, f"key of token {t}")
+        close(s2["vc"][pg, :, row, :], s["vc"][pg, :, row, :].double(), bf, f"value of token {t}")
+        assert s["kc"][pg, :, row, :].abs().max().item() < 1.0e3, "the unfused kernels did not write this row either"
+        touched[pg, row] = True
+    # ... and every other row of both pools still holds its junk
+    mask = touched.to(DEV)[:, None, :, None].expand_as(s2["kc"])
+    assert torch.equal(s2["kc"][~mask], before_k[~mask]) and torch.equal(s2["vc"][~mask], before_v[~mask])
     q_only = torch.empty_like(q)
     o.norm_qkv_rope(x, nw, 1e-6, w, b, s2["positions"], s2["tok_req"], s2["table"], inv, 1.0, q_only, None, None, H, KV, dh)
     assert torch.equal(q_only, q)

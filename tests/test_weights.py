@@ -101,6 +101,37 @@ def test_random_mode_is_seeded_and_follows_the_distributions(tmp_path):
     assert torch.equal(fh.tensor("lm_head.weight"), fa.tensor("lm_head.weight").to(torch.bfloat16))
 
 
+def test_random_tensors_depend_on_seed_name_and_index_only(tmp_path):
+    """The folder that the random mode writes holds, bit for bit, the tensors that the in-memory mode makes; a
+    tensor does not depend on which other tensors exist or in which order they are made; a prefix of a longer
+    tensor of the same name is the shorter tensor (values are keyed by the flat index)."""
+    from boring_llm_b200.weights import TensorSpec, random_tensor, random_tensors
+    cfg = Qwen2Config.from_dict(helpers.TINY["C"])
+    d = str(tmp_path / "m")
+    write_random_model(d, cfg, 9, "bfloat16", 0.02)
+    f = SafetensorsFile(os.path.join(d, "model.safetensors"))
+    specs = build_model(cfg).tensor_specs()
+    mem = random_tensors(specs, 9, torch.bfloat16, 0.02)
+    assert sorted(mem) == sorted(f.names()) and len(mem) == len(specs)
+    for n in reversed(sorted(specs)):                       # another order than the writer's
+        assert torch.equal(mem[n], f.tensor(n)), n
+    alone = random_tensor("model.norm.weight", specs["model.norm.weight"], 9, torch.bfloat16, 0.02)
+    assert torch.equal(alone, f.tensor("model.norm.weight"))
+    long = random_tensor("x", TensorSpec((7, 1000)), 1, torch.float32, 1.0).flatten()
+    short = random_tensor("x", TensorSpec((3, 100)), 1, torch.float32, 1.0).flatten()
+    assert torch.equal(long[:300], short)
+    assert not torch.equal(random_tensor("y", TensorSpec((300,)), 1, torch.float32, 1.0), short)
+    # a standard normal: moments, tails and no correlation between neighbours
+    z = random_tensor("z", TensorSpec((1000, 1000)), 2, torch.float32, 1.0).double()
+    assert abs(z.mean().item()) < 5e-3 and abs(z.std().item() - 1) < 5e-3
+    assert abs((z ** 4).mean().item() - 3.0) < 0.05 and 4.0 < z.abs().max().item() < 6.5
+    assert abs((z[:, 1:] * z[:, :-1]).mean().item()) < 5e-3 and abs((z[1:] * z[:-1]).mean().item()) < 5e-3
+    q = torch.quantile(z.flatten()[:1 << 20].float(), torch.tensor([0.01, 0.25, 0.75, 0.99]))
+    assert torch.allclose(q, torch.tensor([-2.3263, -0.6745, 0.6745, 2.3263]), atol=0.02)
+    ids = random_tensor("t", TensorSpec((5000,), "int_table"), 2, vocab_size=37)
+    assert ids.dtype == torch.int32 and ids.min().item() == 0 and ids.max().item() == 36
+
+
 def test_tied_model_has_no_output_matrix(tmp_path):
     cfg = Qwen2Config.from_dict(helpers.TINY["A"])
     specs = build_model(cfg).tensor_specs()
