@@ -20,6 +20,7 @@ class EngineOptions:
     max_num_batched_tokens: int = 2048  # token budget of one step (-b, src/main.br:674-676)
     prefill_chunk: int = 512            # most prompt tokens of one request in a step (-ub, :677-679)
     cuda_graphs: bool = True            # replay captured decode steps
+    step_graph_after: int = 2           # capture a general step's padded shape when it comes this many times (0: never)
     lookahead: bool = True              # launch the next decode step (its tokens taken on the device) before this one's are read
     device: str = "cuda:0"
 

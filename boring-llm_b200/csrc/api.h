@@ -75,6 +75,8 @@ int bl_attention_prefill_tc(const void* q, const void* k_cache, const void* v_ca
                             void* out, int T, int n_pages, int H, int KV, int dh, int page_size, int window, float scale,
                             void* stream);
 int bl_attention_prefill_tc_status(int* status);
+// Blocks of bl_attention_decode that the current device holds at once for this head size (0: not built).
+int bl_attention_decode_resident_blocks(int dh);
 // Decode shape: reqs[n] = requests with one new token; their keys are cut into n_splits slices (up to 256) that
 // the last block to finish merges. scratch: bl_attention_decode_scratch_floats(n, H, dh, n_splits) floats (none for one slice).
 long long bl_attention_decode_scratch_floats(int n, int H, int dh, int n_splits);

@@ -558,6 +558,19 @@ int launch(const AttnParams& p, dim3 grid, cudaStream_t s) {
     return 0;
 }
 
+template <int DH>
+int decode_resident() {
+    int bytes = Tiles<DH>::DECODE_BYTES;
+    if (bytes < (int)((4 * 16 * (DH + 8) + 128) * sizeof(float))) bytes = (int)((4 * 16 * (DH + 8) + 128) * sizeof(float));
+    if (bytes < (int)((16 * 256 + 16) * sizeof(float))) bytes = (int)((16 * 256 + 16) * sizeof(float));
+    int dev = 0, sms = 0, per_sm = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    if (cudaFuncSetAttribute(attention_mma_kernel<DH, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_mma_kernel<DH, true>, THREADS, (size_t)bytes) != cudaSuccess) return 0;
+    return sms * per_sm;
+}
+
 template <bool DECODE>
 int dispatch(int dh, const AttnParams& p, dim3 grid, cudaStream_t s) {
     switch (dh) {
@@ -585,6 +598,20 @@ int check(int H, int KV, int dh, int page_size, int max_pages, int window, float
 
 extern "C" int bl_attention_mma_supported(int dh, int page_size) {
     return page_size == PAGE && (dh == 16 || dh == 32 || dh == 48 || dh == 64 || dh == 96 || dh == 128);
+}
+
+// Blocks of the decode shape that the current device holds at once (SMs x blocks per SM for this head size), 0 when
+// the head size is not built: launches of about this many blocks fill the device in one round.
+extern "C" int bl_attention_decode_resident_blocks(int dh) {
+    switch (dh) {
+        case 16: return decode_resident<16>();
+        case 32: return decode_resident<32>();
+        case 48: return decode_resident<48>();
+        case 64: return decode_resident<64>();
+        case 96: return decode_resident<96>();
+        case 128: return decode_resident<128>();
+        default: return 0;
+    }
 }
 
 // Prefill shape. tiles: [n_tiles][2] = (request, first token of a 64-token tile inside the request's new tokens).

@@ -159,7 +159,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int head = blockIdx.x % p.H, kvh = head / (p.H / p.KV);
     const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin, ctx = p.ctx_len[r];
     const int* table = p.block_table + (size_t)r * p.max_pages;
-    const int rows_here = min(ROWS, q_len - tok0);                       // > 0 by construction of the tiles
+    const int rows_here = min(ROWS, q_len - tok0);                       // <= 0 only for the padding entries of a replayed step's list
     const int p_first = ctx - q_len + tok0, p_last = p_first + rows_here - 1;
     const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0, hi = p_last;
     const int b_begin = lo / KBLK, nb = rows_here > 0 ? hi / KBLK + 1 - b_begin : 0;
@@ -208,7 +208,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         };
         int loads[2] = {0, 0};                                           // copies started per stage
         ok = __all_sync(0xffffffffu, ok);
-        if (ok && keys && lane == 0) {
+        if (ok && keys && lane == 0 && nb > 0) {                         // (a tile without rows copies nothing and waits for nothing)
             mbar_expect_tx(full_q, Q_BYTES);
             tma_load_2d(base + OFF_Q, &map_q, full_q, head * DH, q_begin + tok0);
         }

@@ -98,12 +98,29 @@ class Engine:
             p2 = self.runner.launch_decode(ahead.entries, rows, from_device=True)
             if p2 is not None:
                 nxt = (ahead, p2)
-        sampled = self.runner.collect_decode(pending)
-        done = self._finish_step(sched, sampled, t0)
+        try:
+            sampled = self.runner.collect_decode(pending)
+            done = self._finish_step(sched, sampled, t0)
+        except BaseException:
+            # The step in flight failed (a kernel gave up on a bounded wait, the read of its tokens failed). The step
+            # ahead has already been launched: it has taken cache positions and random numbers for every row. Nothing of
+            # either step can be kept: forget both and end their requests, so that the scheduler and the cache agree
+            # again before the error reaches the caller.
+            self._inflight = None
+            self._abort_rows(sched.requests + (nxt[0].requests if nxt is not None else []))
+            raise
         if nxt is not None and not any(r.state == RUNNING for r in nxt[0].requests):
             nxt = None                            # every row of the step ahead has ended: nobody reads it
         self._inflight = nxt
         return done
+
+    def _abort_rows(self, requests) -> None:
+        seen = set()
+        for r in requests:
+            if r.request_id in seen:
+                continue
+            seen.add(r.request_id)
+            self.scheduler.abort(r.request_id, "error")
 
     def drain(self) -> List[Request]:
         """Reads the step that was launched ahead, if there is one, so that the host's view is complete.

@@ -112,16 +112,17 @@ class Scheduler:
         self.waiting.append(req)
         return req
 
-    def abort(self, request_id) -> None:
+    def abort(self, request_id, reason: str = "aborted") -> None:
+        """Ends a request wherever it is; its pages and slot go back at once."""
         for req in list(self.running):
             if req.request_id == request_id:
                 self.running.remove(req)
-                self._finish(req, "aborted", live=True)
+                self._finish(req, reason, live=True)
                 return
         for req in list(self.waiting):
             if req.request_id == request_id:
                 self.waiting.remove(req)
-                self._finish(req, "aborted", live=False)
+                self._finish(req, reason, live=False)
                 return
 
     def has_work(self) -> bool:

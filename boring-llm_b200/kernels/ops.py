@@ -299,6 +299,8 @@ def attention_decode(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_sp
         n_counters = n * KV * (-(-(H // KV) // 16))
         counters = _decode_counters.get(q.device)
         if counters is None or counters.numel() < n_counters:
+            if torch.cuda.is_current_stream_capturing():
+                raise KernelError("attention_decode: its counters must exist before a capture (run the step once first)")
             # zero once; every launch leaves them at zero again
             counters = _decode_counters[q.device] = torch.zeros(max(n_counters, 4096), dtype=torch.int32, device=q.device)
     _call(_lib().bl_attention_decode, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
@@ -307,6 +309,16 @@ def attention_decode(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_sp
 
 
 _decode_counters = {}
+_decode_resident = {}
+
+
+def attention_decode_resident_blocks(dh: int) -> int:
+    """Blocks of `attention_decode` that the device holds at once for this head size (asked of the kernel's own
+    occupancy on the current device, once per head size)."""
+    key = (torch.cuda.current_device(), dh)
+    if key not in _decode_resident:
+        _decode_resident[key] = max(1, int(_lib().bl_attention_decode_resident_blocks(dh)))
+    return _decode_resident[key]
 
 
 def attention_decode_scratch(n: int, H: int, dh: int, n_splits: int) -> int:

@@ -4,22 +4,22 @@ from __future__ import annotations
 import math
 from typing import Dict, Optional
 
+import numpy as np
 import torch
 
 from ..cache import PagedKVSpec
 from ..kernels import ops
 from ..weights import TensorSpec, MATRIX, BIAS
-from .base import Part, to_device_matrix, to_device_vector
+from .base import Part, StepPlan, to_device_matrix, to_device_vector
 from .linear import linear, EPI_BIAS, EPI_NONE, EPI_RESIDUAL
 from .norm import RMSNorm
 from .rotary import RotaryTable
 
 FUSED_MAX_ROWS = 64       # steps with at most this many rows take the fused norm + product kernels
 
-
-DECODE_SMS = 148                     # SMs of a B200: launches are sized to fill them once
 PREFILL_TC_MIN_TOKENS = 1024         # steps with fewer prompt tokens keep the 64-row tiles of the mma.sync kernel
 DECODE_MAX_SPLITS = 32               # more slices make the merge longer than they shorten the scan
+PLAN_KEY = "paged attention"         # one plan per step for all attention layers: its lists do not depend on head sizes
 
 
 def tc_attention_tiles(q_lens, ctx_lens):
@@ -35,6 +35,34 @@ def tc_attention_tiles(q_lens, ctx_lens):
             tiles.append([-(-(c - n + min(t0 + 128, n)) // 128), r, t0])
     tiles.sort()
     return [[r, t0] for _, r, t0 in tiles]
+
+
+def attention_plan(q_lens, ctx_lens, filler=None) -> StepPlan:
+    """What the attention kernels walk in one step: the 64-token tiles (and, for steps with many prompt tokens, the
+    128-token tiles in launch order) of the requests with several new tokens, and the list of requests with a
+    single one, with the longest context among those. For a step that will be replayed (`filler` given) the lists
+    are padded to multiples of 8 with entries of the request without tokens, and the longest context is rounded up
+    to a power of two: launches then depend on these sizes only."""
+    tiles64 = [[r, t0] for r, n in enumerate(q_lens) if n > 1 for t0 in range(0, n, 64)]
+    singles = [r for r, n in enumerate(q_lens) if n == 1]
+    use_tc = sum(n for n in q_lens if n > 1) >= PREFILL_TC_MIN_TOKENS
+    tiles128 = tc_attention_tiles(q_lens, ctx_lens) if use_tc else []
+    longest = max((ctx_lens[r] for r in singles), default=0)
+    if filler is not None:
+        pad = lambda n: -(-n // 8) * 8 - n
+        tiles64 = tiles64 + [[filler, 0]] * pad(len(tiles64))
+        tiles128 = [[filler, 0]] * pad(len(tiles128)) + tiles128          # the front of this list is launched last
+        singles = singles + [filler] * pad(len(singles))
+        bucket = 256
+        while bucket < longest:
+            bucket *= 2
+        longest = bucket if singles else 0
+    return StepPlan(
+        arrays={"tiles64": np.asarray(tiles64, dtype=np.int32).reshape(-1, 2),
+                "tiles128": np.asarray(tiles128, dtype=np.int32).reshape(-1, 2),
+                "singles": np.asarray(singles, dtype=np.int32)},
+        host={"longest_single": longest},
+        shape=(len(tiles64), len(tiles128), len(singles), longest))
 
 
 class Mixer(Part):
@@ -141,32 +169,39 @@ class GQAAttention(Mixer):
         linear(ctx, attn, self.wo, x, None, EPI_RESIDUAL)
         return True
 
+    def plan_step(self, q_lens, ctx_lens, filler=None):
+        return PLAN_KEY, attention_plan(q_lens, ctx_lens, filler)
+
     def attend(self, ctx, q, k_cache, v_cache, table, out):
         """Tensor-core kernels for bfloat16 where they are built (pages of 16, common head sizes): one launch for
         the requests with several new tokens (the tcgen05 kernel for head size 64 when the step has many of them),
-        one for those with a single token. Otherwise, and always in
-        float32, the plain kernel."""
+        one for those with a single token. Otherwise, and always in float32, the plain kernel. Which requests those
+        are comes from the step's plan (`attention_plan`)."""
         if not (ctx.fast and ops.attention_mma_supported(q.dtype, self.dh, k_cache.shape[2])):
             ops.attention_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, out,
                                 self.H, self.window, self.scale)
             return
-        if ctx.prefill_tiles is not None:
-            if (ctx.prefill_tokens >= PREFILL_TC_MIN_TOKENS
-                    and ops.attention_prefill_tc_supported(q.dtype, self.dh, k_cache.shape[2])):
-                key = "tcgen05 attention tiles"
-                if key not in ctx.memo:                 # once per step: the other layers find it here
-                    ctx.memo[key] = torch.tensor(tc_attention_tiles(ctx.q_lens, ctx.ctx_lens),
-                                                 dtype=torch.int32, device=ctx.device)
-                ops.attention_prefill_tc(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.memo[key], out,
+        plan = ctx.plans.get(PLAN_KEY)
+        if plan is None:                                 # a step put together without asking the parts: plan it now
+            plan = attention_plan(ctx.q_lens, ctx.ctx_lens)
+            plan.arrays = {k: torch.from_numpy(v).to(ctx.device) for k, v in plan.arrays.items()}
+            ctx.plans[PLAN_KEY] = plan
+        tiles64, tiles128, singles = plan.arrays["tiles64"], plan.arrays["tiles128"], plan.arrays["singles"]
+        if tiles64.shape[0]:
+            if tiles128.shape[0] and ops.attention_prefill_tc_supported(q.dtype, self.dh, k_cache.shape[2]):
+                ops.attention_prefill_tc(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, tiles128, out,
                                          self.H, self.window, self.scale)
             else:
-                ops.attention_prefill(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.prefill_tiles, out,
+                ops.attention_prefill(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, tiles64, out,
                                       self.H, self.window, self.scale)
-        if ctx.decode_reqs is not None:
-            n = ctx.decode_reqs.shape[0]
+        n = singles.shape[0]
+        if n:
+            # as many slices of the keys as fill the device once (the kernel knows how many of its blocks fit)
             groups = self.KV * (-(-(self.H // self.KV) // 16))
-            longest = ctx.max_decode_ctx if self.window <= 0 else min(ctx.max_decode_ctx, self.window + 64)
-            resident = DECODE_SMS * (4 if self.dh <= 64 else 2 if self.dh <= 128 else 1)   # blocks the kernel fits at once
+            longest = plan.host["longest_single"]
+            if self.window > 0:
+                longest = min(longest, self.window + 64)
+            resident = ops.attention_decode_resident_blocks(self.dh)
             n_splits = max(1, min(-(-longest // 64), resident // (n * groups), DECODE_MAX_SPLITS))
-            ops.attention_decode(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, ctx.decode_reqs, n_splits, out,
+            ops.attention_decode(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, singles, n_splits, out,
                                  self.H, self.window, self.scale)

@@ -51,6 +51,28 @@ class Part:
         for c in self.children():
             c.load(tensors, dtype, device)
 
+    # -- per-step plans ----------------------------------------------------------------------------
+    def plan_step(self, q_lens: Sequence[int], ctx_lens: Sequence[int], filler: Optional[int] = None):
+        """Optional: what this part wants worked out on the host before a step runs (lists of work items that its
+        kernels walk, launch shapes), as `(key, StepPlan)` or None. The step function asks every part, keeps one
+        plan per key (layers of one kind share theirs), copies the plan's arrays to the device with the step's own
+        index arrays and hands them back as `ctx.plans[key]`. `q_lens[r]` new tokens bring request r to
+        `ctx_lens[r]` tokens. `filler` is None for a step that runs once; for a step that is captured and
+        replayed with other batches of the same shape it is the index of a request without tokens: the plan's
+        arrays must then have sizes that `StepPlan.shape` determines, padded with entries that point at the
+        filler, and everything that decides a launch must come from `shape` alone."""
+        return None
+
+    def collect_plans(self, q_lens, ctx_lens, filler=None, into: Optional[dict] = None) -> dict:
+        """The plans of this part and of the parts inside it, one per key."""
+        into = {} if into is None else into
+        got = self.plan_step(q_lens, ctx_lens, filler)
+        if got is not None and got[0] not in into:
+            into[got[0]] = got[1]
+        for c in self.children():
+            c.collect_plans(q_lens, ctx_lens, filler, into)
+        return into
+
     def place(self, local: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
         """Default: each local tensor becomes an attribute of the same name."""
         for name, t in local.items():
@@ -68,6 +90,17 @@ def to_device_vector(t: torch.Tensor, dtype: torch.dtype, device) -> torch.Tenso
     if dtype == torch.float32 or t.dtype == torch.float32:
         return t.to(device=device, dtype=torch.float32).contiguous()
     return t.to(device=device, dtype=torch.bfloat16).contiguous()
+
+
+@dataclass
+class StepPlan:
+    """A part's host-side preparation of one step. `arrays`: int32 numpy arrays on the host, replaced by device
+    tensors of the same shapes before the parts run. `host`: plain values for the part's own use. `shape`: a
+    hashable value that, together with the batch's padded sizes, determines every launch the part will make (two
+    steps with equal shapes can replay one captured graph)."""
+    arrays: dict = field(default_factory=dict)
+    host: dict = field(default_factory=dict)
+    shape: tuple = ()
 
 
 @dataclass
@@ -94,10 +127,7 @@ class StepContext:
     slot_list: List[int]
     storage: object                    # cache.CacheStorage
     fast: bool = True                  # False: plain kernels only (the twins)
-    prefill_tiles: Optional[torch.Tensor] = None   # [n, 2] (request, first token of a 64-token tile) for q_len > 1
-    prefill_tokens: int = 0                        # tokens of the requests with q_len > 1
-    decode_reqs: Optional[torch.Tensor] = None     # [n] requests with exactly one new token
-    max_decode_ctx: int = 0                        # longest context among them (an upper bound is enough)
+    plans: dict = field(default_factory=dict)      # key -> StepPlan: what parts worked out on the host for this step
     memo: dict = field(default_factory=dict)       # what a part works out once per step and its other layers reuse
 
     @property

@@ -179,7 +179,7 @@ def collect_rows(steps, outputs):
     return rows
 
 
-def run_inprocess(model_dir, dtype, steps, max_tokens, cuda_graphs=True):
+def run_inprocess(model_dir, dtype, steps, max_tokens, cuda_graphs=True, step_graph_after=2):
     """Replays steps through the engine's runner in this process (what bin/trace_run does)."""
     from boring_llm_b200.config import EngineOptions
     from boring_llm_b200.engine.runner import ModelRunner, StepEntry
@@ -187,7 +187,7 @@ def run_inprocess(model_dir, dtype, steps, max_tokens, cuda_graphs=True):
     cfg, model = load_model(model_dir, dtype, "cuda:0")
     cap = -(-max_tokens // 16) * 16
     opts = EngineOptions(dtype=dtype, page_size=16, max_tokens=cap, ctx_size=min(cfg.max_position_embeddings, cap),
-                         max_num_seqs=8, cuda_graphs=cuda_graphs)
+                         max_num_seqs=8, cuda_graphs=cuda_graphs, step_graph_after=step_graph_after)
     runner = ModelRunner(model, opts)
     outputs = {}
     for s in steps:

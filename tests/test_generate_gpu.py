@@ -157,3 +157,35 @@ def test_lookahead_gives_the_same_tokens_as_stepping_in_turn(model_folders):
         assert s["live_requests"] == 0 and s["pages_in_use"] == [0]
         for p, o in zip(prompts, outs[eng]):                    # (the arrival meets the others one step apart in the two
             check_greedy(d, p, o, "bfloat16")                   # engines, in kernels that round differently: no equality)
+
+
+def test_a_failed_step_with_another_one_ahead_leaves_scheduler_and_cache_in_step(model_folders):
+    """The step in flight fails when its result is checked (here: the check itself is made to raise, no kernel is
+    harmed) while the step ahead has already been launched: both steps' requests end with reason 'error', their
+    pages and slots come back, nothing stays in flight, and the engine serves the next request as if nothing had
+    happened."""
+    from boring_llm_b200 import Engine
+    from boring_llm_b200.kernels.ops import KernelError
+    from boring_llm_b200.sampling.params import SamplingParams
+    d = model_folders("B", "bfloat16", 0.02)
+    prompts = [helpers.random_tokens(320, n, 700 + n) for n in (9, 21, 14)]
+    eng = Engine(d, dtype="bfloat16", ctx_size=128, max_num_seqs=4, max_tokens=1024, prefill_chunk=16)
+    want = eng.generate(prompts, n_predict=12, ignore_eos=True)
+    reqs = [eng.add_request(p, SamplingParams(n_predict=12, ignore_eos=True)) for p in prompts]
+    while eng._inflight is None:
+        eng.step()
+    eng.step()
+    real = eng.runner.check_kernels
+
+    def fail():
+        raise KernelError("a block gave up on a bounded wait (made up by the test)")
+    eng.runner.check_kernels = fail
+    with pytest.raises(KernelError):
+        eng.step()
+    eng.runner.check_kernels = real
+    assert eng._inflight is None and not eng.scheduler.has_work()
+    assert all(r.state == "finished" and r.finish_reason == "error" for r in reqs)
+    eng.runner.cache.check()
+    s = eng.stats()
+    assert s["live_requests"] == 0 and s["pages_in_use"] == [0]
+    assert eng.generate(prompts, n_predict=12, ignore_eos=True) == want

@@ -109,6 +109,33 @@ def test_tcgen05_prefill_attention_inside_the_engine(model_folders, expected, mo
     ops.check_status()
 
 
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_captured_general_steps_replay_what_the_kernels_compute_singly(model_folders, expected, monkeypatch, name):
+    """Steps that mix portions and single tokens are padded to a shape, run kernel by kernel the first time the shape
+    comes and replayed from a captured graph afterwards (here: captured at first sight). The same mixed trace runs
+    twice in one pool: the second pass replays what the first captured, on other pages, and must give the same
+    bits; both must equal the plain implementation."""
+    from boring_llm_b200.parts import attention
+    if name == "D":
+        monkeypatch.setattr(attention, "PREFILL_TC_MIN_TOKENS", 0)     # the tcgen05 attention, with padded tile lists
+    d = model_folders(name, "bfloat16")
+    reqs = requests_for(name)
+    want = expected(name, "bfloat16")
+    steps, peak = helpers.mixed_trace(reqs, seed=13, max_live=4)
+    again = [dict(s, step=s["step"] + len(steps),
+                  entries=[dict(e, id=e["id"] + "'") for e in s["entries"]], end=[r + "'" for r in s["end"]]) for s in steps]
+    outputs, runner = helpers.run_inprocess(d, "bfloat16", steps + again, max_tokens=peak + 64, step_graph_after=1)
+    general = [s for s in steps if any(len(e["tokens"]) > 1 for e in s["entries"])]
+    assert len(runner._step_graphs) >= 1 and runner.graph_steps >= len(general) // 2
+    rows = helpers.collect_rows(steps + again, outputs)
+    check_rows({k: v for k, v in rows.items() if not k[0].endswith("'")}, want, "bfloat16", f"{name} first pass")
+    second = {(rid[:-1], p): v for (rid, p), v in rows.items() if rid.endswith("'")}
+    check_rows(second, want, "bfloat16", f"{name} replayed")
+    for k, v in second.items():
+        assert np.array_equal(v, rows[k]), f"{name}: the replay differs from the first run at {k}"
+    runner.check_kernels()
+
+
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_bfloat16_against_the_pure_plain_implementation(model_folders, name):
     """No rounding on the plain side: a bfloat16 engine stays within a few percent of exact arithmetic
