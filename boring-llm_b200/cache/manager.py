@@ -50,6 +50,7 @@ class PagePool:
         self._free: List[int] = list(range(num_pages - 1, -1, -1))
         self._owner: List[Optional[object]] = [None] * num_pages
         self.high_water = 0
+        self.freed_log: Optional[List[int]] = None     # when a list: every page given back is noted here (debugging)
 
     @property
     def num_free(self) -> int:
@@ -74,6 +75,8 @@ class PagePool:
             raise CacheError(f"page {page} is owned by {self._owner[page]!r}, not by {owner!r}")
         self._owner[page] = None
         self._free.append(page)
+        if self.freed_log is not None:
+            self.freed_log.append(page)
 
     def owner_of(self, page: int):
         return self._owner[page]

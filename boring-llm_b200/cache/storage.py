@@ -37,6 +37,23 @@ class CacheStorage:
                 dtype=_TORCH_DTYPES[sg.spec.dtype], device=self.device))
         manager._on_slot_assigned = self.zero_slot
 
+    def poison_freed_pages(self) -> int:
+        """Debugging aid: fills every page that was given back since the last call (and, the first time, every page
+        that no request holds, the spare page included) with NaN, keys and values in all layers. Freed pages are
+        otherwise left as they are, because nothing may read a request's cache past its length; with poison a
+        kernel that does read there, even with weight zero, turns its output into NaN. Returns the pages filled."""
+        n = 0
+        for g, kv in zip(self.manager.paged_groups, self.kv):
+            if g.pool.freed_log is None:
+                g.pool.freed_log = []
+                pages = [p for p in range(g.pool.num_pages) if g.pool.owner_of(p) is None] + [self.trash_page]
+            else:
+                pages, g.pool.freed_log = [p for p in set(g.pool.freed_log) if g.pool.owner_of(p) is None], []
+            if pages and kv.dtype.is_floating_point:
+                kv[:, :, torch.tensor(pages, dtype=torch.long, device=self.device)] = float("nan")
+                n += len(pages)
+        return n
+
     def zero_slot(self, slot: int) -> None:
         for t in self.state:
             t[:, slot].zero_()

@@ -22,6 +22,7 @@ class EngineOptions:
     cuda_graphs: bool = True            # replay captured decode steps
     step_graph_after: int = 2           # capture a general step's padded shape when it comes this many times (0: never)
     lookahead: bool = True              # launch the next decode step (its tokens taken on the device) before this one's are read
+    debug_poison: bool = False          # fill pages with NaN when they are given back: a read past a request's length shows
     device: str = "cuda:0"
 
     def __post_init__(self):

@@ -284,6 +284,15 @@ class ModelRunner:
     def has_request(self, request_id) -> bool:
         return request_id in self.cache
 
+    def truncate(self, request_id, n_keep: int) -> None:
+        """Keeps the first `n_keep` tokens of a request's cache and gives the pages behind them back; the next step's
+        tokens of that request continue at position `n_keep` (the reference truncates by setting the cache's length,
+        src/model.br:2313-2314, 2330-2342). Refused for a request whose mixer keeps state that cannot be rolled back
+        (anything but pages), or whose window has already given pages of the kept prefix back."""
+        if self.cache.state_groups:
+            raise StepError(f"request {request_id!r}: state of fixed size cannot be truncated; recompute from the start")
+        self.cache.truncate(request_id, n_keep)
+
     # ---- the step ----------------------------------------------------------------------------------
     def _host_buffer(self, n_ints: int) -> torch.Tensor:
         """One of two pinned staging buffers, reused once the copy that last read it is done."""
@@ -447,6 +456,8 @@ class ModelRunner:
         page = self.options.page_size
         if not entries:
             raise StepError("a step needs at least one entry")
+        if self.options.debug_poison:
+            self.storage.poison_freed_pages()
         if self._prepare_decode(entries):
             return
         seen = set()

@@ -179,7 +179,7 @@ def collect_rows(steps, outputs):
     return rows
 
 
-def run_inprocess(model_dir, dtype, steps, max_tokens, cuda_graphs=True, step_graph_after=2):
+def run_inprocess(model_dir, dtype, steps, max_tokens, cuda_graphs=True, step_graph_after=2, debug_poison=False):
     """Replays steps through the engine's runner in this process (what bin/trace_run does)."""
     from boring_llm_b200.config import EngineOptions
     from boring_llm_b200.engine.runner import ModelRunner, StepEntry
@@ -187,10 +187,13 @@ def run_inprocess(model_dir, dtype, steps, max_tokens, cuda_graphs=True, step_gr
     cfg, model = load_model(model_dir, dtype, "cuda:0")
     cap = -(-max_tokens // 16) * 16
     opts = EngineOptions(dtype=dtype, page_size=16, max_tokens=cap, ctx_size=min(cfg.max_position_embeddings, cap),
-                         max_num_seqs=8, cuda_graphs=cuda_graphs, step_graph_after=step_graph_after)
+                         max_num_seqs=8, cuda_graphs=cuda_graphs, step_graph_after=step_graph_after,
+                         debug_poison=debug_poison)
     runner = ModelRunner(model, opts)
     outputs = {}
     for s in steps:
+        for t in s.get("truncate", []):
+            runner.truncate(t["id"], t["keep"])
         entries = [StepEntry(e["id"], e["tokens"], e["want"]) for e in s["entries"]]
         logits = runner.step(entries)
         if logits.shape[0]:
@@ -202,10 +205,10 @@ def run_inprocess(model_dir, dtype, steps, max_tokens, cuda_graphs=True, step_gr
     return outputs, runner
 
 
-def run_trace_program(model_dir, dtype, steps, max_tokens, out_dir, vocab, env=None):
+def run_trace_program(model_dir, dtype, steps, max_tokens, out_dir, vocab, env=None, extra=()):
     """Drives bin/trace_run as a user would: one line in, wait for `done <step>`, next line."""
     cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
-           "--out", out_dir, "--max-tokens", str(max_tokens)]
+           "--out", out_dir, "--max-tokens", str(max_tokens)] + list(extra)
     p = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
     try:
         for s in steps:

@@ -5,6 +5,7 @@ are used again. In float32 and in bfloat16, for three tiny configurations."""
 import os
 
 import numpy as np
+import torch
 import pytest
 
 import helpers
@@ -163,6 +164,62 @@ def test_the_trace_run_program(model_folders, expected, tmp_path, name, dtype):
     outputs = helpers.run_trace_program(d, dtype, steps, peak, out, helpers.TINY[name]["vocab_size"], env)
     rows = helpers.collect_rows(steps, outputs)
     check_rows(rows, expected(name, dtype), dtype, f"trace_run {name} {dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_freed_pages_full_of_nan_change_nothing(model_folders, expected, name, dtype):
+    """Pages are filled with NaN when they are given back (and all of them, with the spare page, at the start): a
+    kernel that reads a key or value past a request's length, in a page of a finished request or behind a window,
+    even to multiply it by zero, would turn logits into NaN. The mixed trace runs twice over in a pool that is
+    just large enough, so every request of the second pass lives in poisoned pages."""
+    d = model_folders(name, dtype)
+    reqs = requests_for(name)
+    steps, peak = helpers.mixed_trace(reqs, seed=21, max_live=4)
+    again = [dict(s, step=s["step"] + len(steps),
+                  entries=[dict(e, id=e["id"] + "'") for e in s["entries"]], end=[r + "'" for r in s["end"]]) for s in steps]
+    outputs, runner = helpers.run_inprocess(d, dtype, steps + again, max_tokens=peak, debug_poison=True,
+                                            step_graph_after=1)
+    runner.storage.poison_freed_pages()
+    # (all but the spare page at the end, where the rows that pad a replayed step write)
+    assert all(torch.isnan(kv[:, :, :-1].float()).all() for kv in runner.storage.kv), "every page was given back: all are poisoned"
+    rows = helpers.collect_rows(steps + again, outputs)
+    check_rows({(rid.rstrip("'"), p): v for (rid, p), v in rows.items() if rid.endswith("'")}, expected(name, dtype), dtype,
+               f"{name} {dtype} on poisoned pages")
+    check_rows({k: v for k, v in rows.items() if not k[0].endswith("'")}, expected(name, dtype), dtype, f"{name} {dtype} first pass")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_truncation_between_steps(model_folders, tmp_path, dtype):
+    """40 tokens are fed, the cache is cut back to its first 23, other tokens follow (in a portion, then one by
+    one): every row must equal the plain implementation on (the first 23 + the other tokens), as if the 17 had
+    never been there; the pages behind the cut come back to the pool. Once in-process with poisoned pages, once
+    through bin/trace_run's `truncate` event. (The reference truncates by setting the length, src/model.br:2313-2314.)"""
+    d = model_folders("A", dtype)
+    vocab = helpers.TINY["A"]["vocab_size"]
+    first = helpers.random_tokens(vocab, 40, 31)
+    other = helpers.random_tokens(vocab, 30, 32)
+    steps = [
+        {"step": 0, "entries": [{"id": "t", "tokens": first, "want": list(range(40))}], "end": []},
+        {"step": 1, "truncate": [{"id": "t", "keep": 23}],
+         "entries": [{"id": "t", "tokens": other[:9], "want": list(range(9))}], "end": []},
+    ] + [{"step": 2 + i, "entries": [{"id": "t", "tokens": [tok], "want": [0]}], "end": ["t"] if i == 20 else []}
+         for i, tok in enumerate(other[9:])]
+    want_first = helpers.plain_logits(d, first, dtype)
+    want_cut = helpers.plain_logits(d, first[:23] + other, dtype)
+
+    def check(outputs, what):
+        helpers.assert_close(outputs[0], want_first, dtype, f"{what}: before the cut")
+        got = np.concatenate([outputs[s["step"]] for s in steps[1:]])
+        helpers.assert_close(got, want_cut[23:], dtype, f"{what}: after the cut")
+
+    outputs, runner = helpers.run_inprocess(d, dtype, steps, max_tokens=64, debug_poison=True)
+    check(outputs, "in process")
+    assert runner.cache.stats()["pages_high_water"] == [4]            # 40 tokens, then 23 + 30 = 53: the pool's 4 pages suffice
+    out = str(tmp_path / "out")
+    check(helpers.run_trace_program(d, dtype, steps, 64, out, vocab, extra=["--poison"]), "trace_run")
+    with pytest.raises(Exception, match="truncate"):
+        runner.add_request("u"); runner.truncate("u", 5)
 
 
 def test_long_decoding_and_first_tokens(model_folders):
