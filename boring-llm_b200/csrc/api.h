@@ -24,13 +24,14 @@ int bl_rmsnorm(const float* x, const int* row_idx, const void* w, int w_dtype, v
 int bl_gemm_plain(const void* x, int x_dtype, const void* w, int w_dtype, const void* bias, int bias_dtype,
                   void* out, int out_dtype, int M, int N, int K, int epilogue, void* stream);
 
-// Splits rows of joined [q | k | v] projections, rotates q and k by position (pairs (j, j + n_rot/2)
-// inside each head, angle = float(position) * inv_freq[j], cos and sin times mscale) and writes k and v
-// into the pages of the token's request. k_cache/v_cache may be null: then only q is produced.
+// Splits rows of joined [q | k | v] projections, rotates q and k by position (inside each head, pair j is
+// (j, j + n_rot/2) for pair_layout 0 and (2j, 2j + 1) for pair_layout 1; angle = float(position) * inv_freq[j],
+// cos and sin times mscale) and writes k and v into the pages of the token's request. k_cache/v_cache may be
+// null: then only q is produced.
 int bl_rope_kv_write(const float* qkv, const int* positions, const int* tok_req, const int* block_table,
                      int max_pages, const float* inv_freq, int rot_half, float mscale,
                      void* q_out, void* k_cache, void* v_cache, int dtype,
-                     int T, int H, int KV, int dh, int page_size, void* stream);
+                     int T, int H, int KV, int dh, int page_size, int pair_layout, void* stream);
 
 // Plain paged causal attention: one warp per (token, head), keys visited in ascending position.
 // Token t of request r = tok_req[t] stands at position ctx_len[r] - (cu_q[r+1] - cu_q[r]) + (t - cu_q[r])
@@ -109,7 +110,7 @@ int bl_norm_qkv_rope(const float* x, const void* norm_w, int norm_w_dtype, float
                      const void* bias, int bias_dtype, const int* positions, const int* tok_req,
                      const int* block_table, int max_pages, const float* inv_freq, float mscale,
                      void* q_out, void* k_cache, void* v_cache, int M, int K, int H, int KV, int dh,
-                     int page_size, void* stream);
+                     int page_size, int pair_layout, void* stream);
 
 // Programmatic dependent launch for the small kernels of a step (on by default): 0 launches them the ordinary way.
 void bl_set_dependent_launch(int on);

@@ -16,6 +16,10 @@
 #define BL_EPI_RESIDUAL 2  // out (32-bit, in place) = out + acc
 #define BL_EPI_SWIGLU 3    // out[m, n] = silu(acc_gate[m, n]) * acc_up[m, n]; W holds gate rows then up rows
 
+// Which two dimensions of a head a rotary position encoding turns together (src/math.br:128-157, its `neox` argument).
+#define BL_PAIRS_HALVES 0        // pair j = (j, j + n_rot / 2)
+#define BL_PAIRS_INTERLEAVED 1   // pair j = (2j, 2j + 1)
+
 void bl_set_error(const char* fmt, ...);
 
 #define BL_FAIL(...) do { bl_set_error(__VA_ARGS__); return 1; } while (0)

@@ -9,11 +9,11 @@
 //     in turn, partial sums added in warp order); the epilogue is one of
 //       PLAIN   out = acc (+ bias), 32-bit                                  (the output head on the final norm)
 //       SWIGLU  out = silu(gate) * up, bfloat16                              (src/math.br:246-261)
-//       QKV     split of the joined q/k/v row, rotation of q and k by position (NEOX pairs (j, j + head/2),
+//       QKV     split of the joined q/k/v row, rotation of q and k by position (pairs (j, j + head/2) or (2j, 2j + 1),
 //               src/math.br:128-157), k and v written into the request's pages, q written out in bfloat16
 //               (src/math_gpu.br:2428-2488, 4008-4076 do split + rotation + append in one dispatch, too).
-//     For QKV the 16 rows of W that a block owns are 8 dimensions j of one head and their partners j + head/2,
-//     so both halves of every rotation pair end up in the same thread.
+//     For QKV the 16 rows of W that a block owns are 8 dimensions of one head and their partners in the rotation
+//     (j + head/2, or 2j + 1 beside 2j), so both halves of every rotation pair end up in the same thread.
 #include "common.cuh"
 #include "api.h"
 
@@ -30,7 +30,7 @@ struct FusedParams {
     // QKV only
     const int* positions; const int* tok_req; const int* block_table; int max_pages;
     const float* inv_freq; float mscale;
-    __nv_bfloat16* k_cache; __nv_bfloat16* v_cache; int H, KV, dh, page_size;
+    __nv_bfloat16* k_cache; __nv_bfloat16* v_cache; int H, KV, dh, page_size, pair_layout;
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -62,8 +62,8 @@ fused_norm_gemm_kernel(const FusedParams p) {
     if (MODE == MODE_QKV) {
         const int tiles_per_head = p.dh / 16;
         hh = tile / tiles_per_head; jt = tile % tiles_per_head;
-        r_lo = hh * p.dh + jt * 8 + g;
-        r_hi = r_lo + p.dh / 2;
+        if (p.pair_layout == BL_PAIRS_INTERLEAVED) { r_lo = hh * p.dh + 2 * (jt * 8 + g); r_hi = r_lo + 1; }
+        else { r_lo = hh * p.dh + jt * 8 + g; r_hi = r_lo + p.dh / 2; }
     } else {
         r_lo = tile * 16 + g;
         r_hi = r_lo + 8;
@@ -90,10 +90,11 @@ fused_norm_gemm_kernel(const FusedParams p) {
     fetch(warp * 32);                                  // W is on its way while the kernel before this one finishes
     {
         const size_t rows_total = MODE == MODE_SWIGLU ? (size_t)2 * p.N : (size_t)n_rows;
-        const size_t first = MODE == MODE_QKV ? (size_t)hh * p.dh + jt * 8 : (size_t)tile * 16;
-        const int span = MODE == MODE_QKV ? 8 : 16;
+        const bool inter = MODE == MODE_QKV && p.pair_layout == BL_PAIRS_INTERLEAVED;    // 16 neighbouring rows, like a plain tile
+        const size_t first = MODE == MODE_QKV ? (size_t)hh * p.dh + jt * (inter ? 16 : 8) : (size_t)tile * 16;
+        const int span = MODE == MODE_QKV && !inter ? 8 : 16;
         bl_prefetch_rows_l2(p.w, first, span, (size_t)K * 2, rows_total);
-        if (MODE == MODE_QKV) bl_prefetch_rows_l2(p.w, first + p.dh / 2, 8, (size_t)K * 2, rows_total);
+        if (MODE == MODE_QKV && !inter) bl_prefetch_rows_l2(p.w, first + p.dh / 2, 8, (size_t)K * 2, rows_total);
         if (MODE == MODE_SWIGLU) bl_prefetch_rows_l2(p.w, (size_t)p.N + first, 16, (size_t)K * 2, rows_total);
     }
     // everything that no earlier kernel of the step writes is fetched before the wait: the norm's weights, and for
@@ -104,8 +105,9 @@ fused_norm_gemm_kernel(const FusedParams p) {
     if (MODE == MODE_QKV && threadIdx.x < 8 * TOK) {
         const int c = threadIdx.x % 8, m = m0 + threadIdx.x / 8;
         if (m < p.M) {
-            const int row_lo = hh * p.dh + jt * 8 + c;
-            if (p.bias) { e_b0 = bl_load_any(p.bias, p.bias_dtype, row_lo); e_b1 = bl_load_any(p.bias, p.bias_dtype, row_lo + p.dh / 2); }
+            const bool inter = p.pair_layout == BL_PAIRS_INTERLEAVED;
+            const int row_lo = hh * p.dh + (inter ? 2 * (jt * 8 + c) : jt * 8 + c), row_hi = inter ? row_lo + 1 : row_lo + p.dh / 2;
+            if (p.bias) { e_b0 = bl_load_any(p.bias, p.bias_dtype, row_lo); e_b1 = bl_load_any(p.bias, p.bias_dtype, row_hi); }
             e_pos = p.positions[m];
             if (hh < p.H + p.KV) {
                 const float angle = (float)e_pos * p.inv_freq[jt * 8 + c];
@@ -220,7 +222,8 @@ fused_norm_gemm_kernel(const FusedParams p) {
             const int c = threadIdx.x % 8, tok = threadIdx.x / 8, m = m0 + tok;
             if (m < p.M) {
                 const float v0 = total(0, c, tok) + e_b0, v1 = total(0, c + 8, tok) + e_b1;
-                const int d0 = jt * 8 + c, d1 = d0 + half;
+                const bool inter = p.pair_layout == BL_PAIRS_INTERLEAVED;
+                const int d0 = inter ? 2 * (jt * 8 + c) : jt * 8 + c, d1 = inter ? d0 + 1 : d0 + half;
                 const float y0 = v0 * e_cs - v1 * e_sn, y1 = v0 * e_sn + v1 * e_cs;     // cos 1, sin 0 for value heads
                 if (hh < p.H) {
                     __nv_bfloat16* q = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)m * p.H + hh) * p.dh;
@@ -327,8 +330,10 @@ extern "C" int bl_norm_qkv_rope(const float* x, const void* norm_w, int norm_w_d
                                 const void* bias, int bias_dtype, const int* positions, const int* tok_req,
                                 const int* block_table, int max_pages, const float* inv_freq, float mscale,
                                 void* q_out, void* k_cache, void* v_cache, int M, int K, int H, int KV, int dh,
-                                int page_size, void* stream) {
+                                int page_size, int pair_layout, void* stream) {
     if (M <= 0) return 0;
+    if (pair_layout != BL_PAIRS_HALVES && pair_layout != BL_PAIRS_INTERLEAVED)
+        BL_FAIL("bl_norm_qkv_rope: unknown pair layout %d (0: (j, j + head/2), 1: (2j, 2j + 1))", pair_layout);
     if (check_common("bl_norm_qkv_rope", x, w_qkv, M, K, norm_w_dtype)) return 1;
     if (H <= 0 || KV <= 0 || dh <= 0 || dh % 16 != 0) BL_FAIL("bl_norm_qkv_rope: head size %d must be a multiple of 16", dh);
     if (page_size <= 0 || max_pages <= 0) BL_FAIL("bl_norm_qkv_rope: bad page size or table width");
@@ -339,7 +344,7 @@ extern "C" int bl_norm_qkv_rope(const float* x, const void* norm_w, int norm_w_d
     p.bias = bias; p.bias_dtype = bias_dtype; p.out = q_out; p.M = M; p.N = (H + 2 * KV) * dh; p.K = K;
     p.positions = positions; p.tok_req = tok_req; p.block_table = block_table; p.max_pages = max_pages;
     p.inv_freq = inv_freq; p.mscale = mscale; p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache;
-    p.H = H; p.KV = KV; p.dh = dh; p.page_size = page_size;
+    p.H = H; p.KV = KV; p.dh = dh; p.page_size = page_size; p.pair_layout = pair_layout;
     const int heads = k_cache ? H + 2 * KV : H;
     return dispatch<MODE_QKV>(p, heads * (dh / 16), (cudaStream_t)stream);
 }

@@ -182,7 +182,7 @@ __global__ void rope_kv_write_kernel(const float* qkv /* written by the kernel b
                                      const int* __restrict__ tok_req, const int* __restrict__ block_table,
                                      int max_pages, const float* __restrict__ inv_freq, int rot_half,
                                      float mscale, TT* __restrict__ q_out, TT* __restrict__ k_cache,
-                                     TT* __restrict__ v_cache, int H, int KV, int dh, int page_size) {
+                                     TT* __restrict__ v_cache, int H, int KV, int dh, int page_size, int pair_layout) {
     bl_pdl_trigger();
     bl_pdl_wait();
     const int t = blockIdx.x;
@@ -236,7 +236,8 @@ __global__ void rope_kv_write_kernel(const float* qkv /* written by the kernel b
         int i0, i1;
         float c = 1.f, s = 0.f;
         if (j < rot_half) {
-            i0 = j; i1 = j + rot_half;
+            if (pair_layout == BL_PAIRS_INTERLEAVED) { i0 = 2 * j; i1 = 2 * j + 1; }
+            else { i0 = j; i1 = j + rot_half; }
             c = cs_sn[j];
             s = cs_sn[rot_half + j];
         } else {                                         // dimensions past the rotated ones pass through
@@ -264,19 +265,21 @@ __global__ void rope_kv_write_kernel(const float* qkv /* written by the kernel b
 extern "C" int bl_rope_kv_write(const float* qkv, const int* positions, const int* tok_req,
                                 const int* block_table, int max_pages, const float* inv_freq,
                                 int rot_half, float mscale, void* q_out, void* k_cache, void* v_cache,
-                                int dtype, int T, int H, int KV, int dh, int page_size, void* stream) {
+                                int dtype, int T, int H, int KV, int dh, int page_size, int pair_layout, void* stream) {
     if (T <= 0) return 0;
+    if (pair_layout != BL_PAIRS_HALVES && pair_layout != BL_PAIRS_INTERLEAVED)
+        BL_FAIL("bl_rope_kv_write: unknown pair layout %d (0: (j, j + n_rot/2), 1: (2j, 2j + 1))", pair_layout);
     if (H <= 0 || KV <= 0 || dh <= 0 || dh % 2 != 0 || page_size <= 0 || max_pages <= 0)
         BL_FAIL("bl_rope_kv_write: bad sizes H=%d KV=%d head=%d page=%d max_pages=%d", H, KV, dh, page_size, max_pages);
     if (rot_half < 0 || rot_half > dh / 2) BL_FAIL("bl_rope_kv_write: %d rotated pairs do not fit a head of %d", rot_half, dh);
     if ((k_cache == nullptr) != (v_cache == nullptr)) BL_FAIL("bl_rope_kv_write: key and value cache must both be given or both be null");
     cudaStream_t s = (cudaStream_t)stream;
     const size_t elem = dtype == BL_F32 ? 4 : 2;
-    const bool vec = rot_half * 2 == dh && rot_half % 4 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)inv_freq & 3) == 0 &&
+    const bool vec = pair_layout == BL_PAIRS_HALVES && rot_half * 2 == dh && rot_half % 4 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)inv_freq & 3) == 0 &&
                      ((uintptr_t)q_out % (4 * elem)) == 0 && ((uintptr_t)k_cache % (4 * elem)) == 0 && ((uintptr_t)v_cache % (4 * elem)) == 0;
     const size_t smem = (size_t)rot_half * 8;
 #define BL_ROPE(TT, VEC) BL_CUDA(bl_launch_dependent(rope_kv_write_kernel<TT, VEC>, dim3(T), dim3(128), smem, s, qkv, positions, tok_req, \
-        block_table, max_pages, inv_freq, rot_half, mscale, (TT*)q_out, (TT*)k_cache, (TT*)v_cache, H, KV, dh, page_size))
+        block_table, max_pages, inv_freq, rot_half, mscale, (TT*)q_out, (TT*)k_cache, (TT*)v_cache, H, KV, dh, page_size, pair_layout))
     if (dtype == BL_F32) { if (vec) BL_ROPE(float, true); else BL_ROPE(float, false); }
     else if (dtype == BL_BF16) { if (vec) BL_ROPE(__nv_bfloat16, true); else BL_ROPE(__nv_bfloat16, false); }
     else BL_FAIL("bl_rope_kv_write: unknown dtype %d", dtype);

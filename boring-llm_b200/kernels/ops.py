@@ -14,6 +14,7 @@ from . import library
 
 F32, BF16 = 0, 1
 EPI_NONE, EPI_BIAS, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
+PAIRS_HALVES, PAIRS_INTERLEAVED = 0, 1
 
 _checked_device = False
 
@@ -160,8 +161,9 @@ def gemm_plain(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Option
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, tok_req: torch.Tensor,
                   block_table: torch.Tensor, inv_freq: torch.Tensor, rot_half: int, mscale: float,
                   q_out: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
-                  H: int, KV: int, dh: int) -> None:
-    """Rotates q and k of joined [q | k | v] rows and writes k, v into the request's pages."""
+                  H: int, KV: int, dh: int, pair_layout: int = 0) -> None:
+    """Rotates q and k of joined [q | k | v] rows and writes k, v into the request's pages. `pair_layout`: which
+    dimensions turn together, PAIRS_HALVES (j, j + rot_half) or PAIRS_INTERLEAVED (2j, 2j + 1)."""
     T = qkv.shape[0]
     _need(qkv, "qkv", torch.float32, (T, (H + 2 * KV) * dh))
     _need(positions, "positions", torch.int32, (T,)); _need(tok_req, "tok_req", torch.int32, (T,))
@@ -175,7 +177,7 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, tok_req: torch.Ten
         page_size = k_cache.shape[2]
     _call(_lib().bl_rope_kv_write, _p(qkv), _p(positions), _p(tok_req), _p(block_table),
           block_table.shape[1], _p(inv_freq), rot_half, ctypes.c_float(mscale), _p(q_out), _p(k_cache),
-          _p(v_cache), _dt(q_out), T, H, KV, dh, page_size, _stream())
+          _p(v_cache), _dt(q_out), T, H, KV, dh, page_size, pair_layout, _stream())
 
 
 def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_req: torch.Tensor,
@@ -409,7 +411,7 @@ def norm_gemm(x: torch.Tensor, norm_w: torch.Tensor, eps: float, w: torch.Tensor
 def norm_qkv_rope(x: torch.Tensor, norm_w: torch.Tensor, eps: float, w_qkv: torch.Tensor, bias: Optional[torch.Tensor],
                   positions: torch.Tensor, tok_req: torch.Tensor, block_table: torch.Tensor, inv_freq: torch.Tensor,
                   mscale: float, q_out: torch.Tensor, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
-                  H: int, KV: int, dh: int) -> None:
+                  H: int, KV: int, dh: int, pair_layout: int = 0) -> None:
     """rmsnorm -> joined q/k/v product (+ bias) -> rotation of q and k -> k, v into the pages, q out, in one launch."""
     M, K = x.shape
     _need(x, "x", torch.float32); _need(norm_w, "norm_w", None, (K,)); _need(w_qkv, "w_qkv", torch.bfloat16, ((H + 2 * KV) * dh, K))
@@ -426,4 +428,5 @@ def norm_qkv_rope(x: torch.Tensor, norm_w: torch.Tensor, eps: float, w_qkv: torc
         page_size = k_cache.shape[2]
     _call(_lib().bl_norm_qkv_rope, _p(x), _p(norm_w), _dt(norm_w), ctypes.c_float(eps), _p(w_qkv), _p(bias),
           _dt(bias) if bias is not None else 0, _p(positions), _p(tok_req), _p(block_table), block_table.shape[1],
-          _p(inv_freq), ctypes.c_float(mscale), _p(q_out), _p(k_cache), _p(v_cache), M, K, H, KV, dh, page_size, _stream())
+          _p(inv_freq), ctypes.c_float(mscale), _p(q_out), _p(k_cache), _p(v_cache), M, K, H, KV, dh, page_size,
+          pair_layout, _stream())

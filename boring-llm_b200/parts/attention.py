@@ -147,7 +147,7 @@ class GQAAttention(Mixer):
         q = ctx.empty((T, self.H * self.dh))
         ops.rope_kv_write(qkv, ctx.positions, ctx.tok_req, table, self.rotary.inv_freq, self.rotary.rot_half,
                           self.rotary.mscale, q, k_cache if write_cache else None,
-                          v_cache if write_cache else None, self.H, self.KV, self.dh)
+                          v_cache if write_cache else None, self.H, self.KV, self.dh, self.rotary.pair_layout)
         attn = ctx.empty((T, self.H * self.dh))
         self.attend(ctx, q, k_cache, v_cache, table, attn)
         linear(ctx, attn, self.wo, residual, None, EPI_RESIDUAL)
@@ -163,7 +163,8 @@ class GQAAttention(Mixer):
         q = ctx.empty((T, self.H * self.dh))
         ops.norm_qkv_rope(x, norm.weight, norm.eps, self.w_qkv, self.b_qkv if self.qkv_bias else None,
                           ctx.positions, ctx.tok_req, table, self.rotary.inv_freq, self.rotary.mscale, q,
-                          k_cache if write_cache else None, v_cache if write_cache else None, self.H, self.KV, self.dh)
+                          k_cache if write_cache else None, v_cache if write_cache else None, self.H, self.KV, self.dh,
+                          self.rotary.pair_layout)
         attn = ctx.empty((T, self.H * self.dh))
         self.attend(ctx, q, k_cache, v_cache, table, attn)
         linear(ctx, attn, self.wo, x, None, EPI_RESIDUAL)

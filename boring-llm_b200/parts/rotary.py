@@ -8,13 +8,20 @@ import torch
 class RotaryTable:
     """Per-pair rotation table, as the reference builds it (src/math.br:107-113, 161-171):
     `inv_freq[j] = 1 / base^(2j / n_rot)` in 32-bit for the n_rot/2 rotated pairs, zero past them, a
-    magnitude scale for cos/sin and the number of rotated pairs. Pairs are NEOX style
-    (j, j + n_rot/2) inside each head (src/math.br:145-148); every variant of rotary scaling is just
+    magnitude scale for cos/sin, the number of rotated pairs, and which dimensions form a pair:
+    "halves" (j, j + n_rot/2) inside each head, the NEOX style of this architecture, or "interleaved"
+    (2j, 2j + 1) (src/math.br:128-157, the `neox` argument). Every variant of rotary scaling is just
     another table, so the kernel never branches on the variant.
     """
 
-    def __init__(self, head_dim: int, base: float, n_rot: int | None = None, mscale: float = 1.0):
+    PAIR_LAYOUTS = {"halves": 0, "interleaved": 1}
+
+    def __init__(self, head_dim: int, base: float, n_rot: int | None = None, mscale: float = 1.0,
+                 pairs: str = "halves"):
         n_rot = head_dim if n_rot is None else n_rot
+        if pairs not in self.PAIR_LAYOUTS:
+            raise ValueError(f"rotary: pairs must be one of {sorted(self.PAIR_LAYOUTS)}, got {pairs!r}")
+        self.pairs, self.pair_layout = pairs, self.PAIR_LAYOUTS[pairs]
         if n_rot % 2 != 0 or n_rot > head_dim or n_rot < 0:
             raise ValueError(f"rotary: {n_rot} rotated dimensions do not fit a head of {head_dim}")
         self.head_dim, self.base, self.n_rot, self.mscale = head_dim, float(base), n_rot, float(mscale)

@@ -122,9 +122,23 @@ def fill_cache(s, k_full, v_full, page):
             s["vc"][pg, :, p % page, :] = v[p].to(s["vc"].dtype)
 
 
+def rope_pairs(x, positions, inv_freq, rot, layout):
+    """Rotation of the first `rot` dimensions of each head: pairs (j, j + rot/2) or (2j, 2j + 1) (src/math.br:128-157)."""
+    if layout == 0:
+        return torch.cat([plain.rope_neox(x[..., :rot], positions, inv_freq), x[..., rot:]], dim=-1)
+    ang = torch.from_numpy((positions.astype(np.float32)[:, None] * inv_freq[None, :]).astype(np.float64))
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    out = x.clone()
+    a, b = x[..., 0:rot:2], x[..., 1:rot:2]
+    out[..., 0:rot:2] = a * c - b * s
+    out[..., 1:rot:2] = a * s + b * c
+    return out
+
+
+@pytest.mark.parametrize("layout", [0, 1])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,KV,dh,rot", [(4, 2, 16, 16), (7, 1, 48, 48), (8, 8, 64, 32), (2, 1, 128, 128)])
-def test_rope_and_cache_write(dtype, H, KV, dh, rot):
+def test_rope_and_cache_write(dtype, H, KV, dh, rot, layout):
     o = ops()
     page = 16
     ctx_lens, q_lens = [5, 40, 17], [5, 9, 1]
@@ -138,14 +152,12 @@ def test_rope_and_cache_write(dtype, H, KV, dh, rot):
     q_out = torch.empty(T, H * dh, dtype=dtype, device=DEV)
     before_k = s["kc"].clone()
     o.rope_kv_write(qkv, s["positions"], s["tok_req"], s["table"], torch.from_numpy(inv).to(DEV), rot // 2, 1.0,
-                    q_out, s["kc"], s["vc"], H, KV, dh)
+                    q_out, s["kc"], s["vc"], H, KV, dh, layout)
     x = qkv.double().cpu()
     pos = s["positions_np"]
 
-    def rot_ref(t, n_heads):                       # NEOX pairs (j, j + rot/2) in the first `rot` dimensions
-        t = t.reshape(T, n_heads, dh)
-        r = plain.rope_neox(t[..., :rot], pos, inv[:rot // 2])
-        return torch.cat([r, t[..., rot:]], dim=-1)
+    def rot_ref(t, n_heads):
+        return rope_pairs(t.reshape(T, n_heads, dh), pos, inv[:rot // 2], rot, layout)
 
     q_ref = rot_ref(x[:, :H * dh], H).reshape(T, H * dh)
     k_ref = rot_ref(x[:, H * dh:(H + KV) * dh], KV)
@@ -163,7 +175,7 @@ def test_rope_and_cache_write(dtype, H, KV, dh, rot):
     # without caches only q is produced
     q2 = torch.empty_like(q_out)
     o.rope_kv_write(qkv, s["positions"], s["tok_req"], s["table"], torch.from_numpy(inv).to(DEV), rot // 2, 1.0,
-                    q2, None, None, H, KV, dh)
+                    q2, None, None, H, KV, dh, layout)
     assert torch.equal(q2, q_out)
 
 
@@ -555,8 +567,8 @@ def test_norm_gemm_fused(M, N, K):
 
 
 @pytest.mark.parametrize("H,KV,dh,d", [(4, 2, 16, 64), (3, 1, 32, 96), (5, 5, 48, 80), (14, 2, 64, 896), (2, 1, 128, 200)])
-@pytest.mark.parametrize("bias", [True, False])
-def test_norm_qkv_rope_fused(H, KV, dh, d, bias):
+@pytest.mark.parametrize("bias,layout", [(True, 0), (False, 0), (True, 1)])
+def test_norm_qkv_rope_fused(H, KV, dh, d, bias, layout):
     """One launch against the three kernels it replaces (norm, joined product with bias, rotation + cache write)."""
     o = ops()
     bf = torch.bfloat16
@@ -578,10 +590,10 @@ def test_norm_qkv_rope_fused(H, KV, dh, d, bias):
     qkv = torch.empty(T, (H + 2 * KV) * dh, device=DEV)
     o.gemm_plain(h, w, qkv, b, o.EPI_BIAS if bias else o.EPI_NONE)
     q_ref = torch.empty(T, H * dh, dtype=bf, device=DEV)
-    o.rope_kv_write(qkv, s["positions"], s["tok_req"], s["table"], inv, dh // 2, 1.0, q_ref, s["kc"], s["vc"], H, KV, dh)
+    o.rope_kv_write(qkv, s["positions"], s["tok_req"], s["table"], inv, dh // 2, 1.0, q_ref, s["kc"], s["vc"], H, KV, dh, layout)
     # fused
     q = torch.full((T, H * dh), float("nan"), dtype=bf, device=DEV)
-    o.norm_qkv_rope(x, nw, 1e-6, w, b, s2["positions"], s2["tok_req"], s2["table"], inv, 1.0, q, s2["kc"], s2["vc"], H, KV, dh)
+    o.norm_qkv_rope(x, nw, 1e-6, w, b, s2["positions"], s2["tok_req"], s2["table"], inv, 1.0, q, s2["kc"], s2["vc"], H, KV, dh, layout)
     close(q, q_ref.double(), bf, "q")
     # the rows that the step's tokens own, one by one (the pools are full of +-1e4 junk, which would set the scale of
     # a comparison of whole pools so high that a key in the wrong row, or no key at all, would pass) ...
@@ -596,5 +608,5 @@ def test_norm_qkv_rope_fused(H, KV, dh, d, bias):
     mask = touched.to(DEV)[:, None, :, None].expand_as(s2["kc"])
     assert torch.equal(s2["kc"][~mask], before_k[~mask]) and torch.equal(s2["vc"][~mask], before_v[~mask])
     q_only = torch.empty_like(q)
-    o.norm_qkv_rope(x, nw, 1e-6, w, b, s2["positions"], s2["tok_req"], s2["table"], inv, 1.0, q_only, None, None, H, KV, dh)
+    o.norm_qkv_rope(x, nw, 1e-6, w, b, s2["positions"], s2["tok_req"], s2["table"], inv, 1.0, q_only, None, None, H, KV, dh, layout)
     assert torch.equal(q_only, q)
