@@ -370,6 +370,35 @@ def gemm_tc_cols(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     _call(_lib().bl_gemm_tc_cols, _p(x), _p(w), _p(out), _dt(out), M, N, K, _stream())
 
 
+# Which matrix-product kernel takes a bfloat16 product of M rows by N columns. The thresholds were measured on a
+# B200 (148 SMs) and live here, beside the kernels they choose between, not in the parts that call them.
+SKINNY_MAX_ROWS = 64                  # up to here W streams through registers (faster than 128-row tcgen05 tiles at 64 rows)
+TC_MIN_COLUMNS_FEW_ROWS = 4096        # 17..64 rows: wide products have enough 128-column tiles for TMA to stream W at full rate
+TC_MIN_COLUMNS_VERY_FEW_ROWS = 32768  # an output head: up to 64 rows take the kernel made for it; without it 128-row tiles win from 9 rows
+PAIR_MIN_ROWS = 256                   # from here on pairs of SMs share 256 x 256 tiles (tcgen05 cta_group::2)
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+         epilogue: int = EPI_NONE, fast: bool = True) -> None:
+    """out = epilogue(x @ w.T) by the kernel that suits the operands: float32 operands, operands the tensor-core
+    kernels cannot take, and `fast=False` run the plain CUDA-core kernel; bfloat16 operands a tensor-core kernel
+    chosen by the number of rows (and, for few rows, of columns)."""
+    if not (fast and gemm_skinny_supported(x, w)):
+        gemm_plain(x, w, out, bias, epilogue)
+        return
+    M, N = x.shape[0], out.shape[1]
+    few_rows_tc = (M > 16 and N >= TC_MIN_COLUMNS_FEW_ROWS) or (M > 8 and N >= TC_MIN_COLUMNS_VERY_FEW_ROWS)
+    if (N >= TC_MIN_COLUMNS_VERY_FEW_ROWS and bias is None and epilogue == EPI_NONE and M <= 64
+            and gemm_tc_cols_supported(x, w)):
+        gemm_tc_cols(x, w, out)                # an output head at decode time: W streams once, as the M side of the product
+    elif M <= SKINNY_MAX_ROWS and not few_rows_tc:
+        gemm_skinny(x, w, out, bias, epilogue)
+    elif M < PAIR_MIN_ROWS:
+        gemm_tc(x, w, out, bias, epilogue)
+    else:
+        gemm_tc_pair(x, w, out, bias, epilogue)
+
+
 def check_status() -> None:
     """Raises if a tensor-core block gave up on one of its bounded waits since the last check. Synchronises."""
     for name, fn in (("bl_gemm_tc", _lib().bl_gemm_tc_status), ("bl_gemm_tc_pair", _lib().bl_gemm_tc_pair_status),
