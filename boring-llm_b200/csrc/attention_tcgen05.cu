@@ -35,22 +35,35 @@ namespace {
 
 constexpr const char* WHO = "bl_attention_prefill_tc";
 
-constexpr int DH = 64;                 // head size
 constexpr int ROWS = 128;              // query rows per block
 constexpr int KBLK = 128;              // keys per block
 constexpr int PAGE = 16;
-constexpr int PAGES = KBLK / PAGE;     // TMA boxes per tensor and block
-constexpr int PAGE_BYTES = PAGE * DH * 2;
-constexpr int THREADS = 2 * ROWS + 96;       // eight row warps (two groups of four), one warp that issues the MMAs, two that copy
-constexpr int Q_BYTES = ROWS * DH * 2, KV_BYTES = KBLK * DH * 2;
-constexpr int MERGE_BYTES = ROWS * 33 * 4;                           // half of a group's output at the merge, rows padded to 33 floats
-constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_MERGE = OFF_V + 2 * KV_BYTES;
-constexpr int OFF_XCH = OFF_MERGE + 2 * MERGE_BYTES;                         // the groups' maxima and sums at the merge: 4 x 128 floats
-constexpr int OFF_BARS = OFF_XCH + 4 * ROWS * 4;
-constexpr int SMEM_BYTES = OFF_BARS + 256;
-constexpr int TMEM_COLS = 512;         // per group: scores 128 columns, P (bfloat16 pairs) 64, share of the output 64
+constexpr int PAGES = KBLK / PAGE;     // pages per key block
+constexpr int ATOM_BYTES = ROWS * 128; // a 128-row operand tile lies in shared memory as atoms of 64 elements (128 bytes) a row
+constexpr int TMEM_COLS = 512;         // scores 2 x 128 columns, P (bfloat16 pairs) 2 x 64, shares of the output 128
 constexpr int COL_P = 2 * KBLK, COL_O = COL_P + 2 * (KBLK / 2);
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+// The two shapes that are built. Head size 64: two groups of row warps, each with its own share of the output (2 x 64
+// columns of tensor memory). Head size 128: one group (a row's 128 outputs, its scores and the 2^x batch fill a
+// thread's registers; twice the tensor-core work per score leaves the single group less to wait for), one share of
+// the output of 128 columns, written by block i + 1 only after block i's has been taken (the row warps take it before
+// they post P of block i + 1). Keys, values and q lie as DH / 64 atoms of 64 dimensions.
+template <int DH_, int GROUPS_>
+struct Shape {
+    static constexpr int DH = DH_, GROUPS = GROUPS_;
+    static constexpr int ATOMS = DH / 64;
+    static constexpr int PAGE_BYTES = PAGE * DH * 2;
+    static constexpr int THREADS = GROUPS * ROWS + 96;   // the row warps, one warp that issues the MMAs, two that copy
+    static constexpr int Q_BYTES = ROWS * DH * 2, KV_BYTES = KBLK * DH * 2;
+    static constexpr int MERGE_ROW = DH / 2 + 1;                          // half of a group's output at the merge, rows padded by one float
+    static constexpr int MERGE_BYTES = GROUPS == 2 ? ROWS * MERGE_ROW * 4 : 0;
+    static constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_MERGE = OFF_V + 2 * KV_BYTES;
+    static constexpr int OFF_XCH = OFF_MERGE + 2 * MERGE_BYTES;          // the groups' maxima and sums at the merge: 4 x 128 floats
+    static constexpr int OFF_BARS = OFF_XCH + 4 * ROWS * 4;
+    static constexpr int SMEM_BYTES = OFF_BARS + 256;
+    static_assert(DH % 64 == 0 && COL_O + GROUPS * DH <= TMEM_COLS && SMEM_BYTES <= 227 * 1024, "shape does not fit an SM");
+};
 
 __device__ int g_status = 0;           // 0 = fine; else the code of the first wait that ran out
 
@@ -117,7 +130,7 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 // kind::f16 instruction descriptors: D 32-bit, A and B bfloat16, N >> 3 at bit 17, M >> 4 at bit 24;
 // bit 16 set: B is MN-major (V lies keys x head size).
 constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(KBLK >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
-constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(DH >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);   // 64 dimensions of the head at a time
 
 // 2^x on the special-function unit (about 2 ulp; 2^-inf = 0, tiny results flush to 0)
 __device__ __forceinline__ float bl_ex2(float x) {
@@ -130,9 +143,14 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
+template <class S>
+__global__ void __launch_bounds__(S::THREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const Params p) {
+    constexpr int DH = S::DH, GROUPS = S::GROUPS, ATOMS = S::ATOMS, PAGE_BYTES = S::PAGE_BYTES;
+    constexpr int Q_BYTES = S::Q_BYTES, KV_BYTES = S::KV_BYTES, MERGE_BYTES = S::MERGE_BYTES, MERGE_ROW = S::MERGE_ROW;
+    constexpr int OFF_Q = S::OFF_Q, OFF_K = S::OFF_K, OFF_V = S::OFF_V, OFF_MERGE = S::OFF_MERGE, OFF_XCH = S::OFF_XCH;
+    constexpr int OFF_BARS = S::OFF_BARS;
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t base = smem_u32(smem);
     const uint32_t bars = base + OFF_BARS;
@@ -148,7 +166,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BARS + 120);
     float* xch = reinterpret_cast<float*>(smem + OFF_XCH);               // [2 groups][maximum, sum][128 rows]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr int ROW_WARPS = 2 * ROWS / 32;                             // two groups of one thread per row
+    constexpr int ROW_WARPS = GROUPS * ROWS / 32;                        // one thread per row in each group
     const bool issuer = warp == ROW_WARPS;                               // after the row warps: the MMA issuer, then two copy warps
 
     // Blocks start in the order of their index: all heads of the list's last tile, then all heads of the tile before.
@@ -168,7 +186,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         *give_up = (base & 1023u) ? 1 : 0;                               // the swizzled tiles need 1024-byte alignment
         if (base & 1023u) atomicCAS(&g_status, 0, 9);
         mbar_init(full_q, 1);
-        mbar_init(l_ready, 2 * ROWS);
+        mbar_init(l_ready, GROUPS * ROWS);
         for (int i = 0; i < 2; ++i) {
             mbar_init(full_k0 + 8 * i, 1); mbar_init(full_v0 + 8 * i, 1);
             mbar_init(s_done0 + 8 * i, 1); mbar_init(o_done0 + 8 * i, 1);
@@ -210,7 +228,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ok = __all_sync(0xffffffffu, ok);
         if (ok && keys && lane == 0 && nb > 0) {                         // (a tile without rows copies nothing and waits for nothing)
             mbar_expect_tx(full_q, Q_BYTES);
-            tma_load_2d(base + OFF_Q, &map_q, full_q, head * DH, q_begin + tok0);
+#pragma unroll
+            for (int a = 0; a < ATOMS; ++a)
+                tma_load_2d(base + OFF_Q + a * ATOM_BYTES, &map_q, full_q, head * DH + a * 64, q_begin + tok0);
         }
         int page = lane < PAGES && nb > 0 ? page_of(b_begin, lane) : -1;
         for (int i = 0; ok && i < nb; ++i) {
@@ -230,7 +250,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (have) mbar_expect_tx(bar, (uint32_t)__popc(have) * PAGE_BYTES); else mbar_arrive(bar);
             }
             __syncwarp();
-            if (lane < PAGES && page >= 0) tma_load_2d(dst + lane * PAGE_BYTES, map, bar, 0, (page * p.KV + kvh) * PAGE);
+            if (lane < PAGES && page >= 0) {
+#pragma unroll
+                for (int a = 0; a < ATOMS; ++a)                         // 16 keys x 64 dimensions a box
+                    tma_load_2d(dst + a * ATOM_BYTES + lane * (PAGE * 128), map, bar, a * 64, (page * p.KV + kvh) * PAGE);
+            }
             __syncwarp();
             ++loads[st];
             page = page_next;
@@ -244,9 +268,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     } else if (issuer) {
         // ================= one warp: lane 0 issues the MMAs
         auto issue_s = [&](int i) {                                      // S = Q . K^T of the i-th block of this tile
-            const uint64_t a = smem_desc(base + OFF_Q), b = smem_desc(base + OFF_K + (i & 1) * KV_BYTES);
 #pragma unroll
-            for (int k = 0; k < DH / 16; ++k) umma_bf16(tmem + (i & 1) * KBLK, a + 2 * k, b + 2 * k, IDESC_S, k != 0);
+            for (int at = 0; at < ATOMS; ++at) {                         // 64 dimensions of the head an atom, 16 a step
+                const uint64_t a = smem_desc(base + OFF_Q + at * ATOM_BYTES);
+                const uint64_t b = smem_desc(base + OFF_K + (i & 1) * KV_BYTES + at * ATOM_BYTES);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) umma_bf16(tmem + (i & 1) * KBLK, a + 2 * k, b + 2 * k, IDESC_S, (at | k) != 0);
+            }
             umma_commit(s_done0 + 8 * (i & 1));
         };
         if (lane == 0 && ok && nb > 0) {
@@ -272,34 +300,36 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 ok = mbar_wait(full_v0 + 8 * st, par, give_up, 5);
                 if (!ok) break;
                 fence_after_sync();
-                const uint64_t bv = smem_desc(base + OFF_V + st * KV_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < KBLK / 16; ++kk)                  // 16 keys a step: 8 columns of P, two 8-row groups of V
-                    umma_bf16_ts(tmem + COL_O + st * DH, tmem + COL_P + st * (KBLK / 2) + kk * 8,
-                                 bv + (uint64_t)(kk * (2048 >> 4)), IDESC_PV, kk != 0);
+                for (int at = 0; at < ATOMS; ++at) {                     // 64 dimensions of the head at a time
+                    const uint64_t bv = smem_desc(base + OFF_V + st * KV_BYTES + at * ATOM_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < KBLK / 16; ++kk)              // 16 keys a step: 8 columns of P, two 8-row groups of V
+                        umma_bf16_ts(tmem + COL_O + (GROUPS == 2 ? st * DH : 0) + at * 64, tmem + COL_P + st * (KBLK / 2) + kk * 8,
+                                     bv + (uint64_t)(kk * (2048 >> 4)), IDESC_PV, kk != 0);
+                }
                 umma_commit(o_done0 + 8 * st);
             }
         }
         __syncwarp();
     } else {
-        // ================= eight warps in two groups of four: group g takes the key blocks i = g, g + 2, ... of the
-        // tile, a thread of it one query row, with a running maximum, sum and output of the group's own (merged at the
-        // end). While one group is in its exponentials the other reads scores, rescales or waits for its product.
-        const int grp = warp >> 2;
+        // ================= the row warps, in GROUPS groups of four: group g takes the key blocks i = g, g + GROUPS, ...
+        // of the tile, a thread of it one query row, with a running maximum, sum and output of the group's own (merged
+        // at the end). With two groups, one is in its exponentials while the other reads scores, rescales or waits for
+        // its product. Block i has its scores, P, stage of keys and values and barriers at index i & 1.
+        const int grp = GROUPS == 2 ? warp >> 2 : 0;
         const int row = (warp & 3) * 32 + lane;                          // row of the tile = lane of tensor memory
         const bool valid = row < rows_here;
         const int pos = valid ? p_first + row : -1;                      // an invalid row sees nothing
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;     // this warp's 32 lanes of tensor memory
-        const uint32_t t_s = tmem + grp * KBLK + lane_off, t_p = tmem + COL_P + grp * (KBLK / 2) + lane_off,
-                       t_o = tmem + COL_O + grp * DH + lane_off;
-        const uint32_t s_done = s_done0 + 8 * grp, o_done = o_done0 + 8 * grp, p_ready = p_ready0 + 8 * grp, full_v = full_v0 + 8 * grp;
         float o[DH];
 #pragma unroll
         for (int j = 0; j < DH; ++j) o[j] = 0.f;
         float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
-        // out = out * alpha + O of the group's own-th block
-        auto add_output = [&](int own, float alpha) -> bool {
-            bool fine = mbar_wait(o_done, (uint32_t)(own & 1), give_up, 11);
+        // out = out * alpha + O of block `blk`
+        auto add_output = [&](int blk, float alpha) -> bool {
+            const uint32_t t_o = tmem + COL_O + (GROUPS == 2 ? (blk & 1) * DH : 0) + lane_off;
+            bool fine = mbar_wait(o_done0 + 8 * (blk & 1), (uint32_t)((blk >> 1) & 1), give_up, 11);
             fine = __all_sync(0xffffffffu, fine);
             if (!fine) return false;
             fence_after_sync();
@@ -314,9 +344,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             return true;
         };
         int last = -1;                                                   // the group's last block
-        for (int i = grp; i < nb; i += 2) {
-            const int b = b_begin + i;
+        for (int i = grp; i < nb; i += GROUPS) {
+            const int b = b_begin + i, st = i & 1;
             const uint32_t par = (uint32_t)((i >> 1) & 1);
+            const uint32_t t_s = tmem + st * KBLK + lane_off, t_p = tmem + COL_P + st * (KBLK / 2) + lane_off;
+            const uint32_t s_done = s_done0 + 8 * st, p_ready = p_ready0 + 8 * st, full_v = full_v0 + 8 * st;
             ok = mbar_wait(s_done, par, give_up, 8) && ok;
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -356,7 +388,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             m = m_new;
             // The share of the group's block before: its product frees P and the columns of the output, which the
             // product of this block will take. It has had the time of this block's scores and first pass.
-            if (last >= 0 && !add_output(last >> 1, alpha_prev)) { ok = false; break; }
+            if (last >= 0 && !add_output(last, alpha_prev)) { ok = false; break; }
             float sm4[4] = {0.f, 0.f, 0.f, 0.f};
             // Second pass, chunks 3 (still in sb), 2, 1, 0: P = 2^(s * scale - m) as bfloat16 into tensor memory, the A
             // operand of the second product: lane = row, two keys to a 32-bit column, 16 columns a chunk.
@@ -392,12 +424,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (k0 + KBLK - 1 > hi || k0 < lo) {
                 ok = mbar_wait(full_v, par, give_up, 10) && ok;
                 if (ok) {
-                    for (int idx = threadIdx.x & (ROWS - 1); idx < KBLK * 8; idx += ROWS) {   // (key row, 16-byte chunk); a row's chunks stay in the row
-                        const int key = k0 + (idx >> 3);
+                    // (atom, key row, 16-byte chunk); the swizzle keeps a row's chunks in the row
+                    for (int idx = threadIdx.x & (ROWS - 1); idx < ATOMS * KBLK * 8; idx += ROWS) {
+                        const int in_atom = idx % (KBLK * 8);
+                        const int key = k0 + (in_atom >> 3);
                         const int first = key / PAGE * PAGE;
                         const bool copied = !(first > hi || first + PAGE - 1 < lo) && table[first / PAGE] >= 0;
                         if (!copied || key > hi)
-                            *reinterpret_cast<uint4*>(smem + OFF_V + grp * KV_BYTES + (idx << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                            *reinterpret_cast<uint4*>(smem + OFF_V + st * KV_BYTES + (idx / (KBLK * 8)) * ATOM_BYTES + (in_atom << 4)) = make_uint4(0u, 0u, 0u, 0u);
                     }
                 }
             }
@@ -409,14 +443,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             last = i;
         }
         ok = __all_sync(0xffffffffu, ok);
-        if (ok && last >= 0) ok = add_output(last >> 1, alpha_prev);
-        // The groups merge: each finishes half of the head's dimensions, and hands the other half of its output,
-        // with its maximum and sum, to the other group through shared memory.
-        {
-            float* mine = reinterpret_cast<float*>(smem + OFF_MERGE + grp * MERGE_BYTES);          // [row][33]
+        if (ok && last >= 0) ok = add_output(last, alpha_prev);
+        if (GROUPS == 1) {
+            // one group holds the whole row: out = o / l
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok && valid) {
+                const float inv = l > 0.f ? 1.0f / l : 0.f;
+                __nv_bfloat16* dst = p.out + ((size_t)(q_begin + tok0 + row) * p.H + head) * DH;
+#pragma unroll
+                for (int j = 0; j < DH; j += 8)
+                    *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16(o[j] * inv, o[j + 1] * inv), pack_bf16(o[j + 2] * inv, o[j + 3] * inv),
+                                                                    pack_bf16(o[j + 4] * inv, o[j + 5] * inv), pack_bf16(o[j + 6] * inv, o[j + 7] * inv));
+            }
+        } else {
+            // The groups merge: each finishes half of the head's dimensions, and hands the other half of its output,
+            // with its maximum and sum, to the other group through shared memory.
+            float* mine = reinterpret_cast<float*>(smem + OFF_MERGE + grp * MERGE_BYTES);          // [row][MERGE_ROW]
             const float* theirs = reinterpret_cast<const float*>(smem + OFF_MERGE + (grp ^ 1) * MERGE_BYTES);
 #pragma unroll
-            for (int j = 0; j < DH / 2; ++j) mine[row * 33 + j] = grp ? o[j] : o[DH / 2 + j];
+            for (int j = 0; j < DH / 2; ++j) mine[row * MERGE_ROW + j] = grp ? o[j] : o[DH / 2 + j];
             xch[(grp * 2) * ROWS + row] = m;
             xch[(grp * 2 + 1) * ROWS + row] = l;
             mbar_arrive(l_ready);
@@ -431,7 +476,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 const float wa = a * inv, wo = a_o * inv;
                 float r[DH / 2];
 #pragma unroll
-                for (int j = 0; j < DH / 2; ++j) r[j] = (grp ? o[DH / 2 + j] : o[j]) * wa + theirs[row * 33 + j] * wo;
+                for (int j = 0; j < DH / 2; ++j) r[j] = (grp ? o[DH / 2 + j] : o[j]) * wa + theirs[row * MERGE_ROW + j] * wo;
                 __nv_bfloat16* dst = p.out + ((size_t)(q_begin + tok0 + row) * p.H + head) * DH + grp * (DH / 2);
 #pragma unroll
                 for (int j = 0; j < DH / 2; j += 8)
@@ -450,7 +495,30 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
 }  // namespace
 
-extern "C" int bl_attention_prefill_tc_supported(int dh, int page_size) { return dh == DH && page_size == PAGE; }
+extern "C" int bl_attention_prefill_tc_supported(int dh, int page_size) { return (dh == 64 || dh == 128) && page_size == PAGE; }
+
+namespace {
+
+template <class S>
+int launch(const void* q, const void* k_cache, const void* v_cache, const Params& p, int n_tiles, int T, int n_pages, cudaStream_t stream) {
+    CUtensorMap mq, mk, mv;
+    if (bl_make_map_bf16(WHO, &mq, q, T, p.H * S::DH, ROWS, 64)) return 1;
+    if (bl_make_map_bf16(WHO, &mk, k_cache, (long long)n_pages * p.KV * PAGE, S::DH, PAGE, 64)) return 1;
+    if (bl_make_map_bf16(WHO, &mv, v_cache, (long long)n_pages * p.KV * PAGE, S::DH, PAGE, 64)) return 1;
+    static bool configured = false;                                      // per shape
+    if (!configured) {
+        BL_CUDA(cudaFuncSetAttribute(attention_tc_kernel<S>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES));
+        configured = true;
+    }
+    // A block waits (griddepcontrol.wait) before it allocates tensor memory or touches data, so it may be launched
+    // while the kernel before it still runs.
+    BL_CUDA(bl_launch_dependent(attention_tc_kernel<S>, dim3(n_tiles * p.H, 1, 1), dim3(S::THREADS), (size_t)S::SMEM_BYTES, stream,
+                                mq, mk, mv, p));
+    BL_CHECK_LAUNCH("bl_attention_prefill_tc");
+    return 0;
+}
+
+}  // namespace
 
 // tiles[n_tiles][2] = (request, first token of the tile's 128 rows within the request's new tokens); the last
 // entries start first. T: rows of q and out; n_pages: pages of the cache tensors (their first dimension).
@@ -459,32 +527,19 @@ extern "C" int bl_attention_prefill_tc(const void* q, const void* k_cache, const
                                        int n_tiles, void* out, int T, int n_pages, int H, int KV, int dh, int page_size,
                                        int window, float scale, void* stream) {
     if (n_tiles <= 0) return 0;
-    if (dh != DH || page_size != PAGE)
-        BL_FAIL("bl_attention_prefill_tc: head size %d with pages of %d tokens is not built (64 with 16 only)", dh, page_size);
+    if ((dh != 64 && dh != 128) || page_size != PAGE)
+        BL_FAIL("bl_attention_prefill_tc: head size %d with pages of %d tokens is not built (64 or 128 with 16 only)", dh, page_size);
     if (H <= 0 || KV <= 0 || H % KV != 0) BL_FAIL("bl_attention_prefill_tc: %d heads cannot share %d key/value heads", H, KV);
     if (max_pages <= 0 || window < 0 || T <= 0 || n_pages <= 0) BL_FAIL("bl_attention_prefill_tc: bad sizes");
     if (!(scale > 0.f)) BL_FAIL("bl_attention_prefill_tc: the scale of the scores must be positive (got %g)", (double)scale);
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15)
         BL_FAIL("bl_attention_prefill_tc: q, the caches and out must be 16-byte aligned");
-    CUtensorMap mq, mk, mv;
-    if (bl_make_map_bf16(WHO, &mq, q, T, H * DH, ROWS, 64)) return 1;
-    if (bl_make_map_bf16(WHO, &mk, k_cache, (long long)n_pages * KV * PAGE, DH, PAGE, 64)) return 1;
-    if (bl_make_map_bf16(WHO, &mv, v_cache, (long long)n_pages * KV * PAGE, DH, PAGE, 64)) return 1;
+    if ((long long)n_tiles * H > 2147483647LL) BL_FAIL("bl_attention_prefill_tc: %d tiles x %d heads are more blocks than a launch takes", n_tiles, H);
     Params p;
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
     p.tiles = tiles; p.H = H; p.KV = KV; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
-    static bool configured = false;
-    if (!configured) {
-        BL_CUDA(cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        configured = true;
-    }
-    // A block waits (griddepcontrol.wait) before it allocates tensor memory or touches data, so it may be launched
-    // while the kernel before it still runs.
-    if ((long long)n_tiles * H > 2147483647LL) BL_FAIL("bl_attention_prefill_tc: %d tiles x %d heads are more blocks than a launch takes", n_tiles, H);
-    BL_CUDA(bl_launch_dependent(attention_tc_kernel, dim3(n_tiles * H, 1, 1), dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)stream,
-                                mq, mk, mv, p));
-    BL_CHECK_LAUNCH("bl_attention_prefill_tc");
-    return 0;
+    if (dh == 64) return launch<Shape<64, 2>>(q, k_cache, v_cache, p, n_tiles, T, n_pages, (cudaStream_t)stream);
+    return launch<Shape<128, 1>>(q, k_cache, v_cache, p, n_tiles, T, n_pages, (cudaStream_t)stream);
 }
 
 // Reads and clears the status word: 0 when no block has given up on a wait since the last call. Codes name the

@@ -450,31 +450,56 @@ def tc_attention(q, kc, vc, tok_req, cu_q, ctx_len, table, out, H, window, scale
         o.attention_decode(q, kc, vc, cu_q, ctx_len, table, torch.tensor(singles, dtype=torch.int32, device=DEV), 1, out, H, window, scale)
 
 
+@pytest.mark.parametrize("dh", [64, 128])
 @pytest.mark.parametrize("H,KV", [(14, 2), (7, 1), (4, 4)])
-def test_attention_tcgen05_shapes(H, KV):
-    """Prefill attention on tcgen05: portions over an existing cache with offsets off every tile and page size,
-    whole prompts of several key blocks, rows past the end of a tile, several requests in one launch."""
+def test_attention_tcgen05_shapes(H, KV, dh):
+    """Prefill attention on tcgen05, head sizes 64 (two groups of row warps) and 128 (one group, two atoms of 64
+    dimensions): portions over an existing cache with offsets off every tile and page size, whole prompts of several
+    key blocks, rows past the end of a tile, several requests in one launch, portions from 2 to 600 tokens."""
     o = ops()
     assert o.attention_prefill_tc_supported(torch.bfloat16, 64, 16)
-    assert not o.attention_prefill_tc_supported(torch.bfloat16, 128, 16)
+    assert o.attention_prefill_tc_supported(torch.bfloat16, 128, 16)
+    assert not o.attention_prefill_tc_supported(torch.bfloat16, 96, 16)
     assert not o.attention_prefill_tc_supported(torch.float32, 64, 16)
-    attention_case(o, tc_attention, torch.bfloat16, H, KV, 64, [333, 70, 16, 33], [70, 70, 2, 17], 0, 2)
-    attention_case(o, tc_attention, torch.bfloat16, H, KV, 64, [64, 65, 128, 200, 129], [64, 1, 128, 1, 65], 0, 3)
-    attention_case(o, tc_attention, torch.bfloat16, H, KV, 64, [1000, 515, 257], [1000, 300, 129], 0, 4)
+    attention_case(o, tc_attention, torch.bfloat16, H, KV, dh, [333, 70, 16, 33], [70, 70, 2, 17], 0, 2)
+    attention_case(o, tc_attention, torch.bfloat16, H, KV, dh, [64, 65, 128, 200, 129], [64, 1, 128, 1, 65], 0, 3)
+    attention_case(o, tc_attention, torch.bfloat16, H, KV, dh, [1000, 515, 257], [1000, 300, 129], 0, 4)
+    attention_case(o, tc_attention, torch.bfloat16, H, KV, dh, [900, 602, 450, 131], [600, 2, 33, 130], 0, 5)
 
 
-def test_attention_tcgen05_long_prompt():
+@pytest.mark.parametrize("dh", [64, 128])
+def test_attention_tcgen05_long_prompt(dh):
     """Twenty key blocks and ten row blocks: the rings of keys, values, P and output shares wrap around many times,
     and a planted key at position 0 decides the last row."""
     o = ops()
-    attention_case(o, tc_attention, torch.bfloat16, 4, 2, 64, [2500, 1400], [2500, 700], 0, 8)
-    attention_case(o, tc_attention, torch.bfloat16, 2, 1, 64, [3000], [1300], 1100, 9)
+    attention_case(o, tc_attention, torch.bfloat16, 4, 2, dh, [2500, 1400], [2500, 700], 0, 8)
+    attention_case(o, tc_attention, torch.bfloat16, 2, 1, dh, [3000], [1300], 1100, 9)
 
 
+@pytest.mark.parametrize("dh", [64, 128])
 @pytest.mark.parametrize("window", [1, 15, 16, 17, 100, 128, 200])
-def test_attention_tcgen05_window_edges(window):
+def test_attention_tcgen05_window_edges(window, dh):
     o = ops()
-    attention_case(o, tc_attention, torch.bfloat16, 4, 2, 64, [200, 131, 700, 17], [150, 1, 500, 2], window, 6)
+    attention_case(o, tc_attention, torch.bfloat16, 4, 2, dh, [200, 131, 700, 17], [150, 1, 500, 2], window, 6)
+
+
+def test_attention_tcgen05_padded_tile_lists():
+    """The tile list of a step that is replayed is padded with tiles of a request without tokens: such blocks must
+    leave at once and write nothing (no copy may be left in flight when they do)."""
+    o = ops()
+    for dh in (64, 128):
+        s = paged_setup([300, 40, 1], [200, 40, 0], 2, dh, 16, torch.bfloat16, 12)
+        g = torch.Generator().manual_seed(5)
+        s["kc"].copy_(torch.randn(s["kc"].shape, generator=g).to(DEV)); s["vc"].copy_(torch.randn(s["vc"].shape, generator=g).to(DEV))
+        q = torch.randn(240, 4 * dh, generator=g).to(torch.bfloat16).to(DEV)
+        want, got = torch.full_like(q, 7.0), torch.full_like(q, 7.0)
+        tiles = [[0, 0], [0, 128], [1, 0]]
+        padded = [[2, 0]] * 5 + tiles
+        t = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+        o.attention_prefill_tc(q, s["kc"], s["vc"], s["cu_q"], s["ctx_len"], s["table"], t(tiles), want, 4, 0, dh ** -0.5)
+        o.attention_prefill_tc(q, s["kc"], s["vc"], s["cu_q"], s["ctx_len"], s["table"], t(padded), got, 4, 0, dh ** -0.5)
+        o.check_status()
+        assert torch.equal(got, want) and not (got == 7.0).all()
 
 
 def test_attention_mma_is_refused_where_it_is_not_built():
