@@ -124,6 +124,15 @@ int bl_gemm_tc_pair(const void* x, const void* w, const void* bias, int bias_dty
                     int M, int N, int K, int epilogue, void* stream);
 int bl_gemm_tc_pair_status(int* status);
 
+// The same product for shapes with few output tiles: a cluster of up to eight blocks shares a tile of 128 rows and
+// cuts K among its blocks; the partial tiles are added up in block order through distributed shared memory
+// (gemm_tcgen05_splitk.cu). Same contract as bl_gemm_tc. bl_gemm_tc_splitk_split: how many blocks would share a tile
+// (1: K is not cut, the kernel has nothing over bl_gemm_tc).
+int bl_gemm_tc_splitk_split(int M, int N, int K, int epilogue);
+int bl_gemm_tc_splitk(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype,
+                      int M, int N, int K, int epilogue, void* stream);
+int bl_gemm_tc_splitk_status(int* status);
+
 #ifdef __cplusplus
 }
 #endif

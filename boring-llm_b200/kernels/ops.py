@@ -354,6 +354,31 @@ def gemm_tc_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Opti
           M, N, K, epilogue, _stream())
 
 
+def gemm_tc_splitk(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                   epilogue: int = EPI_NONE) -> None:
+    """`gemm_tc` for shapes with few output tiles: clusters of up to eight blocks share a tile and cut K among them,
+    their partial tiles added in block order through distributed shared memory."""
+    M, K = x.shape
+    N = out.shape[1]
+    rows_w = 2 * N if epilogue == EPI_SWIGLU else N
+    _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16, (rows_w, K)); _need(out, "out", None, (M, N))
+    if bias is not None:
+        _need(bias, "bias", None, (N,))
+    _call(_lib().bl_gemm_tc_splitk, _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0, _p(out), _dt(out),
+          M, N, K, epilogue, _stream())
+
+
+_splitk_split = {}
+
+
+def gemm_tc_splitk_split(M: int, N: int, K: int, epilogue: int) -> int:
+    """Blocks that would share a tile of this product in `gemm_tc_splitk` (1: it has nothing over `gemm_tc`)."""
+    key = (-(-M // 128), N, K, epilogue == EPI_SWIGLU)
+    if key not in _splitk_split:
+        _splitk_split[key] = int(_lib().bl_gemm_tc_splitk_split(M, N, K, epilogue))
+    return _splitk_split[key]
+
+
 def gemm_tc_cols_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether `gemm_tc_cols` takes these operands: bfloat16, up to 64 rows, 16-byte aligned, x fits shared memory."""
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
@@ -376,6 +401,8 @@ SKINNY_MAX_ROWS = 64                  # up to here W streams through registers (
 TC_MIN_COLUMNS_FEW_ROWS = 4096        # 17..64 rows: wide products have enough 128-column tiles for TMA to stream W at full rate
 TC_MIN_COLUMNS_VERY_FEW_ROWS = 32768  # an output head: up to 64 rows take the kernel made for it; without it 128-row tiles win from 9 rows
 PAIR_MIN_ROWS = 256                   # from here on pairs of SMs share 256 x 256 tiles (tcgen05 cta_group::2)
+SPLITK_MIN_ROWS, SPLITK_MAX_ROWS = 32, 640   # products with few tiles in this range of rows are cut along K over clusters ...
+SPLITK_LONG_K = 2048                  # ... when K is long (measured: K 4,864 by N 896 gains 2x at 128 rows, 1.25x at 512; K 896 gains only up to 128 rows)
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -386,11 +413,14 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[tor
     if not (fast and gemm_skinny_supported(x, w)):
         gemm_plain(x, w, out, bias, epilogue)
         return
-    M, N = x.shape[0], out.shape[1]
+    M, N, K = x.shape[0], out.shape[1], x.shape[1]
     few_rows_tc = (M > 16 and N >= TC_MIN_COLUMNS_FEW_ROWS) or (M > 8 and N >= TC_MIN_COLUMNS_VERY_FEW_ROWS)
     if (N >= TC_MIN_COLUMNS_VERY_FEW_ROWS and bias is None and epilogue == EPI_NONE and M <= 64
             and gemm_tc_cols_supported(x, w)):
         gemm_tc_cols(x, w, out)                # an output head at decode time: W streams once, as the M side of the product
+    elif (epilogue != EPI_SWIGLU and SPLITK_MIN_ROWS <= M <= SPLITK_MAX_ROWS and (K >= SPLITK_LONG_K or 64 < M <= 128)
+          and gemm_tc_splitk_split(M, N, K, epilogue) >= 2):
+        gemm_tc_splitk(x, w, out, bias, epilogue)   # few tiles and a long K (a down projection): clusters cut K among their blocks
     elif M <= SKINNY_MAX_ROWS and not few_rows_tc:
         gemm_skinny(x, w, out, bias, epilogue)
     elif M < PAIR_MIN_ROWS:
@@ -403,7 +433,8 @@ def check_status() -> None:
     """Raises if a tensor-core block gave up on one of its bounded waits since the last check. Synchronises."""
     for name, fn in (("bl_gemm_tc", _lib().bl_gemm_tc_status), ("bl_gemm_tc_pair", _lib().bl_gemm_tc_pair_status),
                      ("bl_attention_prefill_tc", _lib().bl_attention_prefill_tc_status),
-                     ("bl_gemm_tc_cols", _lib().bl_gemm_tc_cols_status)):
+                     ("bl_gemm_tc_cols", _lib().bl_gemm_tc_cols_status),
+                     ("bl_gemm_tc_splitk", _lib().bl_gemm_tc_splitk_status)):
         v = ctypes.c_int(0)
         _call(fn, ctypes.byref(v))
         if v.value != 0:

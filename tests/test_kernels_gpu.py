@@ -517,14 +517,14 @@ def test_attention_mma_is_refused_where_it_is_not_built():
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (1, 7, 8), (130, 200, 96), (257, 129, 264), (300, 608, 176),
-                                   (2048, 1152, 896), (65, 896, 4864), (500, 320, 200)])
-@pytest.mark.parametrize("pair", [False, True])
+                                   (2048, 1152, 896), (65, 896, 4864), (500, 320, 200), (64, 4864, 896), (512, 896, 448)])
+@pytest.mark.parametrize("pair", [False, True, "splitk"])
 def test_gemm_tc_epilogues(M, N, K, pair):
-    """The tcgen05 products (one block per 128 x 128 tile; a pair of blocks per 256 x 256 tile) against 64-bit
-    arithmetic and against their plain twin: tiles that overhang M, N and K, one k block and seventy-six, every
-    epilogue."""
+    """The tcgen05 products (one block per 128 x 128 tile; a pair of blocks per 256 x 256 tile; a cluster of blocks
+    that cut K among them per 128 x 64 or 128 x 128 tile) against 64-bit arithmetic and against their plain twin: tiles
+    that overhang M, N and K, one k block and seventy-six, every epilogue."""
     o = ops()
-    gemm_tc = o.gemm_tc_pair if pair else o.gemm_tc
+    gemm_tc = o.gemm_tc_splitk if pair == "splitk" else o.gemm_tc_pair if pair else o.gemm_tc
     dtype = torch.bfloat16
     x = (data((M, K), 24) * 0.5).to(dtype)
     w = (data((2 * N, K), 25) * 0.25).to(dtype)
