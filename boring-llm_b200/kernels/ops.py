@@ -402,7 +402,15 @@ TC_MIN_COLUMNS_FEW_ROWS = 4096        # 17..64 rows: wide products have enough 1
 TC_MIN_COLUMNS_VERY_FEW_ROWS = 32768  # an output head: up to 64 rows take the kernel made for it; without it 128-row tiles win from 9 rows
 PAIR_MIN_ROWS = 256                   # from here on pairs of SMs share 256 x 256 tiles (tcgen05 cta_group::2)
 SPLITK_MIN_ROWS, SPLITK_MAX_ROWS = 32, 640   # products with few tiles in this range of rows are cut along K over clusters ...
+SPLITK_VERY_LONG_K = 16384            # ... or, below 32 rows, very long (K 18,944 by N 3,584 at 8 rows: 43 us against 72 us through registers)
+STREAM_MIN_BYTES = 128 << 20          # matrices from this size on stream faster through TMA and tcgen05 than through registers, at any number of rows
 SPLITK_LONG_K = 2048                  # ... when K is long (measured: K 4,864 by N 896 gains 2x at 128 rows, 1.25x at 512; K 896 gains only up to 128 rows)
+
+
+def gemm_streams_better(w: torch.Tensor) -> bool:
+    """Whether a matrix is so large that few rows of x are better served by the TMA-fed tcgen05 kernels than by the
+    kernels that stream W through registers (measured on 272 MB at 8 rows: 4.3 TB/s against 2.6 TB/s)."""
+    return w.numel() * w.element_size() >= STREAM_MIN_BYTES
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -414,12 +422,13 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[tor
         gemm_plain(x, w, out, bias, epilogue)
         return
     M, N, K = x.shape[0], out.shape[1], x.shape[1]
-    few_rows_tc = (M > 16 and N >= TC_MIN_COLUMNS_FEW_ROWS) or (M > 8 and N >= TC_MIN_COLUMNS_VERY_FEW_ROWS)
+    few_rows_tc = ((M > 16 and N >= TC_MIN_COLUMNS_FEW_ROWS) or (M > 8 and N >= TC_MIN_COLUMNS_VERY_FEW_ROWS)
+                   or gemm_streams_better(w))
     if (N >= TC_MIN_COLUMNS_VERY_FEW_ROWS and bias is None and epilogue == EPI_NONE and M <= 64
             and gemm_tc_cols_supported(x, w)):
         gemm_tc_cols(x, w, out)                # an output head at decode time: W streams once, as the M side of the product
-    elif (epilogue != EPI_SWIGLU and SPLITK_MIN_ROWS <= M <= SPLITK_MAX_ROWS and (K >= SPLITK_LONG_K or 64 < M <= 128)
-          and gemm_tc_splitk_split(M, N, K, epilogue) >= 2):
+    elif (epilogue != EPI_SWIGLU and M <= SPLITK_MAX_ROWS and (M >= SPLITK_MIN_ROWS or K >= SPLITK_VERY_LONG_K)
+          and (K >= SPLITK_LONG_K or 64 < M <= 128) and gemm_tc_splitk_split(M, N, K, epilogue) >= 2):
         gemm_tc_splitk(x, w, out, bias, epilogue)   # few tiles and a long K (a down projection): clusters cut K among their blocks
     elif M <= SKINNY_MAX_ROWS and not few_rows_tc:
         gemm_skinny(x, w, out, bias, epilogue)

@@ -51,7 +51,7 @@ class SwiGLU(FeedForward):
     def forward_fused_norm(self, ctx, x, norm) -> bool:
         from .norm import RMSNorm
         if not (ctx.fast and ctx.dtype == torch.bfloat16 and x.shape[0] <= FF_FUSED_MAX_ROWS and isinstance(norm, RMSNorm)
-                and ops.norm_gemm_supported(x, self.w_gate_up)):
+                and ops.norm_gemm_supported(x, self.w_gate_up) and not ops.gemm_streams_better(self.w_gate_up)):
             return False
         act = ctx.empty((x.shape[0], self.hidden))
         ops.norm_gemm(x, norm.weight, norm.eps, self.w_gate_up, act, None, EPI_SWIGLU)
