@@ -187,6 +187,7 @@ def measure_decode(eng, batch, steps, warmup, value_regions=3, e2e_regions=0, ch
         eng.step()
     torch.cuda.synchronize()
     regions = []
+    torch.cuda.profiler.start()               # a profiler started with --profile-from-start off sees the timed steps only
     for _ in range(value_regions):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ctx_a = sum(len(r.prompt) + len(r.output) for r in reqs) / batch
@@ -199,6 +200,7 @@ def measure_decode(eng, batch, steps, warmup, value_regions=3, e2e_regions=0, ch
         torch.cuda.synchronize()
         ctx_b = sum(len(r.prompt) + len(r.output) for r in reqs) / batch
         regions.append((e0.elapsed_time(e1), launches, (ctx_a + ctx_b) / 2))
+    torch.cuda.profiler.stop()
     ms, launches, ctx = sorted(regions)[len(regions) // 2]
     out.update(tokens_per_s=batch * steps / (ms / 1e3), ms_per_step=ms / steps, launches=launches, mean_ctx=ctx,
                region_ms=[round(r[0], 3) for r in regions])

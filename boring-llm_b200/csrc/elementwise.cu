@@ -92,18 +92,31 @@ __global__ void rmsnorm_kernel(const float* x /* written by the kernel before: n
 // values stays in registers between the sum of squares and the scaling; nothing is shared between warps, so
 // there is no barrier. A lane adds its squares in index order and the warp's sum is a fixed butterfly: the
 // result of a row depends only on d.
+constexpr int NORM_ROWS_PER_BLOCK = 2;      // small blocks: a few hundred rows still spread over every SM
 template <typename TY>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(32 * NORM_ROWS_PER_BLOCK)
 rmsnorm_rows_kernel(const float* x /* written by the kernel before: no read-only cache */,
                     const int* __restrict__ row_idx, const void* __restrict__ w, int w_dtype, TY* __restrict__ y,
                     int rows, int d, float eps) {
     bl_pdl_trigger();
-    bl_pdl_wait();
     const int lane = threadIdx.x & 31;
-    const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int r = blockIdx.x * NORM_ROWS_PER_BLOCK + (threadIdx.x >> 5);
+    constexpr int NB = 8;
+    // the norm's weights do not depend on the kernel before: a row of up to NB * 128 values has them in registers
+    // before the wait
+    const bool single = d <= NB * 128;
+    float4 wv[NB];
+    if (single) {
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            const int k = j * 128 + lane * 4;
+            wv[j] = k < d ? make_float4(bl_load_any(w, w_dtype, k), bl_load_any(w, w_dtype, k + 1), bl_load_any(w, w_dtype, k + 2),
+                                        bl_load_any(w, w_dtype, k + 3)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    bl_pdl_wait();
     if (r >= rows) return;
     const float* src = x + (size_t)(row_idx ? row_idx[r] : r) * d;
-    constexpr int NB = 8;
     float4 v[NB];
     auto load_batch = [&](int k0) {
 #pragma unroll
@@ -112,7 +125,6 @@ rmsnorm_rows_kernel(const float* x /* written by the kernel before: no read-only
             v[j] = k < d ? *reinterpret_cast<const float4*>(src + k) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     };
-    const bool single = d <= NB * 128;
     float ss = 0.f;
     for (int k0 = 0; k0 < d; k0 += NB * 128) {
         load_batch(k0);
@@ -128,8 +140,10 @@ rmsnorm_rows_kernel(const float* x /* written by the kernel before: no read-only
         for (int j = 0; j < NB; ++j) {
             const int k = k0 + j * 128 + lane * 4;
             if (k >= d) continue;
-            const float o0 = v[j].x * inv * bl_load_any(w, w_dtype, k), o1 = v[j].y * inv * bl_load_any(w, w_dtype, k + 1);
-            const float o2 = v[j].z * inv * bl_load_any(w, w_dtype, k + 2), o3 = v[j].w * inv * bl_load_any(w, w_dtype, k + 3);
+            const float4 ww = single ? wv[j] : make_float4(bl_load_any(w, w_dtype, k), bl_load_any(w, w_dtype, k + 1),
+                                                              bl_load_any(w, w_dtype, k + 2), bl_load_any(w, w_dtype, k + 3));
+            const float o0 = v[j].x * inv * ww.x, o1 = v[j].y * inv * ww.y;
+            const float o2 = v[j].z * inv * ww.z, o3 = v[j].w * inv * ww.w;
             if (sizeof(TY) == 4) {
                 *reinterpret_cast<float4*>(dst + k) = make_float4(o0, o1, o2, o3);
             } else {
@@ -151,9 +165,9 @@ extern "C" int bl_rmsnorm(const float* x, const int* row_idx, const void* w, int
     cudaStream_t s = (cudaStream_t)stream;
     const bool wide = d % 4 == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0;      // 16-byte loads and stores of whole rows
     if (wide && y_dtype == BL_F32)
-        BL_CUDA(bl_launch_dependent(rmsnorm_rows_kernel<float>, dim3((rows + 7) / 8), dim3(256), 0, s, x, row_idx, w, w_dtype, (float*)y, rows, d, eps));
+        BL_CUDA(bl_launch_dependent(rmsnorm_rows_kernel<float>, dim3((rows + NORM_ROWS_PER_BLOCK - 1) / NORM_ROWS_PER_BLOCK), dim3(32 * NORM_ROWS_PER_BLOCK), 0, s, x, row_idx, w, w_dtype, (float*)y, rows, d, eps));
     else if (wide)
-        BL_CUDA(bl_launch_dependent(rmsnorm_rows_kernel<__nv_bfloat16>, dim3((rows + 7) / 8), dim3(256), 0, s, x, row_idx, w, w_dtype, (__nv_bfloat16*)y, rows, d, eps));
+        BL_CUDA(bl_launch_dependent(rmsnorm_rows_kernel<__nv_bfloat16>, dim3((rows + NORM_ROWS_PER_BLOCK - 1) / NORM_ROWS_PER_BLOCK), dim3(32 * NORM_ROWS_PER_BLOCK), 0, s, x, row_idx, w, w_dtype, (__nv_bfloat16*)y, rows, d, eps));
     else if (y_dtype == BL_F32)
         BL_CUDA(bl_launch_dependent(rmsnorm_kernel<float>, dim3(rows), dim3(128), 0, s, x, row_idx, w, w_dtype, (float*)y, d, eps));
     else
