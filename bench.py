@@ -250,6 +250,8 @@ def prefill_timed(eng, portions, reps=5):
         toks = random_prompt(vocab, PREFILL_TOKENS, 7000 + i)
         rid = f"prefill{i}"
         torch.cuda.synchronize()
+        if i == reps + 1:
+            torch.cuda.profiler.start()       # a profiler started with --profile-from-start off sees the last run only
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0 = time.perf_counter()
         e0.record()
@@ -261,6 +263,8 @@ def prefill_timed(eng, portions, reps=5):
         e1.record()
         torch.cuda.synchronize()
         t1 = time.perf_counter()
+        if i == reps + 1:
+            torch.cuda.profiler.stop()
         eng.runner.check_kernels()
         eng.runner.free_request(rid)
         if i >= 2:
@@ -283,6 +287,9 @@ def mixed_timed(eng, n_decoding=63, arrivals=4):
         new = eng.add_request(random_prompt(vocab, PREFILL_TOKENS, 9000 + a), SamplingParams(n_predict=4, ignore_eos=True))
         for s in range(PREFILL_TOKENS // PORTION):
             torch.cuda.synchronize()
+            last = a == arrivals - 1 and s == PREFILL_TOKENS // PORTION - 2
+            if last:
+                torch.cuda.profiler.start()   # a profiler started with --profile-from-start off sees this step only
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             t0 = time.perf_counter()
             e0.record()
@@ -290,6 +297,8 @@ def mixed_timed(eng, n_decoding=63, arrivals=4):
             e1.record()
             torch.cuda.synchronize()
             t1 = time.perf_counter()
+            if last:
+                torch.cuda.profiler.stop()
             if a >= 2:                                          # the first two arrivals' steps meet and capture their shapes
                 rec.append((e0.elapsed_time(e1), (t1 - t0) * 1e3))
         assert new.num_computed >= PREFILL_TOKENS
