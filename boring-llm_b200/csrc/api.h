@@ -41,6 +41,9 @@ int bl_attention_plain(const void* q, const void* k_cache, const void* v_cache, 
                        int max_pages, void* out, int T, int H, int KV, int dh, int page_size,
                        int window, float scale, void* stream);
 
+// x[r, :] += v[:] for every row of the 32-bit residual stream (the bias of a projection that adds into it).
+int bl_add_row_vector(float* x, const void* v, int v_dtype, int rows, int d, void* stream);
+
 // out_ids[r] = index of the first maximum of logits[r, :].
 int bl_argmax(const float* logits, int* out_ids, int rows, int vocab, void* stream);
 

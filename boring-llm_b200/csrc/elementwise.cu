@@ -354,3 +354,27 @@ extern "C" int bl_stamp(unsigned long long* buf, int slot, void* stream) {
     BL_CHECK_LAUNCH("bl_stamp");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// x[r, :] += v for every row: the bias of a projection whose product is added into the 32-bit residual stream
+// (the product kernels' residual epilogue adds the product; the bias is added once, by this kernel, before it:
+// the reference adds a linear layer's bias after its product, src/math.br:84-93, and the sum of three terms does
+// not depend on that order beyond rounding).
+__global__ void add_row_vector_kernel(float* x, const void* __restrict__ v, int v_dtype, int rows, int d) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    const size_t n = (size_t)rows * d;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        x[i] += bl_load_any(v, v_dtype, i % d);
+}
+
+extern "C" int bl_add_row_vector(float* x, const void* v, int v_dtype, int rows, int d, void* stream) {
+    if (rows <= 0) return 0;
+    if (d <= 0) BL_FAIL("bl_add_row_vector: bad width %d", d);
+    if (v_dtype != BL_F32 && v_dtype != BL_BF16) BL_FAIL("bl_add_row_vector: unknown dtype %d", v_dtype);
+    const size_t n = (size_t)rows * d;
+    const int blocks = (int)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
+    BL_CUDA(bl_launch_dependent(add_row_vector_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, v, v_dtype, rows, d));
+    BL_CHECK_LAUNCH("bl_add_row_vector");
+    return 0;
+}

@@ -145,6 +145,13 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
           rows, d, ctypes.c_float(eps), _stream())
 
 
+def add_row_vector(x: torch.Tensor, v: torch.Tensor) -> None:
+    """x[r] += v for every row of the 32-bit residual stream."""
+    rows, d = x.shape
+    _need(x, "x", torch.float32); _need(v, "v", None, (d,))
+    _call(_lib().bl_add_row_vector, _p(x), _p(v), _dt(v), rows, d, _stream())
+
+
 def gemm_plain(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
                epilogue: int = EPI_NONE) -> None:
     """out = epilogue(x @ w.T) on CUDA cores with 32-bit accumulation."""

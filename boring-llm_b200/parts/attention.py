@@ -107,13 +107,12 @@ class GQAAttention(Mixer):
         super().__init__(names)
         if n_heads % n_kv_heads != 0:
             raise ValueError(f"{n_heads} query heads cannot share {n_kv_heads} key/value heads")
-        if out_bias:
-            raise NotImplementedError("an output-projection bias is not supported")
+        self.out_bias = bool(out_bias)
         self.dim, self.H, self.KV, self.dh = dim, n_heads, n_kv_heads, head_dim
         self.rotary = rotary if rotary is not None else RotaryTable(head_dim, 10000.0, n_rot=0)
         self.qkv_bias, self.window = qkv_bias, int(window)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
-        self.w_qkv = self.b_qkv = self.wo = None
+        self.w_qkv = self.b_qkv = self.wo = self.bo = None
 
     def local_specs(self):
         s = {"wq": TensorSpec((self.H * self.dh, self.dim), MATRIX),
@@ -123,6 +122,8 @@ class GQAAttention(Mixer):
         if self.qkv_bias:
             s.update({"bq": TensorSpec((self.H * self.dh,), BIAS), "bk": TensorSpec((self.KV * self.dh,), BIAS),
                       "bv": TensorSpec((self.KV * self.dh,), BIAS)})
+        if self.out_bias:                       # read per file in the reference (src/model.br:500, 1328)
+            s["bo"] = TensorSpec((self.dim,), BIAS)
         return s
 
     def place(self, local, dtype, device):
@@ -133,6 +134,8 @@ class GQAAttention(Mixer):
             if any(t.dtype == torch.float32 for t in b):
                 b = [t.to(torch.float32) for t in b]
             self.b_qkv = to_device_vector(torch.cat(b, dim=0), dtype, device)
+        if self.out_bias:
+            self.bo = to_device_vector(local["bo"], dtype, device)
         self.rotary.to(device)
 
     def cache_spec(self):
@@ -150,6 +153,12 @@ class GQAAttention(Mixer):
                           v_cache if write_cache else None, self.H, self.KV, self.dh, self.rotary.pair_layout)
         attn = ctx.empty((T, self.H * self.dh))
         self.attend(ctx, q, k_cache, v_cache, table, attn)
+        self.project_out(ctx, attn, residual)
+
+    def project_out(self, ctx, attn, residual):
+        """residual += attn . Wo^T (+ bo)."""
+        if self.out_bias:
+            ops.add_row_vector(residual, self.bo)
         linear(ctx, attn, self.wo, residual, None, EPI_RESIDUAL)
 
     def forward_fused_norm(self, ctx, x, norm, cache_layer, write_cache=True) -> bool:
@@ -167,7 +176,7 @@ class GQAAttention(Mixer):
                           self.rotary.pair_layout)
         attn = ctx.empty((T, self.H * self.dh))
         self.attend(ctx, q, k_cache, v_cache, table, attn)
-        linear(ctx, attn, self.wo, x, None, EPI_RESIDUAL)
+        self.project_out(ctx, attn, x)
         return True
 
     def plan_step(self, q_lens, ctx_lens, filler=None):

@@ -9,7 +9,15 @@ import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
-# Tiny configurations of the architecture that differ in every size and option.
+# Tiny configurations of the architecture that differ in every size and option. A and B have the layer sizes of the
+# benchmark description's two tiny configurations (2 layers / hidden 64 / 4:2 heads of 16 / feed-forward 128 / vocabulary
+# 256 / theta 1e4 / eps 1e-6 / tied; 3 layers / 96 / 3:1 heads of 32 / 200 / 320 / theta 1e6 / eps 1e-5 / separate head);
+# they differ from it in two things, on purpose: max_position_embeddings is 512 instead of 128 / 256, so that the
+# replay traces can hold prompts of several pages plus 300 decoded tokens, and the replay tests draw weights with
+# std 0.25 instead of 0.02, which makes attention sharp enough for a lost key to show (the generation tests and the
+# tests against the pure 64-bit implementation use the description's 0.02; its workloads, prompts of 7 / 16 / 33 tokens
+# with 8 greedy tokens and prompts of 1 / 5 / 19 / 64 tokens in portions of 8 with 12 tokens at temperature 0 and 0.8,
+# are those of tests/test_generate_gpu.py).
 TINY = {
     # 2 layers, 4 heads in 2 groups, head 16, tied output head, theta 1e4, eps 1e-6, no window
     "A": dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=2, hidden_size=64,
