@@ -31,3 +31,46 @@ def test_the_tile_with_the_most_keys_is_last_in_the_list():
     assert len(tiles) == 16 + 3
     assert [-(-k // 128) for k in keys] == sorted(-(-k // 128) for k in keys)
     assert tiles[-1][0] == 2                                         # 5000 keys: launched first
+
+
+def test_a_plan_for_a_replayed_step_has_sizes_that_its_shape_determines():
+    """The attention's step plan (host side). For a step that runs once the lists are exact; for a step that is
+    captured and replayed they are padded to multiples of 8 with entries of the request without tokens, the longest
+    context of the single-token requests is rounded up to a power of two, and two batches with the same padded lists
+    have the same shape (they may share a captured graph) although their contents differ."""
+    from boring_llm_b200.parts import attention
+    from boring_llm_b200.parts.attention import attention_plan
+    q_lens, ctx_lens = [1, 130, 1, 70, 1], [900, 400, 33, 70, 2047]
+    exact = attention_plan(q_lens, ctx_lens)
+    assert exact.arrays["singles"].tolist() == [0, 2, 4] and exact.host["longest_single"] == 2047
+    assert exact.arrays["tiles64"].tolist() == [[1, 0], [1, 64], [1, 128], [3, 0], [3, 64]]
+    assert exact.arrays["tiles128"].shape == (0, 2)                                        # 200 prompt tokens: below the threshold
+    assert exact.shape == (5, 0, 3, 2047)
+    # padded: two fillers behind the batch (indices 5 and 6), entries point at the last
+    padded = attention_plan(q_lens + [0, 0], ctx_lens + [1, 1], filler=6)
+    assert padded.arrays["singles"].tolist() == [0, 2, 4, 6, 6, 6, 6, 6] and padded.host["longest_single"] == 2048
+    assert padded.arrays["tiles64"].tolist() == [[1, 0], [1, 64], [1, 128], [3, 0], [3, 64], [6, 0], [6, 0], [6, 0]]
+    assert padded.shape == (8, 0, 8, 2048)
+    other = attention_plan([1, 1, 129, 66, 1, 1, 0, 0], [1500, 2, 129, 100, 1025, 7, 1, 1], filler=7)
+    assert other.shape == padded.shape and other.arrays["singles"].tolist() != padded.arrays["singles"].tolist()
+    # many prompt tokens: the 128-row tiles too, padded at the FRONT (the kernel starts from the end of the list)
+    old = attention.PREFILL_TC_MIN_TOKENS
+    try:
+        attention.PREFILL_TC_MIN_TOKENS = 256
+        big = attention_plan([300, 1, 0], [1000, 50, 1], filler=2)
+    finally:
+        attention.PREFILL_TC_MIN_TOKENS = old
+    t128 = big.arrays["tiles128"].tolist()
+    assert len(t128) == 8 and t128[:5] == [[2, 0]] * 5 and sorted(t128[5:]) == [[0, 0], [0, 128], [0, 256]]
+    assert t128[-1] == [0, 256]                                                            # the tile with the most keys starts first
+    for plan in (exact, padded, big):
+        assert all(a.dtype.name == "int32" for a in plan.arrays.values())
+
+
+def test_parts_collect_one_plan_per_key():
+    """`collect_plans` walks a model's parts and keeps one plan per key: 24 attention layers share one."""
+    import boring_llm_b200 as b
+    import helpers
+    model = b.build_model(b.Qwen2Config.from_dict(helpers.TINY["B"]))
+    plans = model.collect_plans([1, 5], [9, 5])
+    assert list(plans) == ["paged attention"] and plans["paged attention"].arrays["singles"].tolist() == [0]

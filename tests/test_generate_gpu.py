@@ -189,3 +189,40 @@ def test_a_failed_step_with_another_one_ahead_leaves_scheduler_and_cache_in_step
     s = eng.stats()
     assert s["live_requests"] == 0 and s["pages_in_use"] == [0]
     assert eng.generate(prompts, n_predict=12, ignore_eos=True) == want
+
+
+def test_an_engine_from_random_weights_in_memory_equals_one_from_the_folder(tmp_path):
+    """`Engine.from_random` builds the model on the device without a file; `write_random_model` + `Engine(dir)` go through
+    the file: same configuration and seed, same tokens (greedy and sampled), in both dtypes."""
+    from boring_llm_b200 import Engine, EngineOptions, Qwen2Config, write_random_model
+    cfg = Qwen2Config.from_dict(helpers.TINY["B"])
+    prompts = [helpers.random_tokens(320, n, 40 + n) for n in (3, 18)]
+    for dtype in ("bfloat16", "float32"):
+        d = str(tmp_path / dtype)
+        write_random_model(d, cfg, 17, dtype, 0.05)
+        opts = dict(dtype=dtype, ctx_size=64, max_num_seqs=2, max_tokens=128)
+        a = Engine(d, **opts)
+        b = Engine.from_random(cfg, 17, EngineOptions(**opts), std=0.05)
+        for kw in (dict(), dict(temperature=0.7, seed=5)):
+            assert a.generate(prompts, n_predict=10, ignore_eos=True, **kw) == b.generate(prompts, n_predict=10, ignore_eos=True, **kw)
+
+
+def test_captured_steps_are_dropped_least_recently_used_first(model_folders, monkeypatch):
+    """With room for only three captured general steps, a stream of differently shaped steps keeps capturing and
+    dropping graphs; every request still gets the tokens it gets without any captured step."""
+    from boring_llm_b200 import Engine
+    from boring_llm_b200.engine import runner as runner_module
+    monkeypatch.setattr(runner_module, "STEP_GRAPH_CACHE", 3)
+    d = model_folders("A", "bfloat16", 0.02)
+    prompts = [helpers.random_tokens(256, n, 300 + n) for n in (5, 37, 18, 61, 9, 44, 23, 70)]
+    kw = dict(dtype="bfloat16", ctx_size=128, max_num_seqs=3, max_tokens=512, prefill_chunk=16, max_num_batched_tokens=24)
+    plain_engine = Engine(d, cuda_graphs=False, **kw)
+    want = plain_engine.generate(prompts, n_predict=6, ignore_eos=True)
+    eng = Engine(d, step_graph_after=1, **kw)
+    got = eng.generate(prompts, n_predict=6, ignore_eos=True)
+    assert len(eng.runner._step_graphs) <= 3 and eng.runner.graph_steps > 10
+    for p, o in zip(prompts, got):
+        check_greedy(d, p, o, "bfloat16")
+    same = sum(a == b for x, y in zip(want, got) for a, b in zip(x, y))
+    assert same >= 0.9 * 6 * len(prompts)              # (decode graphs cut their attention slices for a bound: rounding may differ)
+    eng.runner.check_kernels()
