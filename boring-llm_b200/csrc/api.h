@@ -81,8 +81,10 @@ int bl_attention_prefill_tc(const void* q, const void* k_cache, const void* v_ca
 int bl_attention_prefill_tc_status(int* status);
 // Blocks of bl_attention_decode that the current device holds at once for this head size (0: not built).
 int bl_attention_decode_resident_blocks(int dh);
-// Decode shape: reqs[n] = requests with one new token; their keys are cut into n_splits slices (up to 256) that
-// the last block to finish merges. scratch: bl_attention_decode_scratch_floats(n, H, dh, n_splits) floats (none for one slice).
+// Decode shape: reqs[n] = requests with one new token; their keys are cut into n_splits slices. With scratch == null
+// (up to 16 slices) the slices of a request are the blocks of one thread-block cluster and merge their partial results
+// through distributed shared memory; with scratch (up to 256 slices) the last block to finish merges them from
+// scratch: bl_attention_decode_scratch_floats(n, H, dh, n_splits) floats (none for one slice).
 long long bl_attention_decode_scratch_floats(int n, int H, int dh, int n_splits);
 // counters: n * KV * ceil((H / KV) / 16) ints that are zero at the call and zero again when it is done.
 int bl_attention_decode(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,

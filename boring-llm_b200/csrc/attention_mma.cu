@@ -66,6 +66,26 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
+constexpr int MAX_CLUSTER_SPLITS = 16;     // slices merged through distributed shared memory (a cluster of 16 needs the non-portable size)
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t peer_shared(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t a) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ float2 ld_cluster_f2(uint32_t a) {
+    float2 v;
+    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a) : "memory");
+    return v;
+}
+
 template <int DH>
 struct Tiles {
     static constexpr int ROW = DH + PAD;
@@ -430,6 +450,8 @@ attention_mma_kernel(const AttnParams p) {
     __syncthreads();
     const int rows_here = min(16, (kvh + 1) * G - head0);
     const int q_tok = q_begin;
+    float* cp_ml = sl + 4 * 16;                                   // [16 rows][max, sum] of this slice, for the cluster's merge
+    float* cp_o = cp_ml + 32;                                     // [16 rows][DH]
     constexpr int D4 = DH / 4;
     if (q_len > 0) {
         for (int i = threadIdx.x; i < rows_here * D4; i += THREADS) {
@@ -448,6 +470,9 @@ attention_mma_kernel(const AttnParams p) {
                 const float inv = L > 0.f ? 1.0f / L : 0.f;
                 *reinterpret_cast<uint2*>(p.out + ((size_t)q_tok * p.H + hd) * DH + d) =
                     make_uint2(pack_bf16(O.x * inv, O.y * inv), pack_bf16(O.z * inv, O.w * inv));
+            } else if (p.part_o == nullptr) {                             // the slices are the blocks of one cluster: the partial result stays here
+                *reinterpret_cast<float4*>(cp_o + row * DH + d) = O;
+                if (d == 0) *reinterpret_cast<float2*>(cp_ml + row * 2) = make_float2(M, L);
             } else {
                 const size_t slot = ((size_t)blockIdx.z * p.H + hd) * p.n_splits + split;
                 *reinterpret_cast<float4*>(p.part_o + slot * DH + d) = O;
@@ -456,6 +481,42 @@ attention_mma_kernel(const AttnParams p) {
         }
     }
     if (p.n_splits == 1 || q_len <= 0) return;
+    if (p.part_o == nullptr) {
+        // The slices of this (request, head group) are the blocks of one cluster, in slice order. Their partial results
+        // meet in distributed shared memory: no scratch in global memory, no fence, no ticket. Every block finishes a
+        // share of the (row, four dimensions) items: out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), slices
+        // added in slice order (FlashDecodeCombineKernel, src/math_gpu.br:3597-3631).
+        cluster_sync_all();                                           // every slice's partial result is written
+        const uint32_t ml_base = (uint32_t)__cvta_generic_to_shared(cp_ml), o_base = (uint32_t)__cvta_generic_to_shared(cp_o);
+        for (int i = split + (int)threadIdx.x * p.n_splits; i < rows_here * D4; i += THREADS * p.n_splits) {
+            const int row = i / D4, d = (i % D4) * 4;
+            float2 ml[MAX_CLUSTER_SPLITS];
+            float4 po[MAX_CLUSTER_SPLITS];
+#pragma unroll
+            for (int s2 = 0; s2 < MAX_CLUSTER_SPLITS; ++s2) {             // all loads on their way before any is used
+                if (s2 >= p.n_splits) break;
+                ml[s2] = ld_cluster_f2(peer_shared(ml_base + (uint32_t)(row * 2) * 4u, (uint32_t)s2));
+                po[s2] = ld_cluster_f4(peer_shared(o_base + (uint32_t)(row * DH + d) * 4u, (uint32_t)s2));
+            }
+            float M = -INFINITY;
+#pragma unroll
+            for (int s2 = 0; s2 < MAX_CLUSTER_SPLITS; ++s2) { if (s2 >= p.n_splits) break; M = fmaxf(M, ml[s2].x); }
+            float L = 0.f;
+            float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int s2 = 0; s2 < MAX_CLUSTER_SPLITS; ++s2) {
+                if (s2 >= p.n_splits) break;
+                const float f = ml[s2].x == -INFINITY ? 0.f : exp2f(ml[s2].x - M);
+                L += ml[s2].y * f;
+                O.x += po[s2].x * f; O.y += po[s2].y * f; O.z += po[s2].z * f; O.w += po[s2].w * f;
+            }
+            const float inv = L > 0.f ? 1.0f / L : 0.f;
+            *reinterpret_cast<uint2*>(p.out + ((size_t)q_tok * p.H + head0 + row) * DH + d) =
+                make_uint2(pack_bf16(O.x * inv, O.y * inv), pack_bf16(O.z * inv, O.w * inv));
+        }
+        cluster_sync_all();                                           // no block leaves while another may still read its partial result
+        return;
+    }
     // The block that finishes last among the slices of this (request, head group) merges them:
     // out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M) (FlashDecodeCombineKernel, src/math_gpu.br:3597-3631).
     // Slices are added in slice order whoever merges, so the result does not depend on which block was last.
@@ -553,6 +614,29 @@ int launch(const AttnParams& p, dim3 grid, cudaStream_t s) {
         BL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<DH, DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
         configured = true;
     }
+    if (DECODE && p.n_splits > 1 && p.part_o == nullptr) {
+        // the slices of a request are the blocks of one cluster (grid.x = slices = cluster size)
+        static int allowed = 0;                                   // largest cluster this kernel may be launched with (0: not asked yet)
+        if (allowed == 0) {
+            BL_CUDA(bl_same_carveout(attention_mma_kernel<DH, DECODE>));
+            allowed = cudaFuncSetAttribute(attention_mma_kernel<DH, DECODE>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess
+                          ? MAX_CLUSTER_SPLITS : 8;
+            (void)cudaGetLastError();
+        }
+        if (p.n_splits > allowed)
+            BL_FAIL("bl_attention_decode: %d slices without scratch memory (clusters of up to %d blocks merge in shared memory)", p.n_splits, allowed);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid; cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = (size_t)bytes; cfg.stream = s;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = p.n_splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = bl_pdl_enabled() ? 1 : 0;
+        cfg.attrs = attr; cfg.numAttrs = 2;
+        BL_CUDA(cudaLaunchKernelEx(&cfg, attention_mma_kernel<DH, DECODE>, p));
+        BL_CHECK_LAUNCH("bl_attention_mma");
+        return 0;
+    }
     BL_CUDA(bl_launch_dependent(attention_mma_kernel<DH, DECODE>, grid, dim3(THREADS), (size_t)bytes, s, p));
     BL_CHECK_LAUNCH("bl_attention_mma");
     return 0;
@@ -643,8 +727,10 @@ extern "C" int bl_attention_decode(const void* q, const void* k_cache, const voi
     if (n <= 0) return 0;
     if (check(H, KV, dh, page_size, max_pages, window, scale)) return 1;
     if (n_splits < 1 || n_splits > 256) BL_FAIL("bl_attention_decode: %d slices (1..256)", n_splits);
-    if (n_splits > 1 && (scratch == nullptr || counters == nullptr))
-        BL_FAIL("bl_attention_decode: slices need scratch memory and zeroed counters");
+    if (n_splits > 1 && scratch != nullptr && counters == nullptr)
+        BL_FAIL("bl_attention_decode: slices merged through scratch memory need zeroed counters");
+    if (n_splits > MAX_CLUSTER_SPLITS && scratch == nullptr)
+        BL_FAIL("bl_attention_decode: more than %d slices need scratch memory and zeroed counters", MAX_CLUSTER_SPLITS);
     AttnParams p;
     p.q = (const __nv_bfloat16*)q; p.kc = (const __nv_bfloat16*)k_cache; p.vc = (const __nv_bfloat16*)v_cache;
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;

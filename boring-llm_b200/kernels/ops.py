@@ -284,11 +284,15 @@ def attention_prefill_tc(q, k_cache, v_cache, cu_q, ctx_len, block_table, tiles,
           ctypes.c_float(scale), _stream())
 
 
+DECODE_CLUSTER_SPLITS = 16     # up to this many slices merge through distributed shared memory (one cluster a request and head group)
+
+
 def attention_decode(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_splits: int, out, H: int, window: int,
                      scale: float, scratch: Optional[torch.Tensor] = None) -> None:
     """Tensor-core attention for requests with one new token; `reqs` int32 [n] lists them. The keys of each are
-    cut into `n_splits` slices; with more than one, `scratch` (float32, `attention_decode_scratch(...)` elements)
-    holds the slices' partial results."""
+    cut into `n_splits` slices. Up to `DECODE_CLUSTER_SPLITS` slices without `scratch`: the slices of a request are
+    the blocks of a cluster and merge in shared memory. More slices, or a `scratch` tensor (float32,
+    `attention_decode_scratch(...)` elements): the partial results go through scratch and the last block merges."""
     T = q.shape[0]
     _, KV, page_size, dh = k_cache.shape
     n = reqs.shape[0]
@@ -297,6 +301,8 @@ def attention_decode(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_sp
     _need(cu_q, "cu_q", torch.int32); _need(ctx_len, "ctx_len", torch.int32); _need(block_table, "block_table", torch.int32)
     _need(reqs, "reqs", torch.int32, (n,))
     need = attention_decode_scratch(n, H, dh, n_splits)
+    if scratch is None and n_splits <= DECODE_CLUSTER_SPLITS:
+        need = 0                               # the slices of a request form a cluster and merge in shared memory: no scratch
     if need:
         if scratch is None:
             scratch = torch.empty(need, dtype=torch.float32, device=q.device)

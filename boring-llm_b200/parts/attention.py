@@ -18,7 +18,7 @@ from .rotary import RotaryTable
 FUSED_MAX_ROWS = 64       # steps with at most this many rows take the fused norm + product kernels
 
 PREFILL_TC_MIN_TOKENS = 256          # steps with fewer prompt tokens keep the 64-row tiles of the mma.sync kernel (measured: 512-token portions gain 8%)
-DECODE_MAX_SPLITS = 32               # more slices make the merge longer than they shorten the scan
+DECODE_MAX_SPLITS = ops.DECODE_CLUSTER_SPLITS   # the slices of a request are one cluster of blocks that merge in shared memory
 PLAN_KEY = "paged attention"         # one plan per step for all attention layers: its lists do not depend on head sizes
 
 

@@ -417,6 +417,26 @@ def mma_attention(q, kc, vc, tok_req, cu_q, ctx_len, table, out, H, window, scal
                 assert (out.float() - ref1.float()).abs().max().item() <= 2e-2 * max(1.0, out.float().abs().max().item())
 
 
+@pytest.mark.parametrize("splits", [2, 5, 8, 13, 16])
+@pytest.mark.parametrize("H,KV,dh,window", [(14, 2, 64, 0), (8, 1, 128, 0), (5, 5, 48, 200)])
+def test_attention_decode_slices_merged_in_a_cluster(H, KV, dh, window, splits):
+    """Up to 16 slices of a request's keys are the blocks of one thread-block cluster and merge their partial results
+    through distributed shared memory (no scratch, no ticket); the same slices through scratch memory, and one slice,
+    must give the same attention (other order of sums: rounding only), and all must equal the plain attention. Short
+    contexts leave slices without keys; a request of one key has fifteen of them."""
+    o = ops()
+
+    def clustered(q, kc, vc, tok_req, cu_q, ctx_len, table, out, H_, window_, scale):
+        reqs = torch.arange(cu_q.shape[0] - 1, dtype=torch.int32, device=DEV)
+        o.attention_decode(q, kc, vc, cu_q, ctx_len, table, reqs, splits, out, H_, window_, scale)
+        through_scratch = torch.empty_like(out)
+        scratch = torch.empty(o.attention_decode_scratch(reqs.shape[0], H_, q.shape[1] // H_, splits), dtype=torch.float32, device=DEV)
+        o.attention_decode(q, kc, vc, cu_q, ctx_len, table, reqs, splits, through_scratch, H_, window_, scale, scratch=scratch)
+        assert (out.float() - through_scratch.float()).abs().max().item() <= 1e-2 * max(1.0, out.float().abs().max().item())
+
+    attention_case(o, clustered, torch.bfloat16, H, KV, dh, [1, 37, 300, 1033, 64, 520], [1] * 6, window, 31)
+
+
 @pytest.mark.parametrize("H,KV,dh", [(4, 2, 16), (7, 1, 64), (8, 1, 128), (3, 3, 48), (14, 2, 64), (6, 2, 32), (34, 2, 96)])
 def test_attention_mma_shapes(H, KV, dh):
     o = ops()

@@ -61,8 +61,11 @@ def test_no_alloc_entry_point_matches_the_allocating_one_twice_in_a_row():
                                                 (5, 4, [300, 45, 1000, 130], 4, 100)]:
         c = _case(seed, n, H, KV, dh, ctx_lens)
         want = torch.empty_like(c["q"])
+        # (with scratch of its own the allocating entry point merges its slices the same way; without, up to 16 slices
+        # merge inside a cluster of blocks, with sums in another order)
+        own = torch.empty(ops.attention_decode_scratch(n, H, dh, n_splits), dtype=torch.float32, device=DEV)
         ops.attention_decode(c["q"], c["kc"], c["vc"], c["cu_q"], c["ctx_len"], c["table"], c["reqs"], n_splits, want,
-                             H, window, 1.0 / math.sqrt(dh))
+                             H, window, 1.0 / math.sqrt(dh), scratch=own)
         got = torch.full_like(c["q"], float("nan"))
         assert _call_no_alloc(lib, c, n_splits, H, KV, dh, got, window) == 0, lib.bl_last_error().decode()
         torch.cuda.synchronize()
