@@ -6,8 +6,10 @@
 //            rows are the query heads that share that key/value head (every key and value is read once
 //            for all of them); each of the four warps streams a page of every 64-key block through a
 //            cp.async ring of its own, with no barrier of the block in the loop; the slices of long contexts
-//            are merged from partial (max, sum, output) triples by whichever block of the (request, head
-//            group) finishes last.
+//            are merged from partial (max, sum, output) triples: up to 16 slices are the blocks of one
+//            thread-block cluster and merge through distributed shared memory, each block finishing a share
+//            of the outputs; more slices (or a caller that brings scratch memory) go through global scratch,
+//            merged by whichever block of the (request, head group) finishes last.
 // Keys and values come from the request's pages through its block table with 16-byte cp.async copies into
 // padded shared-memory tiles. Softmax is the online form of the reference's flash kernels
 // (FlashAttnRegKernel, src/math_gpu.br:3309-3504: running max m, sum l, rescale by exp(m - m_new)); the

@@ -4,7 +4,7 @@ A model with the layer sizes of Qwen2.5-0.5B (hidden 896, 14 query heads on 2 ke
 4,864, vocabulary 151,936; two layers instead of 24) is built by the random-weights mode in device memory. At these
 sizes the engine takes the kernels that the tiny test models never reach: the output head on tcgen05 with W as the
 M side, gate/up on pairs of SMs at N = 9,728, the tcgen05 prefill attention above its token threshold, decode
-attention cut into 32 slices inside a captured graph, tokens fed back on the device one step ahead.
+attention cut into 16 slices (one cluster of blocks a request and head group) inside a captured graph, tokens fed back on the device one step ahead.
 
 Random weights N(0, 0.02) give almost uniform attention, which would hide a lost key among two thousand. So two
 tokens are planted in every prompt, one in the first page and one in the middle, and layer 0 is edited so that
@@ -122,7 +122,7 @@ def test_bfloat16_benchmarked_path_equals_the_plain_implementation():
             print(f"without the planted token at {tok_at}: the last row moves by {effect:.2f} of the scale")
             assert effect > 10 * 1.5e-2, f"the planted key at {tok_at} does not show in the logits ({effect:.3f})"
         # (b) three requests through the engine: chunked and mixed prefill, then 40 decode steps in captured graphs,
-        # launched one ahead, the decode attention in 32 slices
+        # launched one ahead, the decode attention in 16 slices
         prompts = [make_prompt(2100, 2, 1500), make_prompt(1500, 3, 700), make_prompt(700, 4, 350)]
         outs = eng.generate(prompts, n_predict=40, ignore_eos=True)
     finally:
