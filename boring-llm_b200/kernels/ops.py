@@ -323,6 +323,73 @@ def attention_decode(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_sp
           page_size, window, ctypes.c_float(scale), _stream())
 
 
+def attention_decode_tma_supported(dtype: torch.dtype, dh: int, page_size: int) -> bool:
+    return dtype == torch.bfloat16 and bool(library.load().bl_attention_decode_tma_supported(dh, page_size))
+
+
+def attention_decode_tma(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_splits: int, out, H: int, window: int,
+                         scale: float) -> None:
+    """`attention_decode` for head sizes 64 and 128 with keys and values streamed by TMA into per-warp rings and the
+    query heads of a key/value head as the columns of the MMAs; 1 to `DECODE_CLUSTER_SPLITS` slices, which are the
+    blocks of one cluster and send their partial rows to the blocks that finish them."""
+    T = q.shape[0]
+    n_pages, KV, page_size, dh = k_cache.shape
+    n = reqs.shape[0]
+    _need(q, "q", torch.bfloat16, (T, H * dh)); _need(k_cache, "k_cache", torch.bfloat16)
+    _need(v_cache, "v_cache", torch.bfloat16, k_cache.shape); _need(out, "out", torch.bfloat16, (T, H * dh))
+    _need(cu_q, "cu_q", torch.int32); _need(ctx_len, "ctx_len", torch.int32); _need(block_table, "block_table", torch.int32)
+    _need(reqs, "reqs", torch.int32, (n,))
+    _call(_lib().bl_attention_decode_tma, _p(q), _p(k_cache), _p(v_cache), n_pages, _p(cu_q), _p(ctx_len), _p(block_table),
+          block_table.shape[1], _p(reqs), n, n_splits, _p(out), H, KV, dh, page_size, window, ctypes.c_float(scale), _stream())
+
+
+def attention_decode_tma_resident_blocks(dh: int, heads_per_kv: int) -> int:
+    """Blocks of `attention_decode_tma` that the device holds at once (the kernel's own occupancy, asked once)."""
+    key = (torch.cuda.current_device(), dh, heads_per_kv > 8)
+    if key not in _decode_tma_resident:
+        _decode_tma_resident[key] = max(1, int(_lib().bl_attention_decode_tma_resident_blocks(dh, heads_per_kv)))
+    return _decode_tma_resident[key]
+
+
+_decode_tma_resident = {}
+_decode_tma_clusters = {}
+_sm_count = {}
+
+DECODE_TMA_UNIT = 32                  # keys a warp of `attention_decode_tma` takes at a time
+DECODE_TMA_MIN_UNITS = 4              # a slice is worth a block from four units on (one for each warp)
+DECODE_TMA_FEW_UNITS = 6              # up to this many units a warp: latency decides, one block an SM is best (measured)
+
+
+def attention_decode_tma_splits(n: int, KV: int, heads_per_kv: int, dh: int, longest: int) -> int:
+    """Slices for `attention_decode_tma` with n requests whose longest context (or window) has `longest` keys.
+    Measured on a B200: a launch should run in one round (more clusters than the device holds at once cost a second
+    round), slices below 128 keys cost more than they save, and while a warp has only a few units to walk, one block
+    per SM beats two (the step is a chain of latencies); with long walks two blocks per SM keep more bytes in
+    flight. Among the slice counts that qualify, the smallest that gives a warp the fewest units."""
+    dev = torch.cuda.current_device()
+    if dev not in _sm_count:
+        _sm_count[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    groups = KV * (-(-heads_per_kv // (8 if heads_per_kv <= 8 else 16)))
+    clusters = n * groups
+    units = -(-max(1, longest) // DECODE_TMA_UNIT)
+    most = max(1, min(DECODE_CLUSTER_SPLITS, units // DECODE_TMA_MIN_UNITS))
+
+    def per_warp(s):
+        return -(-(-(-units // s)) // 4)
+
+    def fits(s):
+        key = (dev, dh, heads_per_kv > 8)
+        if key not in _decode_tma_clusters:                # asked once, for every cluster size (never inside a later capture)
+            _decode_tma_clusters[key] = [0] + [int(_lib().bl_attention_decode_tma_max_clusters(dh, heads_per_kv, c))
+                                               for c in range(1, DECODE_CLUSTER_SPLITS + 1)]
+        return clusters <= _decode_tma_clusters[key][s]
+
+    one_per_sm = max(1, min(most, _sm_count[dev] // clusters))
+    if per_warp(one_per_sm) <= DECODE_TMA_FEW_UNITS:
+        top = one_per_sm
+    else:
+        top = next((s for s in range(most, 0, -1) if fits(s)), 1)
+    return min(range(1, top + 1), key=lambda s: (per_warp(s), s))
 _decode_counters = {}
 _decode_resident = {}
 
@@ -456,7 +523,8 @@ def check_status() -> None:
     for name, fn in (("bl_gemm_tc", _lib().bl_gemm_tc_status), ("bl_gemm_tc_pair", _lib().bl_gemm_tc_pair_status),
                      ("bl_attention_prefill_tc", _lib().bl_attention_prefill_tc_status),
                      ("bl_gemm_tc_cols", _lib().bl_gemm_tc_cols_status),
-                     ("bl_gemm_tc_splitk", _lib().bl_gemm_tc_splitk_status)):
+                     ("bl_gemm_tc_splitk", _lib().bl_gemm_tc_splitk_status),
+                     ("bl_attention_decode_tma", _lib().bl_attention_decode_tma_status)):
         v = ctypes.c_int(0)
         _call(fn, ctypes.byref(v))
         if v.value != 0:

@@ -207,10 +207,17 @@ class GQAAttention(Mixer):
         n = singles.shape[0]
         if n:
             # as many slices of the keys as fill the device once (the kernel knows how many of its blocks fit)
-            groups = self.KV * (-(-(self.H // self.KV) // 16))
             longest = plan.host["longest_single"]
             if self.window > 0:
                 longest = min(longest, self.window + 64)
+            G = self.H // self.KV
+            if ops.attention_decode_tma_supported(q.dtype, self.dh, k_cache.shape[2]):
+                # head sizes 64 and 128: the TMA-fed kernel, which knows how many slices pay for this many requests
+                n_splits = ops.attention_decode_tma_splits(n, self.KV, G, self.dh, longest)
+                ops.attention_decode_tma(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, singles, n_splits, out,
+                                         self.H, self.window, self.scale)
+                return
+            groups = self.KV * (-(-G // 16))
             resident = ops.attention_decode_resident_blocks(self.dh)
             n_splits = max(1, min(-(-longest // 64), resident // (n * groups), DECODE_MAX_SPLITS))
             ops.attention_decode(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, singles, n_splits, out,

@@ -437,6 +437,56 @@ def test_attention_decode_slices_merged_in_a_cluster(H, KV, dh, window, splits):
     attention_case(o, clustered, torch.bfloat16, H, KV, dh, [1, 37, 300, 1033, 64, 520], [1] * 6, window, 31)
 
 
+def tma_decode(splits, poison=True):
+    """Runs `attention_decode_tma` on the single-token requests of a case. With `poison`, every row of the cache
+    that no request owns (free pages, rows past a request's last key) is NaN first: a kernel that lets such a row
+    into a sum, even with weight zero, shows it."""
+    o = ops()
+
+    def fn(q, kc, vc, tok_req, cu_q, ctx_len, table, out, H, window, scale):
+        if poison:
+            owned = torch.zeros(kc.shape[0], kc.shape[2], dtype=torch.bool, device=DEV)
+            for r, c in enumerate(ctx_len.cpu().tolist()):
+                for j in range(c):
+                    owned[int(table[r, j // 16]), j % 16] = True
+            kc.masked_fill_(~owned[:, None, :, None], float("nan"))
+            vc.masked_fill_(~owned[:, None, :, None], float("nan"))
+        reqs = torch.arange(cu_q.shape[0] - 1, dtype=torch.int32, device=DEV)
+        out.fill_(float("nan"))
+        o.attention_decode_tma(q, kc, vc, cu_q, ctx_len, table, reqs, splits, out, H, window, scale)
+        o.check_status()
+    return fn
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 7, 16])
+@pytest.mark.parametrize("H,KV,dh,window", [(14, 2, 64, 0), (8, 1, 128, 0), (7, 7, 64, 0), (24, 2, 64, 0), (40, 2, 128, 0), (28, 4, 128, 0),
+                                            (14, 2, 64, 200), (16, 1, 128, 33), (6, 2, 64, 1)])
+def test_attention_decode_tma(H, KV, dh, window, splits):
+    """The TMA-fed decode attention against the plain attention: 7, 8, 1, 12, 20 and 16 query heads per key/value
+    head (one and two n-tiles of heads, two blocks per key/value head), contexts of one key, of one page less and
+    more than a unit, of many units per warp, windows that start inside a page and of one key, any number of slices
+    (more slices than units leave slices without keys; more slices than heads leave blocks that own no row)."""
+    o = ops()
+    assert o.attention_decode_tma_supported(torch.bfloat16, dh, 16)
+    attention_case(o, tma_decode(splits), torch.bfloat16, H, KV, dh, [1, 37, 300, 1033, 64, 520, 31, 32, 33, 2500], [1] * 10, window, 41)
+
+
+def test_attention_decode_tma_refuses_other_shapes():
+    from boring_llm_b200.kernels import KernelError
+    o = ops()
+    assert not o.attention_decode_tma_supported(torch.bfloat16, 96, 16)
+    assert not o.attention_decode_tma_supported(torch.float32, 64, 16)
+    i = torch.zeros(2, dtype=torch.int32, device=DEV)
+    q = torch.zeros(1, 2 * 96, dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros(1, 1, 16, 96, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelError, match="head size"):
+        o.attention_decode_tma(q, kc, kc, i, i[:1], i.view(2, 1)[:1], i[:1], 1, q.clone(), 2, 0, 1.0)
+    q = torch.zeros(1, 2 * 64, dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros(1, 1, 16, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelError, match="slices"):
+        o.attention_decode_tma(q, kc, kc, i, i[:1], i.view(2, 1)[:1], i[:1], 17, q.clone(), 2, 0, 1.0)
+
+
 @pytest.mark.parametrize("H,KV,dh", [(4, 2, 16), (7, 1, 64), (8, 1, 128), (3, 3, 48), (14, 2, 64), (6, 2, 32), (34, 2, 96)])
 def test_attention_mma_shapes(H, KV, dh):
     o = ops()

@@ -128,7 +128,7 @@ def test_bfloat16_benchmarked_path_equals_the_plain_implementation():
     finally:
         ops._call = real_call
     assert eng.runner.graph_steps >= 30
-    for name in ("bl_gemm_tc_cols", "bl_gemm_tc_pair", "bl_attention_prefill_tc", "bl_attention_decode",
+    for name in ("bl_gemm_tc_cols", "bl_gemm_tc_pair", "bl_attention_prefill_tc", "bl_attention_decode_tma",
                  "bl_norm_qkv_rope", "bl_norm_gemm", "bl_gemm_skinny"):
         assert name in used, f"{name} was not on the path"
     check_tokens(cfg, T, prompts, outs)
