@@ -247,17 +247,18 @@ def test_argmax_first_maximum_wins():
     assert out.cpu().tolist()[4:] == want[4:]
 
 
-@pytest.mark.parametrize("vocab", [37, 1000, 151936])
-def test_sampler_matches_the_plain_sampler(vocab):
+@pytest.mark.parametrize("vocab,rows", [(37, 24), (1000, 24), (151936, 24), (5000, 48), (3001, 96), (2000, 192)])
+def test_sampler_matches_the_plain_sampler(vocab, rows):
+    """Every combination of the cuts against the plain sampler, token for token. The row counts make the launch use
+    clusters of 8, 4, 2 blocks and single blocks per row; 3,001 logits are not a multiple of four (scalar loads)."""
     o = ops()
     rng = np.random.default_rng(vocab)
-    rows = 24
     logits = (rng.standard_normal((rows, vocab)) * 3).astype(np.float32)
     logits[5, 10] = logits[5, 20] = logits[5].max() + 1      # exact ties at the top
-    temps = np.array([0.0, 0.8, 1.0, 0.3, 2.0, 1.0] * 4, dtype=np.float32)
-    top_k = np.array([0, 0, 40, 5, 0, 2, 0, 1] * 3, dtype=np.int32)
-    top_p = np.array([1.0, 0.9, 1.0, 0.5, 1.0, 1.0, 0.1, 1.0] * 3, dtype=np.float32)
-    min_p = np.array([0.0, 0.0, 0.0, 0.05, 0.2, 0.0] * 4, dtype=np.float32)
+    temps = np.array([0.0, 0.8, 1.0, 0.3, 2.0, 1.0] * (rows // 6), dtype=np.float32)
+    top_k = np.array([0, 0, 40, 5, 0, 2, 0, 1] * (rows // 8), dtype=np.int32)
+    top_p = np.array([1.0, 0.9, 1.0, 0.5, 1.0, 1.0, 0.1, 1.0] * (rows // 8), dtype=np.float32)
+    min_p = np.array([0.0, 0.0, 0.0, 0.05, 0.2, 0.0] * (rows // 6), dtype=np.float32)
     state = plain.seed_rng(7)
     us = []
     want = []
@@ -277,6 +278,58 @@ def test_sampler_matches_the_plain_sampler(vocab):
     out2 = torch.empty_like(out)
     o.sample(t(logits), t(temps), t(top_k), t(top_p), t(min_p), t(np.array(us, dtype=np.float32)), out2)
     assert torch.equal(out, out2)                             # the same on every run
+
+
+def plain_tokens(logits, temps, top_k, top_p, min_p, seed=7):
+    state = plain.seed_rng(seed)
+    us, want = [], []
+    for r in range(logits.shape[0]):
+        u = 0.0
+        if temps[r] > 0:
+            before = state
+            tok, state = plain.sample(before, logits[r], float(temps[r]), int(top_k[r]), float(top_p[r]), float(min_p[r]))
+            u, _ = plain.rng_next_f32(before)
+        else:
+            tok, _ = plain.sample(state, logits[r], 0.0)
+        us.append(u); want.append(tok)
+    return np.array(us, dtype=np.float32), want
+
+
+@pytest.mark.parametrize("shape", ["peaked", "equal", "two values", "wide", "steps"])
+def test_sampler_on_rows_that_are_not_bell_shaped(shape):
+    """Rows that stress the sampler's bucketing: one token far above the rest (everything else in the last
+    buckets), all logits equal (one bucket holds the row: the radix fallback, ties by id), two values, a spread
+    of hundreds (most weights are zero), and plateaus of equal logits larger than shared memory."""
+    o = ops()
+    vocab, rows = 20000, 16
+    rng = np.random.default_rng(len(shape))
+    if shape == "peaked":
+        logits = (rng.standard_normal((rows, vocab)) * 0.5).astype(np.float32)
+        logits[np.arange(rows), rng.integers(0, vocab, rows)] += 12.0
+    elif shape == "equal":
+        logits = np.full((rows, vocab), 1.25, dtype=np.float32)
+    elif shape == "two values":
+        logits = np.where(rng.random((rows, vocab)) < 0.3, 2.0, -1.0).astype(np.float32)
+    elif shape == "wide":
+        logits = (rng.standard_normal((rows, vocab)) * 120).astype(np.float32)
+    else:
+        logits = np.floor(rng.standard_normal((rows, vocab)) * 2).astype(np.float32)      # about 15 distinct values
+    temps = np.array([0.7, 1.0, 1.5, 0.2] * 4, dtype=np.float32)
+    top_k = np.array([0, 0, 50, 6000, 0, 3, 0, 0] * 2, dtype=np.int32)
+    top_p = np.array([1.0, 0.9, 1.0, 1.0, 0.45, 0.99, 1.0, 0.7] * 2, dtype=np.float32)     # (not 0.5: half of 20,000 equal weights
+    min_p = np.array([0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.3, 0.01] * 2, dtype=np.float32)      # is a boundary that 64-bit sums round either way)
+    us, want = plain_tokens(logits, temps, top_k, top_p, min_p, seed=11)
+    t = lambda a: torch.from_numpy(a).to(DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    o.sample(t(logits), t(temps), t(top_k), t(top_p), t(min_p), t(us), out)
+    got = out.cpu().tolist()
+    for r in range(rows):
+        if got[r] != want[r]:
+            # a draw that lands on the boundary between two candidates may fall either way in 32-bit weights: then the
+            # two candidates are neighbours in the descending order and the draw is within rounding of the boundary
+            order = np.argsort(-logits[r].astype(np.float64), kind="stable").tolist()
+            assert abs(order.index(got[r]) - order.index(want[r])) == 1, (shape, r, got[r], want[r])
+    assert sum(g != w for g, w in zip(got, want)) <= 1
 
 
 def test_sampler_distribution():
