@@ -117,12 +117,14 @@ def random_prompt(vocab, n, seed):
     return torch.randint(0, vocab, (n,), generator=g).tolist()
 
 
-def start_requests(eng, lengths, seed):
+def start_requests(eng, lengths, seed, sampled=False):
     """Admits one request per prompt length and steps the engine until every one of them has been prefilled (in
-    portions, several requests to a step, as the scheduler cuts them) and has its first token."""
+    portions, several requests to a step, as the scheduler cuts them) and has its first token. `sampled`: the
+    requests draw their tokens (temperature 0.8, top-k 40, top-p 0.95) instead of taking the largest logit."""
     from boring_llm_b200.sampling.params import SamplingParams
     vocab = eng.runner.vocab_size
-    reqs = [eng.add_request(random_prompt(vocab, n, seed * 1000 + i), SamplingParams(n_predict=-1, ignore_eos=True))
+    how = dict(temperature=0.8, top_k=40, top_p=0.95, seed=seed) if sampled else {}
+    reqs = [eng.add_request(random_prompt(vocab, n, seed * 1000 + i), SamplingParams(n_predict=-1, ignore_eos=True, **how))
             for i, n in enumerate(lengths)]
     while not all(r.output for r in reqs):
         eng.step()
@@ -167,7 +169,7 @@ def check_one_step(eng, reqs):
     return {"ok": True, "rows": len(reqs), "equal": len(reqs) - ties, "near_ties": ties}
 
 
-def measure_decode(eng, batch, steps, warmup, value_regions=3, e2e_regions=0, check=False, seed=1):
+def measure_decode(eng, batch, steps, warmup, value_regions=3, e2e_regions=0, check=False, seed=1, sampled=False):
     """Decode steps of `batch` requests whose contexts end just below the context size. Returns a dict with the
     device-timed figures (median region of `steps` steps), the wall-clock figures when asked for, the kernels launched
     in a region, the mean context inside the timed regions and the result of the one-step check."""
@@ -179,7 +181,7 @@ def measure_decode(eng, batch, steps, warmup, value_regions=3, e2e_regions=0, ch
     ctx0 = CONTEXT - need
     prefill_steps = -(-batch * ctx0 // per_step) + 2
     ctx0 -= prefill_steps
-    reqs = start_requests(eng, [ctx0] * batch, seed)
+    reqs = start_requests(eng, [ctx0] * batch, seed, sampled)
     out = {}
     if check:
         out["checked"] = check_one_step(eng, reqs)
@@ -399,6 +401,7 @@ def main():
     k_small = min(args.steps, 32)
     m1 = measure_decode(eng, 1, k_small, 3, seed=2)
     m64 = measure_decode(eng, 64, k_small, 3, seed=3)
+    m8s = measure_decode(eng, args.batch, k_small, 3, seed=4, sampled=True)     # the same step with drawn tokens
     pre_ms, pre_wall = prefill_timed(eng, [PREFILL_TOKENS])
     pre4_ms, pre4_wall = prefill_timed(eng, [PORTION] * (PREFILL_TOKENS // PORTION))
     mix_ms, mix_wall, mix_host, mix_tokens = mixed_timed(eng)
@@ -434,6 +437,7 @@ def main():
             "decode_b64_hbm_frac": round(hbm_frac(64, m64), 4),
             "decode_b1_ms": round(m1["ms_per_step"], 4), "decode_b64_ms": round(m64["ms_per_step"], 4),
             "decode_b8_graph_replay_ms": round(m8.get("graph_replay_ms", 0.0), 4),
+            "decode_b8_sampled_ms": round(m8s["ms_per_step"], 4),
             "prefill_wall_ms": round(pre_wall, 3),
             "prefill_4x512": round(PREFILL_TOKENS / (pre4_ms / 1e3), 1), "prefill_4x512_ms": round(pre4_ms, 3),
             "prefill_4x512_wall_ms": round(pre4_wall, 3),

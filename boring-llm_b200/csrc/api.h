@@ -106,6 +106,19 @@ int bl_attention_decode_tma(const void* q, const void* k_cache, const void* v_ca
                             void* stream);
 int bl_attention_decode_tma_status(int* status);
 
+// cs[t, j] = cos(positions[t] * inv_freq[j]) * mscale, sn likewise, j < rot_half: the rotation of a step's tokens,
+// worked out once for all layers.
+int bl_rope_table(const int* positions, const float* inv_freq, int rot_half, float mscale, float* cs, float* sn, int T,
+                  void* stream);
+// The joined q/k/v product on pairs of SMs (gemm_tcgen05_pair.cu) with bias, rotation (pairs j, j + dh / 2; cs, sn:
+// [M, dh / 2] from bl_rope_table) and the writes of q and of k and v into the pages of each token's request folded
+// into its epilogue. Head size 64 or 128, pages of 16; null caches: nothing is cached; bias may be null.
+int bl_gemm_tc_pair_qkv_rope_supported(int H, int KV, int dh, int page_size, int K);
+int bl_gemm_tc_pair_qkv_rope(const void* x, const void* w, const void* bias, int bias_dtype, int M, int K,
+                             const int* tok_req, const int* positions, const int* block_table, int max_pages,
+                             const float* cs, const float* sn, void* q_out, void* k_cache, void* v_cache,
+                             int H, int KV, int dh, int page_size, void* stream);
+
 // Matrix product for many rows (prefill) on tcgen05 tensor cores with TMA-fed shared-memory tiles and the
 // accumulator in tensor memory. bfloat16 x[M, K] and W[N, K]; K a multiple of 8, x and W 16-byte aligned.
 int bl_gemm_tc(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype,

@@ -302,6 +302,29 @@ extern "C" int bl_rope_kv_write(const float* qkv, const int* positions, const in
     return 0;
 }
 
+// The rotation of every token of a step, once for all layers: cs[t, j] = cos(pos_t * inv_freq_j) * mscale and
+// sn[t, j] = sin(...) * mscale, with the same 32-bit formulas as the kernels that rotate on the fly.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot_half,
+                                  float mscale, float* __restrict__ cs, float* __restrict__ sn, int T) {
+    bl_pdl_trigger();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * rot_half) return;
+    const int t = i / rot_half, j = i % rot_half;
+    const float angle = (float)positions[t] * inv_freq[j];
+    cs[i] = cosf(angle) * mscale;
+    sn[i] = sinf(angle) * mscale;
+}
+
+extern "C" int bl_rope_table(const int* positions, const float* inv_freq, int rot_half, float mscale, float* cs,
+                             float* sn, int T, void* stream) {
+    if (T <= 0 || rot_half <= 0) return 0;
+    const int n = T * rot_half;
+    BL_CUDA(bl_launch_dependent(rope_table_kernel, dim3((n + 255) / 256), dim3(256), 0, (cudaStream_t)stream, positions,
+                                inv_freq, rot_half, mscale, cs, sn, T));
+    BL_CHECK_LAUNCH("bl_rope_table");
+    return 0;
+}
+
 // ---------------------------------------------------------------------------------------------
 // First maximum wins, as sample_greedy (src/sampling.br:239-249: strict '>').
 __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {

@@ -55,6 +55,18 @@ constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;      // clears the bit that sele
 
 __device__ int g_status2 = 0;
 
+// An epilogue of this file only: the joined q/k/v product of an attention layer, finished in place. A tile of 128
+// columns is whole heads (head size 64 or 128); the accumulator gets its bias, q and k heads are rotated by the
+// token's position (pairs j, j + head size / 2; cos and sin from the step's table), and the bfloat16 results go
+// where the attention kernels read them: q rows, and the key and value pages of the token's request.
+constexpr int EPI_QKV_ROPE = 100;
+struct QkvOut {
+    const int* tok_req; const int* positions; const int* block_table; int max_pages;
+    const float* cs; const float* sn;            // [M, dh / 2]
+    __nv_bfloat16* q; __nv_bfloat16* k_cache; __nv_bfloat16* v_cache;   // caches may be null (nothing is cached)
+    int H, KV, dh;
+};
+
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
         uint32_t ok;
@@ -96,7 +108,7 @@ template <int EPI, typename TO, int BN>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const void* __restrict__ bias, int bias_dtype, TO* __restrict__ out, int M, int N, int K,
-                    int m_pairs, int n_tiles) {
+                    int m_pairs, int n_tiles, const QkvOut qo) {
     constexpr bool GLU = EPI == BL_EPI_SWIGLU;
     constexpr int STAGE_BYTES = stage_bytes(BN), STAGES = stages_for(BN), KS = ksub(BN), B_BYTES = b_bytes(BN);
     static_assert(STAGES <= MAX_STAGES && STAGES * STAGE_BYTES <= RING_BYTES && STAGE_BYTES % 1024 == 0, "ring does not fit");
@@ -228,6 +240,110 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                                                : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
             };
+            if (EPI == EPI_QKV_ROPE) {
+                // This lane's row of the accumulator is one token. The tile's 128 columns are 128 / dh heads; an item is
+                // 32 columns of a head's first half with the 32 that turn with them (dh / 2 further on); the two warps
+                // of a quarter take an item each. Everything that does not depend on the product (where the row goes,
+                // its cosines and sines, the bias) is asked for before the accumulator is waited for.
+                const int dh = qo.dh, half_cols = dh >> 1;
+                const int m = m0 + quarter * 32 + lane;
+                const int c_lo = dh == 64 ? 2 * half : half, c_hi = c_lo + (dh >> 6);     // 32-column chunks of the tile
+                const int n_lo = n0 + c_lo * 32;                                          // first column of the item's low half
+                const int head = n_lo / dh;                                               // q heads, then k heads, then v heads
+                const int j0 = n_lo % dh;                                                 // first pair of the item (0, or 32 for dh 128)
+                const bool turn = head < qo.H + qo.KV;
+                // where this token's row of the head goes (elements from the start of q, or of a cache)
+                __nv_bfloat16* dst_base = nullptr;
+                size_t dst_row = 0;
+                bool row_ok = m < M && n_lo < N;                                          // (the last tile of an odd number of 64-wide heads is half empty)
+                if (head < qo.H) {
+                    dst_base = qo.q;
+                    dst_row = ((size_t)(row_ok ? m : 0) * qo.H + head) * dh;
+                } else {
+                    const bool keys = head < qo.H + qo.KV;
+                    dst_base = keys ? qo.k_cache : qo.v_cache;
+                    const int kvh = keys ? head - qo.H : head - qo.H - qo.KV;
+                    if (dst_base == nullptr) row_ok = false;
+                    if (row_ok) {
+                        const int pos = qo.positions[m];
+                        const int page = qo.block_table[(size_t)qo.tok_req[m] * qo.max_pages + pos / 16];
+                        if (page < 0) row_ok = false;                                     // the host never schedules this; keep memory safe anyway
+                        dst_row = (((size_t)(page < 0 ? 0 : page) * qo.KV + kvh) * 16 + (size_t)(pos % 16)) * dh;
+                    }
+                }
+                const float4* cs4 = reinterpret_cast<const float4*>(qo.cs + (size_t)(m < M ? m : 0) * half_cols + j0);
+                const float4* sn4 = reinterpret_cast<const float4*>(qo.sn + (size_t)(m < M ? m : 0) * half_cols + j0);
+                float4 cw[4], sw[4];                                                      // pairs 0..15 of the item
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    cw[i] = turn ? cs4[i] : make_float4(1.f, 1.f, 1.f, 1.f);
+                    sw[i] = turn ? sn4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                // the bias of the item's 2 x 32 columns (the same for every row): bfloat16 as eight 16-byte words
+                const bool b16 = bias != nullptr && bias_dtype == BL_BF16 && n_lo < N;
+                uint4 bl4[4], bh4[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    bl4[i] = b16 ? reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(bias) + n_lo)[i] : make_uint4(0u, 0u, 0u, 0u);
+                    bh4[i] = b16 ? reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(bias) + n_lo + half_cols)[i] : make_uint4(0u, 0u, 0u, 0u);
+                }
+                const bool b32 = bias != nullptr && bias_dtype == BL_F32 && n_lo < N;
+                if (!mbar_wait(acc_full0 + 8 * buf, (local / 2) & 1, give_up, 3)) break;
+                fence_after_sync();
+                const uint32_t lane_addr = tmem + buf * 256 + ((uint32_t)(quarter * 32) << 16);
+                uint32_t lo[32], hi[32];
+                tmem_ld32(lane_addr + c_lo * 32, lo);
+                tmem_ld32(lane_addr + c_hi * 32, hi);
+                tmem_ld_wait();
+                float4 cw2[4], sw2[4];                                                    // pairs 16..31: on their way while the first are used
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    cw2[i] = turn ? cs4[4 + i] : make_float4(1.f, 1.f, 1.f, 1.f);
+                    sw2[i] = turn ? sn4[4 + i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                uint32_t* st = reinterpret_cast<uint32_t*>(tile);                          // [32 rows][lo 16 words | hi 16 words | 4 unused]
+                const uint32_t* blw = reinterpret_cast<const uint32_t*>(bl4);
+                const uint32_t* bhw = reinterpret_cast<const uint32_t*>(bh4);
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    const float4 c4v = j < 16 ? cw[j >> 2] : cw2[(j - 16) >> 2], s4v = j < 16 ? sw[j >> 2] : sw2[(j - 16) >> 2];
+                    const float c[4] = {c4v.x, c4v.y, c4v.z, c4v.w}, sv[4] = {s4v.x, s4v.y, s4v.z, s4v.w};
+                    float a[4], b[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        // two bfloat16 per word: the even one in the low half
+                        const uint32_t wl = blw[(j + e) >> 1], wh = bhw[(j + e) >> 1];
+                        float ba = __uint_as_float((e & 1) ? (wl & 0xffff0000u) : (wl << 16));
+                        float bb = __uint_as_float((e & 1) ? (wh & 0xffff0000u) : (wh << 16));
+                        if (b32) { ba = reinterpret_cast<const float*>(bias)[n_lo + j + e]; bb = reinterpret_cast<const float*>(bias)[n_lo + half_cols + j + e]; }
+                        const float x0 = __uint_as_float(lo[j + e]) + ba, x1 = __uint_as_float(hi[j + e]) + bb;
+                        a[e] = x0 * c[e] - x1 * sv[e];
+                        b[e] = x0 * sv[e] + x1 * c[e];
+                    }
+                    __nv_bfloat162 p0 = __floats2bfloat162_rn(a[0], a[1]), p1 = __floats2bfloat162_rn(a[2], a[3]);
+                    __nv_bfloat162 p2 = __floats2bfloat162_rn(b[0], b[1]), p3 = __floats2bfloat162_rn(b[2], b[3]);
+                    // through shared memory, so that a row's 64 bytes of each half leave as whole 16-byte words side by side
+                    *reinterpret_cast<uint2*>(st + lane * PITCH + (j >> 1)) = make_uint2(*reinterpret_cast<unsigned*>(&p0), *reinterpret_cast<unsigned*>(&p1));
+                    *reinterpret_cast<uint2*>(st + lane * PITCH + 16 + (j >> 1)) = make_uint2(*reinterpret_cast<unsigned*>(&p2), *reinterpret_cast<unsigned*>(&p3));
+                }
+                __syncwarp();
+#pragma unroll
+                for (int it2 = 0; it2 < 8; ++it2) {
+                    const int row = it2 * 4 + r_sub;
+                    const bool ok = __shfl_sync(0xffffffffu, row_ok ? 1 : 0, row) != 0;
+                    const unsigned long long at = __shfl_sync(0xffffffffu, (unsigned long long)dst_row, row);
+                    if (!ok) continue;
+                    const int w8 = lane & 7;                                              // 16-byte word of the row: 0-3 the low half, 4-7 the high half
+                    const uint4 v = *reinterpret_cast<const uint4*>(st + row * PITCH + 4 * w8);
+                    __nv_bfloat16* dst = dst_base + at + j0 + (w8 < 4 ? w8 * 8 : half_cols + (w8 - 4) * 8);   // (one destination tensor per item)
+                    *reinterpret_cast<uint4*>(dst) = v;
+                }
+                __syncwarp();
+                fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_leader(acc_empty0 + 8 * buf);
+                continue;
+            }
             if (PRELOAD && half < CHUNKS) preload(half);
             if (!mbar_wait(acc_full0 + 8 * buf, (local / 2) & 1, give_up, 3)) break;
             fence_after_sync();
@@ -307,7 +423,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 template <int EPI, typename TO, int BN>
 int launch_bn(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K, int sms,
-              cudaStream_t s) {
+              cudaStream_t s, const QkvOut& qo = QkvOut()) {
     static bool configured = false;
     if (!configured) {
         BL_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI, TO, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
@@ -335,7 +451,7 @@ int launch_bn(const void* x, const void* w, const void* bias, int bias_dtype, vo
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = bl_pdl_enabled() ? 1 : 0;
     cfg.attrs = attr; cfg.numAttrs = 2;
-    BL_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<EPI, TO, BN>, a, b, bias, bias_dtype, (TO*)out, M, N, K, m_pairs, n_tiles));
+    BL_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<EPI, TO, BN>, a, b, bias, bias_dtype, (TO*)out, M, N, K, m_pairs, n_tiles, qo));
     return 0;
 }
 
@@ -391,6 +507,33 @@ extern "C" int bl_gemm_tc_pair(const void* x, const void* w, const void* bias, i
         BL_FAIL("bl_gemm_tc_pair: unknown output dtype %d", out_dtype);
     }
     BL_FAIL("bl_gemm_tc_pair: unknown epilogue %d", epilogue);
+}
+
+// Whether bl_gemm_tc_pair_qkv_rope takes this layer: head size 64 or 128, pages of 16, K as for the other products.
+extern "C" int bl_gemm_tc_pair_qkv_rope_supported(int H, int KV, int dh, int page_size, int K) {
+    return (dh == 64 || dh == 128) && page_size == 16 && H > 0 && KV > 0 && K % 8 == 0;
+}
+
+// The joined q/k/v product of M tokens with its bias, the rotation of q and k (pairs j, j + dh / 2, every pair of a
+// head; cs and sn: [M, dh / 2] from bl_rope_table) and the writes of q (bfloat16 [M, H * dh]) and of k and v into the
+// pages of each token's request (null caches: nothing is cached). W: [(H + 2 KV) * dh, K] bfloat16, q rows first.
+extern "C" int bl_gemm_tc_pair_qkv_rope(const void* x, const void* w, const void* bias, int bias_dtype, int M, int K,
+                                        const int* tok_req, const int* positions, const int* block_table, int max_pages,
+                                        const float* cs, const float* sn, void* q_out, void* k_cache, void* v_cache,
+                                        int H, int KV, int dh, int page_size, void* stream) {
+    if (M <= 0) return 0;
+    if (!bl_gemm_tc_pair_qkv_rope_supported(H, KV, dh, page_size, K))
+        BL_FAIL("bl_gemm_tc_pair_qkv_rope: head size %d, pages of %d, %d + 2 x %d heads, K = %d is not built", dh, page_size, H, KV, K);
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)cs | (uintptr_t)sn) & 15)
+        BL_FAIL("bl_gemm_tc_pair_qkv_rope: x, W, q, the caches and the rotation table must be 16-byte aligned");
+    if (bias != nullptr && bias_dtype != BL_F32 && bias_dtype != BL_BF16) BL_FAIL("bl_gemm_tc_pair_qkv_rope: the bias must be float32 or bfloat16");
+    if ((k_cache == nullptr) != (v_cache == nullptr)) BL_FAIL("bl_gemm_tc_pair_qkv_rope: key and value cache must both be given or both be null");
+    if (max_pages <= 0) BL_FAIL("bl_gemm_tc_pair_qkv_rope: bad table width");
+    QkvOut qo;
+    qo.tok_req = tok_req; qo.positions = positions; qo.block_table = block_table; qo.max_pages = max_pages;
+    qo.cs = cs; qo.sn = sn; qo.q = (__nv_bfloat16*)q_out; qo.k_cache = (__nv_bfloat16*)k_cache; qo.v_cache = (__nv_bfloat16*)v_cache;
+    qo.H = H; qo.KV = KV; qo.dh = dh;
+    return launch_bn<EPI_QKV_ROPE, __nv_bfloat16, 128>(x, w, bias, bias_dtype, nullptr, M, (H + 2 * KV) * dh, K, sm_count(), (cudaStream_t)stream, qo);
 }
 
 extern "C" int bl_gemm_tc_pair_status(int* status) {

@@ -187,6 +187,48 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, tok_req: torch.Ten
           _p(v_cache), _dt(q_out), T, H, KV, dh, page_size, pair_layout, _stream())
 
 
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, rot_half: int, mscale: float):
+    """(cos, sin) of every token's rotation, float32 [T, rot_half] each, scaled by `mscale`: worked out once per step
+    for the kernels that take the rotation from a table."""
+    T = positions.shape[0]
+    _need(positions, "positions", torch.int32, (T,)); _need(inv_freq, "inv_freq", torch.float32)
+    both = torch.empty((2, T, rot_half), dtype=torch.float32, device=positions.device)
+    _call(_lib().bl_rope_table, _p(positions), _p(inv_freq), rot_half, ctypes.c_float(mscale), _p(both[0]), _p(both[1]), T, _stream())
+    return both[0], both[1]
+
+
+def qkv_rope_tc_supported(x: torch.Tensor, w: torch.Tensor, H: int, KV: int, dh: int, page_size: int) -> bool:
+    """Whether `qkv_rope_tc` takes this layer's joined product: bfloat16 operands, 16-byte aligned, head size 64 or
+    128 with every pair of a head rotated, pages of 16."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and bool(library.load().bl_gemm_tc_pair_qkv_rope_supported(H, KV, dh, page_size, x.shape[1])))
+
+
+def qkv_rope_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
+                tok_req: torch.Tensor, block_table: torch.Tensor, cs: torch.Tensor, sn: torch.Tensor, q_out: torch.Tensor,
+                k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], H: int, KV: int, dh: int) -> None:
+    """The joined q/k/v product of many rows on pairs of SMs (tcgen05) with bias, rotation (pairs j, j + dh / 2, from
+    the step's table `rope_table`) and the writes of q and of k and v into the requests' pages in its epilogue."""
+    M, K = x.shape
+    _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16, ((H + 2 * KV) * dh, K))
+    _need(positions, "positions", torch.int32, (M,)); _need(tok_req, "tok_req", torch.int32, (M,))
+    _need(block_table, "block_table", torch.int32)
+    _need(cs, "cs", torch.float32, (M, dh // 2)); _need(sn, "sn", torch.float32, (M, dh // 2))
+    _need(q_out, "q_out", torch.bfloat16, (M, H * dh))
+    if bias is not None:
+        _need(bias, "bias", None, ((H + 2 * KV) * dh,))
+    page_size = 16
+    if k_cache is not None:
+        _need(k_cache, "k_cache", torch.bfloat16); _need(v_cache, "v_cache", torch.bfloat16, k_cache.shape)
+        if k_cache.shape[1] != KV or k_cache.shape[3] != dh:
+            raise KernelError(f"k_cache: shape {tuple(k_cache.shape)} does not hold {KV} heads of {dh}")
+        page_size = k_cache.shape[2]
+    _call(_lib().bl_gemm_tc_pair_qkv_rope, _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0, M, K, _p(tok_req),
+          _p(positions), _p(block_table), block_table.shape[1], _p(cs), _p(sn), _p(q_out), _p(k_cache), _p(v_cache),
+          H, KV, dh, page_size, _stream())
+
+
 def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_req: torch.Tensor,
                     cu_q: torch.Tensor, ctx_len: torch.Tensor, block_table: torch.Tensor,
                     out: torch.Tensor, H: int, window: int, scale: float) -> None:

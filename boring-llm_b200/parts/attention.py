@@ -17,6 +17,7 @@ from .rotary import RotaryTable
 
 FUSED_MAX_ROWS = 64       # steps with at most this many rows take the fused norm + product kernels
 
+QKV_EPILOGUE_MIN_ROWS = ops.PAIR_MIN_ROWS  # from here the joined product runs on pairs of SMs, whose epilogue can rotate and write the cache
 PREFILL_TC_MIN_TOKENS = 256          # steps with fewer prompt tokens keep the 64-row tiles of the mma.sync kernel (measured: 512-token portions gain 8%)
 DECODE_MAX_SPLITS = ops.DECODE_CLUSTER_SPLITS   # the slices of a request are one cluster of blocks that merge in shared memory
 PLAN_KEY = "paged attention"         # one plan per step for all attention layers: its lists do not depend on head sizes
@@ -144,13 +145,20 @@ class GQAAttention(Mixer):
     def forward(self, ctx, h, residual, cache_layer, write_cache=True):
         T = h.shape[0]
         width = (self.H + 2 * self.KV) * self.dh
-        qkv = ctx.empty((T, width), torch.float32)
-        linear(ctx, h, self.w_qkv, qkv, self.b_qkv, EPI_BIAS if self.qkv_bias else EPI_NONE)
         k_cache, v_cache, table = ctx.kv(cache_layer)
         q = ctx.empty((T, self.H * self.dh))
-        ops.rope_kv_write(qkv, ctx.positions, ctx.tok_req, table, self.rotary.inv_freq, self.rotary.rot_half,
-                          self.rotary.mscale, q, k_cache if write_cache else None,
-                          v_cache if write_cache else None, self.H, self.KV, self.dh, self.rotary.pair_layout)
+        if (ctx.fast and T >= QKV_EPILOGUE_MIN_ROWS and self.rotary.pair_layout == 0 and self.rotary.rot_half * 2 == self.dh
+                and ops.qkv_rope_tc_supported(h, self.w_qkv, self.H, self.KV, self.dh, k_cache.shape[2])):
+            # many rows: bias, rotation and the writes of q, k and v are the epilogue of the joined product
+            cs, sn = self.rotary.step_table(ctx)
+            ops.qkv_rope_tc(h, self.w_qkv, self.b_qkv if self.qkv_bias else None, ctx.positions, ctx.tok_req, table, cs, sn,
+                            q, k_cache if write_cache else None, v_cache if write_cache else None, self.H, self.KV, self.dh)
+        else:
+            qkv = ctx.empty((T, width), torch.float32)
+            linear(ctx, h, self.w_qkv, qkv, self.b_qkv, EPI_BIAS if self.qkv_bias else EPI_NONE)
+            ops.rope_kv_write(qkv, ctx.positions, ctx.tok_req, table, self.rotary.inv_freq, self.rotary.rot_half,
+                              self.rotary.mscale, q, k_cache if write_cache else None,
+                              v_cache if write_cache else None, self.H, self.KV, self.dh, self.rotary.pair_layout)
         attn = ctx.empty((T, self.H * self.dh))
         self.attend(ctx, q, k_cache, v_cache, table, attn)
         self.project_out(ctx, attn, residual)

@@ -73,6 +73,7 @@ class DecoderModel(Part):
 
     def forward(self, ctx) -> torch.Tensor:
         """Runs the tokens of `ctx` through every layer and returns 32-bit logits at `ctx.logit_rows`."""
+        ctx.memo.clear()                        # a context may be run again (before a capture, at a replay's capture): nothing is carried over
         x = self.embedding.forward(ctx)
         for call in self.schedule:
             self.blocks[call.block].forward(ctx, x, call.cache, call.write_cache)

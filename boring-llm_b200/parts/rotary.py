@@ -37,3 +37,12 @@ class RotaryTable:
     def to(self, device):
         self.inv_freq = torch.from_numpy(self.inv_freq_host).to(device)
         return self
+
+    def step_table(self, ctx):
+        """(cos, sin), float32 [T, rot_half] each, of the step's tokens: worked out by the first layer that asks and
+        kept in the step's memo for the others (the positions are the same for every layer)."""
+        key = ("rotary table", id(self))
+        if key not in ctx.memo:
+            from ..kernels import ops
+            ctx.memo[key] = ops.rope_table(ctx.positions, self.inv_freq, self.rot_half, self.mscale)
+        return ctx.memo[key]

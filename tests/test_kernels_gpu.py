@@ -758,3 +758,64 @@ def test_norm_qkv_rope_fused(H, KV, dh, d, bias, layout):
     q_only = torch.empty_like(q)
     o.norm_qkv_rope(x, nw, 1e-6, w, b, s2["positions"], s2["tok_req"], s2["table"], inv, 1.0, q_only, None, None, H, KV, dh, layout)
     assert torch.equal(q_only, q)
+
+
+@pytest.mark.parametrize("H,KV,dh,d,bias", [(14, 2, 64, 896, True), (6, 2, 64, 136, False), (2, 1, 128, 200, True), (16, 2, 128, 264, True), (3, 3, 64, 72, True)])
+def test_qkv_rope_in_the_epilogue_of_the_tcgen05_product(H, KV, dh, d, bias):
+    """The joined q/k/v product on pairs of SMs with bias, rotation and the writes of q, k and v in its epilogue,
+    against the three kernels it replaces (product with bias, rotation + cache write) and their float64 formulas:
+    prompts of several requests over existing caches, 700 rows (tiles that overhang M), heads that sit in the same
+    128-column tile as the first key head, and the untouched rest of both pools."""
+    o = ops()
+    bf = torch.bfloat16
+    page = 16
+    ctx_lens, q_lens = [300, 640, 77, 1], [300, 333, 66, 1]
+    s = paged_setup(ctx_lens, q_lens, KV, dh, page, bf, 9)
+    s2 = paged_setup(ctx_lens, q_lens, KV, dh, page, bf, 9)
+    before_k, before_v = s2["kc"].clone(), s2["vc"].clone()
+    T = s["T"]
+    x = (data((T, d), 41) * 0.5).to(bf)
+    w = (data(((H + 2 * KV) * dh, d), 43) * 0.2).to(bf)
+    b = (data(((H + 2 * KV) * dh,), 44) * 0.5).to(bf) if bias else None
+    assert o.qkv_rope_tc_supported(x, w, H, KV, dh, page)
+    j = np.arange(dh // 2, dtype=np.float32)
+    inv = torch.from_numpy(np.float32(1.0) / np.power(np.float32(1.0e4), (np.float32(2.0) * j) / np.float32(dh), dtype=np.float32)).to(DEV)
+    # unfused
+    qkv = torch.empty(T, (H + 2 * KV) * dh, device=DEV)
+    o.gemm_plain(x, w, qkv, b, o.EPI_BIAS if bias else o.EPI_NONE)
+    q_ref = torch.empty(T, H * dh, dtype=bf, device=DEV)
+    o.rope_kv_write(qkv, s["positions"], s["tok_req"], s["table"], inv, dh // 2, 0.75, q_ref, s["kc"], s["vc"], H, KV, dh, 0)
+    # the table holds what the kernels that rotate on the fly work out
+    cs, sn = o.rope_table(s2["positions"], inv, dh // 2, 0.75)
+    ang = s2["positions"].cpu().float()[:, None] * inv.cpu()[None, :]
+    assert torch.allclose(cs.cpu(), torch.cos(ang.double()).float() * 0.75, atol=2e-6)
+    assert torch.allclose(sn.cpu(), torch.sin(ang.double()).float() * 0.75, atol=2e-6)
+    # fused
+    q = torch.full((T, H * dh), float("nan"), dtype=bf, device=DEV)
+    o.qkv_rope_tc(x, w, b, s2["positions"], s2["tok_req"], s2["table"], cs, sn, q, s2["kc"], s2["vc"], H, KV, dh)
+    o.check_status()
+    close(q, q_ref.double(), bf, "q")
+    # against the formulas: q of one row
+    xd, wd = x.double().cpu(), w.double().cpu()
+    t_chk = T - 2
+    row = xd[t_chk] @ wd.T + (b.double().cpu() if bias else 0.0)
+    qh = row[:H * dh].view(1, H, dh)
+    want = plain.rope_neox(qh, s["positions_np"][t_chk:t_chk + 1], inv.cpu().numpy()) * 1.0
+    # (the scale of cos and sin, 0.75, multiplies the rotated head)
+    close(q[t_chk].view(1, H, dh), want * 0.75, bf, "q against the formula")
+    touched = torch.zeros(s["kc"].shape[0], page, dtype=torch.bool)
+    rows_k = torch.empty(T, KV, dh, dtype=bf, device=DEV); rows_k2 = torch.empty_like(rows_k)
+    rows_v = torch.empty_like(rows_k); rows_v2 = torch.empty_like(rows_k)
+    for t in range(T):
+        pg = int(s["table_np"][s["tok_req_np"][t], s["positions_np"][t] // page]); r = int(s["positions_np"][t]) % page
+        rows_k[t], rows_k2[t], rows_v[t], rows_v2[t] = s["kc"][pg, :, r, :], s2["kc"][pg, :, r, :], s["vc"][pg, :, r, :], s2["vc"][pg, :, r, :]
+        touched[pg, r] = True
+    assert rows_k.abs().max().item() < 1.0e3, "the unfused kernels did not write these rows either"
+    close(rows_k2, rows_k.double(), bf, "keys")
+    close(rows_v2, rows_v.double(), bf, "values")
+    mask = touched.to(DEV)[:, None, :, None].expand_as(s2["kc"])
+    assert torch.equal(s2["kc"][~mask], before_k[~mask]) and torch.equal(s2["vc"][~mask], before_v[~mask])
+    q_only = torch.empty_like(q)
+    o.qkv_rope_tc(x, w, b, s2["positions"], s2["tok_req"], s2["table"], cs, sn, q_only, None, None, H, KV, dh)
+    assert torch.equal(q_only, q)
+    o.check_status()
