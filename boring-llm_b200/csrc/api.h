@@ -114,10 +114,21 @@ int bl_rope_table(const int* positions, const float* inv_freq, int rot_half, flo
 // [M, dh / 2] from bl_rope_table) and the writes of q and of k and v into the pages of each token's request folded
 // into its epilogue. Head size 64 or 128, pages of 16; null caches: nothing is cached; bias may be null.
 int bl_gemm_tc_pair_qkv_rope_supported(int H, int KV, int dh, int page_size, int K);
+// ss != null: x holds rows whose RMS norm is pending (bl_gemm_tc_pair_residual_norm); row m of the product is scaled
+// by 1 / sqrt(sum(ss[m, :parts]) * inv_dim + eps) before the bias.
 int bl_gemm_tc_pair_qkv_rope(const void* x, const void* w, const void* bias, int bias_dtype, int M, int K,
                              const int* tok_req, const int* positions, const int* block_table, int max_pages,
                              const float* cs, const float* sn, void* q_out, void* k_cache, void* v_cache,
-                             int H, int KV, int dh, int page_size, void* stream);
+                             int H, int KV, int dh, int page_size, const float* ss, int parts, float inv_dim, float eps,
+                             void* stream);
+// An RMS norm between two products without a pass of its own: the product that adds into the 32-bit residual stream
+// also writes hw = bfloat16(out * norm_w) and per-row sums of squares by tile (ss[M, bl_gemm_tc_pair_norm_parts(M, N)]);
+// the products that read the normed rows take hw and scale their accumulator rows by the row's 1 / sqrt(mean + eps).
+int bl_gemm_tc_pair_norm_parts(int M, int N);
+int bl_gemm_tc_pair_residual_norm(const void* x, const void* w, void* out, int M, int N, int K, const void* norm_w,
+                                  int norm_w_dtype, void* hw, float* ss, void* stream);
+int bl_gemm_tc_pair_swiglu_scaled(const void* hw, const void* w, void* out, int M, int N, int K, const float* ss,
+                                  int parts, float inv_dim, float eps, void* stream);
 
 // Matrix product for many rows (prefill) on tcgen05 tensor cores with TMA-fed shared-memory tiles and the
 // accumulator in tensor memory. bfloat16 x[M, K] and W[N, K]; K a multiple of 8, x and W 16-byte aligned.

@@ -67,6 +67,17 @@ struct QkvOut {
     int H, KV, dh;
 };
 
+// An RMS norm between two products, without a pass of its own. The product that adds into the residual stream
+// (producer) also writes the new stream times the norm's weight as bfloat16 rows (hw) and, per row, the sums of
+// squares of its tiles' columns (ss_out: [M, 2 * tiles], one value per tile and epilogue warp, always added in the
+// same order); the product that reads the normed rows (consumer: SwiGLU, or q/k/v with rotation) takes hw as its x
+// and multiplies each accumulator row by 1 / sqrt(sum of the row's ss_in / dim + eps): the row's scale commutes with
+// the product. Statistics and scale are 32-bit.
+struct NormLink {
+    const void* norm_w; int norm_w_dtype; __nv_bfloat16* hw; float* ss_out;      // producer (null hw: none)
+    const float* ss_in; int parts_in; float inv_dim, eps;                        // consumer (null ss_in: none)
+};
+
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
         uint32_t ok;
@@ -108,7 +119,7 @@ template <int EPI, typename TO, int BN>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const void* __restrict__ bias, int bias_dtype, TO* __restrict__ out, int M, int N, int K,
-                    int m_pairs, int n_tiles, const QkvOut qo) {
+                    int m_pairs, int n_tiles, const QkvOut qo, const NormLink nl) {
     constexpr bool GLU = EPI == BL_EPI_SWIGLU;
     constexpr int STAGE_BYTES = stage_bytes(BN), STAGES = stages_for(BN), KS = ksub(BN), B_BYTES = b_bytes(BN);
     static_assert(STAGES <= MAX_STAGES && STAGES * STAGE_BYTES <= RING_BYTES && STAGE_BYTES % 1024 == 0, "ring does not fit");
@@ -231,6 +242,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // words a lane needs for a chunk are requested before the chunk's accumulator is fetched (for the first
             // chunk: before the accumulator is even waited for), so that their trip to L2 is not paid row by row.
             constexpr bool PRELOAD = EPI == BL_EPI_RESIDUAL && sizeof(TO) == 4;
+            // consumer of a pending norm: the scale of this lane's row (a lane owns a row where the accumulator is read)
+            float row_scale = 1.0f;
+            if ((GLU || EPI == EPI_QKV_ROPE) && nl.ss_in != nullptr) {
+                const int m = m0 + quarter * 32 + lane;
+                if (m < M) {
+                    float sum = 0.f;
+                    for (int q = 0; q < nl.parts_in; ++q) sum += nl.ss_in[(size_t)m * nl.parts_in + q];
+                    row_scale = rsqrtf(sum * nl.inv_dim + nl.eps);
+                }
+            }
+            float ssum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};     // producer of a pending norm: sums of squares of this lane's columns, per row
             float4 res[8];
             auto preload = [&](int c) {
 #pragma unroll
@@ -316,7 +338,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         float ba = __uint_as_float((e & 1) ? (wl & 0xffff0000u) : (wl << 16));
                         float bb = __uint_as_float((e & 1) ? (wh & 0xffff0000u) : (wh << 16));
                         if (b32) { ba = reinterpret_cast<const float*>(bias)[n_lo + j + e]; bb = reinterpret_cast<const float*>(bias)[n_lo + half_cols + j + e]; }
-                        const float x0 = __uint_as_float(lo[j + e]) + ba, x1 = __uint_as_float(hi[j + e]) + bb;
+                        const float x0 = __uint_as_float(lo[j + e]) * row_scale + ba, x1 = __uint_as_float(hi[j + e]) * row_scale + bb;
                         a[e] = x0 * c[e] - x1 * sv[e];
                         b[e] = x0 * sv[e] + x1 * c[e];
                     }
@@ -357,7 +379,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tmem_ld32(lane_addr + BN / 2 + c * 32, u);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(bl_silu_fast(__uint_as_float(r[j])) * __uint_as_float(u[j]));
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(bl_silu_fast(__uint_as_float(r[j]) * row_scale) * (__uint_as_float(u[j]) * row_scale));
                 } else {
                     tmem_ld_wait();
                 }
@@ -371,6 +393,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     b4 = make_float4(bl_load_any(bias, bias_dtype, n), bl_load_any(bias, bias_dtype, n + 1),
                                      bl_load_any(bias, bias_dtype, n + 2), bl_load_any(bias, bias_dtype, n + 3));
                 }
+                const bool link = EPI == BL_EPI_RESIDUAL && nl.hw != nullptr;
+                float4 nw4 = make_float4(0.f, 0.f, 0.f, 0.f);              // the norm's weight of this lane's four columns
+                if (link && n0 + c * 32 + c4 + 3 < N) {
+                    const int n = n0 + c * 32 + c4;
+                    nw4 = make_float4(bl_load_any(nl.norm_w, nl.norm_w_dtype, n), bl_load_any(nl.norm_w, nl.norm_w_dtype, n + 1),
+                                      bl_load_any(nl.norm_w, nl.norm_w_dtype, n + 2), bl_load_any(nl.norm_w, nl.norm_w_dtype, n + 3));
+                }
 #pragma unroll
                 for (int it2 = 0; it2 < 8; ++it2) {
                     const int row = it2 * 4 + r_sub;
@@ -383,6 +412,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         if (EPI == BL_EPI_BIAS) { v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w; }
                         if (sizeof(TO) == 4) {
                             if (EPI == BL_EPI_RESIDUAL) { v.x += res[it2].x; v.y += res[it2].y; v.z += res[it2].z; v.w += res[it2].w; }
+                            if (link) {
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(v.x * nw4.x, v.y * nw4.y), h1 = __floats2bfloat162_rn(v.z * nw4.z, v.w * nw4.w);
+                                uint2 hk;
+                                hk.x = *reinterpret_cast<unsigned*>(&h0); hk.y = *reinterpret_cast<unsigned*>(&h1);
+                                *reinterpret_cast<uint2*>(nl.hw + (size_t)m * N + n) = hk;
+                                ssum[it2] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                            }
                             *reinterpret_cast<float4*>(dst) = v;
                         } else {
                             __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
@@ -405,6 +441,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 __syncwarp();
                 if (PRELOAD && c + 2 < CHUNKS) preload(c + 2);           // on its way while the next accumulator chunk is fetched
             }
+            if (EPI == BL_EPI_RESIDUAL && nl.hw != nullptr) {
+                // the eight lanes that share a row add up; one value per row, tile and epilogue warp of the quarter
+                const int parts = 2 * n_tiles, part = (t / m_pairs) * 2 + half;
+#pragma unroll
+                for (int it2 = 0; it2 < 8; ++it2) {
+                    float q = ssum[it2];
+                    q += __shfl_xor_sync(0xffffffffu, q, 1);
+                    q += __shfl_xor_sync(0xffffffffu, q, 2);
+                    q += __shfl_xor_sync(0xffffffffu, q, 4);
+                    const int m = m0 + quarter * 32 + it2 * 4 + r_sub;
+                    if ((lane & 7) == 0 && m < M) nl.ss_out[(size_t)m * parts + part] = q;
+                }
+            }
             // this warp is done with the buffer: tell the issuer (in the leader block)
             fence_before_sync();
             __syncwarp();
@@ -423,7 +472,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 template <int EPI, typename TO, int BN>
 int launch_bn(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K, int sms,
-              cudaStream_t s, const QkvOut& qo = QkvOut()) {
+              cudaStream_t s, const QkvOut& qo = QkvOut(), const NormLink& nl = NormLink()) {
     static bool configured = false;
     if (!configured) {
         BL_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI, TO, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
@@ -451,7 +500,7 @@ int launch_bn(const void* x, const void* w, const void* bias, int bias_dtype, vo
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = bl_pdl_enabled() ? 1 : 0;
     cfg.attrs = attr; cfg.numAttrs = 2;
-    BL_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<EPI, TO, BN>, a, b, bias, bias_dtype, (TO*)out, M, N, K, m_pairs, n_tiles, qo));
+    BL_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<EPI, TO, BN>, a, b, bias, bias_dtype, (TO*)out, M, N, K, m_pairs, n_tiles, qo, nl));
     return 0;
 }
 
@@ -468,13 +517,14 @@ int sm_count() {
 
 // 256-column tiles unless they would leave SM pairs without a tile while 128-column tiles would not.
 template <int EPI, typename TO>
-int launch(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K, cudaStream_t s) {
+int launch(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K, cudaStream_t s,
+           const NormLink& nl = NormLink()) {
     const int sms = sm_count();
     const int cols256 = EPI == BL_EPI_SWIGLU ? 128 : 256;
     const int m_pairs = (M + 2 * BM - 1) / (2 * BM);
     const int tiles256 = m_pairs * ((N + cols256 - 1) / cols256);
-    if (tiles256 < sms / 2) return launch_bn<EPI, TO, 128>(x, w, bias, bias_dtype, out, M, N, K, sms, s);
-    return launch_bn<EPI, TO, 256>(x, w, bias, bias_dtype, out, M, N, K, sms, s);
+    if (tiles256 < sms / 2) return launch_bn<EPI, TO, 128>(x, w, bias, bias_dtype, out, M, N, K, sms, s, QkvOut(), nl);
+    return launch_bn<EPI, TO, 256>(x, w, bias, bias_dtype, out, M, N, K, sms, s, QkvOut(), nl);
 }
 
 }  // namespace
@@ -509,6 +559,44 @@ extern "C" int bl_gemm_tc_pair(const void* x, const void* w, const void* bias, i
     BL_FAIL("bl_gemm_tc_pair: unknown epilogue %d", epilogue);
 }
 
+// Values per row that bl_gemm_tc_pair_residual_norm writes into `ss` for these sizes (two per tile of columns).
+extern "C" int bl_gemm_tc_pair_norm_parts(int M, int N) {
+    const int sms = sm_count();
+    const int m_pairs = (M + 2 * BM - 1) / (2 * BM);
+    const int cols = m_pairs * ((N + 255) / 256) < sms / 2 ? 128 : 256;
+    return 2 * ((N + cols - 1) / cols);
+}
+
+// out (float32, in place) += x . W^T, as bl_gemm_tc_pair with the residual epilogue, and for the RMS norm that reads
+// `out` next: hw[M, N] = bfloat16(out * norm_w) and ss[M, parts] = sums of squares of out's columns by tile (parts =
+// bl_gemm_tc_pair_norm_parts(M, N)). A product that takes hw as its x and scales its rows by
+// 1 / sqrt(sum(ss[m, :]) / N + eps) computes what it would from the normed rows. N must be a multiple of 4.
+extern "C" int bl_gemm_tc_pair_residual_norm(const void* x, const void* w, void* out, int M, int N, int K, const void* norm_w,
+                                             int norm_w_dtype, void* hw, float* ss, void* stream) {
+    if (M <= 0) return 0;
+    if (N <= 0 || K <= 0 || N % 4 != 0) BL_FAIL("bl_gemm_tc_pair_residual_norm: bad sizes N=%d K=%d (N a multiple of 4)", N, K);
+    if (K % 8 != 0) BL_FAIL("bl_gemm_tc_pair_residual_norm: K=%d is not a multiple of 8", K);
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out | (uintptr_t)hw) & 15) BL_FAIL("bl_gemm_tc_pair_residual_norm: x, W, out and hw must be 16-byte aligned");
+    if (norm_w == nullptr || (norm_w_dtype != BL_F32 && norm_w_dtype != BL_BF16) || hw == nullptr || ss == nullptr)
+        BL_FAIL("bl_gemm_tc_pair_residual_norm: needs the norm's weight (float32 or bfloat16), hw and ss");
+    NormLink nl = NormLink();
+    nl.norm_w = norm_w; nl.norm_w_dtype = norm_w_dtype; nl.hw = (__nv_bfloat16*)hw; nl.ss_out = ss;
+    return launch<BL_EPI_RESIDUAL, float>(x, w, nullptr, 0, out, M, N, K, (cudaStream_t)stream, nl);
+}
+
+// out[M, N] (bfloat16) = silu(r g) * (r u) with g, u = hw . Wg^T, hw . Wu^T and r[m] = 1 / sqrt(sum(ss[m, :parts]) * inv_dim + eps):
+// the SwiGLU product of the rows whose norm bl_gemm_tc_pair_residual_norm left pending.
+extern "C" int bl_gemm_tc_pair_swiglu_scaled(const void* hw, const void* w, void* out, int M, int N, int K, const float* ss,
+                                             int parts, float inv_dim, float eps, void* stream) {
+    if (M <= 0) return 0;
+    if (N <= 0 || K <= 0 || K % 8 != 0) BL_FAIL("bl_gemm_tc_pair_swiglu_scaled: bad sizes N=%d K=%d", N, K);
+    if (((uintptr_t)hw | (uintptr_t)w) & 15) BL_FAIL("bl_gemm_tc_pair_swiglu_scaled: x and W must be 16-byte aligned");
+    if (ss == nullptr || parts <= 0) BL_FAIL("bl_gemm_tc_pair_swiglu_scaled: needs the rows' sums of squares");
+    NormLink nl = NormLink();
+    nl.ss_in = ss; nl.parts_in = parts; nl.inv_dim = inv_dim; nl.eps = eps;
+    return launch<BL_EPI_SWIGLU, __nv_bfloat16>(hw, w, nullptr, 0, out, M, N, K, (cudaStream_t)stream, nl);
+}
+
 // Whether bl_gemm_tc_pair_qkv_rope takes this layer: head size 64 or 128, pages of 16, K as for the other products.
 extern "C" int bl_gemm_tc_pair_qkv_rope_supported(int H, int KV, int dh, int page_size, int K) {
     return (dh == 64 || dh == 128) && page_size == 16 && H > 0 && KV > 0 && K % 8 == 0;
@@ -520,7 +608,8 @@ extern "C" int bl_gemm_tc_pair_qkv_rope_supported(int H, int KV, int dh, int pag
 extern "C" int bl_gemm_tc_pair_qkv_rope(const void* x, const void* w, const void* bias, int bias_dtype, int M, int K,
                                         const int* tok_req, const int* positions, const int* block_table, int max_pages,
                                         const float* cs, const float* sn, void* q_out, void* k_cache, void* v_cache,
-                                        int H, int KV, int dh, int page_size, void* stream) {
+                                        int H, int KV, int dh, int page_size, const float* ss, int parts, float inv_dim,
+                                        float eps, void* stream) {
     if (M <= 0) return 0;
     if (!bl_gemm_tc_pair_qkv_rope_supported(H, KV, dh, page_size, K))
         BL_FAIL("bl_gemm_tc_pair_qkv_rope: head size %d, pages of %d, %d + 2 x %d heads, K = %d is not built", dh, page_size, H, KV, K);
@@ -533,7 +622,9 @@ extern "C" int bl_gemm_tc_pair_qkv_rope(const void* x, const void* w, const void
     qo.tok_req = tok_req; qo.positions = positions; qo.block_table = block_table; qo.max_pages = max_pages;
     qo.cs = cs; qo.sn = sn; qo.q = (__nv_bfloat16*)q_out; qo.k_cache = (__nv_bfloat16*)k_cache; qo.v_cache = (__nv_bfloat16*)v_cache;
     qo.H = H; qo.KV = KV; qo.dh = dh;
-    return launch_bn<EPI_QKV_ROPE, __nv_bfloat16, 128>(x, w, bias, bias_dtype, nullptr, M, (H + 2 * KV) * dh, K, sm_count(), (cudaStream_t)stream, qo);
+    NormLink nl = NormLink();                     // x may be rows whose norm is pending (ss != null): see bl_gemm_tc_pair_residual_norm
+    if (ss != nullptr) { nl.ss_in = ss; nl.parts_in = parts; nl.inv_dim = inv_dim; nl.eps = eps; }
+    return launch_bn<EPI_QKV_ROPE, __nv_bfloat16, 128>(x, w, bias, bias_dtype, nullptr, M, (H + 2 * KV) * dh, K, sm_count(), (cudaStream_t)stream, qo, nl);
 }
 
 extern "C" int bl_gemm_tc_pair_status(int* status) {

@@ -207,9 +207,12 @@ def qkv_rope_tc_supported(x: torch.Tensor, w: torch.Tensor, H: int, KV: int, dh:
 
 def qkv_rope_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
                 tok_req: torch.Tensor, block_table: torch.Tensor, cs: torch.Tensor, sn: torch.Tensor, q_out: torch.Tensor,
-                k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], H: int, KV: int, dh: int) -> None:
+                k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], H: int, KV: int, dh: int,
+                row_sums: Optional[torch.Tensor] = None, eps: float = 0.0) -> None:
     """The joined q/k/v product of many rows on pairs of SMs (tcgen05) with bias, rotation (pairs j, j + dh / 2, from
-    the step's table `rope_table`) and the writes of q and of k and v into the requests' pages in its epilogue."""
+    the step's table `rope_table`) and the writes of q and of k and v into the requests' pages in its epilogue.
+    `row_sums` (with `eps`): x holds rows whose RMS norm is pending (`gemm_residual_norm`); the product's rows are
+    scaled by 1 / sqrt(row_sums[m].sum() / K + eps) before the bias."""
     M, K = x.shape
     _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16, ((H + 2 * KV) * dh, K))
     _need(positions, "positions", torch.int32, (M,)); _need(tok_req, "tok_req", torch.int32, (M,))
@@ -226,7 +229,8 @@ def qkv_rope_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
         page_size = k_cache.shape[2]
     _call(_lib().bl_gemm_tc_pair_qkv_rope, _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0, M, K, _p(tok_req),
           _p(positions), _p(block_table), block_table.shape[1], _p(cs), _p(sn), _p(q_out), _p(k_cache), _p(v_cache),
-          H, KV, dh, page_size, _stream())
+          H, KV, dh, page_size, _p(row_sums), 0 if row_sums is None else row_sums.shape[1], ctypes.c_float(1.0 / K),
+          ctypes.c_float(eps), _stream())
 
 
 def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_req: torch.Tensor,
@@ -558,6 +562,47 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[tor
         gemm_tc(x, w, out, bias, epilogue)
     else:
         gemm_tc_pair(x, w, out, bias, epilogue)
+
+
+def gemm_on_pairs(x: torch.Tensor, w: torch.Tensor, N: int, epilogue: int, fast: bool = True) -> bool:
+    """Whether `gemm` would run this product on pairs of SMs (`gemm_tc_pair`): the kernel whose epilogues can leave an
+    RMS norm pending (`gemm_residual_norm`) and apply a pending one (`gemm_swiglu_scaled`, `qkv_rope_tc`)."""
+    if not (fast and gemm_skinny_supported(x, w)):
+        return False
+    M, K = x.shape
+    if M < PAIR_MIN_ROWS:
+        return False
+    return not (epilogue != EPI_SWIGLU and M <= SPLITK_MAX_ROWS and (K >= SPLITK_LONG_K or 64 < M <= 128)
+                and gemm_tc_splitk_split(M, N, K, epilogue) >= 2)
+
+
+def gemm_residual_norm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, norm_w: torch.Tensor):
+    """out += x @ w.T (32-bit residual stream, in place) on pairs of SMs, and, for the RMS norm with weight `norm_w`
+    that reads `out` next, (hw, ss): hw = bfloat16(out * norm_w) and ss[m, :] = sums of squares of row m's columns by
+    tile. A product that takes hw as its x and scales its rows by 1 / sqrt(ss[m].sum() / N + eps) computes what it would
+    from the normed rows (`gemm_swiglu_scaled`, `qkv_rope_tc` with `row_sums`)."""
+    M, K = x.shape
+    N = out.shape[1]
+    _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16, (N, K)); _need(out, "out", torch.float32, (M, N))
+    _need(norm_w, "norm_w", None, (N,))
+    parts = int(_lib().bl_gemm_tc_pair_norm_parts(M, N))
+    hw = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    ss = torch.empty((M, parts), dtype=torch.float32, device=x.device)
+    _call(_lib().bl_gemm_tc_pair_residual_norm, _p(x), _p(w), _p(out), M, N, K, _p(norm_w), _dt(norm_w), _p(hw), _p(ss), _stream())
+    return hw, ss
+
+
+def gemm_swiglu_scaled(hw: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ss: torch.Tensor, eps: float) -> None:
+    """out = silu(r g) * (r u), g and u the two halves of hw @ w.T, r[m] = 1 / sqrt(ss[m].sum() / K + eps): the SwiGLU
+    product of rows whose RMS norm `gemm_residual_norm` left pending."""
+    M, K = hw.shape
+    N = out.shape[1]
+    _need(hw, "hw", torch.bfloat16); _need(w, "w", torch.bfloat16, (2 * N, K)); _need(out, "out", torch.bfloat16, (M, N))
+    _need(ss, "ss", torch.float32)
+    if ss.shape[0] != M:
+        raise KernelError("gemm_swiglu_scaled: ss and hw differ in rows")
+    _call(_lib().bl_gemm_tc_pair_swiglu_scaled, _p(hw), _p(w), _p(out), M, N, K, _p(ss), ss.shape[1], ctypes.c_float(1.0 / K),
+          ctypes.c_float(eps), _stream())
 
 
 def check_status() -> None:

@@ -10,7 +10,7 @@ import torch
 from ..cache import PagedKVSpec
 from ..kernels import ops
 from ..weights import TensorSpec, MATRIX, BIAS
-from .base import Part, StepPlan, to_device_matrix, to_device_vector
+from .base import PendingNormRows, Part, StepPlan, to_device_matrix, to_device_vector
 from .linear import linear, EPI_BIAS, EPI_NONE, EPI_RESIDUAL
 from .norm import RMSNorm
 from .rotary import RotaryTable
@@ -101,6 +101,7 @@ class GQAAttention(Mixer):
     out.Wo^T added to the residual stream (src/model.br:1328-1334).
     """
     graph_safe = True
+    takes_pending_norm = True            # its first product can finish an RMS norm that the product before has begun
 
     def __init__(self, dim: int, n_heads: int, n_kv_heads: int, head_dim: int, rotary: Optional[RotaryTable],
                  names: Dict[str, str], qkv_bias: bool = True, out_bias: bool = False, window: int = 0,
@@ -147,13 +148,19 @@ class GQAAttention(Mixer):
         width = (self.H + 2 * self.KV) * self.dh
         k_cache, v_cache, table = ctx.kv(cache_layer)
         q = ctx.empty((T, self.H * self.dh))
+        pending = h if isinstance(h, PendingNormRows) else None
+        rows = pending.rows if pending is not None else h
         if (ctx.fast and T >= QKV_EPILOGUE_MIN_ROWS and self.rotary.pair_layout == 0 and self.rotary.rot_half * 2 == self.dh
-                and ops.qkv_rope_tc_supported(h, self.w_qkv, self.H, self.KV, self.dh, k_cache.shape[2])):
-            # many rows: bias, rotation and the writes of q, k and v are the epilogue of the joined product
+                and ops.qkv_rope_tc_supported(rows, self.w_qkv, self.H, self.KV, self.dh, k_cache.shape[2])):
+            # many rows: bias, rotation and the writes of q, k and v are the epilogue of the joined product (and the
+            # scale of a norm that the product before has begun)
             cs, sn = self.rotary.step_table(ctx)
-            ops.qkv_rope_tc(h, self.w_qkv, self.b_qkv if self.qkv_bias else None, ctx.positions, ctx.tok_req, table, cs, sn,
-                            q, k_cache if write_cache else None, v_cache if write_cache else None, self.H, self.KV, self.dh)
+            ops.qkv_rope_tc(rows, self.w_qkv, self.b_qkv if self.qkv_bias else None, ctx.positions, ctx.tok_req, table, cs, sn,
+                            q, k_cache if write_cache else None, v_cache if write_cache else None, self.H, self.KV, self.dh,
+                            row_sums=pending.sums if pending is not None else None, eps=pending.eps if pending is not None else 0.0)
         else:
+            if pending is not None:
+                h = pending.normed(ctx)
             qkv = ctx.empty((T, width), torch.float32)
             linear(ctx, h, self.w_qkv, qkv, self.b_qkv, EPI_BIAS if self.qkv_bias else EPI_NONE)
             ops.rope_kv_write(qkv, ctx.positions, ctx.tok_req, table, self.rotary.inv_freq, self.rotary.rot_half,

@@ -103,6 +103,21 @@ class StepPlan:
     shape: tuple = ()
 
 
+class PendingNormRows:
+    """Rows whose RMS norm has been begun by the product that wrote the residual stream and is finished by the product
+    that reads them: `rows` = bfloat16(stream * norm weight), `sums` [T, parts] = sums of squares of each row of the
+    stream (in parts, added in a fixed order), `eps` and the norm it is. A part that cannot take them asks for
+    `normed(ctx)`, which runs the norm's own kernel on the stream."""
+
+    def __init__(self, rows, sums, norm, stream):
+        self.rows, self.sums, self.norm, self.stream = rows, sums, norm, stream
+        self.eps = norm.eps
+        self.shape = rows.shape
+
+    def normed(self, ctx):
+        return self.norm.forward(ctx, self.stream)
+
+
 @dataclass
 class StepContext:
     """Everything a part may look at while one step runs. Device tensors are int32.
@@ -129,6 +144,8 @@ class StepContext:
     fast: bool = True                  # False: plain kernels only (the twins)
     plans: dict = field(default_factory=dict)      # key -> StepPlan: what parts worked out on the host for this step
     memo: dict = field(default_factory=dict)       # what a part works out once per step and its other layers reuse
+    next_norm: object = None                       # the norm that reads the residual stream after the part that runs now (or None)
+    norm_after_block: object = None                # ... after the block that runs now
 
     @property
     def max_q_len(self) -> int:

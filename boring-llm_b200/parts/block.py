@@ -26,9 +26,23 @@ class PreNormBlock(Part):
 
     def forward(self, ctx, x, cache_layer: Optional[int], write_cache: bool = True) -> None:
         # a mixer or feed-forward may take the norm in front of it into its first kernel (steps with few rows)
+        # (and the product that adds into the stream may begin the norm that reads it next: ctx.next_norm says which,
+        # and a part that can finish such a norm says so with `takes_pending_norm`)
+        ctx.next_norm = self.ffn_norm
         if not self.mixer.forward_fused_norm(ctx, x, self.mixer_norm, cache_layer, write_cache):
-            h = self.mixer_norm.forward(ctx, x)
+            h = self._normed(ctx, self.mixer_norm, x, self.mixer)
             self.mixer.forward(ctx, h, x, cache_layer, write_cache)
+        ctx.next_norm = ctx.norm_after_block
         if not self.ffn.forward_fused_norm(ctx, x, self.ffn_norm):
-            h = self.ffn_norm.forward(ctx, x)
+            h = self._normed(ctx, self.ffn_norm, x, self.ffn)
             self.ffn.forward(ctx, h, x)
+        ctx.next_norm = None
+
+    @staticmethod
+    def _normed(ctx, norm, x, reader):
+        if getattr(reader, "takes_pending_norm", False) and hasattr(norm, "dim"):
+            try:
+                return norm.forward(ctx, x, pending_ok=True)
+            except TypeError:                    # a norm part without the option
+                pass
+        return norm.forward(ctx, x)

@@ -33,6 +33,7 @@ class SwiGLU(FeedForward):
     one joined product over [Wg; Wu] (src/model.br:788-792) whose epilogue combines them
     (src/math_gpu.br:2673-2692); the down product adds into the residual stream."""
     graph_safe = True
+    takes_pending_norm = True            # its first product can finish an RMS norm that the product before has begun
 
     def __init__(self, dim: int, hidden: int, names: Dict[str, str]):
         super().__init__(names)

@@ -75,8 +75,12 @@ class DecoderModel(Part):
         """Runs the tokens of `ctx` through every layer and returns 32-bit logits at `ctx.logit_rows`."""
         ctx.memo.clear()                        # a context may be run again (before a capture, at a replay's capture): nothing is carried over
         x = self.embedding.forward(ctx)
-        for call in self.schedule:
+        for i, call in enumerate(self.schedule):
+            # the norm that reads the stream after this block: the next block's first (the final norm reads a few rows only)
+            after = self.blocks[self.schedule[i + 1].block] if i + 1 < len(self.schedule) else None
+            ctx.norm_after_block = getattr(after, "mixer_norm", None)
             self.blocks[call.block].forward(ctx, x, call.cache, call.write_cache)
+        ctx.norm_after_block = None
         if ctx.logit_rows.shape[0] == 0:
             return ctx.empty((0, self.vocab_size), torch.float32)
         fused = getattr(self.head, "forward_fused_norm", None)

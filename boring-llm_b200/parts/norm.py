@@ -22,7 +22,13 @@ class RMSNorm(Part):
     def local_specs(self):
         return {"weight": TensorSpec((self.dim,), NORM)}
 
-    def forward(self, ctx, x: torch.Tensor, row_idx: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, ctx, x: torch.Tensor, row_idx: Optional[torch.Tensor] = None, pending_ok: bool = False):
+        """The normed rows. `pending_ok`: the caller can finish a norm that the product before it has begun; it then
+        gets `PendingNormRows` when the step holds them for this stream and this norm."""
+        if pending_ok and row_idx is None:
+            held = ctx.memo.get(("pending norm", id(x)))
+            if held is not None and held.norm is self:
+                return held
         rows = x.shape[0] if row_idx is None else row_idx.shape[0]
         out = ctx.empty((rows, self.dim))
         ops.rmsnorm(x, self.weight, self.eps, out, row_idx)

@@ -819,3 +819,90 @@ def test_qkv_rope_in_the_epilogue_of_the_tcgen05_product(H, KV, dh, d, bias):
     o.qkv_rope_tc(x, w, b, s2["positions"], s2["tok_req"], s2["table"], cs, sn, q_only, None, None, H, KV, dh)
     assert torch.equal(q_only, q)
     o.check_status()
+
+
+@pytest.mark.parametrize("M,N,K,F", [(2048, 896, 896, 1216), (700, 136, 264, 200), (300, 2048, 128, 320), (1500, 64, 72, 96)])
+def test_rms_norm_shared_between_two_products(M, N, K, F):
+    """The product that adds into the residual stream leaves the next RMS norm pending (rows times the norm's weight
+    in bfloat16, sums of squares by tile), and the products that read the normed rows finish it in their epilogues:
+    against the plain kernels (product, norm, product) and the float64 formulas, with 256- and 128-column tiles,
+    rows and columns that overhang the tiles, and a row of zeros."""
+    o = ops()
+    bf = torch.bfloat16
+    x = (data((M, K), 51) * 0.5).to(bf)
+    w = (data((N, K), 52) * 0.2).to(bf)
+    stream = data((M, N), 53) * 2
+    stream[5] = 0.0
+    x[5] = 0.0                                                # a row whose new stream is all zeros: scale 1 / sqrt(eps)
+    nw = (data((N,), 54) * 0.25 + 1).to(bf)
+    eps = 1e-5
+    assert o.gemm_on_pairs(x, w, N, o.EPI_RESIDUAL)
+    # the plain way
+    ref = stream.clone()
+    o.gemm_tc_pair(x, w, ref, None, o.EPI_RESIDUAL)
+    h_ref = torch.empty(M, N, dtype=bf, device=DEV)
+    o.rmsnorm(ref, nw, eps, h_ref)
+    # the shared way
+    out = stream.clone()
+    hw, ss = o.gemm_residual_norm(x, w, out, nw)
+    o.check_status()
+    assert torch.equal(out, ref)                              # the stream itself is what the residual epilogue writes
+    want = out.double().cpu()
+    close(hw, want * nw.double().cpu(), bf, "stream times weight")
+    close(ss.sum(dim=1), (want * want).sum(dim=1), torch.float32, "sums of squares")
+    scale = torch.rsqrt((want * want).mean(dim=1) + eps)
+    # SwiGLU over the pending rows against SwiGLU over the normed rows
+    wg = (data((2 * F, N), 55) * 0.1).to(bf)
+    act = torch.full((M, F), float("nan"), dtype=bf, device=DEV)
+    o.gemm_swiglu_scaled(hw, wg, act, ss, eps)
+    o.check_status()
+    act_ref = torch.empty(M, F, dtype=bf, device=DEV)
+    o.gemm_tc_pair(h_ref, wg, act_ref, None, o.EPI_SWIGLU)
+    h64 = want * scale[:, None] * nw.double().cpu()
+    wgd = wg.double().cpu()
+    formula = plain.silu(h64 @ wgd[:F].T) * (h64 @ wgd[F:].T)
+    close(act_ref, formula, bf, "SwiGLU of the normed rows (the kernels as they were)")
+    close(act, formula, bf, "SwiGLU that finishes the norm")
+
+
+def test_qkv_product_finishes_a_pending_norm():
+    """`qkv_rope_tc` with `row_sums`: q, keys and values equal those from the normed rows (norm kernel, then the same
+    product) within bfloat16 rounding, and the float64 formula for q."""
+    o = ops()
+    bf = torch.bfloat16
+    H, KV, dh, d, page = 6, 2, 64, 136, 16
+    ctx_lens, q_lens = [400, 300], [400, 290]
+    s = paged_setup(ctx_lens, q_lens, KV, dh, page, bf, 9)
+    s2 = paged_setup(ctx_lens, q_lens, KV, dh, page, bf, 9)
+    T = s["T"]
+    stream = data((T, d), 61) * 3
+    nw = (data((d,), 62) * 0.25 + 1).to(bf)
+    w = (data(((H + 2 * KV) * dh, d), 63) * 0.2).to(bf)
+    b = (data(((H + 2 * KV) * dh,), 64) * 0.5).to(bf)
+    eps = 1e-6
+    inv = torch.from_numpy(np.float32(1.0) / np.power(np.float32(1.0e4), (np.float32(2.0) * np.arange(dh // 2, dtype=np.float32)) / np.float32(dh), dtype=np.float32)).to(DEV)
+    cs, sn = o.rope_table(s["positions"], inv, dh // 2, 1.0)
+    # what the product before would leave: the stream times the weight, and its rows' sums of squares in three parts
+    hw = (stream * nw.float()).to(bf)
+    sq = (stream * stream)
+    ss = torch.stack([sq[:, :40].sum(1), sq[:, 40:100].sum(1), sq[:, 100:].sum(1)], dim=1).contiguous()
+    h = torch.empty(T, d, dtype=bf, device=DEV)
+    o.rmsnorm(stream, nw, eps, h)
+    q_ref = torch.empty(T, H * dh, dtype=bf, device=DEV)
+    o.qkv_rope_tc(h, w, b, s["positions"], s["tok_req"], s["table"], cs, sn, q_ref, s["kc"], s["vc"], H, KV, dh)
+    q = torch.full((T, H * dh), float("nan"), dtype=bf, device=DEV)
+    o.qkv_rope_tc(hw, w, b, s2["positions"], s2["tok_req"], s2["table"], cs, sn, q, s2["kc"], s2["vc"], H, KV, dh, row_sums=ss, eps=eps)
+    o.check_status()
+    sd = stream.double().cpu()
+    h64 = sd * torch.rsqrt((sd * sd).mean(1, keepdim=True) + eps) * nw.double().cpu()
+    row = h64 @ w.double().cpu().T + b.double().cpu()
+    want = plain.rope_neox(row[:, :H * dh].view(T, H, dh), s["positions_np"], inv.cpu().numpy()).reshape(T, H * dh)
+    close(q_ref, want, bf, "q from the normed rows")
+    close(q, want, bf, "q from the pending rows")
+    owned = torch.zeros(s["kc"].shape[0], page, dtype=torch.bool)
+    for t in range(T):
+        owned[int(s["table_np"][s["tok_req_np"][t], s["positions_np"][t] // page]), int(s["positions_np"][t]) % page] = True
+    mask = owned.to(DEV)[:, None, :, None].expand_as(s["kc"])
+    close(s2["kc"][mask], s["kc"][mask].double(), bf, "keys")
+    close(s2["vc"][mask], s["vc"][mask].double(), bf, "values")
+    assert torch.equal(s2["kc"][~mask], s["kc"][~mask])
