@@ -41,7 +41,7 @@ class RotaryTable:
     def step_table(self, ctx):
         """(cos, sin), float32 [T, rot_half] each, of the step's tokens: worked out by the first layer that asks and
         kept in the step's memo for the others (the positions are the same for every layer)."""
-        key = ("rotary table", id(self))
+        key = ("rotary table", self.head_dim, self.base, self.n_rot, self.mscale)     # the layers' tables are equal, not the same object
         if key not in ctx.memo:
             from ..kernels import ops
             ctx.memo[key] = ops.rope_table(ctx.positions, self.inv_freq, self.rot_half, self.mscale)
