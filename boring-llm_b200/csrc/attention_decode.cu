@@ -239,6 +239,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     const uint32_t base = (raw + 1023u) & ~1023u;                 // the swizzle of a TMA box follows the address: tiles start on 1,024 bytes
     unsigned char* gen = smem_raw + (base - raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    if (threadIdx.x == 0) { tma_prefetch_map(&map_k); tma_prefetch_map(&map_v); }
     bl_pdl_trigger();
     // the step's index arrays are written before its first kernel: they may be read before the wait
     const int r = p.reqs[blockIdx.z];

@@ -152,6 +152,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     constexpr int OFF_Q = S::OFF_Q, OFF_K = S::OFF_K, OFF_V = S::OFF_V, OFF_MERGE = S::OFF_MERGE, OFF_XCH = S::OFF_XCH;
     constexpr int OFF_BARS = S::OFF_BARS;
     extern __shared__ __align__(1024) unsigned char smem[];
+    if (threadIdx.x == 0) { tma_prefetch_map(&map_q); tma_prefetch_map(&map_k); tma_prefetch_map(&map_v); }
     const uint32_t base = smem_u32(smem);
     const uint32_t bars = base + OFF_BARS;
     // barriers, 8 bytes each; [i & 1] of block i for all pairs

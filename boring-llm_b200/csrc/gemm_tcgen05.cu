@@ -54,6 +54,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                const void* __restrict__ bias, int bias_dtype, TO* __restrict__ out, int M, int N, int K) {
     constexpr bool GLU = EPI == BL_EPI_SWIGLU;
     extern __shared__ unsigned char smem_raw[];
+    if (threadIdx.x == 0) { tma_prefetch_map(&map_a); tma_prefetch_map(&map_b); }
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;              // tiles need 1024-byte alignment
     unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t bars = base + STAGES * STAGE_BYTES;                         // full[S], empty[S], accum

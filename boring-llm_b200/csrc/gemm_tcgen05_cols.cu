@@ -75,6 +75,7 @@ gemm_tc_cols_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     constexpr int X_TILE = NT * BK * 2;                                       // one k block of x
     constexpr int TMEM_COLS = NT <= 32 ? 64 : 128;                            // two accumulators of NT columns
     extern __shared__ __align__(1024) unsigned char smem[];
+    if (threadIdx.x == 0) { tma_prefetch_map(&map_x); tma_prefetch_map(&map_w); }
     const uint32_t base = smem_u32(smem);
     const int kblocks = (K + BK - 1) / BK;
     const int x_bytes = kblocks * X_TILE;                                     // a multiple of 1024 (NT >= 16)

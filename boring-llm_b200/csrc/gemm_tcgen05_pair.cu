@@ -125,6 +125,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     static_assert(STAGES <= MAX_STAGES && STAGES * STAGE_BYTES <= RING_BYTES && STAGE_BYTES % 1024 == 0, "ring does not fit");
     constexpr int COLS = GLU ? BN / 2 : BN;                          // output columns per tile
     extern __shared__ unsigned char smem_raw[];
+    if (threadIdx.x == 0) { tma_prefetch_map(&map_a); tma_prefetch_map(&map_b); }
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
     float* staging = reinterpret_cast<float*>(aligned + RING_BYTES);

@@ -73,6 +73,7 @@ gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     // kind::f16 instruction descriptor: D 32-bit, A and B bfloat16 and K-major, N >> 3 at bit 17, M >> 4 at bit 24
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     extern __shared__ unsigned char smem_raw[];
+    if (threadIdx.x == 0) { tma_prefetch_map(&map_a); tma_prefetch_map(&map_b); }
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;              // tiles need 1024-byte alignment
     unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t bars = base + RING_BYTES;                                   // full[S], empty[S], accum

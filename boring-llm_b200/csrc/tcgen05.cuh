@@ -32,6 +32,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
                  :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
 
+// Asks for a tensor map to be brought into the TMA unit's descriptor cache (no register, no wait): at the top of a
+// kernel, so that its first copy does not wait for the descriptor.
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" :: "l"(map) : "memory");
+}
+
 // ---- tcgen05 --------------------------------------------------------------------------------------------------
 // D (tensor memory) (+)= A . B, both operands in shared memory, one block
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
