@@ -36,6 +36,7 @@ SIZES = {
 }
 COMMON = dict(architectures=["Qwen2ForCausalLM"], rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=32768)
 CONTEXT = 4096
+LONG_CONTEXT = 32768           # a further decode point (not the headline): the cache of the live requests outweighs the weights
 PREFILL_TOKENS = 2048
 PORTION = 512                     # the reference's default portion of a prompt (-ub, src/cli_config.br:24-25)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -101,12 +102,12 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_engine(sizes, n_layers, max_seqs, cuda_graphs=True):
+def build_engine(sizes, n_layers, max_seqs, cuda_graphs=True, context=CONTEXT):
     import boring_llm_b200 as b
     from boring_llm_b200.config import EngineOptions
     from boring_llm_b200.engine import Engine
     cfg = b.Qwen2Config.from_dict({**COMMON, **SIZES[sizes], "num_hidden_layers": n_layers})
-    opts = EngineOptions(dtype="bfloat16", ctx_size=CONTEXT, max_num_seqs=max_seqs, max_tokens=(CONTEXT + 16) * max_seqs,
+    opts = EngineOptions(dtype="bfloat16", ctx_size=context, max_num_seqs=max_seqs, max_tokens=(context + 16) * max_seqs,
                          max_num_batched_tokens=PREFILL_TOKENS, prefill_chunk=PORTION, cuda_graphs=cuda_graphs)
     return cfg, Engine.from_random(cfg, 0, opts)               # N(0, 0.02) weights made on the device, no file
 
@@ -169,7 +170,8 @@ def check_one_step(eng, reqs):
     return {"ok": True, "rows": len(reqs), "equal": len(reqs) - ties, "near_ties": ties}
 
 
-def measure_decode(eng, batch, steps, warmup, value_regions=3, e2e_regions=0, check=False, seed=1, sampled=False):
+def measure_decode(eng, batch, steps, warmup, value_regions=3, e2e_regions=0, check=False, seed=1, sampled=False,
+                   context=CONTEXT):
     """Decode steps of `batch` requests whose contexts end just below the context size. Returns a dict with the
     device-timed figures (median region of `steps` steps), the wall-clock figures when asked for, the kernels launched
     in a region, the mean context inside the timed regions and the result of the one-step check."""
@@ -178,7 +180,7 @@ def measure_decode(eng, batch, steps, warmup, value_regions=3, e2e_regions=0, ch
     per_step = eng.options.max_num_batched_tokens
     need = warmup + (value_regions + e2e_regions) * steps + 8
     # the requests that finish their prompts first decode while the others are still being prefilled
-    ctx0 = CONTEXT - need
+    ctx0 = context - need
     prefill_steps = -(-batch * ctx0 // per_step) + 2
     ctx0 -= prefill_steps
     reqs = start_requests(eng, [ctx0] * batch, seed, sampled)
@@ -406,6 +408,13 @@ def main():
     pre4_ms, pre4_wall = prefill_timed(eng, [PORTION] * (PREFILL_TOKENS // PORTION))
     mix_ms, mix_wall, mix_host, mix_tokens = mixed_timed(eng)
     cpu_tps = None if args.no_cpu_baseline else cpu_baseline(args.sizes)
+    # a further point: the same batch at eight times the context (an engine of its own: the pool is sized by the context)
+    del eng
+    import gc, torch
+    gc.collect(); torch.cuda.empty_cache()
+    _, eng_long = build_engine(args.sizes, n_layers, args.batch, context=LONG_CONTEXT)
+    mlong = measure_decode(eng_long, args.batch, 16, 3, value_regions=3, seed=5, context=LONG_CONTEXT)
+    del eng_long
     achieved = hbm_frac(args.batch, m8) * pk["hbm_gbs"]
     headline = args.sizes == "0.5b"
     s = SIZES[args.sizes]
@@ -438,6 +447,9 @@ def main():
             "decode_b1_ms": round(m1["ms_per_step"], 4), "decode_b64_ms": round(m64["ms_per_step"], 4),
             "decode_b8_graph_replay_ms": round(m8.get("graph_replay_ms", 0.0), 4),
             "decode_b8_sampled_ms": round(m8s["ms_per_step"], 4),
+            f"decode_b8_ctx{LONG_CONTEXT}_ms": round(mlong["ms_per_step"], 4),
+            f"decode_b8_ctx{LONG_CONTEXT}_hbm_frac": round(hbm_frac(args.batch, mlong), 4),
+            f"decode_b8_ctx{LONG_CONTEXT}_graph_replay_ms": round(mlong.get("graph_replay_ms", 0.0), 4),
             "prefill_wall_ms": round(pre_wall, 3),
             "prefill_4x512": round(PREFILL_TOKENS / (pre4_ms / 1e3), 1), "prefill_4x512_ms": round(pre4_ms, 3),
             "prefill_4x512_wall_ms": round(pre4_wall, 3),

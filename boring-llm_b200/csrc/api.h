@@ -94,7 +94,8 @@ int bl_attention_decode(const void* q, const void* k_cache, const void* v_cache,
 
 // The decode shape with TMA-fed rings (attention_decode.cu): head sizes 64 and 128, pages of 16, 1..16 slices that are
 // the blocks of one cluster; the MMAs' columns are the query heads of a key/value head (8 or 16 a block). n_pages:
-// pages in k_cache / v_cache. *status = 0 unless a warp gave up on a bounded wait since the last call (synchronises
+// pages in k_cache / v_cache. early != 0: the launch may start under its predecessor's tail (programmatic dependent
+// launch). *status = 0 unless a warp gave up on a bounded wait since the last call (synchronises
 // the device). resident_blocks: blocks the device holds at once for this head size and heads per key/value head.
 int bl_attention_decode_tma_supported(int dh, int page_size);
 int bl_attention_decode_tma_resident_blocks(int dh, int heads_per_kv);
@@ -103,7 +104,7 @@ int bl_attention_decode_tma_max_clusters(int dh, int heads_per_kv, int cluster);
 int bl_attention_decode_tma(const void* q, const void* k_cache, const void* v_cache, int n_pages, const int* cu_q,
                             const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
                             int n_splits, void* out, int H, int KV, int dh, int page_size, int window, float scale,
-                            void* stream);
+                            int early, void* stream);
 int bl_attention_decode_tma_status(int* status);
 
 // cs[t, j] = cos(positions[t] * inv_freq[j]) * mscale, sn likewise, j < rot_half: the rotation of a step's tokens,

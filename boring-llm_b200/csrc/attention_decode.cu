@@ -461,15 +461,19 @@ int configure(int* smem_bytes) {
     return 0;
 }
 
+// early: the kernel may be launched while its predecessor still runs (programmatic dependent launch); it then starts
+// its copies of the cached keys and values under the predecessor's tail. Large clusters of a launch with more blocks
+// than SMs are better launched late: placed while the predecessor's blocks still hold SMs, they pile up two to an SM
+// beside SMs that stay empty, and a long context then runs at the pace of the doubly loaded SMs.
 template <int DH, int NH>
-int launch(const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, dim3 grid, cudaStream_t s) {
+int launch(const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, dim3 grid, bool early, cudaStream_t s) {
     int bytes = 0;
     if (configure<DH, NH>(&bytes)) return 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = (size_t)bytes; cfg.stream = s;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = bl_pdl_enabled() ? 1 : 0;
+    attr[0].val.programmaticStreamSerializationAllowed = bl_pdl_enabled() && early ? 1 : 0;
     attr[1].id = cudaLaunchAttributeClusterDimension;
     attr[1].val.clusterDim.x = p.n_splits; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = p.n_splits > 1 ? 2 : 1;
@@ -531,7 +535,7 @@ extern "C" int bl_attention_decode_tma_max_clusters(int dh, int heads_per_kv, in
 extern "C" int bl_attention_decode_tma(const void* q, const void* k_cache, const void* v_cache, int n_pages, const int* cu_q,
                                        const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
                                        int n_splits, void* out, int H, int KV, int dh, int page_size, int window,
-                                       float scale, void* stream) {
+                                       float scale, int early, void* stream) {
     if (n <= 0) return 0;
     if (!(scale > 0.f)) BL_FAIL("%s: the scale of the scores must be positive (got %g)", WHO, (double)scale);
     if (H <= 0 || KV <= 0 || H % KV != 0) BL_FAIL("%s: %d heads cannot share %d key/value heads", WHO, H, KV);
@@ -550,8 +554,8 @@ extern "C" int bl_attention_decode_tma(const void* q, const void* k_cache, const
     const bool two = G > 8;
     const dim3 grid(n_splits, KV * ((G + (two ? 16 : 8) - 1) / (two ? 16 : 8)), n);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dh == 64) return two ? launch<64, 2>(mk, mv, p, grid, s) : launch<64, 1>(mk, mv, p, grid, s);
-    return two ? launch<128, 2>(mk, mv, p, grid, s) : launch<128, 1>(mk, mv, p, grid, s);
+    if (dh == 64) return two ? launch<64, 2>(mk, mv, p, grid, early != 0, s) : launch<64, 1>(mk, mv, p, grid, early != 0, s);
+    return two ? launch<128, 2>(mk, mv, p, grid, early != 0, s) : launch<128, 1>(mk, mv, p, grid, early != 0, s);
 }
 
 // Reads and clears the status word: 0 when no warp has given up on a wait since the last call. 1: a stage's keys

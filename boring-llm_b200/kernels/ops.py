@@ -385,8 +385,15 @@ def attention_decode_tma(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, 
     _need(v_cache, "v_cache", torch.bfloat16, k_cache.shape); _need(out, "out", torch.bfloat16, (T, H * dh))
     _need(cu_q, "cu_q", torch.int32); _need(ctx_len, "ctx_len", torch.int32); _need(block_table, "block_table", torch.int32)
     _need(reqs, "reqs", torch.int32, (n,))
+    # Large clusters of a launch with more blocks than SMs start only when the kernel before has finished: placed while
+    # its blocks still hold SMs they pile up two to an SM beside empty SMs (measured at batch 8: 54 -> 44 us a layer at
+    # 32,000 tokens, 81 -> 62 at 64,000; small launches gain 2.5 us a layer from the early start)
+    G = H // KV
+    blocks = n * KV * (-(-G // (8 if G <= 8 else 16))) * n_splits
+    early = not (n_splits >= DECODE_TMA_LATE_CLUSTER and blocks > _sms())
     _call(_lib().bl_attention_decode_tma, _p(q), _p(k_cache), _p(v_cache), n_pages, _p(cu_q), _p(ctx_len), _p(block_table),
-          block_table.shape[1], _p(reqs), n, n_splits, _p(out), H, KV, dh, page_size, window, ctypes.c_float(scale), _stream())
+          block_table.shape[1], _p(reqs), n, n_splits, _p(out), H, KV, dh, page_size, window, ctypes.c_float(scale),
+          1 if early else 0, _stream())
 
 
 def attention_decode_tma_resident_blocks(dh: int, heads_per_kv: int) -> int:
@@ -400,6 +407,14 @@ def attention_decode_tma_resident_blocks(dh: int, heads_per_kv: int) -> int:
 _decode_tma_resident = {}
 _decode_tma_clusters = {}
 _sm_count = {}
+DECODE_TMA_LATE_CLUSTER = 8           # clusters from this size on, in launches of more blocks than SMs, are launched late
+
+
+def _sms() -> int:
+    dev = torch.cuda.current_device()
+    if dev not in _sm_count:
+        _sm_count[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return _sm_count[dev]
 
 DECODE_TMA_UNIT = 32                  # keys a warp of `attention_decode_tma` takes at a time
 DECODE_TMA_MIN_UNITS = 4              # a slice is worth a block from four units on (one for each warp)
@@ -413,8 +428,7 @@ def attention_decode_tma_splits(n: int, KV: int, heads_per_kv: int, dh: int, lon
     per SM beats two (the step is a chain of latencies); with long walks two blocks per SM keep more bytes in
     flight. Among the slice counts that qualify, the smallest that gives a warp the fewest units."""
     dev = torch.cuda.current_device()
-    if dev not in _sm_count:
-        _sm_count[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    sms = _sms()
     groups = KV * (-(-heads_per_kv // (8 if heads_per_kv <= 8 else 16)))
     clusters = n * groups
     units = -(-max(1, longest) // DECODE_TMA_UNIT)
@@ -430,7 +444,7 @@ def attention_decode_tma_splits(n: int, KV: int, heads_per_kv: int, dh: int, lon
                                                for c in range(1, DECODE_CLUSTER_SPLITS + 1)]
         return clusters <= _decode_tma_clusters[key][s]
 
-    one_per_sm = max(1, min(most, _sm_count[dev] // clusters))
+    one_per_sm = max(1, min(most, sms // clusters))
     if per_warp(one_per_sm) <= DECODE_TMA_FEW_UNITS:
         top = one_per_sm
     else:
