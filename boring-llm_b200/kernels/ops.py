@@ -418,7 +418,7 @@ def _sms() -> int:
 
 DECODE_TMA_UNIT = 32                  # keys a warp of `attention_decode_tma` takes at a time
 DECODE_TMA_MIN_UNITS = 4              # a slice is worth a block from four units on (one for each warp)
-DECODE_TMA_FEW_UNITS = 6              # up to this many units a warp: latency decides, one block an SM is best (measured)
+DECODE_TMA_FEW_UNITS = 12             # up to this many units a warp, one block an SM is best: it may start under its predecessor (measured inside a layer's chain of kernels: 8 requests of 8,000 tokens 27.1 us a layer against 29.5, of 16,000 33.0 against 34.7; 32 requests of 3,900 want four slices)
 
 
 def attention_decode_tma_splits(n: int, KV: int, heads_per_kv: int, dh: int, longest: int) -> int:
