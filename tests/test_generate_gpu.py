@@ -226,3 +226,42 @@ def test_captured_steps_are_dropped_least_recently_used_first(model_folders, mon
     same = sum(a == b for x, y in zip(want, got) for a, b in zip(x, y))
     assert same >= 0.9 * 6 * len(prompts)              # (decode graphs cut their attention slices for a bound: rounding may differ)
     eng.runner.check_kernels()
+
+
+HEAD128 = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=2, hidden_size=192,
+               num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=328, vocab_size=1000,
+               rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=1024)
+
+
+def test_head_size_128_through_the_tensor_core_paths(tmp_path):
+    """Head size 128 (hidden 192 != 4 x 128, two key/value heads) end to end in bfloat16: prompts of 330 and 290
+    tokens run on the products on pairs of SMs (q/k/v with rotation and cache write in its epilogue, norms shared
+    between products) and the tcgen05 attention, the 24 decoded tokens on the TMA-fed decode attention inside captured
+    graphs. Every token is the plain implementation's choice given the engine's own prefix (near-ties may go either
+    way), and the kernels are seen on the path."""
+    import boring_llm_b200 as b
+    from boring_llm_b200.kernels import ops
+    cfg = b.Qwen2Config.from_dict(HEAD128)
+    d = str(tmp_path / "head128")
+    b.write_random_model(d, cfg, seed=5, dtype="bfloat16", std=0.05)
+    used = set()
+    real_call = ops._call
+
+    def spy(fn, *args):
+        used.add(fn.__name__)
+        return real_call(fn, *args)
+
+    ops._call = spy
+    try:
+        eng = b.Engine(d, dtype="bfloat16", ctx_size=512, max_num_seqs=4, max_tokens=2048, max_num_batched_tokens=1024,
+                       prefill_chunk=512)
+        prompts = [helpers.random_tokens(1000, 330, 61), helpers.random_tokens(1000, 290, 62)]
+        outs = eng.generate(prompts, n_predict=24, ignore_eos=True)
+    finally:
+        ops._call = real_call
+    for p_, o_ in zip(prompts, outs):
+        check_greedy(d, p_, o_, "bfloat16")
+    for name in ("bl_gemm_tc_pair_qkv_rope", "bl_gemm_tc_pair_residual_norm", "bl_gemm_tc_pair_swiglu_scaled",
+                 "bl_attention_prefill_tc", "bl_attention_decode_tma", "bl_rope_table"):
+        assert name in used, f"{name} was not on the path"
+    assert eng.runner.graph_steps >= 10
