@@ -10,16 +10,16 @@
 // its elements are not added into shared-memory histograms on the common path (152,000 atomic additions by one SM
 // cost tens of microseconds a pass):
 //   1. the eight blocks of a cluster share the row. Each scans its share for the maximum (the greedy token, and
-//      the softmax's reference point) and hands its candidate to all the others through distributed shared memory;
-//      greedy rows are done here;
-//   2. each block then sums its share's weights in registers (64-bit fixed point, no atomics) and keeps the largest
-//      logit of each of its warps; sums and warp maxima go to the first block, which does the rest alone;
-//   3. the c-th largest of the cluster's 256 warp maxima is a bound with at least c logits above it (c = k for
-//      top-k, else 256, which leaves about a thousand). Every block knows all warp maxima, works out the same
-//      bound, and sends the logits of its share that reach it to the first block (an atomic counter and a store in
-//      that block's shared memory). The first block then holds the head of the row's descending order as an
-//      unsorted list and does the rest alone;
-//   4. a step (top-k, top-p, the draw) over the list: the members' weights are added into 2,048 buckets that are
+//      the softmax's reference point) and hands its candidate, and the largest logit of each of its warps, to all
+//      the others through distributed shared memory; greedy rows are done here;
+//   2. the c-th largest of the cluster's 256 warp maxima is a bound with at least c logits above it (c = k for
+//      top-k, else 256, which leaves about a thousand); every block works out the same bound. In one more pass over
+//      its share a block sends the logits that reach the bound to the first block (an atomic counter and a store in
+//      that block's shared memory) and sums the share's weights in registers (64-bit fixed point, no atomics). The
+//      first block then holds the head of the row's descending order and the row's totals, and does the rest alone;
+//   3. a list of up to 1,024 candidates (a top-k's, a peaked row's) is sorted once (logit descending, id ascending);
+//      top-k, top-p, min-p and the draw are then running sums over a prefix of it, and a cut is a shorter prefix;
+//   4. a step over a longer list: the members' weights are added into 2,048 buckets that are
 //      linear in (maximum - logit), a scan finds the bucket in which the running weight reaches the target, that
 //      bucket's few candidates are sorted (logit descending, id ascending) and a scan of their weights finds the
 //      candidate, which becomes the members' new end. The totals of a step that looks at all of the row come from 2.
@@ -38,6 +38,7 @@ namespace {
 constexpr int THREADS = 1024;
 constexpr int NB = 2048;                         // buckets linear in (maximum - logit); the last takes what lies further, and NaN
 constexpr int CAP = 4096;                        // candidates that shared memory holds
+constexpr int SORT_MAX = 1024;                   // lists up to this length are sorted once (a bitonic sort of 1,024: 55 stages)
 constexpr int SCAN_BLOCKS = 8;                   // blocks of a cluster that share the scan for the maximum
 constexpr float FIXED_ONE = 1099511627776.0f;    // 2^40
 constexpr float ZERO_BELOW = 28.5f;              // exp(-28.5) * 2^40 < 1/2: weights this far below the largest are 0
@@ -321,6 +322,19 @@ __device__ unsigned long long target_of(const Target& t, unsigned long long tota
     return (unsigned long long)tgt;
 }
 
+// A step over a SORTED list (logit descending, id ascending) whose first n entries are the members, or head them:
+// the position at which the running weight reaches the target; -1 when the list only heads a longer order (of total
+// weight `outside` >= 0) and the target lies beyond it.
+__device__ int sorted_step(const RowCtx& c, int mode, const Target& t, int n, long long outside, Shared& S) {
+    for (int j = threadIdx.x; j < n; j += THREADS)
+        S.scan[j] = weight_of(c, from_key(~(unsigned)(S.items[j] >> 32)), mode);
+    __syncthreads();
+    const unsigned long long own = block_scan(S.scan, n, S);
+    const unsigned long long target = target_of(t, outside < 0 ? own : (unsigned long long)outside);
+    if (outside >= 0 && target > own) return -1;
+    return first_at_least(S.scan, n, target, S);
+}
+
 // One step (top-k, top-p or the draw): the member at which the running weight of the members, in descending order,
 // reaches the target; it is the members' new end (or the drawn token). LIST: the members are looked for in the list
 // of n_src candidates in shared memory, else in the whole row. `outside` < 0: what is walked holds every member and a
@@ -440,6 +454,9 @@ sample_kernel(const float* logits /* written by the kernel before */, int vocab,
         better(best, bidx, v2, i2);
     }
     if (lane == 0) { S.red_v[warp] = best; S.red_i[warp] = bidx; }
+    // (this warp's largest logit, for every block of the cluster: see step 3)
+    if (lane < parts) st_remote(in_block(&S.cl_wmax[part * (THREADS / 32) + warp], lane), bidx == 0x7fffffff ? 0u : sort_key(best));
+    if (threadIdx.x == 0) S.n_items = 0u;
     __syncthreads();
     if (threadIdx.x == 0)
         for (int w = 1; w < THREADS / 32; ++w) better(S.red_v[0], S.red_i[0], S.red_v[w], S.red_i[w]);
@@ -466,39 +483,13 @@ sample_kernel(const float* logits /* written by the kernel before */, int vocab,
     const int k = top_k[r];
     const float p = top_p[r], mp = min_p[r];
     const bool cut_k = k > 0 && k < vocab;
-    // ---- 2. this block's share of the row's totals, and its warps' largest logits ---------------------------------
+    // ---- 2. the head of the descending order, and this block's share of the row's totals, in one pass --------------------
+    // The c-th largest of the cluster's warp maxima is a bound that at least c logits reach (every block works out the
+    // same one); what reaches it goes to the first block's list.
     const int n_max = parts * (THREADS / 32);      // warp maxima of the cluster
     const bool k_in_list = cut_k && k <= n_max;    // the k largest are sure to be in the list
     {
-        unsigned long long z1 = 0ull, w2 = 0ull, w2m = 0ull;
-        unsigned tkey = 0u;
-        const bool sums = !cut_k;                  // after a top-k every later total is one over the members found then
-        for (int i = i_begin + threadIdx.x; i < i_end; i += THREADS) {
-            const float l = row[i];
-            tkey = max(tkey, sort_key(l));
-            if (sums) {
-                if (p < 1.0f) z1 += weight_of(c, l, 1);
-                const unsigned long long w = weight_of(c, l, 2);
-                w2 += w;
-                if (mp > 0.f && expf(l - lmax) >= mp) w2m += w;
-            }
-        }
-        tkey = __reduce_max_sync(0xffffffffu, tkey);
-        if (lane < parts) st_remote(in_block(&S.cl_wmax[part * (THREADS / 32) + warp], lane), tkey);
-        if (sums) {
-            z1 = block_sum(z1, S); w2 = block_sum(w2, S); w2m = block_sum(w2m, S);
-        }
-        if (threadIdx.x == 0) {
-            st_remote(in_block(&S.cl_sum[part][0], 0), z1);
-            st_remote(in_block(&S.cl_sum[part][1], 0), w2);
-            st_remote(in_block(&S.cl_sum[part][2], 0), w2m);
-            S.n_items = 0u;
-        }
-    }
-    if (parts > 1) cluster_sync_all(); else __syncthreads();
-    // ---- 3. the head of the descending order: what reaches the c-th largest warp maximum --------------------------------
-    {
-        const int c_th = k_in_list ? k : n_max;   // at least this many logits reach the bound
+        const int c_th = k_in_list ? k : n_max;
         if (threadIdx.x < n_max) {
             const unsigned long long mine = item_of(S.cl_wmax[threadIdx.x], threadIdx.x);
             int smaller = 0;
@@ -508,12 +499,29 @@ sample_kernel(const float* logits /* written by the kernel before */, int vocab,
         __syncthreads();
         const unsigned bound = S.bound;
         const uint32_t counter = in_block(&S.n_items, 0), list = in_block(&S.items[0], 0);
+        unsigned long long z1 = 0ull, w2 = 0ull, w2m = 0ull;
+        const bool sums = !cut_k;                  // after a top-k every later total is one over the members found then
         for (int i = i_begin + threadIdx.x; i < i_end; i += THREADS) {
-            const unsigned key = sort_key(row[i]);
+            const float l = row[i];
+            const unsigned key = sort_key(l);
             if (key >= bound) {
                 const unsigned at = add_remote(counter, 1u);
                 if (at < (unsigned)CAP) st_remote(list + at * 8u, item_of(key, i));
             }
+            if (sums) {
+                if (p < 1.0f) z1 += weight_of(c, l, 1);
+                const unsigned long long w = weight_of(c, l, 2);
+                w2 += w;
+                if (mp > 0.f && expf(l - lmax) >= mp) w2m += w;
+            }
+        }
+        if (sums) {
+            z1 = block_sum(z1, S); w2 = block_sum(w2, S); w2m = block_sum(w2m, S);
+        }
+        if (threadIdx.x == 0) {
+            st_remote(in_block(&S.cl_sum[part][0], 0), z1);
+            st_remote(in_block(&S.cl_sum[part][1], 0), w2);
+            st_remote(in_block(&S.cl_sum[part][2], 0), w2m);
         }
     }
     if (parts > 1) cluster_sync_all(); else __syncthreads();
@@ -521,41 +529,69 @@ sample_kernel(const float* logits /* written by the kernel before */, int vocab,
     unsigned long long Z1 = 0ull, W2 = 0ull, W2M = 0ull;
     for (int b = 0; b < parts; ++b) { Z1 += S.cl_sum[b][0]; W2 += S.cl_sum[b][1]; W2M += S.cl_sum[b][2]; }
     bool have_list = S.n_items <= (unsigned)CAP;   // else the bound let too many through (equal logits): the steps walk the row
-    const int n_list = have_list ? (int)S.n_items : 0;
+    int n_list = have_list ? (int)S.n_items : 0;
     bool complete = false;                         // the list holds every member
     bool reached;
     __syncthreads();
+    // A short list (a top-k's, a peaked row's) is sorted once; its steps are then running sums over a prefix of it, and a
+    // cut is a shorter prefix. A long one stays unsorted: its steps bucket it (step<true>).
+    const bool sorted = have_list && n_list <= SORT_MAX;
+    if (sorted) {
+        int m = 1;
+        while (m < n_list) m <<= 1;
+        for (int j = n_list + threadIdx.x; j < m; j += THREADS) S.items[j] = ~0ull;
+        __syncthreads();
+        block_sort(S.items, m);
+    }
+    auto end_of_list = [&]() { Cut e; e.key = ~(unsigned)(S.items[n_list - 1] >> 32); e.idx = (int)(unsigned)S.items[n_list - 1]; return e; };
     // ---- 4. the cuts and the draw ----------------------------------------------------------------------------------------
     if (cut_k) {                                   // rank_candidates keeps the k largest (:280-371)
         Target t; t.fraction = false; t.value = (double)k; t.at_least_one = false;
-        if (have_list && n_list >= k) { c.cut = step<true>(c, 0, t, n_list, -1, &reached, S); complete = true; }
-        else { c.cut = step<false>(c, 0, t, 0, -1, &reached, S); have_list = false; }
+        if (have_list && n_list >= k) {
+            if (sorted) { n_list = k; c.cut = end_of_list(); }
+            else c.cut = step<true>(c, 0, t, n_list, -1, &reached, S);
+            complete = true;
+        } else { c.cut = step<false>(c, 0, t, 0, -1, &reached, S); have_list = false; }
     }
     if (p < 1.0f) {                                // smallest prefix whose probability reaches top_p (:531-541)
         Target t; t.fraction = true; t.value = (double)p; t.at_least_one = true;
         reached = false;
         Cut cut;
-        if (have_list) cut = step<true>(c, 1, t, n_list, complete ? -1ll : (long long)Z1, &reached, S);
+        if (have_list && sorted) {
+            const int pos = sorted_step(c, 1, t, n_list, complete ? -1ll : (long long)Z1, S);
+            if (pos >= 0) { n_list = pos + 1; cut = end_of_list(); reached = true; }
+        } else if (have_list) {
+            cut = step<true>(c, 1, t, n_list, complete ? -1ll : (long long)Z1, &reached, S);
+        }
         if (reached) { c.cut = cut; complete = true; }
         else { c.cut = step<false>(c, 1, t, 0, -1, &reached, S); have_list = false; }
     }
     if (mp > 0.f) {                                // keep while probs[i] >= probs[0] * min_p (:546-551)
         c.min_p = mp;
-        if (have_list && !complete) {
-            // a candidate of the list that fails the test: then so does everything beyond the list
-            if (threadIdx.x == 0) S.found = 0;
+        if (have_list && (sorted || !complete)) {
+            // the first candidate of the list that fails the test: everything behind it fails too, in the list and beyond
+            if (threadIdx.x == 0) S.found = n_list;
             __syncthreads();
             for (int j = threadIdx.x; j < n_list; j += THREADS)
-                if (!(expf(from_key(~(unsigned)(S.items[j] >> 32)) - lmax) >= mp)) S.found = 1;
+                if (!(expf(from_key(~(unsigned)(S.items[j] >> 32)) - lmax) >= mp)) atomicMin(&S.found, j);
             __syncthreads();
-            complete = S.found != 0;
+            const int first_out = S.found;
             __syncthreads();
+            if (first_out < n_list) {
+                complete = true;
+                if (sorted) { n_list = max(1, first_out); c.cut = end_of_list(); }
+            }
         }
     }
     Target t; t.fraction = true; t.value = (double)uniform[r]; t.at_least_one = false;
     reached = false;
     Cut drawn;
-    if (have_list) drawn = step<true>(c, 2, t, n_list, complete ? -1ll : (long long)(mp > 0.f ? W2M : W2), &reached, S);
+    if (have_list && sorted) {
+        const int pos = sorted_step(c, 2, t, n_list, complete ? -1ll : (long long)(mp > 0.f ? W2M : W2), S);
+        if (pos >= 0) { drawn.key = 0u; drawn.idx = (int)(unsigned)S.items[pos]; reached = true; }
+    } else if (have_list) {
+        drawn = step<true>(c, 2, t, n_list, complete ? -1ll : (long long)(mp > 0.f ? W2M : W2), &reached, S);
+    }
     if (!reached) drawn = step<false>(c, 2, t, 0, -1, &reached, S);
     if (threadIdx.x == 0) out_ids[r] = drawn.idx;
 }
