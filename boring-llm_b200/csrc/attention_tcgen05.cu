@@ -12,13 +12,14 @@
 //   O_b = P . V      tcgen05.mma, M 128 x N 64 x K 128, V as it lies in its pages (keys x head size: the
 //                    MN-major form of the B operand), O_b in tensor memory;
 //   out = out * 2^(m_old - m) + O_b   in registers.
-// Eleven warps: eight own the rows, in two groups of four that take the even and the odd key blocks (each with a
+// Twelve warps: eight own the rows, in two groups of four that take the even and the odd key blocks (each with a
 // running maximum, sum and output of its own, merged at the end as the slices of a split are); one issues the
-// MMAs (lane 0), two issue the TMA copies of keys and of values (a box costs its issuing lane about 0.1 us, so
-// the sixteen boxes of a block are kept off the MMAs' path). They meet only at mbarriers. Each group has its own
-// scores, P, share of the output (256 of the 512 tensor-memory columns) and stage of keys and values: while one
-// group waits for its product and its next scores the other has the SM's arithmetic (the 2^x of the
-// special-function unit above all, which bounds the kernel). The loops over a row's scores stay rolled in pairs of
+// first product and one the second (lane 0 each), two issue the TMA copies of keys and of values (a box costs its
+// issuing lane about 0.1 us, so the sixteen boxes of a block are kept off the MMAs' path). They meet only at
+// mbarriers. The scores rotate through three buffers of tensor memory (P lies over the upper half of the scores
+// it was made from), each group has its own share of the output and stage of keys and values: a group's next
+// scores are computed while it is in its current block, and while one group waits for a product the other has the
+// SM's arithmetic (the 2^x of the special-function unit above all). The loops over a row's scores stay rolled in pairs of
 // 32-score loads, and the bounded waits are not unrolled: warps at different places of the code must all find it
 // in the instruction cache. One block per SM.
 // Pages come from the request's block table, one TMA box (16 keys x 64) per page and tensor.
@@ -40,8 +41,10 @@ constexpr int KBLK = 128;              // keys per block
 constexpr int PAGE = 16;
 constexpr int PAGES = KBLK / PAGE;     // pages per key block
 constexpr int ATOM_BYTES = ROWS * 128; // a 128-row operand tile lies in shared memory as atoms of 64 elements (128 bytes) a row
-constexpr int TMEM_COLS = 512;         // scores 2 x 128 columns, P (bfloat16 pairs) 2 x 64, shares of the output 128
-constexpr int COL_P = 2 * KBLK, COL_O = COL_P + 2 * (KBLK / 2);
+constexpr int TMEM_COLS = 512;         // three buffers of scores of 128 columns (P, as bfloat16 pairs, takes the upper 64 of its scores' buffer), shares of the output 128
+constexpr int SBUFS = 3;
+constexpr int COL_P = KBLK / 2;        // within a buffer of scores
+constexpr int COL_O = SBUFS * KBLK;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 // The two shapes that are built. Head size 64: two groups of row warps, each with its own share of the output (2 x 64
@@ -54,7 +57,7 @@ struct Shape {
     static constexpr int DH = DH_, GROUPS = GROUPS_;
     static constexpr int ATOMS = DH / 64;
     static constexpr int PAGE_BYTES = PAGE * DH * 2;
-    static constexpr int THREADS = GROUPS * ROWS + 96;   // the row warps, one warp that issues the MMAs, two that copy
+    static constexpr int THREADS = GROUPS * ROWS + 128;  // the row warps, a warp that issues S = Q K^T, two that copy, one that issues O = P V
     static constexpr int Q_BYTES = ROWS * DH * 2, KV_BYTES = KBLK * DH * 2;
     static constexpr int MERGE_ROW = DH / 2 + 1;                          // half of a group's output at the merge, rows padded by one float
     static constexpr int MERGE_BYTES = GROUPS == 2 ? ROWS * MERGE_ROW * 4 : 0;
@@ -79,6 +82,14 @@ struct Params {
 // take issue slots from the row warps of its scheduler.
 template <bool SLEEP = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up, int code) {
+    if (!SLEEP) {
+        // most of these waits find their phase complete: the test that cannot block answers in half the time of
+        // the one that may
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
 #pragma unroll 1
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
         uint32_t ok;
@@ -155,20 +166,24 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (threadIdx.x == 0) { tma_prefetch_map(&map_q); tma_prefetch_map(&map_k); tma_prefetch_map(&map_v); }
     const uint32_t base = smem_u32(smem);
     const uint32_t bars = base + OFF_BARS;
-    // barriers, 8 bytes each; [i & 1] of block i for all pairs
+    // barriers, 8 bytes each; [i & 1] of block i for the pairs, [i % 3] for the triples
     const uint32_t full_q = bars;
     const uint32_t full_k0 = bars + 8;          // keys copied
     const uint32_t full_v0 = bars + 24;         // values copied
-    const uint32_t s_done0 = bars + 40;         // scores in tensor memory (and the keys' stage free again)
-    const uint32_t o_done0 = bars + 56;         // share of the output in tensor memory (and P and the values' stage free again)
-    const uint32_t p_ready0 = bars + 88;        // P in tensor memory, scores read: 128 arrivals
+    const uint32_t o_done0 = bars + 40;         // share of the output in tensor memory (and the values' stage free again)
+    const uint32_t s_done0 = bars + 56;         // x 3: scores in tensor memory (and the keys' stage free again)
+    const uint32_t p_ready0 = bars + 80;        // x 3: P in tensor memory, scores read: 128 arrivals
     const uint32_t l_ready = bars + 104;        // both groups have posted their maxima, sums and half of their output
+    const uint32_t buf_free0 = bars + 128;      // x 3: the second product has read P: the buffer may take the scores of block i + 3
     volatile int* give_up = reinterpret_cast<volatile int*>(smem + OFF_BARS + 112);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BARS + 120);
     float* xch = reinterpret_cast<float*>(smem + OFF_XCH);               // [2 groups][maximum, sum][128 rows]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int ROW_WARPS = GROUPS * ROWS / 32;                        // one thread per row in each group
-    const bool issuer = warp == ROW_WARPS;                               // after the row warps: the MMA issuer, then two copy warps
+    // after the row warps: the issuer of the first product (it also owns the tensor memory), two copy warps, the
+    // issuer of the second product. One thread issuing both was the kernel's bottleneck: twelve MMAs, two commits and
+    // three waits a key block took it 1,800 cycles, as long as a group of row warps needs for the block's softmax.
+    const bool issuer = warp == ROW_WARPS, issuer_pv = warp == ROW_WARPS + 3;
 
     // Blocks start in the order of their index: all heads of the list's last tile, then all heads of the tile before.
     // The list is sorted by keys, so the launch runs longest tile first and the short ones fill the tail (with the
@@ -189,9 +204,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         mbar_init(full_q, 1);
         mbar_init(l_ready, GROUPS * ROWS);
         for (int i = 0; i < 2; ++i) {
-            mbar_init(full_k0 + 8 * i, 1); mbar_init(full_v0 + 8 * i, 1);
-            mbar_init(s_done0 + 8 * i, 1); mbar_init(o_done0 + 8 * i, 1);
-            mbar_init(p_ready0 + 8 * i, ROWS);
+            mbar_init(full_k0 + 8 * i, 1); mbar_init(full_v0 + 8 * i, 1); mbar_init(o_done0 + 8 * i, 1);
+        }
+        for (int i = 0; i < SBUFS; ++i) {
+            mbar_init(s_done0 + 8 * i, 1); mbar_init(p_ready0 + 8 * i, ROWS); mbar_init(buf_free0 + 8 * i, 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -209,11 +225,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     fence_after_sync();
     const uint32_t tmem = *tmem_slot;
     bl_pdl_trigger();                                                    // the next kernel may start its own preamble (it waits before it touches data)
-    // tensor memory: scores of block i in columns 128 (i & 1) .., its P in columns 256 + 64 (i & 1) .., its share of
-    // the output in columns 384 + 64 (i & 1) ..
+    // tensor memory: scores of block i in columns 128 (i % 3) .., its P over the upper 64 of them, its share of the
+    // output in columns 384 + 64 (i & 1) .. (head size 128: 384 ..)
     bool ok = !*give_up;
 
-    if (warp > ROW_WARPS) {
+    if (warp == ROW_WARPS + 1 || warp == ROW_WARPS + 2) {
         // ================= two warps: the copies of the keys (and q) and of the values, a page per lane 0..7.
         // Issuing a box costs its lane about 0.1 us, one lane after the other: two warps keep the sixteen boxes of a
         // block off the path of the MMAs.
@@ -238,10 +254,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int st = i & 1;
             const int page_next = lane < PAGES && i + 1 < nb ? page_of(b_begin + i + 1, lane) : -1;   // on its way during this block's copies
             if (i >= 2) {                                                // the stage is free once block i - 2 has been multiplied
-                const int own = (i - 2) >> 1;                            // which of its group's blocks that one was
                 if (lane == 0)
-                    ok = keys ? mbar_wait<true>(s_done0 + 8 * st, (uint32_t)(own & 1), give_up, 3)
-                              : mbar_wait<true>(o_done0 + 8 * st, (uint32_t)(own & 1), give_up, 7);
+                    ok = keys ? mbar_wait<true>(s_done0 + 8 * ((i - 2) % SBUFS), (uint32_t)(((i - 2) / SBUFS) & 1), give_up, 3)
+                              : mbar_wait<true>(o_done0 + 8 * st, (uint32_t)(((i - 2) >> 1) & 1), give_up, 7);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
             }
@@ -274,9 +289,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 const uint64_t a = smem_desc(base + OFF_Q + at * ATOM_BYTES);
                 const uint64_t b = smem_desc(base + OFF_K + (i & 1) * KV_BYTES + at * ATOM_BYTES);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) umma_bf16(tmem + (i & 1) * KBLK, a + 2 * k, b + 2 * k, IDESC_S, (at | k) != 0);
+                for (int k = 0; k < 4; ++k) umma_bf16(tmem + (i % SBUFS) * KBLK, a + 2 * k, b + 2 * k, IDESC_S, (at | k) != 0);
             }
-            umma_commit(s_done0 + 8 * (i & 1));
+            umma_commit(s_done0 + 8 * (i % SBUFS));
         };
         if (lane == 0 && ok && nb > 0) {
             ok = mbar_wait<true>(full_q, 0, give_up, 1) && mbar_wait<true>(full_k0, 0, give_up, 2);
@@ -285,20 +300,27 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 ok = mbar_wait<true>(full_k0 + 8, 0, give_up, 2);
                 if (ok) { fence_after_sync(); issue_s(1); }
             }
-            for (int i = 0; ok && i < nb; ++i) {
-                const int st = i & 1, own = i >> 1;
-                const uint32_t par = (uint32_t)(own & 1);
-                // the group has read the scores of block i, written P and taken the share of its block before: first the
-                // scores of its next block, which it waits for, into the same columns; then O_i = P . V
-                ok = mbar_wait(p_ready0 + 8 * st, par, give_up, 4);
+            // The scores of block j go where block j - 3 had its scores and its P, once the second product of that
+            // block has read P. With three buffers a group's next scores are computed while it works on its
+            // current block (with two, each group had one buffer, and waited through copy-free 500 ns for the
+            // product after every block).
+            for (int j = 2; ok && j < nb; ++j) {
+                if (j >= SBUFS) ok = mbar_wait(buf_free0 + 8 * ((j - SBUFS) % SBUFS), (uint32_t)(((j - SBUFS) / SBUFS) & 1), give_up, 4);
+                ok = ok && mbar_wait(full_k0 + 8 * (j & 1), (uint32_t)((j >> 1) & 1), give_up, 6);
                 if (!ok) break;
-                if (i + 2 < nb) {
-                    ok = mbar_wait(full_k0 + 8 * st, par ^ 1, give_up, 6);
-                    if (!ok) break;
-                    fence_after_sync();
-                    issue_s(i + 2);
-                }
-                ok = mbar_wait(full_v0 + 8 * st, par, give_up, 5);
+                fence_after_sync();
+                issue_s(j);
+            }
+        }
+        __syncwarp();
+    } else if (issuer_pv) {
+        // ================= one warp: lane 0 issues O_i = P . V once the group has written P of block i (and has taken
+        // the share of its block before out of the columns that this one goes to)
+        if (lane == 0 && ok) {
+            for (int i = 0; ok && i < nb; ++i) {
+                const int st = i & 1, buf = i % SBUFS;
+                ok = mbar_wait(p_ready0 + 8 * buf, (uint32_t)((i / SBUFS) & 1), give_up, 12) &&
+                     mbar_wait(full_v0 + 8 * st, (uint32_t)((i >> 1) & 1), give_up, 5);
                 if (!ok) break;
                 fence_after_sync();
 #pragma unroll
@@ -306,10 +328,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const uint64_t bv = smem_desc(base + OFF_V + st * KV_BYTES + at * ATOM_BYTES);
 #pragma unroll
                     for (int kk = 0; kk < KBLK / 16; ++kk)              // 16 keys a step: 8 columns of P, two 8-row groups of V
-                        umma_bf16_ts(tmem + COL_O + (GROUPS == 2 ? st * DH : 0) + at * 64, tmem + COL_P + st * (KBLK / 2) + kk * 8,
+                        umma_bf16_ts(tmem + COL_O + (GROUPS == 2 ? st * DH : 0) + at * 64, tmem + buf * KBLK + COL_P + kk * 8,
                                      bv + (uint64_t)(kk * (2048 >> 4)), IDESC_PV, kk != 0);
                 }
                 umma_commit(o_done0 + 8 * st);
+                umma_commit(buf_free0 + 8 * buf);
             }
         }
         __syncwarp();
@@ -334,23 +357,31 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             fine = __all_sync(0xffffffffu, fine);
             if (!fine) return false;
             fence_after_sync();
+            // two loads on their way at a time (the registers of the scores are free here)
 #pragma unroll
-            for (int h = 0; h < DH / 32; ++h) {
-                uint32_t v[32];
+            for (int h = 0; h < DH / 32; h += 2) {
+                uint32_t v[32], w[32];
                 tmem_ld32(t_o + h * 32, v);
+                tmem_ld32(t_o + h * 32 + 32, w);
                 tmem_ld_wait(v);
 #pragma unroll
                 for (int j = 0; j < 32; ++j) o[h * 32 + j] = o[h * 32 + j] * alpha + __uint_as_float(v[j]);
+                tmem_ld_wait(w);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o[h * 32 + 32 + j] = o[h * 32 + 32 + j] * alpha + __uint_as_float(w[j]);
             }
             return true;
         };
         int last = -1;                                                   // the group's last block
         for (int i = grp; i < nb; i += GROUPS) {
-            const int b = b_begin + i, st = i & 1;
+            const int b = b_begin + i, st = i & 1, buf = i % SBUFS;
             const uint32_t par = (uint32_t)((i >> 1) & 1);
-            const uint32_t t_s = tmem + st * KBLK + lane_off, t_p = tmem + COL_P + st * (KBLK / 2) + lane_off;
-            const uint32_t s_done = s_done0 + 8 * st, p_ready = p_ready0 + 8 * st, full_v = full_v0 + 8 * st;
-            ok = mbar_wait(s_done, par, give_up, 8) && ok;
+            // P goes over the upper half of the scores it is made from: by the time a chunk of P is written, the
+            // scores under it are in registers (chunks are taken in the order 3, 2, 1, 0; P of chunk c lies under
+            // the scores of chunk 2 + c / 2)
+            const uint32_t t_s = tmem + buf * KBLK + lane_off, t_p = t_s + COL_P;
+            const uint32_t s_done = s_done0 + 8 * buf, p_ready = p_ready0 + 8 * buf, full_v = full_v0 + 8 * st;
+            ok = mbar_wait(s_done, (uint32_t)((i / SBUFS) & 1), give_up, 8) && ok;
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             fence_after_sync();
@@ -387,9 +418,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const float m_use = m_new == -INFINITY ? 0.f : m_new;        // a row that has seen no key yet
             const float alpha = bl_ex2(m - m_use);                       // 2^-inf = 0 on the first block
             m = m_new;
-            // The share of the group's block before: its product frees P and the columns of the output, which the
-            // product of this block will take. It has had the time of this block's scores and first pass.
-            if (last >= 0 && !add_output(last, alpha_prev)) { ok = false; break; }
             float sm4[4] = {0.f, 0.f, 0.f, 0.f};
             // Second pass, chunks 3 (still in sb), 2, 1, 0: P = 2^(s * scale - m) as bfloat16 into tensor memory, the A
             // operand of the second product: lane = row, two keys to a 32-bit column, 16 columns a chunk.
@@ -420,6 +448,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (cp) { tmem_ld_wait(sb); tmem_ld32(t_s, sa); }
             }
             l = l * alpha + ((sm4[0] + sm4[1]) + (sm4[2] + sm4[3]));
+            // The share of the group's block before: taking it frees the columns that the product of this block will
+            // write. That product was issued a block ago; by now it is done.
+            if (last >= 0 && !add_output(last, alpha_prev)) { ok = false; break; }
             // the values of this block: rows that were not copied, or that lie past the last key, become zeros
             // (their P is 0, and 0 times whatever an old request left in a page must stay 0)
             if (k0 + KBLK - 1 > hi || k0 < lo) {
@@ -544,8 +575,8 @@ extern "C" int bl_attention_prefill_tc(const void* q, const void* k_cache, const
 }
 
 // Reads and clears the status word: 0 when no block has given up on a wait since the last call. Codes name the
-// wait: 1 q, 2 first keys, 3 / 7 a stage of keys / values to become free, 4 P, 5 values, 6 keys of the block after
-// next, 8 scores, 10 values (row warps), 11 a share of the output, 14 the other group at the merge, 9 shared
+// wait: 1 q, 2 first keys, 3 / 7 a stage of keys / values to become free, 4 a buffer of scores to become free, 12 P,
+// 5 values, 6 keys, 8 scores, 10 values (row warps), 11 a share of the output, 14 the other group at the merge, 9 shared
 // memory not 1024-byte aligned.
 // Synchronises the device.
 extern "C" int bl_attention_prefill_tc_status(int* status) {
