@@ -113,6 +113,29 @@ __device__ __forceinline__ void mbar_wait_plain(uint32_t bar, uint32_t parity) {
         if (ok) return;
     }
 }
+// Two 32-bit floats in one 64-bit register, for the instructions that work on both at once (half the issue slots of
+// the scalar forms; each lane is rounded as the scalar instruction rounds it).
+__device__ __forceinline__ uint64_t f2_pack(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
 // D (+)= A . B with the A operand in tensor memory (lane = row, a 32-bit column = two bfloat16 along K)
 __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
@@ -175,6 +198,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const uint32_t p_ready0 = bars + 80;        // x 3: P in tensor memory, scores read: 128 arrivals
     const uint32_t l_ready = bars + 104;        // both groups have posted their maxima, sums and half of their output
     const uint32_t buf_free0 = bars + 128;      // x 3: the second product has read P: the buffer may take the scores of block i + 3
+    const uint32_t o_final0 = bars + 152;       // x GROUPS: the group's last second product has been added (one phase)
     volatile int* give_up = reinterpret_cast<volatile int*>(smem + OFF_BARS + 112);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BARS + 120);
     float* xch = reinterpret_cast<float*>(smem + OFF_XCH);               // [2 groups][maximum, sum][128 rows]
@@ -209,6 +233,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int i = 0; i < SBUFS; ++i) {
             mbar_init(s_done0 + 8 * i, 1); mbar_init(p_ready0 + 8 * i, ROWS); mbar_init(buf_free0 + 8 * i, 1);
         }
+        for (int i = 0; i < GROUPS; ++i) mbar_init(o_final0 + 8 * i, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // q, the newest keys and values, the output buffer and the tensor memory of the SM belong to the kernels before
@@ -305,8 +330,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             // current block (with two, each group had one buffer, and waited through copy-free 500 ns for the
             // product after every block).
             for (int j = 2; ok && j < nb; ++j) {
-                if (j >= SBUFS) ok = mbar_wait(buf_free0 + 8 * ((j - SBUFS) % SBUFS), (uint32_t)(((j - SBUFS) / SBUFS) & 1), give_up, 4);
-                ok = ok && mbar_wait(full_k0 + 8 * (j & 1), (uint32_t)((j >> 1) & 1), give_up, 6);
+                // (the keys have long been copied when the buffer becomes free: that wait first, off the path)
+                ok = mbar_wait(full_k0 + 8 * (j & 1), (uint32_t)((j >> 1) & 1), give_up, 6);
+                if (ok && j >= SBUFS) ok = mbar_wait(buf_free0 + 8 * ((j - SBUFS) % SBUFS), (uint32_t)(((j - SBUFS) / SBUFS) & 1), give_up, 4);
                 if (!ok) break;
                 fence_after_sync();
                 issue_s(j);
@@ -319,8 +345,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (lane == 0 && ok) {
             for (int i = 0; ok && i < nb; ++i) {
                 const int st = i & 1, buf = i % SBUFS;
-                ok = mbar_wait(p_ready0 + 8 * buf, (uint32_t)((i / SBUFS) & 1), give_up, 12) &&
-                     mbar_wait(full_v0 + 8 * st, (uint32_t)((i >> 1) & 1), give_up, 5);
+                ok = mbar_wait(full_v0 + 8 * st, (uint32_t)((i >> 1) & 1), give_up, 5) &&       // copied long before P is there
+                     mbar_wait(p_ready0 + 8 * buf, (uint32_t)((i / SBUFS) & 1), give_up, 12);
                 if (!ok) break;
                 fence_after_sync();
 #pragma unroll
@@ -329,10 +355,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
                     for (int kk = 0; kk < KBLK / 16; ++kk)              // 16 keys a step: 8 columns of P, two 8-row groups of V
                         umma_bf16_ts(tmem + COL_O + (GROUPS == 2 ? st * DH : 0) + at * 64, tmem + buf * KBLK + COL_P + kk * 8,
-                                     bv + (uint64_t)(kk * (2048 >> 4)), IDESC_PV, kk != 0);
+                                     bv + (uint64_t)(kk * (2048 >> 4)), IDESC_PV, (kk == 0 && i < GROUPS) ? 0u : 1u);   // the group's first block starts its sum
                 }
                 umma_commit(o_done0 + 8 * st);
                 umma_commit(buf_free0 + 8 * buf);
+                if (i + GROUPS >= nb) umma_commit(o_final0 + 8 * (GROUPS == 2 ? st : 0));   // the group's last block
             }
         }
         __syncwarp();
@@ -346,31 +373,27 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const bool valid = row < rows_here;
         const int pos = valid ? p_first + row : -1;                      // an invalid row sees nothing
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;     // this warp's 32 lanes of tensor memory
-        float o[DH];
-#pragma unroll
-        for (int j = 0; j < DH; ++j) o[j] = 0.f;
-        float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
-        // out = out * alpha + O of block `blk`
-        auto add_output = [&](int blk, float alpha) -> bool {
-            const uint32_t t_o = tmem + COL_O + (GROUPS == 2 ? (blk & 1) * DH : 0) + lane_off;
+        // The group's output accumulates in tensor memory over its key blocks (the second product adds to it). m is
+        // the reference the row's weights are taken against: the running maximum as of the last time it was moved,
+        // which is when a block's maximum exceeds it by more than RESCALE (weights then reach 2^RESCALE at most: far
+        // inside bfloat16 and 32-bit range, with the same relative rounding). Moving it costs a pass over the
+        // accumulated output (load, scale, store), which after a row's first blocks is rare.
+        constexpr float RESCALE = 8.f;
+        float m = -INFINITY, l = 0.f;
+        const uint32_t t_o = tmem + COL_O + (GROUPS == 2 ? grp * DH : 0) + lane_off;
+        // Waits until the second product of block `blk` has been added. A wait on a barrier's phase is valid only
+        // while the barrier is at most one phase behind the one asked for (phases are told apart by parity alone).
+        // The group does not look at every one of these phases; what keeps it in step is the rotation of the score
+        // buffers: the scores of block i, which the group has seen, were issued after the second product of block
+        // i - 3 had completed, and with it all before it. So inside block i the products up to i - 3 are done, and a
+        // wait for the product of the group's block before (i - 2, or i - 1 with one group) is valid. After the
+        // last block nothing bounds how far the barrier has come (a question about a phase two back, or one
+        // ahead, gets the wrong answer): the end of the group's last product has a barrier of its own.
+        auto output_done = [&](int blk) -> bool {
             bool fine = mbar_wait(o_done0 + 8 * (blk & 1), (uint32_t)((blk >> 1) & 1), give_up, 11);
             fine = __all_sync(0xffffffffu, fine);
-            if (!fine) return false;
-            fence_after_sync();
-            // two loads on their way at a time (the registers of the scores are free here)
-#pragma unroll
-            for (int h = 0; h < DH / 32; h += 2) {
-                uint32_t v[32], w[32];
-                tmem_ld32(t_o + h * 32, v);
-                tmem_ld32(t_o + h * 32 + 32, w);
-                tmem_ld_wait(v);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) o[h * 32 + j] = o[h * 32 + j] * alpha + __uint_as_float(v[j]);
-                tmem_ld_wait(w);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) o[h * 32 + 32 + j] = o[h * 32 + 32 + j] * alpha + __uint_as_float(w[j]);
-            }
-            return true;
+            if (fine) fence_after_sync();
+            return fine;
         };
         int last = -1;                                                   // the group's last block
         for (int i = grp; i < nb; i += GROUPS) {
@@ -401,7 +424,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             auto chunk_max = [&](uint32_t (&s)[32], int c) {
                 if (!all_seen) mask(s, c);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(s[j]));
+                for (int j = 0; j < 32; j += 2) mx[(j >> 1) & 3] = max3(mx[(j >> 1) & 3], __uint_as_float(s[j]), __uint_as_float(s[j + 1]));
             };
             // First pass, the maximum of the raw scores; 32 scores a load, the next load on its way meanwhile. The
             // loops over pairs of chunks stay rolled: both groups, at different places of this code, must find it in
@@ -415,10 +438,33 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             // the scale is positive: the maximum of the scaled scores is the scaled maximum
             const float m_new = fmaxf(m, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2);
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;        // a row that has seen no key yet
-            const float alpha = bl_ex2(m - m_use);                       // 2^-inf = 0 on the first block
-            m = m_new;
-            float sm4[4] = {0.f, 0.f, 0.f, 0.f};
+            float alpha = 1.f;
+            // (a row's first keys: -inf + RESCALE is -inf, below any score; a row without keys so far stays as it is)
+            if (__any_sync(0xffffffffu, m_new > m + RESCALE)) {
+                alpha = bl_ex2(m - (m_new == -INFINITY ? 0.f : m_new));   // 2^-inf = 0 on the first keys
+                m = m_new;
+                if (last >= 0) {                                          // what has been added so far moves to the new reference
+                    if (!output_done(last)) { ok = false; break; }
+#pragma unroll
+                    for (int h = 0; h < DH / 32; ++h) {
+                        uint32_t v[32];
+                        tmem_ld32(t_o + h * 32, v);
+                        tmem_ld_wait(v);
+                        uint32_t lo16[16], hi16[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            lo16[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+                            hi16[j] = __float_as_uint(__uint_as_float(v[16 + j]) * alpha);
+                        }
+                        tmem_st16(t_o + h * 32, lo16);
+                        tmem_st16(t_o + h * 32 + 16, hi16);
+                    }
+                }
+            }
+            const float m_use = m == -INFINITY ? 0.f : m;                // a row that has seen no key yet
+            // sums of the row's weights in four parts: keys 0, 4, 8, .. and 1, 5, 9, .. (sum2[0]), 2, 6, .. and 3, 7, .. (sum2[1])
+            uint64_t sum2[2] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};
+            const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), minus_m2 = f2_pack(-m_use, -m_use);
             // Second pass, chunks 3 (still in sb), 2, 1, 0: P = 2^(s * scale - m) as bfloat16 into tensor memory, the A
             // operand of the second product: lane = row, two keys to a 32-bit column, 16 columns a chunk.
             auto chunk_exp = [&](uint32_t (&s)[32], int c) {
@@ -427,14 +473,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 // back to back (volatile keeps them together), then the sums and the pairs
                 float x[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) x[j] = fmaf(__uint_as_float(s[j]), p.scale_log2, -m_use);
+                for (int j = 0; j < 32; j += 2)
+                    f2_unpack(f2_fma(f2_pack(__uint_as_float(s[j]), __uint_as_float(s[j + 1])), scale2, minus_m2), x[j], x[j + 1]);
 #pragma unroll
                 for (int j = 0; j < 32; ++j) asm volatile("ex2.approx.ftz.f32 %0, %0;" : "+f"(x[j]));
                 uint32_t pk[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    sm4[j & 1] += x[2 * j];
-                    sm4[2 + (j & 1)] += x[2 * j + 1];
+                    sum2[j & 1] = f2_add(sum2[j & 1], f2_pack(x[2 * j], x[2 * j + 1]));
                     pk[j] = pack_bf16(x[2 * j], x[2 * j + 1]);
                 }
                 tmem_st16(t_p + 16 * c, pk);
@@ -447,13 +493,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 chunk_exp(sa, 2 * cp);
                 if (cp) { tmem_ld_wait(sb); tmem_ld32(t_s, sa); }
             }
-            l = l * alpha + ((sm4[0] + sm4[1]) + (sm4[2] + sm4[3]));
-            // The share of the group's block before: taking it frees the columns that the product of this block will
-            // write. That product was issued a block ago; by now it is done.
-            if (last >= 0 && !add_output(last, alpha_prev)) { ok = false; break; }
+            float s_a, s_b, s_c, s_d;
+            f2_unpack(sum2[0], s_a, s_c);
+            f2_unpack(sum2[1], s_b, s_d);
+            l = l * alpha + ((s_a + s_b) + (s_c + s_d));
             // the values of this block: rows that were not copied, or that lie past the last key, become zeros
             // (their P is 0, and 0 times whatever an old request left in a page must stay 0)
             if (k0 + KBLK - 1 > hi || k0 < lo) {
+                // (once the product before has been added, the values of two blocks ago have been copied: the
+                // barrier of this block's values is one phase behind at most)
+                if (last >= 0 && !output_done(last)) { ok = false; break; }
                 ok = mbar_wait(full_v, par, give_up, 10) && ok;
                 if (ok) {
                     // (atom, key row, 16-byte chunk); the swizzle keeps a row's chunks in the row
@@ -471,11 +520,27 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tmem_st_wait();
             fence_before_sync();
             mbar_arrive(p_ready);
-            alpha_prev = alpha;
             last = i;
         }
         ok = __all_sync(0xffffffffu, ok);
-        if (ok && last >= 0) ok = add_output(last, alpha_prev);
+        float o[DH];                                                     // the row's output against m, not yet divided by l
+#pragma unroll
+        for (int j = 0; j < DH; ++j) o[j] = 0.f;
+        if (ok && last >= 0) {
+            ok = mbar_wait(o_final0 + 8 * grp, 0, give_up, 13);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) fence_after_sync();
+            if (ok) {
+#pragma unroll
+                for (int h = 0; h < DH / 32; ++h) {
+                    uint32_t v[32];
+                    tmem_ld32(t_o + h * 32, v);
+                    tmem_ld_wait(v);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[h * 32 + j] = __uint_as_float(v[j]);
+                }
+            }
+        }
         if (GROUPS == 1) {
             // one group holds the whole row: out = o / l
             ok = __all_sync(0xffffffffu, ok);
@@ -576,7 +641,7 @@ extern "C" int bl_attention_prefill_tc(const void* q, const void* k_cache, const
 
 // Reads and clears the status word: 0 when no block has given up on a wait since the last call. Codes name the
 // wait: 1 q, 2 first keys, 3 / 7 a stage of keys / values to become free, 4 a buffer of scores to become free, 12 P,
-// 5 values, 6 keys, 8 scores, 10 values (row warps), 11 a share of the output, 14 the other group at the merge, 9 shared
+// 5 values, 6 keys, 8 scores, 13 the group's last product, 10 values (row warps), 11 a share of the output, 14 the other group at the merge, 9 shared
 // memory not 1024-byte aligned.
 // Synchronises the device.
 extern "C" int bl_attention_prefill_tc_status(int* status) {

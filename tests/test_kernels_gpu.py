@@ -186,7 +186,9 @@ def attention_case(o, fn, dtype, H, KV, dh, ctx_lens, q_lens, window, seed, plan
     k_full = [torch.randn(c, KV, dh, generator=g, dtype=torch.float64) for c in ctx_lens]
     v_full = [torch.randn(c, KV, dh, generator=g, dtype=torch.float64) for c in ctx_lens]
     q_rows = [torch.randn(q, H, dh, generator=g, dtype=torch.float64) for q in q_lens]
-    if plant:
+    if callable(plant):
+        plant(k_full, v_full, q_rows)
+    elif plant:
         # one far key per request gets a score that stands out for the last query: a kernel that
         # skips it, reads a neighbour or the wrong page changes the output beyond any tolerance
         for r, c in enumerate(ctx_lens):
@@ -604,6 +606,31 @@ def test_attention_tcgen05_long_prompt(dh):
 def test_attention_tcgen05_window_edges(window, dh):
     o = ops()
     attention_case(o, tc_attention, torch.bfloat16, 4, 2, dh, [200, 131, 700, 17], [150, 1, 500, 2], window, 6)
+
+
+@pytest.mark.parametrize("dh", [64, 128])
+def test_attention_tcgen05_moving_maximum(dh):
+    """The output accumulates in tensor memory against a reference maximum that is moved only when a key block's
+    maximum exceeds it by 2^8, and moving it rescales what has accumulated. Keys planted along the prompt score higher
+    and higher for every query: by 17 (in powers of two) at keys 300, 700, 1,100, 1,500 and 1,900, which moves the
+    reference in even and in odd key blocks after many blocks have been added, and by 4 at keys 450 and 1,300, which
+    does not (those rows' weights exceed 1). Every planted key has its own value vector, so a rescale that is
+    skipped, done twice or done with the wrong factor changes the output wholesale."""
+    o = ops()
+    at = {5: 0.5, 300: 1.5, 450: 1.85, 700: 3.0, 1100: 4.5, 1300: 4.85, 1500: 6.0, 1900: 7.5}
+
+    def plant(k_full, v_full, q_rows):
+        for r in range(len(k_full)):
+            q_rows[r][:, :, 0] = math.sqrt(dh)                    # score of a planted key: 8 x its strength
+            k_full[r][:, :, 0] = 0.0
+            for pos, strength in at.items():
+                if pos < k_full[r].shape[0]:
+                    k_full[r][pos] = 0.0
+                    k_full[r][pos, :, 0] = 8.0 * strength
+                    v_full[r][pos] = 0.0
+                    v_full[r][pos, :, pos % dh] = 30.0
+    attention_case(o, tc_attention, torch.bfloat16, 4, 2, dh, [2100, 1400, 2048], [2100, 900, 333], 0, 21, plant=plant)
+    attention_case(o, tc_attention, torch.bfloat16, 2, 1, dh, [2000], [2000], 500, 22, plant=plant)
 
 
 def test_attention_tcgen05_padded_tile_lists():
