@@ -62,6 +62,11 @@ int bl_repeat_penalty(float* logits, int rows, int vocab, const int* tokens, con
 // into tensor-core registers. K must be a multiple of 8, x and W 16-byte aligned. Same epilogues as bl_gemm_plain.
 int bl_gemm_skinny(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype,
                    int M, int N, int K, int epilogue, void* stream);
+int bl_gemm_skinny_norm_parts(int N);
+int bl_gemm_skinny_residual_norm(const void* x, const void* w, void* out, int M, int N, int K, const void* norm_w,
+                                 int norm_w_dtype, void* hw, float* ss, void* stream);
+int bl_gemm_skinny_scaled(const void* hw, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype,
+                          int M, int N, int K, int epilogue, const float* ss, int parts, float eps, void* stream);
 
 // Tensor-core paged attention (bfloat16, pages of 16 tokens, head sizes 16/32/48/64/96/128).
 int bl_attention_mma_supported(int dh, int page_size);
@@ -155,7 +160,6 @@ int bl_norm_qkv_rope(const float* x, const void* norm_w, int norm_w_dtype, float
                      const int* block_table, int max_pages, const float* inv_freq, float mscale,
                      void* q_out, void* k_cache, void* v_cache, int M, int K, int H, int KV, int dh,
                      int page_size, int pair_layout, void* stream);
-
 // Programmatic dependent launch for the small kernels of a step (on by default): 0 launches them the ordinary way.
 void bl_set_dependent_launch(int on);
 

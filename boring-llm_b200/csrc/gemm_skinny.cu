@@ -28,6 +28,17 @@ __device__ __forceinline__ uint4 ld16(const __nv_bfloat16* p, bool ok) {
     return ok ? __ldg(reinterpret_cast<const uint4*>(p)) : make_uint4(0u, 0u, 0u, 0u);
 }
 
+// An RMS norm shared between two products without a pass of its own (few rows: decode steps).
+// The product that adds into the residual stream (residual epilogue) also writes, for the norm that reads the stream
+// next, hw = bfloat16(stream * norm weight) and, per row and block of 16 columns, the sum of the squares of the new
+// stream (ss_out[row][block]). A product that takes hw as its x (ss_in set) multiplies each row of its result by
+// 1 / sqrt(sum(ss_in[row][:]) / dim + eps): the row's scale commutes with the product. Statistics and scale in 32-bit,
+// the partial sums added in a fixed order.
+struct SkinnyLink {
+    const void* norm_w; int norm_w_dtype; __nv_bfloat16* hw; float* ss_out;      // producer
+    const float* ss_in; int parts_in; float inv_dim, eps;                         // consumer
+};
+
 // MT: groups of 8 tokens handled by one block (M tile = 8 * MT). NW: warps per block (8, or 16 for long K).
 // DEEP: two batches of loads in flight per warp (few blocks, each short: hide the trips to memory); without it one
 // batch and half the registers, so that twice as many blocks fit an SM (many blocks: HBM throughput is what counts).
@@ -36,10 +47,11 @@ __global__ void __launch_bounds__(NW * 32, DEEP ? 1 : (NW == 8 ? 4 : 2))
 gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no read-only cache */,
                    const __nv_bfloat16* __restrict__ w,
                    const void* __restrict__ bias, int bias_dtype, TO* out,
-                   int M, int N, int K, int m_groups) {
+                   int M, int N, int K, int m_groups, const SkinnyLink lk) {
     constexpr bool GLU = EPI == BL_EPI_SWIGLU;
     constexpr int TOK = MT * 8;
     __shared__ float red[GLU ? 2 : 1][NW][COLS][TOK + 1];
+    __shared__ float row_scale[TOK];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = (blockIdx.x / m_groups) * COLS;
@@ -111,9 +123,24 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
     const bool e_ok = threadIdx.x < COLS * TOK && e_n < N && e_m < M;
     float e_add = 0.f;
     if (EPI == BL_EPI_BIAS && e_ok) e_add = bl_load_any(bias, bias_dtype, e_n);
+    const bool begins_norm = EPI == BL_EPI_RESIDUAL && lk.hw != nullptr;
+    float e_nw = 0.f;                                             // the next norm's weight of this thread's column
+    if (begins_norm && e_ok) e_nw = bl_load_any(lk.norm_w, lk.norm_w_dtype, e_n);
     bl_pdl_wait();
     if (EPI == BL_EPI_RESIDUAL && e_ok) e_add = bl_load(out + (size_t)e_m * N + e_n);   // on its way during the product
     fetch_x(b0, warp * 32);
+    if (lk.ss_in != nullptr) {
+        // the scale of each of this block's rows, while the product's operands are on their way: warp w adds up the
+        // partial sums of rows w, w + NW, ... (a lane its share in ascending order, then the warp's fixed tree)
+        for (int i = warp; i < TOK; i += NW) {
+            const int m = m0 + i;
+            float sum = 0.f;
+            if (m < M)
+                for (int q = lane; q < lk.parts_in; q += 32) sum += lk.ss_in[(size_t)m * lk.parts_in + q];
+            sum = bl_warp_sum(sum);
+            if (lane == 0) row_scale[i] = 1.0f / sqrtf(sum * lk.inv_dim + lk.eps);
+        }
+    }
     // two batches per trip of the loop, so that the buffers keep their names (and their registers)
     if (DEEP) {
         for (int kc0 = warp * 32; kc0 < K; kc0 += 2 * STEP) {
@@ -142,17 +169,29 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
     }
     __syncthreads();
     // the first COLS * TOK threads each own one output element (their residual or bias is already in a register)
+    // (every lane of a warp makes the same number of trips: COLS * TOK is a multiple of 32)
     for (int i = threadIdx.x; i < COLS * TOK; i += NW * 32) {
         const int c = i % COLS, tok = i / COLS;
         const int n = n0 + c, m = m0 + tok;
-        if (n >= N || m >= M) continue;
+        const bool valid = n < N && m < M;
         float v = 0.f, u = 0.f;
+        if (valid) {
 #pragma unroll
-        for (int wp = 0; wp < NW; ++wp) { v += red[0][wp][c][tok]; if (GLU) u += red[1][wp][c][tok]; }
-        TO* dst = out + (size_t)m * N + n;
-        if (EPI == BL_EPI_BIAS || EPI == BL_EPI_RESIDUAL) v += (i == threadIdx.x) ? e_add : (EPI == BL_EPI_BIAS ? bl_load_any(bias, bias_dtype, n) : bl_load(dst));
-        if (GLU) v = bl_silu(v) * u;
-        bl_store(dst, v);
+            for (int wp = 0; wp < NW; ++wp) { v += red[0][wp][c][tok]; if (GLU) u += red[1][wp][c][tok]; }
+            if (lk.ss_in != nullptr) { const float r = row_scale[tok]; v *= r; if (GLU) u *= r; }
+            TO* dst = out + (size_t)m * N + n;
+            if (EPI == BL_EPI_BIAS || EPI == BL_EPI_RESIDUAL) v += (i == threadIdx.x) ? e_add : (EPI == BL_EPI_BIAS ? bl_load_any(bias, bias_dtype, n) : bl_load(dst));
+            if (GLU) v = bl_silu(v) * u;
+            bl_store(dst, v);
+        }
+        if (begins_norm) {                                        // (the same for the whole block)
+            // a token's 16 columns lie in 16 neighbouring lanes: their squares are added there, always in this order
+            float sq = valid ? v * v : 0.f;
+#pragma unroll
+            for (int o = 8; o; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (valid) lk.hw[(size_t)m * N + n] = __float2bfloat16_rn(v * ((i == threadIdx.x) ? e_nw : bl_load_any(lk.norm_w, lk.norm_w_dtype, n)));
+            if (c == 0 && m < M) lk.ss_out[(size_t)m * (gridDim.x / m_groups) + blockIdx.x / m_groups] = sq;
+        }
     }
 }
 
@@ -268,11 +307,11 @@ int launch_cols(const void* x, const void* w, const void* bias, int bias_dtype, 
 
 template <int MT, typename TO, int NW, bool DEEP>
 int launch_nw(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K,
-              int epi, cudaStream_t s) {
+              int epi, const SkinnyLink& lk, cudaStream_t s) {
     const int m_groups = (M + MT * 8 - 1) / (MT * 8);
     const int blocks = ((N + COLS - 1) / COLS) * m_groups;
 #define BL_GO(E) BL_CUDA(bl_launch_dependent(gemm_skinny_kernel<MT, E, TO, NW, DEEP>, dim3(blocks), dim3(NW * 32), 0, s, \
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, bias_dtype, (TO*)out, M, N, K, m_groups))
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, bias_dtype, (TO*)out, M, N, K, m_groups, lk))
     switch (epi) {
         case BL_EPI_NONE: BL_GO(BL_EPI_NONE); break;
         case BL_EPI_BIAS: BL_GO(BL_EPI_BIAS); break;
@@ -287,22 +326,26 @@ int launch_nw(const void* x, const void* w, const void* bias, int bias_dtype, vo
 // Long rows of W are cut over 16 warps instead of 8: fewer trips to memory one after the other per warp.
 template <int MT, typename TO>
 int launch(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K,
-           int epi, cudaStream_t s) {
+           int epi, const SkinnyLink& lk, cudaStream_t s) {
     const int m_groups = (M + MT * 8 - 1) / (MT * 8);
     const int blocks = ((N + COLS - 1) / COLS) * m_groups;
+    const bool linked = lk.hw != nullptr || lk.ss_in != nullptr;
     // the choice depends on N alone, so that a row's result is the same whatever else is in the batch
-    if ((N + COLS - 1) / COLS > 4 * 148 && epi != BL_EPI_SWIGLU) return launch_cols<MT, TO>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
-    if (blocks > 4 * 148) return launch_nw<MT, TO, 8, false>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
-    if (K >= 2048 && MT == 1 && epi != BL_EPI_SWIGLU) return launch_nw<1, TO, 16, true>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
-    return launch_nw<MT, TO, 8, true>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
+    if ((N + COLS - 1) / COLS > 4 * 148 && epi != BL_EPI_SWIGLU) {
+        if (linked) BL_FAIL("bl_gemm_skinny_linked: %d columns run on the kernel of whole warps per column block, which shares no norm", N);
+        return launch_cols<MT, TO>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
+    }
+    if (blocks > 4 * 148) return launch_nw<MT, TO, 8, false>(x, w, bias, bias_dtype, out, M, N, K, epi, lk, s);
+    if (K >= 2048 && MT == 1 && epi != BL_EPI_SWIGLU) return launch_nw<1, TO, 16, true>(x, w, bias, bias_dtype, out, M, N, K, epi, lk, s);
+    return launch_nw<MT, TO, 8, true>(x, w, bias, bias_dtype, out, M, N, K, epi, lk, s);
 }
 
 }  // namespace
 
-// bfloat16 x and W; K a multiple of 8 and both base addresses 16-byte aligned (16-byte loads); any M, N.
-// Meant for M up to a few dozen: W is read once per 32 tokens.
-extern "C" int bl_gemm_skinny(const void* x, const void* w, const void* bias, int bias_dtype, void* out,
-                              int out_dtype, int M, int N, int K, int epilogue, void* stream) {
+namespace {
+
+int run(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype, int M, int N, int K,
+        int epilogue, const SkinnyLink& lk, void* stream) {
     if (M <= 0) return 0;
     if (N <= 0 || K <= 0) BL_FAIL("bl_gemm_skinny: bad sizes N=%d K=%d", N, K);
     if (K % 8 != 0) BL_FAIL("bl_gemm_skinny: K=%d is not a multiple of 8 (use the plain kernel)", K);
@@ -313,14 +356,50 @@ extern "C" int bl_gemm_skinny(const void* x, const void* w, const void* bias, in
         BL_FAIL("bl_gemm_skinny: the residual stream is 32-bit; output dtype must be float32");
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == BL_F32) {
-        if (M <= 8) return launch<1, float>(x, w, bias, bias_dtype, out, M, N, K, epilogue, s);
-        if (M <= 16) return launch<2, float>(x, w, bias, bias_dtype, out, M, N, K, epilogue, s);
-        return launch<4, float>(x, w, bias, bias_dtype, out, M, N, K, epilogue, s);
+        if (M <= 8) return launch<1, float>(x, w, bias, bias_dtype, out, M, N, K, epilogue, lk, s);
+        if (M <= 16) return launch<2, float>(x, w, bias, bias_dtype, out, M, N, K, epilogue, lk, s);
+        return launch<4, float>(x, w, bias, bias_dtype, out, M, N, K, epilogue, lk, s);
     }
     if (out_dtype == BL_BF16) {
-        if (M <= 8) return launch<1, __nv_bfloat16>(x, w, bias, bias_dtype, out, M, N, K, epilogue, s);
-        if (M <= 16) return launch<2, __nv_bfloat16>(x, w, bias, bias_dtype, out, M, N, K, epilogue, s);
-        return launch<4, __nv_bfloat16>(x, w, bias, bias_dtype, out, M, N, K, epilogue, s);
+        if (M <= 8) return launch<1, __nv_bfloat16>(x, w, bias, bias_dtype, out, M, N, K, epilogue, lk, s);
+        if (M <= 16) return launch<2, __nv_bfloat16>(x, w, bias, bias_dtype, out, M, N, K, epilogue, lk, s);
+        return launch<4, __nv_bfloat16>(x, w, bias, bias_dtype, out, M, N, K, epilogue, lk, s);
     }
     BL_FAIL("bl_gemm_skinny: unknown output dtype %d", out_dtype);
+}
+
+}  // namespace
+
+// bfloat16 x and W; K a multiple of 8 and both base addresses 16-byte aligned (16-byte loads); any M, N.
+// Meant for M up to a few dozen: W is read once per 32 tokens.
+extern "C" int bl_gemm_skinny(const void* x, const void* w, const void* bias, int bias_dtype, void* out,
+                              int out_dtype, int M, int N, int K, int epilogue, void* stream) {
+    return run(x, w, bias, bias_dtype, out, out_dtype, M, N, K, epilogue, SkinnyLink{}, stream);
+}
+
+// Partial sums of squares per row that the linked residual product writes: one per block of 16 columns.
+extern "C" int bl_gemm_skinny_norm_parts(int N) { return (N + COLS - 1) / COLS; }
+
+// out += x . W^T (32-bit residual stream, in place) and, for the RMS norm with weight norm_w that reads out next:
+// hw[M, N] = bfloat16(out * norm_w), ss[M, parts] = sums of squares of the new rows by block of 16 columns
+// (parts = bl_gemm_skinny_norm_parts(N)).
+extern "C" int bl_gemm_skinny_residual_norm(const void* x, const void* w, void* out, int M, int N, int K,
+                                            const void* norm_w, int norm_w_dtype, void* hw, float* ss, void* stream) {
+    if (norm_w == nullptr || hw == nullptr || ss == nullptr || (norm_w_dtype != BL_F32 && norm_w_dtype != BL_BF16))
+        BL_FAIL("bl_gemm_skinny_residual_norm: needs a float32 or bfloat16 norm weight, hw and ss");
+    SkinnyLink lk = {};
+    lk.norm_w = norm_w; lk.norm_w_dtype = norm_w_dtype; lk.hw = (__nv_bfloat16*)hw; lk.ss_out = ss;
+    return run(x, w, nullptr, 0, out, BL_F32, M, N, K, BL_EPI_RESIDUAL, lk, stream);
+}
+
+// out = epilogue(r * (hw . W^T)) with r[m] = 1 / sqrt(sum(ss[m][:]) / K + eps): the product of rows whose RMS norm
+// the linked residual product left pending. Epilogues: none, bias, SwiGLU.
+extern "C" int bl_gemm_skinny_scaled(const void* hw, const void* w, const void* bias, int bias_dtype, void* out,
+                                     int out_dtype, int M, int N, int K, int epilogue, const float* ss, int parts,
+                                     float eps, void* stream) {
+    if (ss == nullptr || parts <= 0) BL_FAIL("bl_gemm_skinny_scaled: needs the rows' partial sums of squares");
+    if (epilogue == BL_EPI_RESIDUAL) BL_FAIL("bl_gemm_skinny_scaled: the residual epilogue takes no pending norm");
+    SkinnyLink lk = {};
+    lk.ss_in = ss; lk.parts_in = parts; lk.inv_dim = 1.0f / (float)K; lk.eps = eps;
+    return run(hw, w, bias, bias_dtype, out, out_dtype, M, N, K, epilogue, lk, stream);
 }

@@ -558,36 +558,79 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[tor
     """out = epilogue(x @ w.T) by the kernel that suits the operands: float32 operands, operands the tensor-core
     kernels cannot take, and `fast=False` run the plain CUDA-core kernel; bfloat16 operands a tensor-core kernel
     chosen by the number of rows (and, for few rows, of columns)."""
+    {"plain": gemm_plain, "cols": lambda x, w, out, bias, epilogue: gemm_tc_cols(x, w, out), "splitk": gemm_tc_splitk,
+     "skinny": gemm_skinny, "tc": gemm_tc, "pair": gemm_tc_pair}[gemm_kernel(x, w, out.shape[1], bias, epilogue, fast)](
+        x, w, out, bias, epilogue)
+
+
+def gemm_kernel(x: torch.Tensor, w: torch.Tensor, N: int, bias: Optional[torch.Tensor], epilogue: int, fast: bool = True) -> str:
+    """Which kernel `gemm` runs this product on: "plain", "cols" (an output head at decode time: W streams once, as the
+    M side of the product), "splitk" (few tiles and a long K, a down projection: clusters cut K among their blocks),
+    "skinny" (few rows: W streams through registers), "tc" or "pair" (tcgen05 tiles on one SM, on pairs of SMs)."""
     if not (fast and gemm_skinny_supported(x, w)):
-        gemm_plain(x, w, out, bias, epilogue)
-        return
-    M, N, K = x.shape[0], out.shape[1], x.shape[1]
+        return "plain"
+    M, K = x.shape
     few_rows_tc = ((M > 16 and N >= TC_MIN_COLUMNS_FEW_ROWS) or (M > 8 and N >= TC_MIN_COLUMNS_VERY_FEW_ROWS)
                    or gemm_streams_better(w))
     if (N >= TC_MIN_COLUMNS_VERY_FEW_ROWS and bias is None and epilogue == EPI_NONE and M <= 64
             and gemm_tc_cols_supported(x, w)):
-        gemm_tc_cols(x, w, out)                # an output head at decode time: W streams once, as the M side of the product
-    elif (epilogue != EPI_SWIGLU and M <= SPLITK_MAX_ROWS and (M >= SPLITK_MIN_ROWS or K >= SPLITK_VERY_LONG_K)
-          and (K >= SPLITK_LONG_K or 64 < M <= 128) and gemm_tc_splitk_split(M, N, K, epilogue) >= 2):
-        gemm_tc_splitk(x, w, out, bias, epilogue)   # few tiles and a long K (a down projection): clusters cut K among their blocks
-    elif M <= SKINNY_MAX_ROWS and not few_rows_tc:
-        gemm_skinny(x, w, out, bias, epilogue)
-    elif M < PAIR_MIN_ROWS:
-        gemm_tc(x, w, out, bias, epilogue)
-    else:
-        gemm_tc_pair(x, w, out, bias, epilogue)
+        return "cols"
+    if (epilogue != EPI_SWIGLU and M <= SPLITK_MAX_ROWS and (M >= SPLITK_MIN_ROWS or K >= SPLITK_VERY_LONG_K)
+            and (K >= SPLITK_LONG_K or 64 < M <= 128) and gemm_tc_splitk_split(M, N, K, epilogue) >= 2):
+        return "splitk"
+    if M <= SKINNY_MAX_ROWS and not few_rows_tc:
+        return "skinny"
+    return "tc" if M < PAIR_MIN_ROWS else "pair"
 
 
 def gemm_on_pairs(x: torch.Tensor, w: torch.Tensor, N: int, epilogue: int, fast: bool = True) -> bool:
     """Whether `gemm` would run this product on pairs of SMs (`gemm_tc_pair`): the kernel whose epilogues can leave an
     RMS norm pending (`gemm_residual_norm`) and apply a pending one (`gemm_swiglu_scaled`, `qkv_rope_tc`)."""
-    if not (fast and gemm_skinny_supported(x, w)):
-        return False
+    return gemm_kernel(x, w, N, None, epilogue, fast) == "pair"
+
+
+SKINNY_LINK_MIN_ROWS = 2       # steps of this many rows ...
+SKINNY_LINK_MAX_ROWS = 16      # ... to this many share a norm between two register-streaming products (measured at the 0.5B
+                               # sizes: a decode step 2 % faster at 2 rows, 6 % at 4, 4 % at 8, 1 % at 16; 2 % slower at 1 row)
+SKINNY_LINK_MAX_BLOCKS = 592   # (column blocks of 16 that the linked kernel takes)
+
+
+def gemm_skinny_links_norm(x: torch.Tensor, w: torch.Tensor, N: int, epilogue: int, fast: bool = True) -> bool:
+    """Whether `gemm` would run this product on the register-streaming kernel at a row count where that kernel's
+    epilogues begin an RMS norm (`gemm_skinny_residual_norm`) and finish one (`gemm_skinny_scaled`)."""
+    return (SKINNY_LINK_MIN_ROWS <= x.shape[0] <= SKINNY_LINK_MAX_ROWS and -(-N // 16) <= SKINNY_LINK_MAX_BLOCKS
+            and gemm_kernel(x, w, N, None, epilogue, fast) == "skinny")
+
+
+def gemm_skinny_residual_norm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, norm_w: torch.Tensor):
+    """out += x @ w.T (32-bit residual stream, in place) on the register-streaming kernel, and, for the RMS norm with
+    weight `norm_w` that reads `out` next, (hw, ss): hw = bfloat16(out * norm_w), ss[m, :] = sums of squares of row m
+    by block of 16 columns (what `gemm_residual_norm` gives on pairs of SMs, for decode steps)."""
     M, K = x.shape
-    if M < PAIR_MIN_ROWS:
-        return False
-    return not (epilogue != EPI_SWIGLU and M <= SPLITK_MAX_ROWS and (K >= SPLITK_LONG_K or 64 < M <= 128)
-                and gemm_tc_splitk_split(M, N, K, epilogue) >= 2)
+    N = out.shape[1]
+    _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16, (N, K)); _need(out, "out", torch.float32, (M, N))
+    _need(norm_w, "norm_w", None, (N,))
+    parts = int(_lib().bl_gemm_skinny_norm_parts(N))
+    hw = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    ss = torch.empty((M, parts), dtype=torch.float32, device=x.device)
+    _call(_lib().bl_gemm_skinny_residual_norm, _p(x), _p(w), _p(out), M, N, K, _p(norm_w), _dt(norm_w), _p(hw), _p(ss), _stream())
+    return hw, ss
+
+
+def gemm_skinny_scaled(hw: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ss: torch.Tensor, eps: float,
+                       bias: Optional[torch.Tensor] = None, epilogue: int = EPI_NONE) -> None:
+    """out = epilogue(r * (hw @ w.T)), r[m] = 1 / sqrt(ss[m].sum() / K + eps): the product of rows whose RMS norm
+    `gemm_skinny_residual_norm` (or `gemm_residual_norm`) left pending. Epilogues: none, bias, SwiGLU."""
+    M, K = hw.shape
+    N = out.shape[1]
+    _need(hw, "hw", torch.bfloat16); _need(w, "w", torch.bfloat16, ((2 * N if epilogue == EPI_SWIGLU else N), K))
+    _need(out, "out", None, (M, N)); _need(ss, "ss", torch.float32)
+    if ss.shape[0] != M:
+        raise KernelError("gemm_skinny_scaled: ss and hw differ in rows")
+    if bias is not None:
+        _need(bias, "bias", None, (N,))
+    _call(_lib().bl_gemm_skinny_scaled, _p(hw), _p(w), _p(bias), _dt(bias) if bias is not None else 0, _p(out), _dt(out),
+          M, N, K, epilogue, _p(ss), ss.shape[1], ctypes.c_float(eps), _stream())
 
 
 def gemm_residual_norm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, norm_w: torch.Tensor):

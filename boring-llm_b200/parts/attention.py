@@ -103,6 +103,12 @@ class GQAAttention(Mixer):
     graph_safe = True
     takes_pending_norm = True            # its first product can finish an RMS norm that the product before has begun
 
+    def takes_pending_norm_at(self, rows: int) -> bool:
+        """... in steps with enough rows for the product on pairs of SMs (with few rows the norm is part of the q/k/v
+        kernel, which reads the stream itself: measured, a norm begun by the layer before's down projection made a
+        batch-8 decode step 4 % slower)."""
+        return rows >= QKV_EPILOGUE_MIN_ROWS
+
     def __init__(self, dim: int, n_heads: int, n_kv_heads: int, head_dim: int, rotary: Optional[RotaryTable],
                  names: Dict[str, str], qkv_bias: bool = True, out_bias: bool = False, window: int = 0,
                  scale: Optional[float] = None):

@@ -103,6 +103,14 @@ class StepPlan:
     shape: tuple = ()
 
 
+def takes_pending_norm(part, rows: int) -> bool:
+    """Whether `part` finishes an RMS norm that the product before it has begun, in a step of `rows` rows: its
+    `takes_pending_norm_at(rows)` if it has one, else its flag `takes_pending_norm`. The product before begins the
+    norm only then (beginning it costs its epilogue a little; a reader that norms the stream itself gains nothing)."""
+    at = getattr(part, "takes_pending_norm_at", None)
+    return bool(at(rows)) if at is not None else bool(getattr(part, "takes_pending_norm", False))
+
+
 class PendingNormRows:
     """Rows whose RMS norm has been begun by the product that wrote the residual stream and is finished by the product
     that reads them: `rows` = bfloat16(stream * norm weight), `sums` [T, parts] = sums of squares of each row of the

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 from typing import Optional
 
-from .base import Part
+from .base import Part, takes_pending_norm
 
 
 class PreNormBlock(Part):
@@ -27,8 +27,9 @@ class PreNormBlock(Part):
     def forward(self, ctx, x, cache_layer: Optional[int], write_cache: bool = True) -> None:
         # a mixer or feed-forward may take the norm in front of it into its first kernel (steps with few rows)
         # (and the product that adds into the stream may begin the norm that reads it next: ctx.next_norm says which,
-        # and a part that can finish such a norm says so with `takes_pending_norm`)
-        ctx.next_norm = self.ffn_norm
+        # and a part that can finish such a norm says so with `takes_pending_norm`, or, by the step's number of rows,
+        # with `takes_pending_norm_at`)
+        ctx.next_norm = self.ffn_norm if takes_pending_norm(self.ffn, x.shape[0]) else None
         if not self.mixer.forward_fused_norm(ctx, x, self.mixer_norm, cache_layer, write_cache):
             h = self._normed(ctx, self.mixer_norm, x, self.mixer)
             self.mixer.forward(ctx, h, x, cache_layer, write_cache)
@@ -40,7 +41,7 @@ class PreNormBlock(Part):
 
     @staticmethod
     def _normed(ctx, norm, x, reader):
-        if getattr(reader, "takes_pending_norm", False) and hasattr(norm, "dim"):
+        if takes_pending_norm(reader, x.shape[0]) and hasattr(norm, "dim"):
             try:
                 return norm.forward(ctx, x, pending_ok=True)
             except TypeError:                    # a norm part without the option

@@ -54,6 +54,9 @@ class SwiGLU(FeedForward):
         if not (ctx.fast and ctx.dtype == torch.bfloat16 and x.shape[0] <= FF_FUSED_MAX_ROWS and isinstance(norm, RMSNorm)
                 and ops.norm_gemm_supported(x, self.w_gate_up) and not ops.gemm_streams_better(self.w_gate_up)):
             return False
+        held = ctx.memo.get(("pending norm", id(x)))
+        if held is not None and held.norm is norm:
+            return False                # the product before has begun this norm: `forward` finishes it in gate/up's epilogue
         act = ctx.empty((x.shape[0], self.hidden))
         ops.norm_gemm(x, norm.weight, norm.eps, self.w_gate_up, act, None, EPI_SWIGLU)
         linear(ctx, act, self.w_down, x, None, EPI_RESIDUAL)

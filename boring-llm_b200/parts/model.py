@@ -7,7 +7,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ..weights import TensorSpec
-from .base import Part
+from .base import Part, takes_pending_norm
 
 
 @dataclass(frozen=True)
@@ -78,7 +78,8 @@ class DecoderModel(Part):
         for i, call in enumerate(self.schedule):
             # the norm that reads the stream after this block: the next block's first (the final norm reads a few rows only)
             after = self.blocks[self.schedule[i + 1].block] if i + 1 < len(self.schedule) else None
-            ctx.norm_after_block = getattr(after, "mixer_norm", None)
+            reader = getattr(after, "mixer", None)
+            ctx.norm_after_block = getattr(after, "mixer_norm", None) if takes_pending_norm(reader, x.shape[0]) else None
             self.blocks[call.block].forward(ctx, x, call.cache, call.write_cache)
         ctx.norm_after_block = None
         if ctx.logit_rows.shape[0] == 0:

@@ -892,6 +892,57 @@ def test_rms_norm_shared_between_two_products(M, N, K, F):
     close(act, formula, bf, "SwiGLU that finishes the norm")
 
 
+@pytest.mark.parametrize("M,N,K,F", [(8, 896, 896, 4864), (1, 896, 4864, 304), (13, 136, 264, 72), (16, 2048, 2048, 640), (3, 40, 64, 24)])
+def test_rms_norm_shared_between_two_products_of_a_decode_step(M, N, K, F):
+    """The same on the register-streaming kernel (steps of up to 16 rows): the residual epilogue writes the stream, the
+    stream times the next norm's weight in bfloat16 and each row's sums of squares by block of 16 columns; the product
+    that reads those rows scales its sums by the rows' 1 / sqrt(mean + eps). Against the kernels as they were
+    (product, norm, product), and the float64 formulas; widths that are no multiple of 16, one row, a row of zeros,
+    the long-K form of the kernel (16 warps)."""
+    o = ops()
+    bf = torch.bfloat16
+    x = (data((M, K), 51) * 0.5).to(bf)
+    w = (data((N, K), 52) * 0.2).to(bf)
+    stream = data((M, N), 53) * 2
+    if M > 2:
+        stream[2] = 0.0
+        x[2] = 0.0                                            # a row whose new stream is all zeros: scale 1 / sqrt(eps)
+    nw = (data((N,), 54) * 0.25 + 1).to(bf)
+    eps = 1e-5
+    assert o.gemm_skinny_links_norm(x, w, N, o.EPI_RESIDUAL) == (M >= 2)      # (the kernels take one row; the dispatch does not send it)
+    ref = stream.clone()
+    o.gemm_skinny(x, w, ref, None, o.EPI_RESIDUAL)
+    h_ref = torch.empty(M, N, dtype=bf, device=DEV)
+    o.rmsnorm(ref, nw, eps, h_ref)
+    out = stream.clone()
+    hw, ss = o.gemm_skinny_residual_norm(x, w, out, nw)
+    assert torch.equal(out, ref)                              # the stream itself is what the residual epilogue writes
+    assert ss.shape == (M, -(-N // 16))
+    want = out.double().cpu()
+    close(hw, want * nw.double().cpu(), bf, "stream times weight")
+    close(ss.sum(dim=1), (want * want).sum(dim=1), torch.float32, "sums of squares")
+    col = torch.arange(N) // 16
+    by_block = torch.zeros(M, ss.shape[1], dtype=torch.float64).index_add_(1, col, want * want)
+    close(ss, by_block, torch.float32, "sums of squares by block of 16 columns")
+    scale = torch.rsqrt((want * want).mean(dim=1) + eps)
+    h64 = want * scale[:, None] * nw.double().cpu()
+    # SwiGLU over the pending rows against SwiGLU over the normed rows
+    wg = (data((2 * F, N), 55) * 0.1).to(bf)
+    act = torch.full((M, F), float("nan"), dtype=bf, device=DEV)
+    o.gemm_skinny_scaled(hw, wg, act, ss, eps, None, o.EPI_SWIGLU)
+    act_ref = torch.empty(M, F, dtype=bf, device=DEV)
+    o.gemm_skinny(h_ref, wg, act_ref, None, o.EPI_SWIGLU)
+    wgd = wg.double().cpu()
+    formula = plain.silu(h64 @ wgd[:F].T) * (h64 @ wgd[F:].T)
+    close(act_ref, formula, bf, "SwiGLU of the normed rows (the kernels as they were)")
+    close(act, formula, bf, "SwiGLU that finishes the norm")
+    # a plain product with a bias, 32-bit out
+    b = data((F,), 56)
+    y = torch.full((M, F), float("nan"), dtype=torch.float32, device=DEV)
+    o.gemm_skinny_scaled(hw, wg[:F].contiguous(), y, ss, eps, b, o.EPI_BIAS)
+    close(y, h64 @ wgd[:F].T + b.double().cpu(), bf, "product with bias that finishes the norm")
+
+
 def test_qkv_product_finishes_a_pending_norm():
     """`qkv_rope_tc` with `row_sums`: q, keys and values equal those from the normed rows (norm kernel, then the same
     product) within bfloat16 rounding, and the float64 formula for q."""

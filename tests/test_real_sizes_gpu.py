@@ -129,7 +129,7 @@ def test_bfloat16_benchmarked_path_equals_the_plain_implementation():
         ops._call = real_call
     assert eng.runner.graph_steps >= 30
     for name in ("bl_gemm_tc_cols", "bl_gemm_tc_pair", "bl_attention_prefill_tc", "bl_attention_decode_tma",
-                 "bl_norm_qkv_rope", "bl_norm_gemm", "bl_gemm_skinny"):
+                 "bl_norm_qkv_rope", "bl_gemm_skinny_residual_norm", "bl_gemm_skinny_scaled", "bl_gemm_skinny"):
         assert name in used, f"{name} was not on the path"
     check_tokens(cfg, T, prompts, outs)
     # the same with every step in turn and no captured graph (other slice counts in the decode attention)
