@@ -111,3 +111,27 @@ cudaError_t bl_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block,
     cfg.attrs = &attr; cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
+
+// The same for a kernel whose neighbouring blocks form clusters of `cluster_x` (grid.x a multiple of it).
+template <typename... KArgs, typename... Args>
+cudaError_t bl_launch_dependent_clusters(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                         unsigned cluster_x, Args... args) {
+    static thread_local const void* seen[16];
+    static thread_local int n_seen = 0;
+    bool known = false;
+    for (int i = 0; i < n_seen; ++i) if (seen[i] == (const void*)kernel) { known = true; break; }
+    if (!known) {
+        cudaError_t e = bl_same_carveout(kernel);
+        if (e != cudaSuccess) return e;
+        if (n_seen < 16) seen[n_seen++] = (const void*)kernel;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = bl_pdl_enabled() ? 1 : 0;
+    attrs[1].id = cudaLaunchAttributeClusterDimension;
+    attrs[1].val.clusterDim.x = cluster_x; attrs[1].val.clusterDim.y = 1; attrs[1].val.clusterDim.z = 1;
+    cfg.attrs = attrs; cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

@@ -39,10 +39,14 @@ struct SkinnyLink {
     const float* ss_in; int parts_in; float inv_dim, eps;                         // consumer
 };
 
+// SPLIT 2: two neighbouring blocks (a cluster) share 16 columns and cut K in two; the second hands its sums to the first
+// through distributed shared memory, and the first adds them to its own (always in this order) before the epilogue.
+// For a long K on few column blocks (a down projection at decode time: 56 blocks would leave most SMs idle, and each
+// of the 56 would pull its 155 KB of W and all of x through one SM's port to L2).
 // MT: groups of 8 tokens handled by one block (M tile = 8 * MT). NW: warps per block (8, or 16 for long K).
 // DEEP: two batches of loads in flight per warp (few blocks, each short: hide the trips to memory); without it one
 // batch and half the registers, so that twice as many blocks fit an SM (many blocks: HBM throughput is what counts).
-template <int MT, int EPI, typename TO, int NW, bool DEEP>
+template <int MT, int EPI, typename TO, int NW, bool DEEP, int SPLIT = 1>
 __global__ void __launch_bounds__(NW * 32, DEEP ? 1 : (NW == 8 ? 4 : 2))
 gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no read-only cache */,
                    const __nv_bfloat16* __restrict__ w,
@@ -52,10 +56,15 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
     constexpr int TOK = MT * 8;
     __shared__ float red[GLU ? 2 : 1][NW][COLS][TOK + 1];
     __shared__ float row_scale[TOK];
+    __shared__ float peer_sums[SPLIT == 2 ? COLS * TOK : 1];      // the second block's sums, written by it into the first
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = (blockIdx.x / m_groups) * COLS;
-    const int m0 = (blockIdx.x % m_groups) * TOK;
+    const int tile = blockIdx.x / SPLIT, part = SPLIT == 2 ? (int)(blockIdx.x % SPLIT) : 0;   // (a cluster is SPLIT neighbouring blocks)
+    const int n0 = (tile / m_groups) * COLS;
+    const int m0 = (tile % m_groups) * TOK;
+    // this block's share of K: whole 32-wide chunks
+    const int k_cut = SPLIT == 2 ? ((K / 2 + 31) / 32) * 32 : K;
+    const int k_begin = part == 0 ? 0 : k_cut, k_end = part == 0 ? min(K, k_cut) : K;
     float acc[MT][4], acu[GLU ? MT : 1][4];
 #pragma unroll
     for (int j = 0; j < MT; ++j)
@@ -79,7 +88,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int k = kc0 + u * NW * 32 + 8 * t;
-            const bool k_ok = k < K;
+            const bool k_ok = k < k_end;
             bt.a_lo[u] = ld16(w_lo + k, lo_ok && k_ok);
             bt.a_hi[u] = ld16(w_hi + k, hi_ok && k_ok);
             if (GLU) { bt.g_lo[u] = ld16(u_lo + k, lo_ok && k_ok); bt.g_hi[u] = ld16(u_hi + k, hi_ok && k_ok); }
@@ -92,8 +101,8 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
 #pragma unroll
             for (int j = 0; j < MT; ++j) {
                 const int tok = m0 + 8 * j + g;
-                bt.b[u][j] = (tok < M && k < K) ? *reinterpret_cast<const uint4*>(x + (size_t)tok * K + k)
-                                                : make_uint4(0u, 0u, 0u, 0u);
+                bt.b[u][j] = (tok < M && k < k_end) ? *reinterpret_cast<const uint4*>(x + (size_t)tok * K + k)
+                                                    : make_uint4(0u, 0u, 0u, 0u);
             }
         }
     };
@@ -114,13 +123,22 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
     Batch b0;
     Batch b1;        // used only when DEEP
     bl_pdl_trigger();
-    fetch_w(b0, warp * 32);
-    bl_prefetch_rows_l2(w, n0, COLS, (size_t)K * 2, (size_t)(GLU ? 2 * N : N));
-    if (GLU) bl_prefetch_rows_l2(w, (size_t)N + n0, COLS, (size_t)K * 2, (size_t)2 * N);
+    fetch_w(b0, k_begin + warp * 32);
+    if (SPLIT == 2) {
+        // this block's half of the 16 rows of W: the 128-byte lines of k_begin .. k_end of each row
+        const int lines = ((k_end - k_begin) * 2 + 127) / 128;
+        for (int i = threadIdx.x; i < COLS * lines; i += NW * 32) {
+            const int r = n0 + i / lines;
+            if (r < N) bl_prefetch_l2(reinterpret_cast<const char*>(w + (size_t)r * K + k_begin) + (size_t)(i % lines) * 128);
+        }
+    } else {
+        bl_prefetch_rows_l2(w, n0, COLS, (size_t)K * 2, (size_t)(GLU ? 2 * N : N));
+        if (GLU) bl_prefetch_rows_l2(w, (size_t)N + n0, COLS, (size_t)K * 2, (size_t)2 * N);
+    }
     // this thread's output element and, for the bias epilogue, its bias
     const int e_c = threadIdx.x % COLS, e_tok = threadIdx.x / COLS;
     const int e_n = n0 + e_c, e_m = m0 + e_tok;
-    const bool e_ok = threadIdx.x < COLS * TOK && e_n < N && e_m < M;
+    const bool e_ok = threadIdx.x < COLS * TOK && e_n < N && e_m < M && part == 0;
     float e_add = 0.f;
     if (EPI == BL_EPI_BIAS && e_ok) e_add = bl_load_any(bias, bias_dtype, e_n);
     const bool begins_norm = EPI == BL_EPI_RESIDUAL && lk.hw != nullptr;
@@ -128,7 +146,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
     if (begins_norm && e_ok) e_nw = bl_load_any(lk.norm_w, lk.norm_w_dtype, e_n);
     bl_pdl_wait();
     if (EPI == BL_EPI_RESIDUAL && e_ok) e_add = bl_load(out + (size_t)e_m * N + e_n);   // on its way during the product
-    fetch_x(b0, warp * 32);
+    fetch_x(b0, k_begin + warp * 32);
     if (lk.ss_in != nullptr) {
         // the scale of each of this block's rows, while the product's operands are on their way: warp w adds up the
         // partial sums of rows w, w + NW, ... (a lane its share in ascending order, then the warp's fixed tree)
@@ -143,18 +161,18 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
     }
     // two batches per trip of the loop, so that the buffers keep their names (and their registers)
     if (DEEP) {
-        for (int kc0 = warp * 32; kc0 < K; kc0 += 2 * STEP) {
-            const bool more1 = kc0 + STEP < K;
+        for (int kc0 = k_begin + warp * 32; kc0 < k_end; kc0 += 2 * STEP) {
+            const bool more1 = kc0 + STEP < k_end;
             if (more1) { fetch_w(b1, kc0 + STEP); fetch_x(b1, kc0 + STEP); }
             multiply(b0);
             if (!more1) break;
-            if (kc0 + 2 * STEP < K) { fetch_w(b0, kc0 + 2 * STEP); fetch_x(b0, kc0 + 2 * STEP); }
+            if (kc0 + 2 * STEP < k_end) { fetch_w(b0, kc0 + 2 * STEP); fetch_x(b0, kc0 + 2 * STEP); }
             multiply(b1);
         }
     } else {
-        for (int kc0 = warp * 32; kc0 < K; kc0 += STEP) {
+        for (int kc0 = k_begin + warp * 32; kc0 < k_end; kc0 += STEP) {
             multiply(b0);
-            if (kc0 + STEP < K) { fetch_w(b0, kc0 + STEP); fetch_x(b0, kc0 + STEP); }
+            if (kc0 + STEP < k_end) { fetch_w(b0, kc0 + STEP); fetch_x(b0, kc0 + STEP); }
         }
     }
     // c0, c1: (column g, tokens 2t, 2t+1); c2, c3: (column g + 8, tokens 2t, 2t+1)
@@ -168,6 +186,23 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
         }
     }
     __syncthreads();
+    if (SPLIT == 2) {
+        // the second block adds up its warps' sums and stores them into the first block's shared memory; both meet
+        // at the cluster's barrier (release / acquire), after which the first reads them
+        static_assert(SPLIT == 1 || !GLU, "the split kernel has one matrix per column");
+        if (part == 1) {
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(peer_sums)), "r"(0u));
+            for (int i = threadIdx.x; i < COLS * TOK; i += NW * 32) {
+                float v = 0.f;
+#pragma unroll
+                for (int wp = 0; wp < NW; ++wp) v += red[0][wp][i % COLS][i / COLS];
+                asm volatile("st.shared::cluster.f32 [%0], %1;" :: "r"(remote + 4u * (uint32_t)i), "f"(v) : "memory");
+            }
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (part == 1) return;
+    }
     // the first COLS * TOK threads each own one output element (their residual or bias is already in a register)
     // (every lane of a warp makes the same number of trips: COLS * TOK is a multiple of 32)
     for (int i = threadIdx.x; i < COLS * TOK; i += NW * 32) {
@@ -178,6 +213,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
         if (valid) {
 #pragma unroll
             for (int wp = 0; wp < NW; ++wp) { v += red[0][wp][c][tok]; if (GLU) u += red[1][wp][c][tok]; }
+            if (SPLIT == 2) v += peer_sums[i];
             if (lk.ss_in != nullptr) { const float r = row_scale[tok]; v *= r; if (GLU) u *= r; }
             TO* dst = out + (size_t)m * N + n;
             if (EPI == BL_EPI_BIAS || EPI == BL_EPI_RESIDUAL) v += (i == threadIdx.x) ? e_add : (EPI == BL_EPI_BIAS ? bl_load_any(bias, bias_dtype, n) : bl_load(dst));
@@ -190,7 +226,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
 #pragma unroll
             for (int o = 8; o; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
             if (valid) lk.hw[(size_t)m * N + n] = __float2bfloat16_rn(v * ((i == threadIdx.x) ? e_nw : bl_load_any(lk.norm_w, lk.norm_w_dtype, n)));
-            if (c == 0 && m < M) lk.ss_out[(size_t)m * (gridDim.x / m_groups) + blockIdx.x / m_groups] = sq;
+            if (c == 0 && m < M) lk.ss_out[(size_t)m * (gridDim.x / SPLIT / m_groups) + tile / m_groups] = sq;
         }
     }
 }
@@ -323,6 +359,33 @@ int launch_nw(const void* x, const void* w, const void* bias, int bias_dtype, vo
     return 0;
 }
 
+// The long-K kernel (16 warps, one group of 8 tokens) with K cut over the two blocks of a cluster.
+template <typename TO>
+int launch_split(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K,
+                 int epi, const SkinnyLink& lk, cudaStream_t s) {
+    const int blocks = (N + COLS - 1) / COLS;
+#define BL_GO(E) BL_CUDA(bl_launch_dependent_clusters(gemm_skinny_kernel<1, E, TO, 16, true, 2>, dim3(2 * blocks), dim3(16 * 32), 0, s, 2u, \
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, bias_dtype, (TO*)out, M, N, K, 1, lk))
+    switch (epi) {
+        case BL_EPI_NONE: BL_GO(BL_EPI_NONE); break;
+        case BL_EPI_BIAS: BL_GO(BL_EPI_BIAS); break;
+        case BL_EPI_RESIDUAL: BL_GO(BL_EPI_RESIDUAL); break;
+        default: BL_FAIL("bl_gemm_skinny: the kernel that cuts K over two blocks has no epilogue %d", epi);
+    }
+#undef BL_GO
+    return 0;
+}
+
+int sm_count() {
+    static int sms = 0;                                          // (of the current device at the first call)
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    return sms;
+}
+
 // Long rows of W are cut over 16 warps instead of 8: fewer trips to memory one after the other per warp.
 template <int MT, typename TO>
 int launch(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K,
@@ -336,6 +399,8 @@ int launch(const void* x, const void* w, const void* bias, int bias_dtype, void*
         return launch_cols<MT, TO>(x, w, bias, bias_dtype, out, M, N, K, epi, s);
     }
     if (blocks > 4 * 148) return launch_nw<MT, TO, 8, false>(x, w, bias, bias_dtype, out, M, N, K, epi, lk, s);
+    // (this choice, too, depends on N and K alone)
+    if (K >= 2048 && MT == 1 && epi != BL_EPI_SWIGLU && 2 * blocks <= sm_count()) return launch_split<TO>(x, w, bias, bias_dtype, out, M, N, K, epi, lk, s);
     if (K >= 2048 && MT == 1 && epi != BL_EPI_SWIGLU) return launch_nw<1, TO, 16, true>(x, w, bias, bias_dtype, out, M, N, K, epi, lk, s);
     return launch_nw<MT, TO, 8, true>(x, w, bias, bias_dtype, out, M, N, K, epi, lk, s);
 }

@@ -379,8 +379,12 @@ def test_kernels_refuse_what_they_cannot_run():
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 7, 8), (8, 1152, 896), (5, 200, 96), (17, 129, 80), (33, 64, 264), (64, 4864 // 8, 176),
-                                   (100, 50, 64), (3, 9500, 72), (20, 9481, 40), (40, 9600, 64)])
+                                   (100, 50, 64), (3, 9500, 72), (20, 9481, 40), (40, 9600, 64),
+                                   (8, 896, 4864), (3, 130, 2056), (8, 2400, 2048), (1, 16, 4096), (7, 1184, 2048)])
 def test_gemm_skinny_epilogues(M, N, K):
+    """(The last shapes have a long K and at most 8 rows: with few column blocks K is cut over the two blocks of a
+    cluster, the second handing its sums to the first: 56, 9, 1 and 74 column blocks, a K that is no multiple of 32;
+    2,400 columns are too many blocks for that and run the long-K kernel unsplit.)"""
     o = ops()
     dtype = torch.bfloat16
     x = (data((M, K), 14) * 0.5).to(dtype)
@@ -407,10 +411,12 @@ def test_gemm_skinny_epilogues(M, N, K):
     o.gemm_skinny(x[M - 1:M].contiguous(), wn, one)
     o.gemm_skinny(x, wn, out)
     assert torch.equal(one[0], out[M - 1])
-    # and it is the plain kernel's twin
-    twin = torch.empty(M, N, device=DEV)
-    o.gemm_plain(x, wn, twin)
-    close(out, twin.double(), torch.float32, "twin")
+    # and it is the plain kernel's twin (where K is short enough for the plain kernel's one 32-bit chain per output
+    # to stay inside this bound itself: at K = 4,864 it is 2.1e-5 of the scale off the 64-bit product, this kernel 1e-5)
+    if K <= 1024:
+        twin = torch.empty(M, N, device=DEV)
+        o.gemm_plain(x, wn, twin)
+        close(out, twin.double(), torch.float32, "twin")
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 151936 // 16, 896), (16, 1000, 200), (17, 333, 72), (32, 4100, 896), (5, 130, 8), (33, 700, 136), (64, 2100, 896)])
