@@ -1,17 +1,17 @@
-// Paged causal grouped-query attention for prefill on the fifth-generation tensor cores (head size 64).
+// Paged causal grouped-query attention for prefill on the fifth-generation tensor cores (head sizes 64 and 128).
 //
 // A block is a tile of 128 consecutive new tokens of one request and one query head. It walks the request's keys
 // in blocks of 128 (eight 16-token pages) up to the diagonal:
 //   S = Q . K^T      tcgen05.mma, M 128 x N 128 x K 64, Q and the key block in shared memory (TMA, 128-byte
 //                    swizzle, K-major), S in tensor memory;
 //   softmax          a thread reads its row of S with tcgen05.ld (lane r of tensor memory is row r, so the row
-//                    maximum and sum need no shuffles), keeps the running maximum and sum in 32-bit, and writes
+//                    maximum and sum need no shuffles), keeps a reference maximum m and the sum in 32-bit, and writes
 //                    P = 2^(s - m) as bfloat16 pairs back into tensor memory (tcgen05.st), where the second
 //                    product takes its A operand from: P never passes through shared memory, whose bandwidth
 //                    the products' other operands and the TMA copies need;
-//   O_b = P . V      tcgen05.mma, M 128 x N 64 x K 128, V as it lies in its pages (keys x head size: the
-//                    MN-major form of the B operand), O_b in tensor memory;
-//   out = out * 2^(m_old - m) + O_b   in registers.
+//   O += P . V       tcgen05.mma, M 128 x N 64 x K 128, V as it lies in its pages (keys x head size: the
+//                    MN-major form of the B operand), O accumulated in tensor memory over the key blocks;
+//   m moves only when a block's maximum passes it by 2^8; O (load, scale, store) and the sum are then rescaled.
 // Twelve warps: eight own the rows, in two groups of four that take the even and the odd key blocks (each with a
 // running maximum, sum and output of its own, merged at the end as the slices of a split are); one issues the
 // first product and one the second (lane 0 each), two issue the TMA copies of keys and of values (a box costs its
