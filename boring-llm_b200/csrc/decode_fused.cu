@@ -121,6 +121,48 @@ fused_norm_gemm_kernel(const FusedParams p) {
 
     __syncthreads();                                   // the norm weights are in shared memory
     // normalise this block's rows into shared memory: warp w takes rows w, w + 8, ...
+    constexpr int NB = 8;                              // 16-byte words per lane that hold a row of up to 1,024 values
+    if (MT > 1 && K <= NB * 128) {
+        // A warp's MT rows at once: all their words are on their way before the first sum is taken (one trip to L2
+        // for the warp instead of one per row: at 64 rows a block's norm took 4 us of the kernel's 8). Each row's
+        // arithmetic is what the loop below does for it, in the same order.
+        float4 v[MT][NB];
+#pragma unroll
+        for (int r = 0; r < MT; ++r) {
+            const int m = m0 + warp + r * WARPS;
+            const float* src = p.x + (size_t)(m < p.M ? (p.row_idx ? p.row_idx[m] : m) : 0) * K;
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                const int k = j * 128 + lane * 4;
+                v[r][j] = (m < p.M && k < K) ? *reinterpret_cast<const float4*>(src + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < MT; ++r) {
+            const int i = warp + r * WARPS, m = m0 + i;
+            __nv_bfloat16* dst = xs + (size_t)i * XROW;
+            if (m >= p.M) {
+                for (int k = lane * 4; k < K; k += 128) *reinterpret_cast<uint2*>(dst + k) = make_uint2(0u, 0u);
+                continue;
+            }
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < NB; ++j) { ss += v[r][j].x * v[r][j].x; ss += v[r][j].y * v[r][j].y; ss += v[r][j].z * v[r][j].z; ss += v[r][j].w * v[r][j].w; }
+            ss = bl_warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)K + p.eps);
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                const int k = j * 128 + lane * 4;
+                if (k >= K) continue;
+                const float4 nw = *reinterpret_cast<const float4*>(nws + k);
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v[r][j].x * inv * nw.x, v[r][j].y * inv * nw.y);
+                __nv_bfloat162 hi = __floats2bfloat162_rn(v[r][j].z * inv * nw.z, v[r][j].w * inv * nw.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<unsigned*>(&lo); pk.y = *reinterpret_cast<unsigned*>(&hi);
+                *reinterpret_cast<uint2*>(dst + k) = pk;
+            }
+        }
+    } else
     for (int i = warp; i < TOK; i += WARPS) {
         const int m = m0 + i;
         __nv_bfloat16* dst = xs + (size_t)i * XROW;
@@ -131,7 +173,6 @@ fused_norm_gemm_kernel(const FusedParams p) {
         // The row is read in batches of NB 16-byte words per lane, all on their way at once; a row of up to
         // NB * 128 values stays in registers between the sum of squares and the scaling.
         const float* src = p.x + (size_t)(p.row_idx ? p.row_idx[m] : m) * K;
-        constexpr int NB = 8;
         float4 v[NB];
         auto load_batch = [&](int k0) {
 #pragma unroll
