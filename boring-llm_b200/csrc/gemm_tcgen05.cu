@@ -23,9 +23,13 @@ namespace {
 
 constexpr const char* WHO = "bl_gemm_tc";
 
-constexpr int BM = 128, BN = 128, BK = 64, STAGES = 3;
+constexpr int BM = 128, BN = 128, BK = 64;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+// Stages of the ring: three, so that two blocks share an SM, where a launch has more blocks than SMs; six where it
+// has fewer (a block then has an SM to itself, and three 32 KB stages in flight against a microsecond of latency
+// are 100 GB/s: gate/up of a 64-row decode step, 76 blocks that each stream 344 KB, took 9 us).
+constexpr int STAGES_SHARED = 3, STAGES_ALONE = 6;
+constexpr int smem_bytes(int stages) { return stages * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */; }
 constexpr int TMEM_COLS = 128;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
@@ -48,7 +52,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // kind::f16 instruction descriptor: D 32-bit, A and B bfloat16 and K-major, N >> 3 at bit 17, M >> 4 at bit 24.
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
-template <int EPI, typename TO>
+template <int EPI, typename TO, int STAGES>
 __global__ void __launch_bounds__(128)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const void* __restrict__ bias, int bias_dtype, TO* __restrict__ out, int M, int N, int K) {
@@ -215,21 +219,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+int sm_count() {
+    static int sms = 0;                                          // (of the current device at the first call)
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    return sms;
+}
+
+template <int EPI, typename TO, int STAGES>
+int launch_stages(const CUtensorMap& a, const CUtensorMap& b, const void* bias, int bias_dtype, void* out, int M, int N, int K,
+                  dim3 grid, cudaStream_t s) {
+    static bool configured = false;
+    if (!configured) {
+        BL_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<EPI, TO, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(STAGES)));
+        configured = true;
+    }
+    // a block waits (griddepcontrol.wait) before it allocates tensor memory or touches x and out, so it may be launched
+    // while its predecessor still runs
+    BL_CUDA(bl_launch_dependent(gemm_tc_kernel<EPI, TO, STAGES>, grid, dim3(128), (size_t)smem_bytes(STAGES), s, a, b, bias, bias_dtype, (TO*)out, M, N, K));
+    BL_CHECK_LAUNCH("bl_gemm_tc");
+    return 0;
+}
+
 template <int EPI, typename TO>
 int launch(const CUtensorMap& a, const CUtensorMap& b, const void* bias, int bias_dtype, void* out, int M, int N, int K,
            cudaStream_t s) {
-    static bool configured = false;
-    if (!configured) {
-        BL_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        configured = true;
-    }
     const int cols_per_tile = EPI == BL_EPI_SWIGLU ? BN / 2 : BN;
     dim3 grid((N + cols_per_tile - 1) / cols_per_tile, (M + BM - 1) / BM);
-    // a block waits (griddepcontrol.wait) before it allocates tensor memory or touches x and out, so it may be launched
-    // while its predecessor still runs
-    BL_CUDA(bl_launch_dependent(gemm_tc_kernel<EPI, TO>, grid, dim3(128), (size_t)SMEM_BYTES, s, a, b, bias, bias_dtype, (TO*)out, M, N, K));
-    BL_CHECK_LAUNCH("bl_gemm_tc");
-    return 0;
+    // (the sums of a tile do not depend on the depth of the ring)
+    if ((long long)grid.x * grid.y <= sm_count()) return launch_stages<EPI, TO, STAGES_ALONE>(a, b, bias, bias_dtype, out, M, N, K, grid, s);
+    return launch_stages<EPI, TO, STAGES_SHARED>(a, b, bias, bias_dtype, out, M, N, K, grid, s);
 }
 
 }  // namespace
