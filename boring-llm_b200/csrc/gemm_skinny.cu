@@ -47,7 +47,7 @@ struct SkinnyLink {
 // DEEP: two batches of loads in flight per warp (few blocks, each short: hide the trips to memory); without it one
 // batch and half the registers, so that twice as many blocks fit an SM (many blocks: HBM throughput is what counts).
 template <int MT, int EPI, typename TO, int NW, bool DEEP, int SPLIT = 1>
-__global__ void __launch_bounds__(NW * 32, DEEP ? 1 : (NW == 8 ? 4 : 2))
+__global__ void __launch_bounds__(NW * 32, DEEP ? (EPI == BL_EPI_SWIGLU && MT == 2 ? 2 : 1) : (NW == 8 ? 4 : 2))
 gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no read-only cache */,
                    const __nv_bfloat16* __restrict__ w,
                    const void* __restrict__ bias, int bias_dtype, TO* out,
@@ -81,7 +81,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
     // the current one is multiplied: a trip to L2 costs far more than the arithmetic of a batch. The first
     // batch of W, and the whole slice of W as an L2 prefetch, are issued before the kernel waits for its
     // predecessor, since W does not depend on it.
-    constexpr int UNROLL = (GLU || MT > 2) ? 2 : 4;
+    constexpr int UNROLL = (GLU || MT > 2 || (MT == 2 && NW == 16)) ? 2 : 4;   // (16 warps of 128 registers: two groups of tokens leave room for two loads a batch)
     constexpr int STEP = UNROLL * NW * 32;
     struct Batch { uint4 a_lo[UNROLL], a_hi[UNROLL], g_lo[GLU ? UNROLL : 1], g_hi[GLU ? UNROLL : 1], b[UNROLL][MT]; };
     auto fetch_w = [&](Batch& bt, int kc0) {
@@ -359,12 +359,12 @@ int launch_nw(const void* x, const void* w, const void* bias, int bias_dtype, vo
     return 0;
 }
 
-// The long-K kernel (16 warps, one group of 8 tokens) with K cut over the two blocks of a cluster.
-template <typename TO>
+// The long-K kernel (16 warps, one or two groups of 8 tokens) with K cut over the two blocks of a cluster.
+template <int MT, typename TO>
 int launch_split(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int M, int N, int K,
                  int epi, const SkinnyLink& lk, cudaStream_t s) {
     const int blocks = (N + COLS - 1) / COLS;
-#define BL_GO(E) BL_CUDA(bl_launch_dependent_clusters(gemm_skinny_kernel<1, E, TO, 16, true, 2>, dim3(2 * blocks), dim3(16 * 32), 0, s, 2u, \
+#define BL_GO(E) BL_CUDA(bl_launch_dependent_clusters(gemm_skinny_kernel<MT, E, TO, 16, true, 2>, dim3(2 * blocks), dim3(16 * 32), 0, s, 2u, \
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, bias_dtype, (TO*)out, M, N, K, 1, lk))
     switch (epi) {
         case BL_EPI_NONE: BL_GO(BL_EPI_NONE); break;
@@ -400,7 +400,7 @@ int launch(const void* x, const void* w, const void* bias, int bias_dtype, void*
     }
     if (blocks > 4 * 148) return launch_nw<MT, TO, 8, false>(x, w, bias, bias_dtype, out, M, N, K, epi, lk, s);
     // (this choice, too, depends on N and K alone)
-    if (K >= 2048 && MT == 1 && epi != BL_EPI_SWIGLU && 2 * blocks <= sm_count()) return launch_split<TO>(x, w, bias, bias_dtype, out, M, N, K, epi, lk, s);
+    if (K >= 2048 && MT <= 2 && epi != BL_EPI_SWIGLU && 2 * blocks <= sm_count()) return launch_split<(MT <= 2 ? MT : 1), TO>(x, w, bias, bias_dtype, out, M, N, K, epi, lk, s);
     if (K >= 2048 && MT == 1 && epi != BL_EPI_SWIGLU) return launch_nw<1, TO, 16, true>(x, w, bias, bias_dtype, out, M, N, K, epi, lk, s);
     return launch_nw<MT, TO, 8, true>(x, w, bias, bias_dtype, out, M, N, K, epi, lk, s);
 }

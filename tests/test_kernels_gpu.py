@@ -380,9 +380,10 @@ def test_kernels_refuse_what_they_cannot_run():
 
 @pytest.mark.parametrize("M,N,K", [(1, 7, 8), (8, 1152, 896), (5, 200, 96), (17, 129, 80), (33, 64, 264), (64, 4864 // 8, 176),
                                    (100, 50, 64), (3, 9500, 72), (20, 9481, 40), (40, 9600, 64),
-                                   (8, 896, 4864), (3, 130, 2056), (8, 2400, 2048), (1, 16, 4096), (7, 1184, 2048)])
+                                   (8, 896, 4864), (3, 130, 2056), (8, 2400, 2048), (1, 16, 4096), (7, 1184, 2048),
+                                   (16, 896, 4864), (9, 130, 2056), (12, 1184, 2048)])
 def test_gemm_skinny_epilogues(M, N, K):
-    """(The last shapes have a long K and at most 8 rows: with few column blocks K is cut over the two blocks of a
+    """(The last shapes have a long K and at most 16 rows: with few column blocks K is cut over the two blocks of a
     cluster, the second handing its sums to the first: 56, 9, 1 and 74 column blocks, a K that is no multiple of 32;
     2,400 columns are too many blocks for that and run the long-K kernel unsplit.)"""
     o = ops()
