@@ -49,6 +49,15 @@ class SwiGLU(FeedForward):
         self.w_gate_up = to_device_matrix(torch.cat([local["w_gate"], local["w_up"]], dim=0), dtype, device)
         self.w_down = to_device_matrix(local["w_down"], dtype, device)
 
+    def takes_pending_norm_at(self, rows: int) -> bool:
+        """gate/up finishes a norm that the product before has begun where it runs on pairs of SMs (many rows) or on the
+        register-streaming kernel (a decode step's 2 to 16 rows, a matrix of up to 592 blocks of 16 columns that does
+        not stream better through TMA); elsewhere the product before need not begin one."""
+        if rows >= ops.PAIR_MIN_ROWS:
+            return True
+        return (ops.SKINNY_LINK_MIN_ROWS <= rows <= ops.SKINNY_LINK_MAX_ROWS and self.w_gate_up is not None
+                and -(-self.hidden // 16) <= ops.SKINNY_LINK_MAX_BLOCKS and not ops.gemm_streams_better(self.w_gate_up))
+
     def forward_fused_norm(self, ctx, x, norm) -> bool:
         from .norm import RMSNorm
         if not (ctx.fast and ctx.dtype == torch.bfloat16 and x.shape[0] <= FF_FUSED_MAX_ROWS and isinstance(norm, RMSNorm)
