@@ -276,7 +276,7 @@ def prefill_timed(eng, portions, reps=5):
     return statistics.median(dev), statistics.median(wall)
 
 
-def mixed_timed(eng, n_decoding=63, arrivals=4):
+def mixed_timed(eng, n_decoding=63, arrivals=6):
     """Steps that hold one portion of 512 prompt tokens beside `n_decoding` single tokens: the decoding requests'
     contexts are spread from 512 to about 3,600, then prompts of 2,048 tokens arrive one after the other and are
     prefilled in four steps each while the others go on decoding. Returns the medians over these steps of the device
