@@ -14,7 +14,6 @@
 
 namespace {
 
-constexpr int WARPS = 8;
 constexpr int COLS = 16;          // output columns (rows of W) per block
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,

@@ -558,9 +558,19 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[tor
     """out = epilogue(x @ w.T) by the kernel that suits the operands: float32 operands, operands the tensor-core
     kernels cannot take, and `fast=False` run the plain CUDA-core kernel; bfloat16 operands a tensor-core kernel
     chosen by the number of rows (and, for few rows, of columns)."""
-    {"plain": gemm_plain, "cols": lambda x, w, out, bias, epilogue: gemm_tc_cols(x, w, out), "splitk": gemm_tc_splitk,
-     "skinny": gemm_skinny, "tc": gemm_tc, "pair": gemm_tc_pair}[gemm_kernel(x, w, out.shape[1], bias, epilogue, fast)](
-        x, w, out, bias, epilogue)
+    kind = gemm_kernel(x, w, out.shape[1], bias, epilogue, fast)
+    if kind == "plain":
+        gemm_plain(x, w, out, bias, epilogue)
+    elif kind == "cols":
+        gemm_tc_cols(x, w, out)
+    elif kind == "splitk":
+        gemm_tc_splitk(x, w, out, bias, epilogue)
+    elif kind == "skinny":
+        gemm_skinny(x, w, out, bias, epilogue)
+    elif kind == "tc":
+        gemm_tc(x, w, out, bias, epilogue)
+    else:
+        gemm_tc_pair(x, w, out, bias, epilogue)
 
 
 def gemm_kernel(x: torch.Tensor, w: torch.Tensor, N: int, bias: Optional[torch.Tensor], epilogue: int, fast: bool = True) -> str:
