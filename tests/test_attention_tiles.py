@@ -74,3 +74,29 @@ def test_parts_collect_one_plan_per_key():
     model = b.build_model(b.Qwen2Config.from_dict(helpers.TINY["B"]))
     plans = model.collect_plans([1, 5], [9, 5])
     assert list(plans) == ["paged attention"] and plans["paged attention"].arrays["singles"].tolist() == [0]
+
+
+def test_who_takes_a_norm_that_the_product_before_has_begun():
+    """`takes_pending_norm(part, rows)`: a part's `takes_pending_norm_at(rows)` decides where it has one, else its
+    flag; a part that says nothing (the toy parts of the tests) and no part at all take none. The attention takes one
+    from the row count of the products on pairs of SMs on (with fewer rows its norm is part of its own kernel)."""
+    from boring_llm_b200.parts.base import takes_pending_norm
+    from boring_llm_b200.parts.attention import GQAAttention, QKV_EPILOGUE_MIN_ROWS
+
+    class Silent:
+        pass
+
+    class Flag:
+        takes_pending_norm = True
+
+    class ByRows:
+        takes_pending_norm = True
+
+        def takes_pending_norm_at(self, rows):
+            return rows % 2 == 0
+
+    assert not takes_pending_norm(None, 8) and not takes_pending_norm(Silent(), 8)
+    assert takes_pending_norm(Flag(), 1) and takes_pending_norm(Flag(), 4096)
+    assert takes_pending_norm(ByRows(), 8) and not takes_pending_norm(ByRows(), 9)
+    at = GQAAttention.takes_pending_norm_at
+    assert not at(None, 8) and not at(None, QKV_EPILOGUE_MIN_ROWS - 1) and at(None, QKV_EPILOGUE_MIN_ROWS) and at(None, 2048)
